@@ -1,0 +1,98 @@
+// extern "C" surface of the library: argument marshalling only.
+#include "common.cuh"
+#include "../../include/cinnamon_b200.h"
+#include <mutex>
+
+namespace cinn {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int sm_count() {
+    static int cached[64];
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    std::lock_guard<std::mutex> lk(mu);
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+int quantize(bool blockwise, const void* x, int dtype, int64_t M, int64_t N, int64_t ld_m, int64_t ld_n, void* q,
+             float* scales, int bm, int bn, int round_scale, int div_mode, cudaStream_t st);
+int requant_row_to_block(const void* xq, const float* xs, int64_t M, int64_t K, void* out, float* scales,
+                         int transpose_out, int div_mode, cudaStream_t st);
+int dequantize(const void* q, const float* scales, void* out, int out_dtype, int64_t M, int64_t N, int bm, int bn,
+               cudaStream_t st);
+int transpose_bytes(const void* in, int64_t ld_in, void* out, int64_t R, int64_t C, cudaStream_t st);
+int fp8_gemm(const void* A, const float* sA, int64_t ld_sa, const void* B, const float* sB, int64_t sbk, int64_t sbn,
+             void* C, int64_t M, int64_t N, int64_t K, int b_layout, int out_dtype, cudaStream_t st);
+int fp8_grouped_gemm(const void* A, const float* sA, const void* W, const float* sW, const int64_t* starts,
+                     const int64_t* ends, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* C, int out_dtype,
+                     cudaStream_t st);
+
+int read_device_status(int* out, int reset);
+
+}  // namespace cinn
+
+extern "C" {
+
+int cinn_version(void) { return 100; }
+
+const char* cinn_last_error(void) { return cinn::g_err; }
+
+int cinn_quant_rowwise(const void* x, int x_dtype, int64_t M, int64_t N, int64_t ld_m, int64_t ld_n, void* q,
+                       float* scales, int block_size, int round_scale, int div_mode, void* stream) {
+    return cinn::quantize(false, x, x_dtype, M, N, ld_m, ld_n, q, scales, 1, block_size, round_scale, div_mode,
+                          (cudaStream_t)stream);
+}
+
+int cinn_quant_blockwise(const void* x, int x_dtype, int64_t M, int64_t N, int64_t ld_m, int64_t ld_n, void* q,
+                         float* scales, int block_m, int block_n, int round_scale, int div_mode, void* stream) {
+    return cinn::quantize(true, x, x_dtype, M, N, ld_m, ld_n, q, scales, block_m, block_n, round_scale, div_mode,
+                          (cudaStream_t)stream);
+}
+
+int cinn_requant_row_to_block(const void* xq, const float* xs, int64_t M, int64_t K, void* out, float* scales,
+                              int transpose_out, int div_mode, void* stream) {
+    return cinn::requant_row_to_block(xq, xs, M, K, out, scales, transpose_out, div_mode, (cudaStream_t)stream);
+}
+
+int cinn_dequant(const void* q, const float* scales, void* out, int out_dtype, int64_t M, int64_t N, int block_m,
+                 int block_n, void* stream) {
+    return cinn::dequantize(q, scales, out, out_dtype, M, N, block_m, block_n, (cudaStream_t)stream);
+}
+
+int cinn_transpose_bytes(const void* in, int64_t ld_in, void* out, int64_t R, int64_t C, void* stream) {
+    return cinn::transpose_bytes(in, ld_in, out, R, C, (cudaStream_t)stream);
+}
+
+int cinn_fp8_gemm(const void* A, const float* sA, int64_t ld_sa, const void* B, const float* sB, int64_t sb_stride_k,
+                  int64_t sb_stride_n, void* C, int64_t M, int64_t N, int64_t K, int b_layout, int out_dtype,
+                  void* stream) {
+    return cinn::fp8_gemm(A, sA, ld_sa, B, sB, sb_stride_k, sb_stride_n, C, M, N, K, b_layout, out_dtype,
+                          (cudaStream_t)stream);
+}
+
+int cinn_fp8_grouped_gemm(const void* A, const float* sA, const void* W, const float* sW, const int64_t* starts,
+                          const int64_t* ends, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* C,
+                          int out_dtype, void* stream) {
+    return cinn::fp8_grouped_gemm(A, sA, W, sW, starts, ends, E, T, d_in, d_out, C, out_dtype, (cudaStream_t)stream);
+}
+
+int cinn_device_status(int* out, int reset) {
+    if (!out) { cinn::set_error("cinn_device_status: null pointer"); return CINN_ERR_INVALID; }
+    return cinn::read_device_status(out, reset);
+}
+
+}  // extern "C"

@@ -1,0 +1,550 @@
+// Block-scaled FP8 GEMM for sm_100a: tcgen05 MMAs on e4m3 tiles that TMA stages in
+// shared memory, fp32 partial sums in tensor memory (TMEM), and a CUDA-core
+// "promotion" of every 128-deep K block: partial * sA[row, kb] * sB[kb, nb] is
+// added to fp32 registers.  Semantics of cinnamon's fp8_gemm_kernel
+// (src/kernels.py:618-664); the grouped variant follows grouped_gemm_kernel
+// (src/kernels.py:466-523) with the same e4m3 operands and scales.
+//
+// One persistent CTA per SM, 10 warps:
+//   warps 0-7  epilogue: tcgen05.ld a K block's partial tile, scale, accumulate, store the
+//              finished tile with row/column predicates (ragged expert tails need no padding)
+//   warp  8    TMA producer (one lane): A 128x128 B and B 256x128 B tiles, 128-byte swizzle
+//   warp  9    TMEM allocation + MMA issue (one lane): four 128x256x32 MMAs per K block into
+//              one of two 256-column TMEM buffers, so block i+1 runs while block i is promoted
+// Every wait is bounded: when one runs out the kernel records a code in a device status
+// word, every role leaves its loop, TMEM is freed and the kernel returns.
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+
+namespace cinn {
+
+constexpr int BM = 128;            // tile rows
+constexpr int BN = 256;            // tile columns (two 128-column scale blocks)
+constexpr int BK = 128;            // bytes (= e4m3 elements) per K block: one scale block, one swizzle row
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK;   // 16 KiB
+constexpr int B_BYTES = BN * BK;   // 32 KiB
+constexpr int EPI_WARPS = 8;
+constexpr int THREADS = (EPI_WARPS + 2) * 32;
+constexpr int TMEM_COLS = 512;
+constexpr int MAX_EXPERTS = 2048;
+constexpr int GROUP_M = 16;        // rasterisation: m-tiles per L2 group (dense)
+
+// device status word: 0 = fine, otherwise (role << 8) | reason
+__device__ int g_device_status = 0;
+
+struct GemmParams {
+    const float* sA; int64_t sa_stride_m, sa_stride_k;
+    const float* sB; int64_t sb_stride_k, sb_stride_n, sb_stride_e;
+    void* C; int64_t ldc;
+    int M, N, K;                   // dense: A is (M, K); grouped: M = total rows T
+    const int64_t* starts; const int64_t* ends; int E; int b_rows_per_expert;
+};
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;   // about two seconds
+
+// Bounded wait.  Returns false when the kernel is being abandoned.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t spin = 1;; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 255u) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                atomicCAS(&g_device_status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint32_t bar, uint32_t dst, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc], e4m3 x e4m3 -> fp32
+__device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// 32 lanes x 16 consecutive fp32 columns: thread i receives TMEM lane (base lane + i)
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, Blackwell descriptor version 1.
+// lbo / sbo in bytes.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;     // descriptor version
+    d |= (uint64_t)2 << 61;     // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor for kind::f8f6f4: fp32 accumulate, e4m3 x e4m3, A K-major.
+__host__ __device__ constexpr uint32_t make_idesc(bool b_mn_major) {
+    return (1u << 4)                              // D format: fp32
+           | (0u << 7) | (0u << 10)               // A, B format: e4m3
+           | (0u << 15)                           // A major: K
+           | ((b_mn_major ? 1u : 0u) << 16)       // B major
+           | ((uint32_t)(BN >> 3) << 17)          // N
+           | ((uint32_t)(BM >> 4) << 24);         // M
+}
+
+// ---------------------------------------------------------------------------
+// tile schedule shared by all roles
+// ---------------------------------------------------------------------------
+struct TileInfo {
+    int m0;        // first row of A / C
+    int m_end;     // one past the last valid row for this tile
+    int n0;        // first output column
+    int expert;
+};
+
+template <bool GROUPED>
+__device__ __forceinline__ int total_tiles(const GemmParams& p, const int* cum) {
+    const int n_tiles = (p.N + BN - 1) / BN;
+    if constexpr (GROUPED) return cum[p.E] * n_tiles;
+    else return ((p.M + BM - 1) / BM) * n_tiles;
+}
+
+template <bool GROUPED>
+__device__ __forceinline__ TileInfo tile_info(const GemmParams& p, const int* cum, int t) {
+    TileInfo ti;
+    const int n_tiles = (p.N + BN - 1) / BN;
+    if constexpr (GROUPED) {
+        const int mt = t / n_tiles;
+        ti.n0 = (t - mt * n_tiles) * BN;
+        int lo = 0, hi = p.E;                      // largest e with cum[e] <= mt
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (cum[mid] <= mt) lo = mid; else hi = mid;
+        }
+        ti.expert = lo;
+        const long long s = p.starts[lo], e = p.ends[lo];
+        ti.m0 = (int)s + (mt - cum[lo]) * BM;
+        ti.m_end = (int)(e < (long long)p.M ? e : (long long)p.M);
+    } else {
+        const int m_tiles = (p.M + BM - 1) / BM;
+        const int per_group = GROUP_M * n_tiles;
+        const int g = t / per_group;
+        const int first_m = g * GROUP_M;
+        const int gsize = min(GROUP_M, m_tiles - first_m);
+        const int r = t - g * per_group;
+        ti.m0 = (first_m + r % gsize) * BM;
+        ti.n0 = (r / gsize) * BN;
+        ti.m_end = p.M;
+        ti.expert = 0;
+    }
+    return ti;
+}
+
+template <int OUT> struct OutT;
+template <> struct OutT<CINN_BF16> { using type = __nv_bfloat16; };
+template <> struct OutT<CINN_F16> { using type = __half; };
+template <> struct OutT<CINN_F32> { using type = float; };
+
+template <int OUT>
+__device__ __forceinline__ void store8(void* C, int64_t off, const float* a, bool vec, int ncols) {
+    using T = typename OutT<OUT>::type;
+    T* dst = reinterpret_cast<T*>(C) + off;
+    if (vec && ncols >= 8) {
+        if constexpr (OUT == CINN_F32) {
+            reinterpret_cast<float4*>(dst)[0] = make_float4(a[0], a[1], a[2], a[3]);
+            reinterpret_cast<float4*>(dst)[1] = make_float4(a[4], a[5], a[6], a[7]);
+        } else if constexpr (OUT == CINN_BF16) {
+            uint4 v;
+            __nv_bfloat162 t0 = __floats2bfloat162_rn(a[0], a[1]), t1 = __floats2bfloat162_rn(a[2], a[3]);
+            __nv_bfloat162 t2 = __floats2bfloat162_rn(a[4], a[5]), t3 = __floats2bfloat162_rn(a[6], a[7]);
+            v.x = *reinterpret_cast<uint32_t*>(&t0); v.y = *reinterpret_cast<uint32_t*>(&t1);
+            v.z = *reinterpret_cast<uint32_t*>(&t2); v.w = *reinterpret_cast<uint32_t*>(&t3);
+            *reinterpret_cast<uint4*>(dst) = v;
+        } else {
+            uint4 v;
+            __half2 t0 = __floats2half2_rn(a[0], a[1]), t1 = __floats2half2_rn(a[2], a[3]);
+            __half2 t2 = __floats2half2_rn(a[4], a[5]), t3 = __floats2half2_rn(a[6], a[7]);
+            v.x = *reinterpret_cast<uint32_t*>(&t0); v.y = *reinterpret_cast<uint32_t*>(&t1);
+            v.z = *reinterpret_cast<uint32_t*>(&t2); v.w = *reinterpret_cast<uint32_t*>(&t3);
+            *reinterpret_cast<uint4*>(dst) = v;
+        }
+    } else {
+        for (int i = 0; i < 8 && i < ncols; ++i) {
+            if constexpr (OUT == CINN_F32) dst[i] = a[i];
+            else if constexpr (OUT == CINN_BF16) dst[i] = __float2bfloat16_rn(a[i]);
+            else dst[i] = __float2half_rn(a[i]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// the kernel
+// ---------------------------------------------------------------------------
+template <bool B_MN, bool GROUPED, int OUT>
+__global__ void __launch_bounds__(THREADS, 1)
+fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + STAGES * A_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_BYTES + B_BYTES));
+    // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem full, [2S+2..2S+4) tmem empty
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* cum = reinterpret_cast<int*>(tmem_slot + 2);          // grouped: E + 1 prefix counts of m-tiles
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+    const uint32_t tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
+
+    if (threadIdx.x == 0) *abort_flag = 0;
+    if (warp == EPI_WARPS && lane == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, EPI_WARPS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == EPI_WARPS + 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if constexpr (GROUPED) {
+        if (warp == 0) {                           // prefix sum of per-expert m-tile counts
+            int carry = 0;
+            for (int base = 0; base < p.E; base += 32) {
+                const int e = base + lane;
+                int cnt = 0;
+                if (e < p.E) {
+                    long long s = p.starts[e], t = p.ends[e];
+                    if (t > (long long)p.M) t = p.M;
+                    if (s < 0) s = 0;
+                    if (t > s) cnt = (int)((t - s + BM - 1) / BM);
+                }
+                int incl = cnt;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += v;
+                }
+                if (e < p.E) cum[e] = carry + incl - cnt;
+                carry += __shfl_sync(0xffffffffu, incl, 31);
+            }
+            if (lane == 0) cum[p.E] = carry;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int KB = (p.K + BK - 1) / BK;
+    const int n_total = total_tiles<GROUPED>(p, cum);
+
+    if (warp == EPI_WARPS) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool alive = true;
+            for (int t = blockIdx.x; t < n_total && alive; t += gridDim.x) {
+                const TileInfo ti = tile_info<GROUPED>(p, cum, t);
+                const int b_row0 = GROUPED ? ti.expert * p.b_rows_per_expert : 0;
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, (1 << 8) | 1)) { alive = false; break; }
+                    const uint32_t fb = full0 + 8 * s;
+                    mbar_expect_tx(fb, A_BYTES + B_BYTES);
+                    tma_load_2d(&tmA, fb, smem_u32(smem_a + s * A_BYTES), kb * BK, ti.m0);
+                    if constexpr (!B_MN) {
+                        tma_load_2d(&tmB, fb, smem_u32(smem_b + s * B_BYTES), kb * BK, b_row0 + ti.n0);
+                    } else {
+                        tma_load_2d(&tmB, fb, smem_u32(smem_b + s * B_BYTES), ti.n0, b_row0 + kb * BK);
+                        tma_load_2d(&tmB, fb, smem_u32(smem_b + s * B_BYTES + B_BYTES / 2), ti.n0 + 128, b_row0 + kb * BK);
+                    }
+                }
+            }
+            if (!alive) {
+                // abandoned: let the copies already issued land before shared memory is given up
+                const uint32_t issued = it;
+                for (uint32_t j = (issued > STAGES ? issued - STAGES : 0); j < issued; ++j) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(full0 + 8 * (j % STAGES), (j / STAGES) & 1)) {
+                        if (clock64() - t0 > WAIT_LIMIT_CYCLES) break;
+                    }
+                }
+            }
+        }
+    } else if (warp == EPI_WARPS + 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(B_MN);
+            uint32_t it = 0;
+            bool alive = true;
+            for (int t = blockIdx.x; t < n_total && alive; t += gridDim.x) {
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    const uint32_t b = it & 1, bph = (it >> 1) & 1;
+                    if (!mbar_wait(tempty0 + 8 * b, bph ^ 1, abort_flag, (2 << 8) | 2)) { alive = false; break; }
+                    if (!mbar_wait(full0 + 8 * s, ph, abort_flag, (2 << 8) | 1)) { alive = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem_a + s * A_BYTES);
+                    const uint32_t b_addr = smem_u32(smem_b + s * B_BYTES);
+                    const uint32_t d = tmem_base + b * BN;
+#pragma unroll
+                    for (int k = 0; k < BK / 32; ++k) {
+                        const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024);
+                        const uint64_t bd = B_MN ? make_smem_desc(b_addr + k * 32 * 128, B_BYTES / 2, 1024)
+                                                 : make_smem_desc(b_addr + k * 32, 16, 1024);
+                        tc_mma_f8(d, ad, bd, idesc, k > 0 ? 1u : 0u);
+                    }
+                    tc_commit(empty0 + 8 * s);      // the stage may be refilled once these MMAs retire
+                    tc_commit(tfull0 + 8 * b);      // and the partial tile is ready for promotion
+                }
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ------------------------------
+        const int q = warp & 3, h = warp >> 2;
+        uint32_t it = 0;
+        bool alive = true;
+        const bool vec_ok = (OUT == CINN_F32) ? (p.ldc % 4 == 0) : (p.ldc % 8 == 0);
+        for (int t = blockIdx.x; t < n_total && alive; t += gridDim.x) {
+            const TileInfo ti = tile_info<GROUPED>(p, cum, t);
+            const int row = ti.m0 + q * 32 + lane;
+            const bool rvalid = row < ti.m_end;
+            const int col0 = ti.n0 + h * 128;
+            const bool cvalid = col0 < p.N;
+            const float* sa_ptr = p.sA + (int64_t)(rvalid ? row : ti.m0) * p.sa_stride_m;
+            const float* sb_ptr = p.sB + (int64_t)ti.expert * p.sb_stride_e + (int64_t)(cvalid ? col0 / 128 : 0) * p.sb_stride_n;
+            float acc[128];
+#pragma unroll
+            for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+            float sa_n = __ldg(sa_ptr), sb_n = __ldg(sb_ptr);
+            for (int kb = 0; kb < KB; ++kb, ++it) {
+                const float s = sa_n * sb_n;
+                if (kb + 1 < KB) {
+                    sa_n = __ldg(sa_ptr + (int64_t)(kb + 1) * p.sa_stride_k);
+                    sb_n = __ldg(sb_ptr + (int64_t)(kb + 1) * p.sb_stride_k);
+                }
+                const uint32_t b = it & 1, bph = (it >> 1) & 1;
+                if (!mbar_wait(tfull0 + 8 * b, bph, abort_flag, (3 << 8) | 1)) { alive = false; break; }
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * BN + h * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    float v[16];
+                    tc_ld16(taddr + c * 16, v);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) acc[c * 16 + j] = fmaf(v[j], s, acc[c * 16 + j]);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty0 + 8 * b);
+            }
+            if (alive && rvalid && cvalid) {
+                const int64_t base = (int64_t)row * p.ldc + col0;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int ncols = p.N - (col0 + j * 8);
+                    if (ncols > 0) store8<OUT>(p.C, base + j * 8, &acc[j * 8], vec_ok, ncols);
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == EPI_WARPS + 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeFn get_encode() {
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+            qr == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(p);
+    });
+    return fn;
+}
+
+// 2-D byte tensor: inner extent `inner` bytes (contiguous), `rows` rows of pitch `pitch` bytes
+static int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows, uint64_t pitch, uint32_t box_inner,
+                    uint32_t box_rows) {
+    EncodeFn enc = get_encode();
+    if (!enc) { set_error("cuTensorMapEncodeTiled is not available from the CUDA driver"); return CINN_ERR_CUDA; }
+    cuuint64_t dims[2] = {inner, rows};
+    cuuint64_t strides[1] = {pitch};
+    cuuint32_t box[2] = {box_inner, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with CUresult %d (base %p inner %llu rows %llu pitch %llu)", (int)r, base,
+                  (unsigned long long)inner, (unsigned long long)rows, (unsigned long long)pitch);
+        return CINN_ERR_CUDA;
+    }
+    return CINN_OK;
+}
+
+static size_t smem_bytes(int E) {
+    return (size_t)STAGES * (A_BYTES + B_BYTES) + 1024 + (2 * STAGES + 4) * 8 + 16 + 4 * (size_t)(E + 2);
+}
+
+template <bool B_MN, bool GROUPED, int OUT>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
+    auto kern = fp8_gemm_kernel<B_MN, GROUPED, OUT>;
+    const size_t smem = smem_bytes(GROUPED ? p.E : 0);
+    static thread_local size_t configured[64] = {};   // per instantiation, per thread, per device
+    int dev = 0;
+    CINN_CHECK_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || configured[dev] < smem) {
+        CINN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (dev >= 0 && dev < 64) configured[dev] = smem;
+    }
+    kern<<<grid, THREADS, smem, st>>>(ta, tb, p);
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+template <bool B_MN, bool GROUPED>
+static int launch_out(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int out_dtype, int grid,
+                      cudaStream_t st) {
+    switch (out_dtype) {
+        case CINN_BF16: return launch<B_MN, GROUPED, CINN_BF16>(ta, tb, p, grid, st);
+        case CINN_F32: return launch<B_MN, GROUPED, CINN_F32>(ta, tb, p, grid, st);
+        case CINN_F16: return launch<B_MN, GROUPED, CINN_F16>(ta, tb, p, grid, st);
+        default: set_error("GEMM: unknown output dtype tag %d", out_dtype); return CINN_ERR_INVALID;
+    }
+}
+
+static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int fp8_gemm(const void* A, const float* sA, int64_t ld_sa, const void* B, const float* sB, int64_t sbk, int64_t sbn,
+             void* C, int64_t M, int64_t N, int64_t K, int b_layout, int out_dtype, cudaStream_t st) {
+    CINN_CHECK_ARG(M >= 0 && N >= 0 && K >= 0, "fp8_gemm: negative shape");
+    if (M == 0 || N == 0) return CINN_OK;
+    CINN_CHECK_ARG(A && sA && B && sB && C, "fp8_gemm: null pointer");
+    CINN_CHECK_ARG(K > 0, "fp8_gemm: K must be positive");
+    CINN_CHECK_ARG(M < (1LL << 31) && N < (1LL << 31) && K < (1LL << 31), "fp8_gemm: dimension too large");
+    CINN_CHECK_ARG(K % 16 == 0, "fp8_gemm: K (%lld) must be a multiple of 16", (long long)K);
+    CINN_CHECK_ARG(al16(A) && al16(B) && al16(C), "fp8_gemm: A, B and C must be 16-byte aligned");
+    CINN_CHECK_ARG(b_layout == 0 || b_layout == 1, "fp8_gemm: unknown B layout %d", b_layout);
+    CINN_CHECK_ARG(b_layout == 0 || N % 16 == 0, "fp8_gemm: B stored (K, N) needs N %% 16 == 0");
+    CUtensorMap ta, tb;
+    int rc = make_map(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)K, BK, BM);
+    if (rc) return rc;
+    if (b_layout == 0) rc = make_map(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, BN);
+    else rc = make_map(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)N, 128, BK);
+    if (rc) return rc;
+    GemmParams p{};
+    p.sA = sA; p.sa_stride_m = ld_sa; p.sa_stride_k = 1;
+    p.sB = sB; p.sb_stride_k = sbk; p.sb_stride_n = sbn; p.sb_stride_e = 0;
+    p.C = C; p.ldc = N; p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.starts = nullptr; p.ends = nullptr; p.E = 1; p.b_rows_per_expert = 0;
+    const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    return b_layout == 0 ? launch_out<false, false>(ta, tb, p, out_dtype, grid, st)
+                         : launch_out<true, false>(ta, tb, p, out_dtype, grid, st);
+}
+
+int fp8_grouped_gemm(const void* A, const float* sA, const void* W, const float* sW, const int64_t* starts,
+                     const int64_t* ends, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* C, int out_dtype,
+                     cudaStream_t st) {
+    CINN_CHECK_ARG(E >= 0 && T >= 0 && d_in >= 0 && d_out >= 0, "grouped_gemm: negative shape");
+    if (E == 0 || T == 0 || d_out == 0) return CINN_OK;
+    CINN_CHECK_ARG(A && sA && W && sW && starts && ends && C, "grouped_gemm: null pointer");
+    CINN_CHECK_ARG(E <= MAX_EXPERTS, "grouped_gemm: at most %d experts are supported (got %lld)", MAX_EXPERTS, (long long)E);
+    CINN_CHECK_ARG(d_in > 0 && d_in % 16 == 0, "grouped_gemm: d_in (%lld) must be a positive multiple of 16", (long long)d_in);
+    CINN_CHECK_ARG(T < (1LL << 31) && d_out < (1LL << 31) && d_in < (1LL << 31) && E * d_out < (1LL << 31),
+                   "grouped_gemm: dimension too large");
+    CINN_CHECK_ARG(al16(A) && al16(W) && al16(C), "grouped_gemm: A, W and C must be 16-byte aligned");
+    CUtensorMap ta, tb;
+    int rc = make_map(&ta, A, (uint64_t)d_in, (uint64_t)T, (uint64_t)d_in, BK, BM);
+    if (rc) return rc;
+    rc = make_map(&tb, W, (uint64_t)d_in, (uint64_t)(E * d_out), (uint64_t)d_in, BK, BN);
+    if (rc) return rc;
+    const int64_t nkb = (d_in + 127) / 128, nnb = (d_out + 127) / 128;
+    GemmParams p{};
+    p.sA = sA; p.sa_stride_m = nkb; p.sa_stride_k = 1;
+    p.sB = sW; p.sb_stride_k = 1; p.sb_stride_n = nkb; p.sb_stride_e = nnb * nkb;
+    p.C = C; p.ldc = d_out; p.M = (int)T; p.N = (int)d_out; p.K = (int)d_in;
+    p.starts = starts; p.ends = ends; p.E = (int)E; p.b_rows_per_expert = (int)d_out;
+    return launch_out<false, true>(ta, tb, p, out_dtype, sm_count(), st);
+}
+
+int read_device_status(int* out, int reset) {
+    int v = 0;
+    CINN_CHECK_CUDA(cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)));
+    if (reset && v != 0) {
+        int z = 0;
+        CINN_CHECK_CUDA(cudaMemcpyToSymbol(g_device_status, &z, sizeof(int)));
+    }
+    *out = v;
+    return CINN_OK;
+}
+
+}  // namespace cinn

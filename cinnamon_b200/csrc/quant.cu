@@ -1,0 +1,564 @@
+// FP8 (e4m3) quantisers and de-quantisers: HBM-bound amax / scale / cast passes.
+//
+// Arithmetic follows cinnamon's Triton kernels (src/kernels.py:41-71 row-wise,
+// :97-132 block-wise, :149-173 block de-quantise, :262-281 row-wise
+// de-quantise): amax over the tile with masked elements counted as 0, floor
+// 1e-4, scale = amax/448 (or the next power of two), q = clamp(x/scale) -> e4m3.
+// The division flavour is a template parameter: div.full.f32 is what Triton
+// emits for those kernels on a GPU, IEEE division is what a CPU computes.
+//
+// Layout: every kernel moves 16-byte vectors per lane where alignment allows,
+// reduces amax with warp shuffles, and writes packed e4m3 (4-16 bytes per lane).
+#include "common.cuh"
+
+namespace cinn {
+
+// ---------------------------------------------------------------------------
+// typed 8-element / 4-element vector loads, widened to fp32
+// ---------------------------------------------------------------------------
+template <typename T> struct Elem;
+template <> struct Elem<__nv_bfloat16> {
+    static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+        uint4 r = *reinterpret_cast<const uint4*>(p);
+        uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    static __device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
+        uint2 r = *reinterpret_cast<const uint2*>(p);
+        v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xffff0000u);
+        v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xffff0000u);
+    }
+};
+template <> struct Elem<__half> {
+    static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ void load8(const __half* p, float (&v)[8]) {
+        uint4 r = *reinterpret_cast<const uint4*>(p);
+        const __half2* h = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+    }
+    static __device__ __forceinline__ void load4(const __half* p, float (&v)[4]) {
+        uint2 r = *reinterpret_cast<const uint2*>(p);
+        const __half2* h = reinterpret_cast<const __half2*>(&r);
+        float2 a = __half22float2(h[0]), b = __half22float2(h[1]);
+        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    }
+};
+template <> struct Elem<float> {
+    static __device__ __forceinline__ float to_f(float v) { return v; }
+    static __device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+        float4 a = *reinterpret_cast<const float4*>(p);
+        float4 b = *reinterpret_cast<const float4*>(p + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    static __device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+        float4 a = *reinterpret_cast<const float4*>(p);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    }
+};
+
+// ---------------------------------------------------------------------------
+// Row-wise 1x128, contiguous rows, vector path.
+// A half-warp owns one tile (16 lanes x 8 elements); each thread keeps UNROLL
+// tiles in flight so the loads of several tiles overlap.
+// ---------------------------------------------------------------------------
+template <typename T, int DIV, bool ROUND, int UNROLL>
+__global__ void __launch_bounds__(256)
+quant_row_vec_kernel(const T* __restrict__ x, int64_t ld, uint8_t* __restrict__ q, float* __restrict__ scales,
+                     int N, int nb, int64_t total_tiles) {
+    const int sub = threadIdx.x & 15;
+    const int64_t hw = (int64_t)blockIdx.x * 16 + (threadIdx.x >> 4);
+    const int64_t n_hw = (int64_t)gridDim.x * 16;
+    // warp-uniform trip count: both half-warps of a warp run the same number of rounds
+    const int64_t warp_first = hw & ~(int64_t)1;
+    for (int64_t t0 = warp_first; t0 < total_tiles; t0 += n_hw * UNROLL) {
+        float v[UNROLL][8];
+        int64_t tile[UNROLL];
+        bool inb[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int64_t t = t0 + (hw & 1) + (int64_t)u * n_hw;
+            tile[u] = t;
+            const int64_t row = t / nb;
+            const int col = (int)(t - row * nb) * 128 + sub * 8;
+            inb[u] = (t < total_tiles) && (col < N);
+            if (inb[u]) {
+                Elem<T>::load8(x + row * ld + col, v[u]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[u][i] = 0.0f;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[u][i]));
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            const float s = scale_from_amax<DIV, ROUND>(amax);
+            float y[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) y[i] = scaled_clamped<DIV>(v[u][i], s);
+            if (inb[u]) {
+                const int64_t t = tile[u];
+                const int64_t row = t / nb;
+                const int col = (int)(t - row * nb) * 128 + sub * 8;
+                uint2 o2;
+                o2.x = cvt_e4m3x4(y[0], y[1], y[2], y[3]);
+                o2.y = cvt_e4m3x4(y[4], y[5], y[6], y[7]);
+                *reinterpret_cast<uint2*>(q + row * (int64_t)N + col) = o2;
+            }
+            if (sub == 0 && tile[u] < total_tiles) scales[tile[u]] = s;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Row-wise, arbitrary strides / ragged sizes / any tile length: one warp per tile.
+// ---------------------------------------------------------------------------
+template <typename T, int DIV, bool ROUND>
+__global__ void __launch_bounds__(256)
+quant_row_generic_kernel(const T* __restrict__ x, int64_t ld_m, int64_t ld_n, uint8_t* __restrict__ q,
+                         float* __restrict__ scales, int N, int nb, int block, int64_t total_tiles) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int64_t n_warps = (int64_t)gridDim.x * 8;
+    for (int64_t t = warp; t < total_tiles; t += n_warps) {
+        const int64_t row = t / nb;
+        const int c0 = (int)(t - row * nb) * block;
+        const int c1 = min(c0 + block, N);
+        float amax = 0.0f;
+        for (int c = c0 + lane; c < c1; c += 32) amax = fmaxf(amax, fabsf(Elem<T>::to_f(x[row * ld_m + c * ld_n])));
+        amax = warp_max(amax);
+        const float s = scale_from_amax<DIV, ROUND>(amax);
+        for (int c = c0 + lane; c < c1; c += 32) {
+            const float y = scaled_clamped<DIV>(Elem<T>::to_f(x[row * ld_m + c * ld_n]), s);
+            q[row * (int64_t)N + c] = (uint8_t)(cvt_e4m3x2(y, 0.0f) & 0xff);
+        }
+        if (lane == 0) scales[t] = s;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Row-wise 1x128 over a TRANSPOSED view: logical x is (M, N) with element
+// (m, n) at x[m + n * L], i.e. the tile axis n is the strided one.  This is
+// what the weight-gradient path needs (tiles along tokens of dy^T,
+// src/kernels.py:781-783) without first materialising the transpose.
+// One CTA: 64 logical rows (contiguous in memory) x one 128-wide tile.
+// ---------------------------------------------------------------------------
+template <typename T, int DIV, bool ROUND>
+__global__ void __launch_bounds__(256)
+quant_row_transposed_kernel(const T* __restrict__ x, int64_t L, uint8_t* __restrict__ q,
+                            float* __restrict__ scales, int M, int N, int nb) {
+    constexpr int TM = 64;            // logical rows per CTA
+    constexpr int PITCH = 128 + 16;   // bytes per staged output row
+    __shared__ float s_amax[8][TM];
+    __shared__ __align__(16) uint8_t s_out[TM * PITCH];
+
+    const int cb = blockIdx.x;                  // tile index along n
+    const int m0 = blockIdx.y * TM;
+    const int n0 = cb * 128;
+    const int g = threadIdx.x & 7;              // which 8-wide m chunk
+    const int nr = threadIdx.x >> 3;            // 0..31: n row within a pass
+    const int warp = threadIdx.x >> 5;
+
+    float v[4][8];
+    const int m = m0 + g * 8;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const int n = n0 + p * 32 + nr;
+        if (n < N && m < M) {
+            Elem<T>::load8(x + (int64_t)n * L + m, v[p]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[p][i] = 0.0f;
+        }
+    }
+    float am[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float a = fmaxf(fmaxf(fabsf(v[0][i]), fabsf(v[1][i])), fmaxf(fabsf(v[2][i]), fabsf(v[3][i])));
+        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 8));
+        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 16));
+        am[i] = a;
+    }
+    if ((threadIdx.x & 31) < 8) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s_amax[warp][g * 8 + i] = am[i];
+    }
+    __syncthreads();
+    float sc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float a = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) a = fmaxf(a, s_amax[w][g * 8 + i]);
+        sc[i] = scale_from_amax<DIV, ROUND>(a);
+    }
+    if (nr == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (m + i < M) scales[(int64_t)(m + i) * nb + cb] = sc[i];
+    }
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const int nl = p * 32 + nr;
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+            const uint16_t two = cvt_e4m3x2(scaled_clamped<DIV>(v[p][i], sc[i]), scaled_clamped<DIV>(v[p][i + 1], sc[i + 1]));
+            s_out[(g * 8 + i) * PITCH + nl] = (uint8_t)(two & 0xff);
+            s_out[(g * 8 + i + 1) * PITCH + nl] = (uint8_t)(two >> 8);
+        }
+    }
+    __syncthreads();
+    // 64 rows x 8 chunks of 16 bytes
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int idx = threadIdx.x + r * 256;
+        const int ml = idx >> 3, ch = idx & 7;
+        const int mm = m0 + ml, n = n0 + ch * 16;
+        if (mm < M && n < N) {
+            const uint4 val = *reinterpret_cast<const uint4*>(&s_out[ml * PITCH + ch * 16]);
+            *reinterpret_cast<uint4*>(q + (int64_t)mm * N + n) = val;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Block-wise 128x128, vector path: one CTA per block, 8 warps x 16 rows,
+// each lane 4 consecutive columns; the whole block stays in registers between
+// the amax and the cast, so the input is read exactly once.
+// ---------------------------------------------------------------------------
+template <typename T, int DIV, bool ROUND>
+__global__ void __launch_bounds__(256)
+quant_block_vec_kernel(const T* __restrict__ x, int64_t ld, uint8_t* __restrict__ q, float* __restrict__ scales,
+                       int M, int N, int nb) {
+    __shared__ float s_red[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r0 = blockIdx.y * 128, c = blockIdx.x * 128 + lane * 4;
+    float v[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int r = r0 + warp + i * 8;
+        if (r < M && c < N) {
+            Elem<T>::load4(x + (int64_t)r * ld + c, v[i]);
+        } else {
+            v[i][0] = v[i][1] = v[i][2] = v[i][3] = 0.0f;
+        }
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) amax = fmaxf(amax, fabsf(v[i][j]));
+    amax = warp_max(amax);
+    if (lane == 0) s_red[warp] = amax;
+    __syncthreads();
+    amax = s_red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) amax = fmaxf(amax, s_red[w]);
+    const float s = scale_from_amax<DIV, ROUND>(amax);
+    if (threadIdx.x == 0) scales[(int64_t)blockIdx.y * nb + blockIdx.x] = s;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int r = r0 + warp + i * 8;
+        if (r < M && c < N) {
+            const uint32_t o = cvt_e4m3x4(scaled_clamped<DIV>(v[i][0], s), scaled_clamped<DIV>(v[i][1], s),
+                                          scaled_clamped<DIV>(v[i][2], s), scaled_clamped<DIV>(v[i][3], s));
+            *reinterpret_cast<uint32_t*>(q + (int64_t)r * N + c) = o;
+        }
+    }
+}
+
+// Block-wise, arbitrary strides / block sizes: one CTA per block, two passes.
+template <typename T, int DIV, bool ROUND>
+__global__ void __launch_bounds__(256)
+quant_block_generic_kernel(const T* __restrict__ x, int64_t ld_m, int64_t ld_n, uint8_t* __restrict__ q,
+                           float* __restrict__ scales, int M, int N, int bm, int bn, int nb) {
+    __shared__ float s_red[8];
+    const int r0 = blockIdx.y * bm, c0 = blockIdx.x * bn;
+    const int rows = min(bm, M - r0), cols = min(bn, N - c0);
+    const int count = rows * cols;
+    float amax = 0.0f;
+    for (int i = threadIdx.x; i < count; i += 256) {
+        const int r = r0 + i / cols, c = c0 + i % cols;
+        amax = fmaxf(amax, fabsf(Elem<T>::to_f(x[(int64_t)r * ld_m + (int64_t)c * ld_n])));
+    }
+    amax = warp_max(amax);
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = s_red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) amax = fmaxf(amax, s_red[w]);
+    const float s = scale_from_amax<DIV, ROUND>(amax);
+    if (threadIdx.x == 0) scales[(int64_t)blockIdx.y * nb + blockIdx.x] = s;
+    for (int i = threadIdx.x; i < count; i += 256) {
+        const int r = r0 + i / cols, c = c0 + i % cols;
+        const float y = scaled_clamped<DIV>(Elem<T>::to_f(x[(int64_t)r * ld_m + (int64_t)c * ld_n]), s);
+        q[(int64_t)r * N + c] = (uint8_t)(cvt_e4m3x2(y, 0.0f) & 0xff);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Re-quantise row-scaled e4m3 to block-scaled e4m3 in one pass: the weight-
+// gradient path de-quantises x row-wise to fp32 and quantises it again in
+// 128x128 blocks (src/kernels.py:784-787).  Here the fp32 product lives only
+// in registers.  Optionally the block-scaled bytes are written transposed
+// (K x M), so that the token axis is contiguous.
+// ---------------------------------------------------------------------------
+template <int DIV, bool TRANSPOSE_OUT>
+__global__ void __launch_bounds__(256)
+requant_row_to_block_kernel(const uint8_t* __restrict__ xq, const float* __restrict__ xs, int nkb_in,
+                            uint8_t* __restrict__ out, float* __restrict__ scales, int M, int K, int nb) {
+    __shared__ float s_red[8];
+    __shared__ __align__(16) uint8_t s_t[TRANSPOSE_OUT ? 128 * (128 + 16) : 16];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = lane & 7;                      // 16-byte chunk within the 128-byte row
+    const int r0 = blockIdx.y * 128, c = blockIdx.x * 128 + sub * 16;
+    float v[4][16];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const int r = r0 + p * 32 + warp * 4 + (lane >> 3);
+        if (r < M && c < K) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(xq + (int64_t)r * K + c);
+            const float rs = xs[(int64_t)r * nkb_in + blockIdx.x];
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 a = e4m3x2_to_float2((uint16_t)(w[j] & 0xffff));
+                const float2 b = e4m3x2_to_float2((uint16_t)(w[j] >> 16));
+                v[p][4 * j + 0] = __fmul_rn(a.x, rs); v[p][4 * j + 1] = __fmul_rn(a.y, rs);
+                v[p][4 * j + 2] = __fmul_rn(b.x, rs); v[p][4 * j + 3] = __fmul_rn(b.y, rs);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[p][j] = 0.0f;
+        }
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int p = 0; p < 4; ++p)
+#pragma unroll
+        for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[p][j]));
+    amax = warp_max(amax);
+    if (lane == 0) s_red[warp] = amax;
+    __syncthreads();
+    amax = s_red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) amax = fmaxf(amax, s_red[w]);
+    const float s = scale_from_amax<DIV, false>(amax);
+    if (threadIdx.x == 0) scales[(int64_t)blockIdx.y * nb + blockIdx.x] = s;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const int rl = p * 32 + warp * 4 + (lane >> 3);
+        const int r = r0 + rl;
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            o[j] = cvt_e4m3x4(scaled_clamped<DIV>(v[p][4 * j], s), scaled_clamped<DIV>(v[p][4 * j + 1], s),
+                              scaled_clamped<DIV>(v[p][4 * j + 2], s), scaled_clamped<DIV>(v[p][4 * j + 3], s));
+        if constexpr (!TRANSPOSE_OUT) {
+            if (r < M && c < K) *reinterpret_cast<uint4*>(out + (int64_t)r * K + c) = make_uint4(o[0], o[1], o[2], o[3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                s_t[(sub * 16 + j) * (128 + 16) + rl] = (uint8_t)((o[j >> 2] >> (8 * (j & 3))) & 0xff);
+        }
+    }
+    if constexpr (TRANSPOSE_OUT) {
+        __syncthreads();
+        // out is (K, M): row k holds 128 consecutive tokens of this block
+#pragma unroll
+        for (int rep = 0; rep < 4; ++rep) {
+            const int idx = threadIdx.x + rep * 256;
+            const int kl = idx >> 3, ch = idx & 7;
+            const int k = blockIdx.x * 128 + kl, m = r0 + ch * 16;
+            if (k < K && m < M)
+                *reinterpret_cast<uint4*>(out + (int64_t)k * M + m) =
+                    *reinterpret_cast<const uint4*>(&s_t[kl * (128 + 16) + ch * 16]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// De-quantisers
+// ---------------------------------------------------------------------------
+// out[r, c] = e4m3(q[r, c]) * scales[(r / bm) * ncb + c / bn]; OUT = bf16 or fp32.
+template <typename OUT>
+__global__ void __launch_bounds__(256)
+dequant_kernel(const uint8_t* __restrict__ q, const float* __restrict__ scales, OUT* __restrict__ out,
+               int64_t M, int N, int bm, int bn, int ncb) {
+    const int64_t total = M * (int64_t)N;
+    for (int64_t i = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4; i < total; i += (int64_t)gridDim.x * 1024) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t e = i + j;
+            if (e < total) {
+                const int64_t r = e / N;
+                const int c = (int)(e - r * N);
+                const float2 f = e4m3x2_to_float2((uint16_t)q[e]);
+                const float y = __fmul_rn(f.x, scales[(r / bm) * ncb + c / bn]);
+                if constexpr (sizeof(OUT) == 2) out[e] = __float2bfloat16_rn(y); else out[e] = y;
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// byte transpose (used when a caller hands fp8_matmul an operand whose
+// reduction axis is not the contiguous one)
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+transpose_bytes_kernel(const uint8_t* __restrict__ in, int64_t ld_in, uint8_t* __restrict__ out, int R, int C) {
+    // in: R x C (row pitch ld_in) -> out: C x R contiguous; 64 x 64 tiles
+    __shared__ uint8_t t[64][64 + 4];
+    const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+    for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+        const int r = i >> 6, c = i & 63;
+        if (r0 + r < R && c0 + c < C) t[r][c] = in[(int64_t)(r0 + r) * ld_in + c0 + c];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+        const int c = i >> 6, r = i & 63;
+        if (r0 + r < R && c0 + c < C) out[(int64_t)(c0 + c) * R + r0 + r] = t[r][c];
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host-side dispatch
+// ---------------------------------------------------------------------------
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <typename T, int DIV, bool ROUND>
+static int launch_rowwise(const T* x, int64_t M, int64_t N, int64_t ld_m, int64_t ld_n, uint8_t* q, float* scales,
+                          int block, cudaStream_t st) {
+    const int nb = (int)((N + block - 1) / block);
+    const int64_t tiles = M * nb;
+    if (tiles == 0) return CINN_OK;
+    const int sms = sm_count();
+    if (block == 128 && ld_n == 1 && N % 8 == 0 && ld_m % 8 == 0 && aligned16(x) && aligned16(q)) {
+        constexpr int UNROLL = 4;
+        int64_t blocks = (tiles + 16 * UNROLL - 1) / (16 * UNROLL);
+        const int64_t cap = (int64_t)sms * 8;
+        if (blocks > cap) blocks = cap;
+        quant_row_vec_kernel<T, DIV, ROUND, UNROLL><<<(unsigned)blocks, 256, 0, st>>>(x, ld_m, q, scales, (int)N, nb, tiles);
+    } else if (block == 128 && ld_m == 1 && ld_n >= M && M % 8 == 0 && ld_n % 8 == 0 && N % 16 == 0 && aligned16(x) &&
+               aligned16(q) && M > 1) {
+        dim3 grid((unsigned)nb, (unsigned)((M + 63) / 64));
+        quant_row_transposed_kernel<T, DIV, ROUND><<<grid, 256, 0, st>>>(x, ld_n, q, scales, (int)M, (int)N, nb);
+    } else {
+        int64_t blocks = (tiles + 7) / 8;
+        const int64_t cap = (int64_t)sms * 16;
+        if (blocks > cap) blocks = cap;
+        quant_row_generic_kernel<T, DIV, ROUND><<<(unsigned)blocks, 256, 0, st>>>(x, ld_m, ld_n, q, scales, (int)N, nb, block, tiles);
+    }
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+template <typename T, int DIV, bool ROUND>
+static int launch_blockwise(const T* x, int64_t M, int64_t N, int64_t ld_m, int64_t ld_n, uint8_t* q, float* scales,
+                            int bm, int bn, cudaStream_t st) {
+    const int mb = (int)((M + bm - 1) / bm), nb = (int)((N + bn - 1) / bn);
+    if (mb == 0 || nb == 0) return CINN_OK;
+    CINN_CHECK_ARG(mb <= 65535, "block-wise quantiser: more than 65535 row blocks (%d)", mb);
+    dim3 grid((unsigned)nb, (unsigned)mb);
+    const bool a = sizeof(T) == 4 ? aligned16(x) : ((reinterpret_cast<uintptr_t>(x) & 7) == 0);
+    if (bm == 128 && bn == 128 && ld_n == 1 && N % 4 == 0 && ld_m % 4 == 0 && a && (reinterpret_cast<uintptr_t>(q) & 3) == 0) {
+        quant_block_vec_kernel<T, DIV, ROUND><<<grid, 256, 0, st>>>(x, ld_m, q, scales, (int)M, (int)N, nb);
+    } else {
+        quant_block_generic_kernel<T, DIV, ROUND><<<grid, 256, 0, st>>>(x, ld_m, ld_n, q, scales, (int)M, (int)N, bm, bn, nb);
+    }
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+template <typename T>
+static int dispatch_quant(bool blockwise, const T* x, int64_t M, int64_t N, int64_t ld_m, int64_t ld_n, uint8_t* q,
+                          float* scales, int bm, int bn, int round_scale, int div_mode, cudaStream_t st) {
+#define CINN_Q(DIV, RND)                                                                              \
+    return blockwise ? launch_blockwise<T, DIV, RND>(x, M, N, ld_m, ld_n, q, scales, bm, bn, st)      \
+                     : launch_rowwise<T, DIV, RND>(x, M, N, ld_m, ld_n, q, scales, bn, st)
+    if (div_mode == CINN_DIV_FULL) { if (round_scale) { CINN_Q(CINN_DIV_FULL, true); } else { CINN_Q(CINN_DIV_FULL, false); } }
+    else                           { if (round_scale) { CINN_Q(CINN_DIV_RN, true); }   else { CINN_Q(CINN_DIV_RN, false); } }
+#undef CINN_Q
+}
+
+int quantize(bool blockwise, const void* x, int dtype, int64_t M, int64_t N, int64_t ld_m, int64_t ld_n, void* q,
+             float* scales, int bm, int bn, int round_scale, int div_mode, cudaStream_t st) {
+    CINN_CHECK_ARG(M >= 0 && N >= 0, "quantise: negative shape (%lld, %lld)", (long long)M, (long long)N);
+    if (M == 0 || N == 0) return CINN_OK;
+    CINN_CHECK_ARG(x && q && scales, "quantise: null pointer");
+    CINN_CHECK_ARG(N < (1LL << 31) && M < (1LL << 31), "quantise: dimension too large");
+    CINN_CHECK_ARG(bm >= 1 && bn >= 1 && bn <= 65536 && bm <= 65536, "quantise: bad tile %dx%d", bm, bn);
+    CINN_CHECK_ARG(div_mode == CINN_DIV_FULL || div_mode == CINN_DIV_RN, "quantise: unknown div_mode %d", div_mode);
+    CINN_CHECK_ARG(ld_m >= 0 && ld_n >= 0, "quantise: negative strides are not supported");
+    switch (dtype) {
+        case CINN_BF16: return dispatch_quant(blockwise, (const __nv_bfloat16*)x, M, N, ld_m, ld_n, (uint8_t*)q, scales, bm, bn, round_scale, div_mode, st);
+        case CINN_F16:  return dispatch_quant(blockwise, (const __half*)x, M, N, ld_m, ld_n, (uint8_t*)q, scales, bm, bn, round_scale, div_mode, st);
+        case CINN_F32:  return dispatch_quant(blockwise, (const float*)x, M, N, ld_m, ld_n, (uint8_t*)q, scales, bm, bn, round_scale, div_mode, st);
+        default: set_error("quantise: unknown dtype tag %d", dtype); return CINN_ERR_INVALID;
+    }
+}
+
+int requant_row_to_block(const void* xq, const float* xs, int64_t M, int64_t K, void* out, float* scales,
+                         int transpose_out, int div_mode, cudaStream_t st) {
+    CINN_CHECK_ARG(M >= 0 && K >= 0, "requant: negative shape");
+    if (M == 0 || K == 0) return CINN_OK;
+    CINN_CHECK_ARG(xq && xs && out && scales, "requant: null pointer");
+    CINN_CHECK_ARG(K % 16 == 0 && aligned16(xq) && aligned16(out), "requant: K must be a multiple of 16 and buffers 16-byte aligned");
+    CINN_CHECK_ARG(!transpose_out || M % 16 == 0, "requant: transposed output needs M %% 16 == 0");
+    CINN_CHECK_ARG(M < (1LL << 31) && K < (1LL << 31), "requant: dimension too large");
+    const int nb = (int)((K + 127) / 128), mb = (int)((M + 127) / 128);
+    CINN_CHECK_ARG(mb <= 65535, "requant: too many row blocks");
+    dim3 grid((unsigned)nb, (unsigned)mb);
+    const uint8_t* in = (const uint8_t*)xq;
+    uint8_t* o = (uint8_t*)out;
+    if (div_mode == CINN_DIV_FULL) {
+        if (transpose_out) requant_row_to_block_kernel<CINN_DIV_FULL, true><<<grid, 256, 0, st>>>(in, xs, nb, o, scales, (int)M, (int)K, nb);
+        else requant_row_to_block_kernel<CINN_DIV_FULL, false><<<grid, 256, 0, st>>>(in, xs, nb, o, scales, (int)M, (int)K, nb);
+    } else {
+        if (transpose_out) requant_row_to_block_kernel<CINN_DIV_RN, true><<<grid, 256, 0, st>>>(in, xs, nb, o, scales, (int)M, (int)K, nb);
+        else requant_row_to_block_kernel<CINN_DIV_RN, false><<<grid, 256, 0, st>>>(in, xs, nb, o, scales, (int)M, (int)K, nb);
+    }
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+int dequantize(const void* q, const float* scales, void* out, int out_dtype, int64_t M, int64_t N, int bm, int bn,
+               cudaStream_t st) {
+    CINN_CHECK_ARG(M >= 0 && N >= 0, "dequantise: negative shape");
+    if (M == 0 || N == 0) return CINN_OK;
+    CINN_CHECK_ARG(q && scales && out, "dequantise: null pointer");
+    CINN_CHECK_ARG(bm >= 1 && bn >= 1, "dequantise: bad tile");
+    CINN_CHECK_ARG(N < (1LL << 31), "dequantise: N too large");
+    const int ncb = (int)((N + bn - 1) / bn);
+    int64_t blocks = (M * N + 1023) / 1024;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    if (out_dtype == CINN_BF16)
+        dequant_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)q, scales, (__nv_bfloat16*)out, M, (int)N, bm, bn, ncb);
+    else if (out_dtype == CINN_F32)
+        dequant_kernel<float><<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)q, scales, (float*)out, M, (int)N, bm, bn, ncb);
+    else { set_error("dequantise: output dtype must be bf16 or fp32"); return CINN_ERR_INVALID; }
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+int transpose_bytes(const void* in, int64_t ld_in, void* out, int64_t R, int64_t C, cudaStream_t st) {
+    if (R == 0 || C == 0) return CINN_OK;
+    CINN_CHECK_ARG(in && out, "transpose: null pointer");
+    CINN_CHECK_ARG(R < (1LL << 31) && C < (1LL << 31) && (R + 63) / 64 <= 65535, "transpose: shape too large");
+    dim3 grid((unsigned)((C + 63) / 64), (unsigned)((R + 63) / 64));
+    transpose_bytes_kernel<<<grid, 256, 0, st>>>((const uint8_t*)in, ld_in, (uint8_t*)out, (int)R, (int)C);
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+}  // namespace cinn

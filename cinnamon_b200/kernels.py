@@ -1,0 +1,392 @@
+"""Drop-in replacement for cinnamon's ``src/kernels.py`` on B200.
+
+Same module-level names, argument meaning, return conventions and error
+behaviour as the reference file (shyampathak22/cinnamon, src/kernels.py); the
+GPU work is done by hand-written sm_100a kernels reached through the C ABI of
+``libcinnamon_b200.so`` (include/cinnamon_b200.h).  There is no Triton import,
+no backend dispatch and no CPU path: a CPU tensor raises ``AssertionError``
+exactly where the reference asserts ``x.is_cuda``.
+
+Differences a caller can observe, all deliberate:
+  * ``FP8MatmulFunction`` feeds the GEMM the weight as stored, (N, K), instead of
+    materialising ``w_fp8.t().contiguous()`` (reference :748-749); the weight
+    gradient quantises ``dy`` along tokens straight from ``dy`` (no
+    ``.t().contiguous()`` copy, reference :781-783) and re-quantises ``x`` in one
+    fused pass (no fp32 temporary, reference :784-787).  Values are unchanged.
+  * ``moe_grouped_gemm`` multiplies e4m3 operands with 1x128 / 128x128 scales (the
+    reference multiplies in fp16); it still returns fp16 and accepts ``dtype=``.
+  * the fp32 division flavour of the quantisers is selectable: ``"full"`` is the PTX
+    ``div.full.f32`` Triton emits for the reference on a GPU (default), ``"rn"`` is
+    IEEE division (what a CPU computes).  ``CINN_DIV_MODE`` or ``set_div_mode``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from . import _lib
+from ._compat_ops import (SparseAttentionFunction, lightning_indexer_fused,  # noqa: F401
+                          sparse_attention)
+
+_L = _lib.lib
+FP8_E4M3_MAX = 448.0
+
+_DTYPE_TAG = {torch.bfloat16: _lib.BF16, torch.float32: _lib.F32, torch.float16: _lib.F16}
+_DIV_MODE = {"full": _lib.DIV_FULL, "rn": _lib.DIV_RN}[os.environ.get("CINN_DIV_MODE", "full")]
+
+# number of kernels of this library launched since import (the benchmark reports it)
+launch_count = 0
+
+
+def set_div_mode(mode: str) -> None:
+    """``"full"`` (div.full.f32, matches the reference's Triton kernels on a GPU) or
+    ``"rn"`` (IEEE division, matches a CPU restatement)."""
+    global _DIV_MODE
+    _DIV_MODE = {"full": _lib.DIV_FULL, "rn": _lib.DIV_RN}[mode]
+
+
+def get_div_mode() -> str:
+    return "full" if _DIV_MODE == _lib.DIV_FULL else "rn"
+
+
+def _stream(t: torch.Tensor) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _ptr(t: torch.Tensor) -> ctypes.c_void_p:
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _count(n: int = 1) -> None:
+    global launch_count
+    launch_count += n
+
+
+def device_status(reset: bool = True) -> int:
+    """Device-side status word (0 = no kernel gave up on a bounded wait). Synchronises."""
+    out = ctypes.c_int(0)
+    _lib.check(_L.cinn_device_status(ctypes.byref(out), int(reset)), "cinn_device_status")
+    return out.value
+
+
+def _as_quant_input(x: torch.Tensor) -> torch.Tensor:
+    if x.dtype not in _DTYPE_TAG:
+        x = x.float()
+    if x.stride(0) < 0 or x.stride(1) < 0:
+        x = x.contiguous()
+    return x
+
+
+# -----------------------------------------------------------------------------
+# quantisers (reference: src/kernels.py:178-314)
+# -----------------------------------------------------------------------------
+def quantize_fp8_rowwise(x: torch.Tensor, block_size: int = 128, round_scale: bool = False):
+    """Row-wise 1 x block_size quantisation (reference src/kernels.py:178-216).
+
+    Returns ``(x_fp8 [M, N] float8_e4m3fn, scales [M, ceil(N/block_size)] fp32)``,
+    both freshly allocated and contiguous.  ``x`` may have any strides; a transposed
+    view is read in place."""
+    assert x.is_cuda, "Input must be on CUDA"
+    assert x.ndim == 2, "Input must be 2D for now"
+    x = _as_quant_input(x)
+    M, N = x.shape
+    nb = (N + block_size - 1) // block_size
+    with torch.cuda.device(x.device):
+        q = torch.empty((M, N), dtype=torch.float8_e4m3fn, device=x.device)
+        s = torch.empty((M, nb), dtype=torch.float32, device=x.device)
+        _lib.check(_L.cinn_quant_rowwise(_ptr(x), _DTYPE_TAG[x.dtype], M, N, x.stride(0), x.stride(1), _ptr(q),
+                                         _ptr(s), block_size, int(bool(round_scale)), _DIV_MODE, _stream(x)),
+                   "cinn_quant_rowwise")
+    _count()
+    return q, s
+
+
+def quantize_fp8_blockwise(x: torch.Tensor, block_m: int = 128, block_n: int = 128, round_scale: bool = False):
+    """Block-wise block_m x block_n quantisation (reference src/kernels.py:219-259).
+
+    Returns ``(x_fp8 [M, N], scales [ceil(M/block_m), ceil(N/block_n)])``."""
+    assert x.is_cuda, "Input must be on CUDA"
+    assert x.ndim == 2, "Input must be 2D"
+    x = _as_quant_input(x)
+    M, N = x.shape
+    mb, nb = (M + block_m - 1) // block_m, (N + block_n - 1) // block_n
+    with torch.cuda.device(x.device):
+        q = torch.empty((M, N), dtype=torch.float8_e4m3fn, device=x.device)
+        s = torch.empty((mb, nb), dtype=torch.float32, device=x.device)
+        _lib.check(_L.cinn_quant_blockwise(_ptr(x), _DTYPE_TAG[x.dtype], M, N, x.stride(0), x.stride(1), _ptr(q),
+                                           _ptr(s), block_m, block_n, int(bool(round_scale)), _DIV_MODE, _stream(x)),
+                   "cinn_quant_blockwise")
+    _count()
+    return q, s
+
+
+def _dequant(x_fp8, scales, block_m, block_n, out_dtype):
+    M, N = x_fp8.shape
+    x_fp8 = x_fp8.contiguous()
+    scales = scales.contiguous().float()
+    with torch.cuda.device(x_fp8.device):
+        out = torch.empty((M, N), dtype=out_dtype, device=x_fp8.device)
+        _lib.check(_L.cinn_dequant(_ptr(x_fp8), _ptr(scales), _ptr(out), _DTYPE_TAG[out_dtype], M, N, block_m, block_n,
+                                   _stream(x_fp8)), "cinn_dequant")
+    _count()
+    return out
+
+
+def dequantize_fp8_rowwise(x_fp8: torch.Tensor, scales: torch.Tensor, block_size: int = 128) -> torch.Tensor:
+    """fp32 = e4m3 * per-tile scale (reference src/kernels.py:262-281, pure torch there)."""
+    assert x_fp8.is_cuda, "Input must be on CUDA"
+    return _dequant(x_fp8, scales, 1, block_size, torch.float32)
+
+
+def dequantize_fp8(x_fp8: torch.Tensor, scales: torch.Tensor, block_m: int = 128, block_n: int = 128) -> torch.Tensor:
+    """bf16 = e4m3 * per-block scale (reference src/kernels.py:284-314).  ``scales`` is
+    used flattened with row pitch ceil(N/block_n), so ``block_m=1`` de-quantises
+    row-wise scales as the reference's round-trip test does (tests/test_kernels.py:57)."""
+    assert x_fp8.is_cuda, "Input must be on CUDA"
+    return _dequant(x_fp8, scales.flatten(), block_m, block_n, torch.bfloat16)
+
+
+def requantize_rowwise_to_blockwise(x_fp8: torch.Tensor, x_scale: torch.Tensor, transpose_out: bool = False):
+    """Fused ``quantize_fp8_blockwise(dequantize_fp8_rowwise(x_fp8, x_scale))`` (reference
+    src/kernels.py:784-787) without the fp32 temporary.  Returns block-scaled bytes
+    (M, K) - or (K, M) with ``transpose_out`` - and scales (ceil(M/128), ceil(K/128))."""
+    assert x_fp8.is_cuda, "Input must be on CUDA"
+    M, K = x_fp8.shape
+    x_fp8 = x_fp8.contiguous()
+    x_scale = x_scale.contiguous()
+    with torch.cuda.device(x_fp8.device):
+        out = torch.empty((K, M) if transpose_out else (M, K), dtype=torch.float8_e4m3fn, device=x_fp8.device)
+        s = torch.empty(((M + 127) // 128, (K + 127) // 128), dtype=torch.float32, device=x_fp8.device)
+        _lib.check(_L.cinn_requant_row_to_block(_ptr(x_fp8), _ptr(x_scale), M, K, _ptr(out), _ptr(s),
+                                                int(transpose_out), _DIV_MODE, _stream(x_fp8)),
+                   "cinn_requant_row_to_block")
+    _count()
+    return out, s
+
+
+# -----------------------------------------------------------------------------
+# GEMM (reference: src/kernels.py:667-702)
+# -----------------------------------------------------------------------------
+def _gemm(a, a_scales, b, b_layout, sb, sb_stride_k, sb_stride_n, M, N, K, out_dtype):
+    with torch.cuda.device(a.device):
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        _lib.check(_L.cinn_fp8_gemm(_ptr(a), _ptr(a_scales), a_scales.stride(0), _ptr(b), _ptr(sb), sb_stride_k,
+                                    sb_stride_n, _ptr(out), M, N, K, b_layout, _DTYPE_TAG[out_dtype], _stream(a)),
+                   "cinn_fp8_gemm")
+    _count()
+    return out
+
+
+def fp8_matmul_dsv3(a: torch.Tensor, b: torch.Tensor, a_scales: torch.Tensor, b_scales: torch.Tensor,
+                    out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """C = A @ B with DeepSeek-V3 scaling (reference src/kernels.py:667-702).
+
+    a: (M, K) e4m3; b: (K, N) e4m3 with any strides (a ``.t()`` view of an (N, K)
+    weight is consumed in place); a_scales: (M, ceil(K/128)); b_scales:
+    (ceil(K/128), ceil(N/128)).  fp32 accumulation, bf16 result (``out_dtype`` may
+    ask for fp32)."""
+    assert a.is_cuda and b.is_cuda, "Inputs must be on CUDA"
+    M, K = a.shape
+    K2, N = b.shape
+    assert K == K2, f"Dimension mismatch: {K} vs {K2}"
+    if a.stride(1) != 1 or a.stride(0) != K:
+        a = a.contiguous()
+    if a_scales.stride(1) != 1:
+        a_scales = a_scales.contiguous()
+    if b.stride(0) == 1 and b.stride(1) == K:          # (N, K) storage seen through .t()
+        layout = _lib.B_NK
+    elif b.stride(1) == 1 and b.stride(0) == N:
+        layout = _lib.B_KN
+    else:
+        b = b.contiguous()
+        layout = _lib.B_KN
+    return _gemm(a, a_scales.float(), b, layout, b_scales, b_scales.stride(0), b_scales.stride(1), M, N, K, out_dtype)
+
+
+def _fp8_quantize_tensor(x: torch.Tensor):
+    """Per-tensor quantisation helper kept for name compatibility (reference :705-713, unused there)."""
+    abs_max = x.abs().max().clamp(min=1e-12)
+    scale = abs_max / 448.0
+    x_fp8 = (x / scale).clamp(-448, 448).to(torch.float8_e4m3fn)
+    return x_fp8, scale.float().reshape(1).to(x.device)
+
+
+def _pad_to_multiple(x: torch.Tensor, multiple: int = 16):
+    """Reference :716-723 (unused there)."""
+    M, K = x.shape
+    pad_m = (multiple - M % multiple) % multiple
+    pad_k = (multiple - K % multiple) % multiple
+    if pad_m > 0 or pad_k > 0:
+        x = torch.nn.functional.pad(x, (0, pad_k, 0, pad_m))
+    return x, (M, K)
+
+
+def _unpad(x: torch.Tensor, orig_shape):
+    """Reference :726-728 (unused there)."""
+    return x[:orig_shape[0], :orig_shape[1]]
+
+
+class FP8MatmulFunction(torch.autograd.Function):
+    """DeepSeek-V3 style FP8 matmul (reference src/kernels.py:731-794):
+    activations / gradients 1x128, weights 128x128, e4m3 everywhere."""
+
+    @staticmethod
+    def forward(ctx, x, weight, round_scale):
+        assert x.is_cuda, "Input must be on CUDA"
+        x_shape = x.shape
+        x_flat = x.reshape(-1, x_shape[-1])
+        M, K = x_flat.shape
+        N = weight.shape[0]
+        x_fp8, x_scale = quantize_fp8_rowwise(x_flat, block_size=128, round_scale=round_scale)     # :746
+        w_fp8, w_scale = quantize_fp8_blockwise(weight.float() if weight.dtype not in _DTYPE_TAG else weight,
+                                                block_m=128, block_n=128)                            # :747
+        # :748-752 without the transposed copies: B stays (N, K); sB[kb, nb] = w_scale[nb, kb]
+        out = _gemm(x_fp8, x_scale, w_fp8, _lib.B_NK, w_scale, w_scale.stride(1), w_scale.stride(0), M, N, K,
+                    torch.bfloat16)
+        ctx.save_for_backward(x_fp8, x_scale, w_fp8, w_scale)
+        ctx.x_shape = x_shape
+        ctx.round_scale = round_scale
+        return out.reshape(*x_shape[:-1], -1)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x_fp8, x_scale, w_fp8, w_scale = ctx.saved_tensors
+        x_shape = ctx.x_shape
+        round_scale = ctx.round_scale
+        N, K = w_fp8.shape
+        grad_flat = grad_output.reshape(-1, grad_output.shape[-1])
+        if grad_flat.stride(1) != 1:
+            grad_flat = grad_flat.contiguous()
+        M = grad_flat.shape[0]
+        # dgrad (:771-774): dy (M, N) @ W (N, K); W is the B operand stored (reduction, output)
+        grad_fp8, grad_scale = quantize_fp8_rowwise(grad_flat, block_size=128, round_scale=round_scale)
+        grad_x = _gemm(grad_fp8, grad_scale, w_fp8, _lib.B_KN, w_scale, w_scale.stride(0), w_scale.stride(1), M, K, N,
+                       torch.bfloat16)
+        # wgrad (:781-788): dy^T quantised along tokens, x re-quantised in 128x128 blocks
+        grad_fp8_t, grad_scale_t = quantize_fp8_rowwise(grad_flat.t(), block_size=128, round_scale=round_scale)
+        x_fp8_block, x_scale_block = requantize_rowwise_to_blockwise(x_fp8, x_scale)
+        grad_weight = _gemm(grad_fp8_t, grad_scale_t, x_fp8_block, _lib.B_KN, x_scale_block, x_scale_block.stride(0),
+                            x_scale_block.stride(1), N, K, M, torch.bfloat16)
+        return grad_x.reshape(x_shape), grad_weight, None
+
+
+class FP8Linear(torch.nn.Module):
+    """FP8 Linear layer (reference src/kernels.py:797-840): fp32 master weight,
+    bias added after the matmul, ``round_scale`` applied to activations and gradients."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, round_scale: bool = False):
+        super().__init__()
+        self.in_features = in_features
+        self.out_features = out_features
+        self.round_scale = round_scale
+        self.weight = torch.nn.Parameter(torch.empty(out_features, in_features))
+        torch.nn.init.normal_(self.weight, mean=0.0, std=0.02)
+        if bias:
+            self.bias = torch.nn.Parameter(torch.zeros(out_features))
+        else:
+            self.register_parameter("bias", None)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.is_cuda:
+            out = FP8MatmulFunction.apply(x, self.weight, self.round_scale)
+        else:
+            # the reference does the same: an unquantised linear on CPU tensors (:823-824)
+            out = torch.nn.functional.linear(x, self.weight, None)
+        if self.bias is not None:
+            out = out + self.bias
+        return out
+
+    @classmethod
+    def from_linear(cls, linear: torch.nn.Linear, round_scale: bool = False) -> "FP8Linear":
+        fp8_linear = cls(linear.in_features, linear.out_features, bias=linear.bias is not None,
+                         round_scale=round_scale)
+        fp8_linear.weight = torch.nn.Parameter(linear.weight.data.clone())
+        if linear.bias is not None:
+            fp8_linear.bias = torch.nn.Parameter(linear.bias.data.clone())
+        return fp8_linear
+
+
+def convert_to_fp8(model: torch.nn.Module, exclude_names: list = None) -> torch.nn.Module:
+    """Swap eligible ``nn.Linear`` modules for ``FP8Linear`` in place (reference
+    src/kernels.py:843-905): names containing embedding / lm_head / router / norm /
+    attn / indexer are kept, as is any layer with a dimension below 128; ``round_scale``
+    is switched on for names containing w_out, w1 or w2."""
+    default_exclude = ["embedding", "lm_head", "router", "norm", "attn", "indexer"]
+    exclude_names = (exclude_names or []) + default_exclude
+    round_scale_names = ["w_out", "w1", "w2"]
+    for name, module in list(model.named_modules()):
+        if not isinstance(module, torch.nn.Linear):
+            continue
+        if any(excl in name for excl in exclude_names):
+            continue
+        if module.in_features < 128 or module.out_features < 128:
+            print(f"[FP8] Auto-excluding {name}: shape ({module.out_features}, {module.in_features}) < 128")
+            continue
+        parts = name.rsplit(".", 1)
+        if len(parts) == 2:
+            parent = model.get_submodule(parts[0])
+            attr_name = parts[1]
+        else:
+            parent, attr_name = model, name
+        round_scale = any(key in name for key in round_scale_names)
+        setattr(parent, attr_name, FP8Linear.from_linear(module, round_scale=round_scale))
+    return model
+
+
+# -----------------------------------------------------------------------------
+# MoE grouped GEMM (reference: src/kernels.py:526-581)
+# -----------------------------------------------------------------------------
+def quantize_expert_weights(weights: torch.Tensor):
+    """(E, d_out, d_in) -> e4m3 bytes of the same shape + scales (E, ceil(d_out/128), ceil(d_in/128)).
+    Each expert's matrix is quantised in 128x128 blocks like a dense weight (reference :747)."""
+    assert weights.is_cuda and weights.ndim == 3
+    E, d_out, d_in = weights.shape
+    w = weights if weights.dtype in _DTYPE_TAG else weights.float()
+    w = w.contiguous()
+    nob, nkb = (d_out + 127) // 128, (d_in + 127) // 128
+    if d_out % 128 == 0:
+        q, s = quantize_fp8_blockwise(w.view(E * d_out, d_in))
+        return q.view(E, d_out, d_in), s.view(E, nob, nkb)
+    q = torch.empty((E, d_out, d_in), dtype=torch.float8_e4m3fn, device=w.device)
+    s = torch.empty((E, nob, nkb), dtype=torch.float32, device=w.device)
+    for e in range(E):
+        qe, se = quantize_fp8_blockwise(w[e])
+        q[e], s[e] = qe, se
+    return q, s
+
+
+def fp8_grouped_gemm(x_fp8, x_scale, w_fp8, w_scale, expert_starts, expert_ends, out_dtype=torch.float16,
+                     out: torch.Tensor = None):
+    """Grouped GEMM on already-quantised operands.  Rows outside every expert's range are
+    left as allocated (the reference leaves them uninitialised too, :550)."""
+    T, d_in = x_fp8.shape
+    E, d_out, _ = w_fp8.shape
+    starts = expert_starts.to(torch.int64).contiguous()
+    ends = expert_ends.to(torch.int64).contiguous()
+    with torch.cuda.device(x_fp8.device):
+        if out is None:
+            out = torch.empty((T, d_out), dtype=out_dtype, device=x_fp8.device)
+        _lib.check(_L.cinn_fp8_grouped_gemm(_ptr(x_fp8), _ptr(x_scale), _ptr(w_fp8), _ptr(w_scale), _ptr(starts),
+                                            _ptr(ends), E, T, d_in, d_out, _ptr(out), _DTYPE_TAG[out.dtype],
+                                            _stream(x_fp8)), "cinn_fp8_grouped_gemm")
+    _count()
+    return out
+
+
+def moe_grouped_gemm(sorted_x: torch.Tensor, weights: torch.Tensor, expert_starts: torch.Tensor,
+                     expert_ends: torch.Tensor, max_expert_tokens: int = None,
+                     dtype: torch.dtype = torch.float16) -> torch.Tensor:
+    """Grouped GEMM for MoE (reference src/kernels.py:526-581): for each expert e,
+    ``out[starts[e]:ends[e]] = sorted_x[starts[e]:ends[e]] @ weights[e].T``.
+
+    ``expert_starts`` / ``expert_ends`` are read on the device; ``max_expert_tokens`` is
+    accepted for signature compatibility and ignored (no grid depends on it, so the
+    caller's ``.item()`` synchronisation is unnecessary).  Tokens and weights are quantised
+    to e4m3 on the fly; returns fp16 like the reference unless ``dtype`` says otherwise."""
+    assert sorted_x.is_cuda and weights.is_cuda, "Inputs must be on CUDA"
+    x = sorted_x if sorted_x.stride(-1) == 1 else sorted_x.contiguous()
+    x_fp8, x_scale = quantize_fp8_rowwise(x, block_size=128)
+    w_fp8, w_scale = quantize_expert_weights(weights)
+    return fp8_grouped_gemm(x_fp8, x_scale, w_fp8, w_scale, expert_starts, expert_ends, out_dtype=dtype)

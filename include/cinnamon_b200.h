@@ -1,0 +1,107 @@
+/* cinnamon_b200 — C ABI of the B200 (sm_100a) FP8 training kernels.
+ *
+ * A drop-in for the GPU half of cinnamon's src/kernels.py (shyampathak22/cinnamon):
+ * each entry point replaces one Triton launch of that file.  Every pointer is a
+ * DEVICE pointer unless stated otherwise; sizes are in elements; `stream` is a
+ * cudaStream_t passed as void* (NULL = the legacy default stream).  Nothing here
+ * synchronises the host with the device.
+ *
+ * Every function returns 0 on success or one of the CINN_ERR_* codes; the text of
+ * the last failure on the calling thread is available from cinn_last_error().
+ * The reference signals bad arguments with Python `assert` (src/kernels.py:194-195,
+ * 237-238, 296, 683); the Python layer above this ABI turns non-zero codes into
+ * AssertionError / RuntimeError accordingly.
+ */
+#ifndef CINNAMON_B200_H
+#define CINNAMON_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CINN_OK 0
+#define CINN_ERR_INVALID 1
+#define CINN_ERR_CUDA 2
+#define CINN_ERR_UNSUPPORTED 3
+#define CINN_ERR_DEVICE 4
+
+/* element type tags */
+#define CINN_BF16 0
+#define CINN_F32 1
+#define CINN_F16 2
+
+/* fp32 division flavour used for amax/448 and x/scale */
+#define CINN_DIV_FULL 0 /* PTX div.full.f32: what Triton emits for the reference kernels on a GPU */
+#define CINN_DIV_RN 1   /* IEEE round-to-nearest: what a CPU restatement of the reference computes */
+
+/* layout of the B operand of cinn_fp8_gemm */
+#define CINN_B_NK 0 /* B stored (N, K), reduction axis contiguous  (a weight as nn.Linear keeps it) */
+#define CINN_B_KN 1 /* B stored (K, N), output axis contiguous     (what fp8_matmul_dsv3 documents) */
+
+int cinn_version(void);
+const char* cinn_last_error(void);
+
+/* Row-wise 1 x block_size quantisation to e4m3 with one fp32 scale per tile.
+ * Replaces quantize_fp8_rowwise_kernel + quantize_fp8_rowwise (src/kernels.py:19-71, 178-216).
+ * x: (M, N) of x_dtype, element (m, n) at x[m*ld_m + n*ld_n] (any non-negative strides, as the
+ * reference passes x.stride(), :209).  q: (M, N) bytes, contiguous.  scales: (M, ceil(N/block_size)). */
+int cinn_quant_rowwise(const void* x, int x_dtype, int64_t M, int64_t N, int64_t ld_m, int64_t ld_n,
+                       void* q, float* scales, int block_size, int round_scale, int div_mode, void* stream);
+
+/* Block-wise block_m x block_n quantisation.
+ * Replaces quantize_fp8_blockwise_kernel + quantize_fp8_blockwise (src/kernels.py:74-132, 219-259).
+ * scales: (ceil(M/block_m), ceil(N/block_n)). */
+int cinn_quant_blockwise(const void* x, int x_dtype, int64_t M, int64_t N, int64_t ld_m, int64_t ld_n,
+                         void* q, float* scales, int block_m, int block_n, int round_scale, int div_mode,
+                         void* stream);
+
+/* Row-scaled e4m3 (1x128 tiles) -> block-scaled e4m3 (128x128) in one pass.
+ * Replaces dequantize_fp8_rowwise followed by quantize_fp8_blockwise in the weight-gradient path
+ * (src/kernels.py:784-787) without the fp32 temporary.  xq: (M, K) bytes, xs: (M, ceil(K/128)).
+ * out: (M, K) bytes, or (K, M) when transpose_out != 0.  scales: (ceil(M/128), ceil(K/128)). */
+int cinn_requant_row_to_block(const void* xq, const float* xs, int64_t M, int64_t K, void* out, float* scales,
+                              int transpose_out, int div_mode, void* stream);
+
+/* out[r, c] = e4m3(q[r, c]) * scales[(r / block_m) * ceil(N/block_n) + c / block_n].
+ * Replaces dequantize_fp8_kernel + dequantize_fp8 (bf16 out, src/kernels.py:135-173, 284-314) and
+ * dequantize_fp8_rowwise (fp32 out with block_m = 1, src/kernels.py:262-281). */
+int cinn_dequant(const void* q, const float* scales, void* out, int out_dtype, int64_t M, int64_t N,
+                 int block_m, int block_n, void* stream);
+
+/* out (C, R) = in (R, C; row pitch ld_in) transposed, bytes.  Replaces the `.t().contiguous()` copies of
+ * e4m3 operands (src/kernels.py:748). */
+int cinn_transpose_bytes(const void* in, int64_t ld_in, void* out, int64_t R, int64_t C, void* stream);
+
+/* Block-scaled FP8 GEMM:  C[M, N] = sum_kb (A[:, kb] * sA[:, kb]) @ (B[kb, :] * sB[kb, nb]).
+ * Replaces fp8_gemm_kernel + fp8_matmul_dsv3 (src/kernels.py:588-664, 667-702).
+ * A: (M, K) e4m3, K contiguous.  sA: (M, ceil(K/128)) fp32, row pitch ld_sa.
+ * B: e4m3 in the layout named by b_layout.  sB: element (kb, nb) at sB[kb*sb_stride_k + nb*sb_stride_n].
+ * C: (M, N) contiguous, out_dtype CINN_BF16 (what the reference returns) or CINN_F32.
+ * K must be a multiple of 16; N a multiple of 8 for bf16 output, 4 for fp32 output. */
+int cinn_fp8_gemm(const void* A, const float* sA, int64_t ld_sa, const void* B, const float* sB,
+                  int64_t sb_stride_k, int64_t sb_stride_n, void* C, int64_t M, int64_t N, int64_t K,
+                  int b_layout, int out_dtype, void* stream);
+
+/* Grouped (per-expert) block-scaled FP8 GEMM over ragged row ranges:
+ * for each expert e:  C[starts[e]:ends[e], :] = A[starts[e]:ends[e], :] @ W[e]^T.
+ * Replaces grouped_gemm_kernel + moe_grouped_gemm (src/kernels.py:440-523, 526-581); the reference runs it in
+ * fp16, here the operands are e4m3 with 1x128 / 128x128 scales like the dense GEMM.
+ * A: (T, d_in) e4m3.  sA: (T, ceil(d_in/128)).  W: (E, d_out, d_in) e4m3.  sW: (E, ceil(d_out/128), ceil(d_in/128)).
+ * starts/ends: int64 device arrays of length E, read on the device (no host synchronisation, no padding).
+ * C: (T, d_out).  Rows that belong to no expert are left untouched. */
+int cinn_fp8_grouped_gemm(const void* A, const float* sA, const void* W, const float* sW,
+                          const int64_t* starts, const int64_t* ends, int64_t E, int64_t T, int64_t d_in,
+                          int64_t d_out, void* C, int out_dtype, void* stream);
+
+/* Reads (and with reset != 0 clears) the device-side status word of the current device into the HOST int
+ * *out.  0 means no kernel of this library has given up on a bounded wait since the last reset; any other
+ * value is (role << 8) | reason.  This call synchronises with the device.  No counterpart in the reference,
+ * whose kernels have no waits. */
+int cinn_device_status(int* out, int reset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

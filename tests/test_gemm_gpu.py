@@ -1,0 +1,177 @@
+"""Block-scaled FP8 GEMM parity: CUDA (through the C ABI) against the float64
+dequantise -> matmul oracle.  Tolerance from the specification: relative
+Frobenius error <= 1e-3 on the fp32 result; the bf16 result is compared with the
+float64 result rounded to bf16."""
+import numpy as np
+import pytest
+import torch
+
+from _util import rel_fro
+from oracle import fp8_oracle as O
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3          # rel-Frobenius bound of the specification (fp32 output)
+
+
+@pytest.fixture(scope="module")
+def K():
+    from cinnamon_b200 import kernels
+    kernels.set_div_mode("rn")
+    yield kernels
+    assert kernels.device_status() == 0, "a kernel gave up on a bounded wait"
+    kernels.set_div_mode("full")
+
+
+def _operands(M, N, Kd, seed):
+    x, w, _ = O.make_linear_case(M, Kd, N, seed)
+    xq, xs = O.quantize_rowwise(x, 128)
+    wq, ws = O.quantize_blockwise(w.float(), 128, 128)
+    return xq, xs, wq, ws
+
+
+def _f8(t):
+    return t.cuda().view(torch.float8_e4m3fn)
+
+
+SHAPES = [(128, 256, 128), (256, 512, 512), (130, 576, 512), (130, 576, 640), (1, 128, 256), (300, 64, 1024),
+          (4096, 2048, 512), (257, 1000, 144)]
+
+
+@pytest.mark.parametrize("M,N,Kd", SHAPES)
+def test_gemm_weight_layout_nk(K, M, N, Kd):
+    """B given as the (N, K) weight seen through .t(): the forward layout."""
+    xq, xs, wq, ws = _operands(M, N, Kd, seed=M + N + Kd)
+    ref = O.fp8_matmul_f64(xq, wq.t(), xs, ws.t())
+    out32 = K.fp8_matmul_dsv3(_f8(xq), _f8(wq).t(), xs.cuda(), ws.cuda().t(), out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert K.device_status() == 0
+    err = rel_fro(out32, ref)
+    maxabs = float((out32.cpu().double() - ref).abs().max())
+    print(f"[{M}x{N}x{Kd}] fp32 rel-Fro {err:.3e} max-abs {maxabs:.3e}")
+    assert err <= TOL
+    assert err <= 2e-5          # e4m3 products are exact, only fp32 accumulation rounds
+    out16 = K.fp8_matmul_dsv3(_f8(xq), _f8(wq).t(), xs.cuda(), ws.cuda().t())
+    assert out16.dtype == torch.bfloat16
+    ref16 = ref.to(torch.bfloat16)
+    diff = (out16.cpu().view(torch.int16).int() - ref16.view(torch.int16).int()).abs()
+    assert diff.max().item() <= 1 and (diff != 0).float().mean().item() < 1e-2
+
+
+@pytest.mark.parametrize("M,N,Kd", [(128, 256, 128), (256, 512, 512), (130, 576, 640), (300, 64, 1024), (4096, 2048, 512)])
+def test_gemm_layout_kn(K, M, N, Kd):
+    """B stored (K, N) as fp8_matmul_dsv3 documents (src/kernels.py:669)."""
+    xq, xs, wq, ws = _operands(M, N, Kd, seed=7 + M + N + Kd)
+    b = wq.t().contiguous()
+    bs = ws.t().contiguous()
+    ref = O.fp8_matmul_f64(xq, b, xs, bs)
+    out32 = K.fp8_matmul_dsv3(_f8(xq), _f8(b), xs.cuda(), bs.cuda(), out_dtype=torch.float32)
+    err = rel_fro(out32, ref)
+    print(f"[KN {M}x{N}x{Kd}] fp32 rel-Fro {err:.3e}")
+    assert err <= TOL and err <= 2e-5
+
+
+def test_gemm_is_deterministic(K):
+    xq, xs, wq, ws = _operands(512, 1024, 1024, seed=5)
+    a = K.fp8_matmul_dsv3(_f8(xq), _f8(wq).t(), xs.cuda(), ws.cuda().t(), out_dtype=torch.float32)
+    b = K.fp8_matmul_dsv3(_f8(xq), _f8(wq).t(), xs.cuda(), ws.cuda().t(), out_dtype=torch.float32)
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("M,Kd,N,rs", [(256, 512, 384, False), (512, 256, 640, True), (4096, 512, 2048, False)])
+def test_autograd_function_matches_oracle(K, M, Kd, N, rs):
+    """FP8MatmulFunction forward / dgrad / wgrad (src/kernels.py:739-794)."""
+    x, w, dy = O.make_linear_case(M, Kd, N, seed=11 + M)
+    ref_out, saved = O.fp8_linear_forward(x, w, rs)
+    ref_gx, ref_gw = O.fp8_linear_backward(dy, saved, rs)
+    xg = x.cuda().requires_grad_(True)
+    wg = w.float().cuda().requires_grad_(True)
+    out = K.FP8MatmulFunction.apply(xg, wg, rs)
+    out.backward(dy.cuda())
+    assert out.dtype == torch.bfloat16 and xg.grad.shape == x.shape and wg.grad.shape == w.shape
+    for name, got, ref in (("fwd", out, ref_out), ("dgrad", xg.grad, ref_gx), ("wgrad", wg.grad, ref_gw)):
+        ref16 = ref.to(torch.bfloat16)
+        diff = (got.detach().to(torch.bfloat16).cpu().view(torch.int16).int() - ref16.view(torch.int16).int()).abs()
+        err = rel_fro(got.detach().float(), ref)
+        print(f"{name}: rel-Fro(bf16 out) {err:.3e}, max bf16 ulp {diff.max().item()}")
+        assert diff.max().item() <= 1, name
+        assert err < 4e-3, name          # bf16 rounding alone costs ~1.7e-3
+
+
+def test_fp8_linear_module(K):
+    g = torch.Generator().manual_seed(3)
+    lin = K.FP8Linear(256, 384, bias=True, round_scale=True).cuda()
+    x = torch.randn(2, 65, 256, generator=g).cuda()
+    y = lin(x)
+    assert y.shape == (2, 65, 384)
+    ref, _ = O.fp8_linear_forward(x.cpu().reshape(-1, 256), lin.weight.detach().cpu(), True)
+    ref = ref.reshape(2, 65, 384) + lin.bias.detach().cpu().double()
+    assert rel_fro(y.float(), ref) < 4e-3
+    y.sum().backward()
+    assert lin.weight.grad is not None and lin.weight.grad.dtype == torch.float32
+
+
+def _grouped_case(E, d_in, d_out, counts, seed, gap=0):
+    g = torch.Generator().manual_seed(seed)
+    T = sum(counts) + gap
+    x = torch.randn(T, d_in, generator=g).bfloat16()
+    w = (torch.randn(E, d_out, d_in, generator=g) * 0.02).bfloat16()
+    ends = torch.tensor(counts).cumsum(0)
+    starts = ends - torch.tensor(counts)
+    return x, w, starts, ends
+
+
+GROUPED = {
+    "equal_reference_case": (8, 512, 128, [32] * 8),                       # tests/test_kernels.py:131-155
+    "ragged": (6, 256, 384, [5, 0, 130, 1, 257, 64]),
+    "empty_first_last": (5, 384, 256, [0, 200, 0, 129, 0]),
+    "one_owns_all": (4, 256, 512, [0, 0, 700, 0]),
+    "single_tokens": (16, 128, 128, [1] * 16),
+    "wide_k": (3, 1024, 320, [100, 300, 28]),
+}
+
+
+@pytest.mark.parametrize("name", list(GROUPED))
+def test_grouped_gemm(K, name):
+    E, d_in, d_out, counts = GROUPED[name]
+    x, w, starts, ends = _grouped_case(E, d_in, d_out, counts, seed=len(name), gap=9)
+    ref = O.grouped_gemm_fp8_f64(x, w, starts, ends)
+    xq, xs = K.quantize_fp8_rowwise(x.cuda())
+    wq, ws = K.quantize_expert_weights(w.cuda())
+    T = x.shape[0]
+    out = torch.full((T, d_out), 777.0, dtype=torch.float32, device="cuda")       # canary everywhere
+    K.fp8_grouped_gemm(xq, xs, wq, ws, starts.cuda(), ends.cuda(), out=out)
+    torch.cuda.synchronize()
+    assert K.device_status() == 0
+    used = int(ends[-1])
+    assert torch.all(out[used:] == 777.0), "rows outside every expert's range were written"
+    err = rel_fro(out[:used], ref[:used])
+    print(f"{name}: rel-Fro {err:.3e}")
+    assert err <= TOL and err <= 2e-5
+    # the drop-in entry point: fp16 result like the reference, loose check like its own test
+    out16 = K.moe_grouped_gemm(x.cuda(), w.cuda(), starts.cuda(), ends.cuda())
+    assert out16.dtype == torch.float16 and out16.shape == (T, d_out)
+    plain = O.grouped_gemm_f64(x, w, starts, ends)
+    rel = ((plain[:used] - out16[:used].cpu().double()).abs() / (plain[:used].abs() + 1e-6))
+    assert rel.median().item() < 0.08
+
+
+def test_config2_full_size_sampled(K):
+    """16384 x 18432 x 7168 forward; rows sampled for the float64 check."""
+    M, Kd, N = 16384, 7168, 18432
+    g = torch.Generator().manual_seed(1002)
+    x = torch.randn(M, Kd, generator=g).bfloat16().cuda()
+    w = (torch.randn(N, Kd, generator=g) * 0.02).bfloat16().cuda()
+    xq, xs = K.quantize_fp8_rowwise(x)
+    wq, ws = K.quantize_fp8_blockwise(w)
+    out = K.fp8_matmul_dsv3(xq, wq.t(), xs, ws.t(), out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert K.device_status() == 0
+    rows = torch.tensor([0, 1, 127, 128, 5000, 8191, 12345, 16383])
+    ref = O.fp8_matmul_f64(xq[rows.cuda()].view(torch.uint8).cpu(), wq.view(torch.uint8).cpu().t(),
+                           xs[rows.cuda()].cpu(), ws.cpu().t())
+    err = rel_fro(out[rows.cuda()], ref)
+    print(f"C2 forward sampled rows: rel-Fro {err:.3e}")
+    assert err <= TOL and err <= 2e-5
+    # linearity in the activation scales: doubling sA doubles the result exactly
+    out2 = K.fp8_matmul_dsv3(xq, wq.t(), xs * 2, ws.t(), out_dtype=torch.float32)
+    assert torch.equal(out2, out * 2)
