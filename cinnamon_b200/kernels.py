@@ -38,6 +38,8 @@ _DIV_MODE = {"full": _lib.DIV_FULL, "rn": _lib.DIV_RN}[os.environ.get("CINN_DIV_
 
 # number of kernels of this library launched since import (the benchmark reports it)
 launch_count = 0
+# when set to a list, every GEMM launch appends a (start, end) pair of CUDA events to it
+gemm_events = None
 
 
 def set_div_mode(mode: str) -> None:
@@ -172,9 +174,16 @@ def requantize_rowwise_to_blockwise(x_fp8: torch.Tensor, x_scale: torch.Tensor, 
 def _gemm(a, a_scales, b, b_layout, sb, sb_stride_k, sb_stride_n, M, N, K, out_dtype):
     with torch.cuda.device(a.device):
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        ev = None
+        if gemm_events is not None:
+            ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            ev[0].record()
         _lib.check(_L.cinn_fp8_gemm(_ptr(a), _ptr(a_scales), a_scales.stride(0), _ptr(b), _ptr(sb), sb_stride_k,
                                     sb_stride_n, _ptr(out), M, N, K, b_layout, _DTYPE_TAG[out_dtype], _stream(a)),
                    "cinn_fp8_gemm")
+        if ev is not None:
+            ev[1].record()
+            gemm_events.append(ev)
     _count()
     return out
 
@@ -264,11 +273,18 @@ class FP8MatmulFunction(torch.autograd.Function):
         grad_fp8, grad_scale = quantize_fp8_rowwise(grad_flat, block_size=128, round_scale=round_scale)
         grad_x = _gemm(grad_fp8, grad_scale, w_fp8, _lib.B_KN, w_scale, w_scale.stride(0), w_scale.stride(1), M, K, N,
                        torch.bfloat16)
-        # wgrad (:781-788): dy^T quantised along tokens, x re-quantised in 128x128 blocks
+        # wgrad (:781-788): dy^T quantised along tokens, x re-quantised in 128x128 blocks.
+        # The token axis is the reduction axis here; the GEMM wants it in multiples of 16, so a
+        # ragged token count is padded with zero rows (they change neither an amax nor a sum).
+        Mp = (M + 15) // 16 * 16
+        if Mp != M:
+            grad_flat = torch.nn.functional.pad(grad_flat, (0, 0, 0, Mp - M))
+            x_fp8 = torch.nn.functional.pad(x_fp8.view(torch.uint8), (0, 0, 0, Mp - M)).view(torch.float8_e4m3fn)
+            x_scale = torch.nn.functional.pad(x_scale, (0, 0, 0, Mp - M), value=1.0)
         grad_fp8_t, grad_scale_t = quantize_fp8_rowwise(grad_flat.t(), block_size=128, round_scale=round_scale)
         x_fp8_block, x_scale_block = requantize_rowwise_to_blockwise(x_fp8, x_scale)
         grad_weight = _gemm(grad_fp8_t, grad_scale_t, x_fp8_block, _lib.B_KN, x_scale_block, x_scale_block.stride(0),
-                            x_scale_block.stride(1), N, K, M, torch.bfloat16)
+                            x_scale_block.stride(1), N, K, Mp, torch.bfloat16)
         return grad_x.reshape(x_shape), grad_weight, None
 
 

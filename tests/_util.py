@@ -28,3 +28,14 @@ def ulp_distance(a_bits: np.ndarray, b_bits: np.ndarray) -> np.ndarray:
 
 def rel_fro(a, ref):
     return O.rel_fro(a.detach().cpu(), ref)
+
+
+def assert_bf16_close(got: torch.Tensor, ref64: torch.Tensor, what=""):
+    """A bf16 result against the float64 result: each element within one bf16 rounding
+    step (2^-8 relative) of the exact value, plus the fp32 accumulation error, which is
+    relative to the size of the whole result, not of the element (matters next to zero)."""
+    g = got.detach().cpu().double()
+    r = ref64.double()
+    tol = r.abs() * 2.0 ** -8 + 1e-5 * r.pow(2).mean().sqrt()
+    bad = (g - r).abs() > tol
+    assert not bad.any(), f"{what}: {int(bad.sum())} of {bad.numel()} elements off by more than a bf16 step"
