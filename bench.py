@@ -168,7 +168,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--shape", default=None, help="M,K,N of a smaller case (profiling captures); default is the FFN workload")
     args = ap.parse_args()
+    if args.shape:
+        global M, K, N, FLOP_PER_STEP, WORKLOAD
+        M, K, N = (int(v) for v in args.shape.split(","))
+        FLOP_PER_STEP = 3 * 2.0 * M * N * K
+        WORKLOAD = f"fp8_linear_fwd_bwd M={M} K={K} N={N} (reduced case, not the headline workload)"
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     if args.impl == "reference":
@@ -278,7 +284,7 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
             "config": {"workload": WORKLOAD, "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
-                       "l2": "inputs larger than L2 (x 235 MB, W 528 MB, dy 604 MB)"},
+                       "l2": f"inputs larger than L2 (x {M * K * 2 >> 20} MiB, W {N * K * 4 >> 20} MiB, dy {M * N * 2 >> 20} MiB)"},
             "roofline": {"kernel": "fp8_gemm_kernel", "bound": "tensor", "achieved": achieved, "peak": fp8_peak,
                          "unit": "TFLOP/s", "frac": (achieved / fp8_peak) if achieved else None,
                          "peak_source": f"2 x bf16_tflops_sustained of {peak_kind} MEASURED_PEAKS (dense FP8 runs at twice "
