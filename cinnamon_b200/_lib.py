@@ -11,7 +11,7 @@ import os
 from .build import LIB_PATH
 
 OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE = 0, 1, 2, 3, 4
-BF16, F32, F16 = 0, 1, 2
+BF16, F32, F16, F32_BF16 = 0, 1, 2, 3
 DIV_FULL, DIV_RN = 0, 1
 B_NK, B_KN = 0, 1
 

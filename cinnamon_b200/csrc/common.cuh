@@ -18,6 +18,7 @@
 #define CINN_BF16 0
 #define CINN_F32 1
 #define CINN_F16 2
+#define CINN_F32_BF16 3   // GEMM output only: fp32 storage of the value rounded to bf16
 
 // division flavour of the quantisers
 #define CINN_DIV_FULL 0   // PTX div.full.f32: what Triton emits for the reference kernels on a GPU
@@ -84,8 +85,10 @@ __device__ __forceinline__ float scale_from_amax(float amax) {
 template <int DIV>
 __device__ __forceinline__ float scaled_clamped(float x, float s) {
     float y = div_f32<DIV>(x, s);
-    // max then min, both dropping a NaN operand (PTX max.f32 / min.f32)
-    return fminf(fmaxf(y, -kFp8Max), kFp8Max);
+    // The reference clamps with max(y, -448) then min(., 448), both dropping a NaN operand.
+    // Only the max is kept: it turns NaN into -448 as the reference does; the upper (and lower)
+    // clamp is what the saturating e4m3 conversion that always follows does anyway.
+    return fmaxf(y, -kFp8Max);
 }
 
 // two fp32 -> two e4m3 bytes (lo in bits 0-7, hi in bits 8-15), RNE, finite saturation

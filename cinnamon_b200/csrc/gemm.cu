@@ -26,7 +26,7 @@ constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK;   // 16 KiB
 constexpr int B_BYTES = BN * BK;   // 32 KiB
 constexpr int EPI_WARPS = 8;
-constexpr int THREADS = (EPI_WARPS + 2) * 32;
+constexpr int THREADS = (EPI_WARPS + 4) * 32;   // warps 8-11: producer, MMA, two idle (a full warpgroup for setmaxnreg)
 constexpr int TMEM_COLS = 512;
 constexpr int MAX_EXPERTS = 2048;
 constexpr int GROUP_M = 16;        // rasterisation: m-tiles per L2 group (dense)
@@ -120,6 +120,20 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 32 lanes x 32 consecutive fp32 columns, not yet waited for
+__device__ __forceinline__ void tc_ld32_nowait(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// register budget: the kernel starts with 168 registers per thread (384 threads); the
+// epilogue warpgroups grow to 232 once the producer / MMA warpgroup has shrunk to 40
+__device__ __forceinline__ void reg_grow() { asm volatile("setmaxnreg.inc.sync.aligned.u32 232;"); }
+__device__ __forceinline__ void reg_shrink() { asm volatile("setmaxnreg.dec.sync.aligned.u32 40;"); }
+
 // Shared-memory matrix descriptor, 128-byte swizzle, Blackwell descriptor version 1.
 // lbo / sbo in bytes.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
@@ -194,13 +208,20 @@ template <int OUT> struct OutT;
 template <> struct OutT<CINN_BF16> { using type = __nv_bfloat16; };
 template <> struct OutT<CINN_F16> { using type = __half; };
 template <> struct OutT<CINN_F32> { using type = float; };
+template <> struct OutT<CINN_F32_BF16> { using type = float; };   // fp32 storage of the bf16-rounded value
 
 template <int OUT>
 __device__ __forceinline__ void store8(void* C, int64_t off, const float* a, bool vec, int ncols) {
     using T = typename OutT<OUT>::type;
     T* dst = reinterpret_cast<T*>(C) + off;
+    float b[8];
+    if constexpr (OUT == CINN_F32_BF16) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) b[i] = __bfloat162float(__float2bfloat16_rn(a[i]));
+        a = b;
+    }
     if (vec && ncols >= 8) {
-        if constexpr (OUT == CINN_F32) {
+        if constexpr (OUT == CINN_F32 || OUT == CINN_F32_BF16) {
             reinterpret_cast<float4*>(dst)[0] = make_float4(a[0], a[1], a[2], a[3]);
             reinterpret_cast<float4*>(dst)[1] = make_float4(a[4], a[5], a[6], a[7]);
         } else if constexpr (OUT == CINN_BF16) {
@@ -220,7 +241,7 @@ __device__ __forceinline__ void store8(void* C, int64_t off, const float* a, boo
         }
     } else {
         for (int i = 0; i < 8 && i < ncols; ++i) {
-            if constexpr (OUT == CINN_F32) dst[i] = a[i];
+            if constexpr (OUT == CINN_F32 || OUT == CINN_F32_BF16) dst[i] = a[i];
             else if constexpr (OUT == CINN_BF16) dst[i] = __float2bfloat16_rn(a[i]);
             else dst[i] = __float2half_rn(a[i]);
         }
@@ -289,7 +310,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int KB = (p.K + BK - 1) / BK;
     const int n_total = total_tiles<GROUPED>(p, cum);
 
-    if (warp == EPI_WARPS) {
+    if (warp >= EPI_WARPS) {
+      reg_shrink();
+      if (warp == EPI_WARPS) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             uint32_t it = 0;
@@ -352,12 +375,14 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
             }
         }
+      }
     } else {
+        reg_grow();
         // ------------------------------ epilogue ------------------------------
         const int q = warp & 3, h = warp >> 2;
         uint32_t it = 0;
         bool alive = true;
-        const bool vec_ok = (OUT == CINN_F32) ? (p.ldc % 4 == 0) : (p.ldc % 8 == 0);
+        const bool vec_ok = (OUT == CINN_F32 || OUT == CINN_F32_BF16) ? (p.ldc % 4 == 0) : (p.ldc % 8 == 0);
         for (int t = blockIdx.x; t < n_total && alive; t += gridDim.x) {
             const TileInfo ti = tile_info<GROUPED>(p, cum, t);
             const int row = ti.m0 + q * 32 + lane;
@@ -380,16 +405,22 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 if (!mbar_wait(tfull0 + 8 * b, bph, abort_flag, (3 << 8) | 1)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * BN + h * 128;
+                // two loads of 64 columns: one TMEM round trip per 64 FMAs; the buffer is handed
+                // back to the MMA warp as soon as the second half sits in registers
+                uint32_t r[64];
+                tc_ld32_nowait(taddr, r);
+                tc_ld32_nowait(taddr + 32, r + 32);
+                tc_wait_ld();
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    float v[16];
-                    tc_ld16(taddr + c * 16, v);
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) acc[c * 16 + j] = fmaf(v[j], s, acc[c * 16 + j]);
-                }
+                for (int j = 0; j < 64; ++j) acc[j] = fmaf(__uint_as_float(r[j]), s, acc[j]);
+                tc_ld32_nowait(taddr + 64, r);
+                tc_ld32_nowait(taddr + 96, r + 32);
+                tc_wait_ld();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty0 + 8 * b);
+#pragma unroll
+                for (int j = 0; j < 64; ++j) acc[64 + j] = fmaf(__uint_as_float(r[j]), s, acc[64 + j]);
             }
             if (alive && rvalid && cvalid) {
                 const int64_t base = (int64_t)row * p.ldc + col0;
@@ -477,6 +508,7 @@ static int launch_out(const CUtensorMap& ta, const CUtensorMap& tb, const GemmPa
         case CINN_BF16: return launch<B_MN, GROUPED, CINN_BF16>(ta, tb, p, grid, st);
         case CINN_F32: return launch<B_MN, GROUPED, CINN_F32>(ta, tb, p, grid, st);
         case CINN_F16: return launch<B_MN, GROUPED, CINN_F16>(ta, tb, p, grid, st);
+        case CINN_F32_BF16: return launch<B_MN, GROUPED, CINN_F32_BF16>(ta, tb, p, grid, st);
         default: set_error("GEMM: unknown output dtype tag %d", out_dtype); return CINN_ERR_INVALID;
     }
 }

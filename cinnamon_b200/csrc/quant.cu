@@ -10,6 +10,7 @@
 // Layout: every kernel moves 16-byte vectors per lane where alignment allows,
 // reduces amax with warp shuffles, and writes packed e4m3 (4-16 bytes per lane).
 #include "common.cuh"
+#include <type_traits>
 
 namespace cinn {
 
@@ -64,57 +65,105 @@ template <> struct Elem<float> {
 
 // ---------------------------------------------------------------------------
 // Row-wise 1x128, contiguous rows, vector path.
-// A half-warp owns one tile (16 lanes x 8 elements); each thread keeps UNROLL
-// tiles in flight so the loads of several tiles overlap.
+// A half-warp owns one tile (16 lanes x 8 elements).  Each thread keeps UNROLL tiles per
+// round and fetches the raw vectors of the next round before it converts the current one,
+// so loads stay in flight during the arithmetic.  Tile coordinates advance incrementally
+// (no division in the loop).
 // ---------------------------------------------------------------------------
+template <typename T> struct Raw8 { uint4 a; };
+template <> struct Raw8<float> { float4 a, b; };
+
+template <typename T>
+__device__ __forceinline__ Raw8<T> load_raw8(const T* p) {
+    Raw8<T> r;
+    if constexpr (sizeof(T) == 4) {
+        r.a = __ldcs(reinterpret_cast<const float4*>(p));
+        r.b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
+    } else {
+        r.a = __ldcs(reinterpret_cast<const uint4*>(p));
+    }
+    return r;
+}
+template <typename T>
+__device__ __forceinline__ Raw8<T> zero_raw8() {
+    Raw8<T> r;
+    if constexpr (sizeof(T) == 4) { r.a = make_float4(0.f, 0.f, 0.f, 0.f); r.b = r.a; }
+    else r.a = make_uint4(0u, 0u, 0u, 0u);
+    return r;
+}
+template <typename T>
+__device__ __forceinline__ void unpack_raw8(const Raw8<T>& r, float (&v)[8]) {
+    if constexpr (sizeof(T) == 4) {
+        v[0] = r.a.x; v[1] = r.a.y; v[2] = r.a.z; v[3] = r.a.w; v[4] = r.b.x; v[5] = r.b.y; v[6] = r.b.z; v[7] = r.b.w;
+    } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+    } else {
+        const __half2* h = reinterpret_cast<const __half2*>(&r.a);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+    }
+}
+
 template <typename T, int DIV, bool ROUND, int UNROLL>
 __global__ void __launch_bounds__(256)
 quant_row_vec_kernel(const T* __restrict__ x, int64_t ld, uint8_t* __restrict__ q, float* __restrict__ scales,
-                     int N, int nb, int64_t total_tiles) {
+                     int N, int nb, int64_t total_tiles, int step_rows, int step_cols) {
+    // the n-th tile of this half-warp is hw + n * n_hw; (step_rows, step_cols) = divmod(n_hw, nb)
     const int sub = threadIdx.x & 15;
     const int64_t hw = (int64_t)blockIdx.x * 16 + (threadIdx.x >> 4);
     const int64_t n_hw = (int64_t)gridDim.x * 16;
-    // warp-uniform trip count: both half-warps of a warp run the same number of rounds
-    const int64_t warp_first = hw & ~(int64_t)1;
-    for (int64_t t0 = warp_first; t0 < total_tiles; t0 += n_hw * UNROLL) {
-        float v[UNROLL][8];
-        int64_t tile[UNROLL];
-        bool inb[UNROLL];
+    int64_t t = hw;                                  // this half-warp's next tile to FETCH
+    int row = (int)(hw / nb);
+    int cb = (int)(hw - (int64_t)row * nb);
+    int64_t tw = hw & ~(int64_t)1;                   // warp-uniform loop variable
+
+    Raw8<T> nxt[UNROLL];
+    int64_t nxt_off[UNROLL];                         // output offset row * N + col, or -1
+    int64_t nxt_tile[UNROLL];
+    auto fetch = [&]() {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const int64_t t = t0 + (hw & 1) + (int64_t)u * n_hw;
-            tile[u] = t;
-            const int64_t row = t / nb;
-            const int col = (int)(t - row * nb) * 128 + sub * 8;
-            inb[u] = (t < total_tiles) && (col < N);
-            if (inb[u]) {
-                Elem<T>::load8(x + row * ld + col, v[u]);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) v[u][i] = 0.0f;
-            }
+            const int col = cb * 128 + sub * 8;
+            const bool live = t < total_tiles;
+            const bool inb = live && col < N;
+            nxt[u] = inb ? load_raw8<T>(x + (int64_t)row * ld + col) : zero_raw8<T>();
+            nxt_off[u] = inb ? (int64_t)row * N + col : -1;
+            nxt_tile[u] = live ? t : -1;
+            t += n_hw;
+            row += step_rows;
+            cb += step_cols;
+            if (cb >= nb) { cb -= nb; row += 1; }
         }
+    };
+    fetch();
+    for (; tw < total_tiles; tw += n_hw * UNROLL) {
+        Raw8<T> cur[UNROLL];
+        int64_t off[UNROLL], tile[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) { cur[u] = nxt[u]; off[u] = nxt_off[u]; tile[u] = nxt_tile[u]; }
+        if (tw + n_hw * UNROLL < total_tiles) fetch();
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
+            float v[8];
+            unpack_raw8<T>(cur[u], v);
             float amax = 0.0f;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[u][i]));
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
 #pragma unroll
             for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
             const float s = scale_from_amax<DIV, ROUND>(amax);
             float y[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) y[i] = scaled_clamped<DIV>(v[u][i], s);
-            if (inb[u]) {
-                const int64_t t = tile[u];
-                const int64_t row = t / nb;
-                const int col = (int)(t - row * nb) * 128 + sub * 8;
+            for (int i = 0; i < 8; ++i) y[i] = scaled_clamped<DIV>(v[i], s);
+            if (off[u] >= 0) {
                 uint2 o2;
                 o2.x = cvt_e4m3x4(y[0], y[1], y[2], y[3]);
                 o2.y = cvt_e4m3x4(y[4], y[5], y[6], y[7]);
-                *reinterpret_cast<uint2*>(q + row * (int64_t)N + col) = o2;
+                __stcs(reinterpret_cast<uint2*>(q + off[u]), o2);
             }
-            if (sub == 0 && tile[u] < total_tiles) scales[tile[u]] = s;
+            if (sub == 0 && tile[u] >= 0) scales[tile[u]] = s;
         }
     }
 }
@@ -157,24 +206,25 @@ __global__ void __launch_bounds__(256)
 quant_row_transposed_kernel(const T* __restrict__ x, int64_t L, uint8_t* __restrict__ q,
                             float* __restrict__ scales, int M, int N, int nb) {
     constexpr int TM = 64;            // logical rows per CTA
-    constexpr int PITCH = 128 + 16;   // bytes per staged output row
     __shared__ float s_amax[8][TM];
-    __shared__ __align__(16) uint8_t s_out[TM * PITCH];
+    // staged output: 64 logical rows x 128 bytes; the 16-byte chunk index of a row is XOR-ed
+    // with (row / 8) so that the 4-byte stores of a warp fall into 32 different banks
+    __shared__ __align__(16) uint32_t s_out[TM * 32];
 
     const int cb = blockIdx.x;                  // tile index along n
     const int m0 = blockIdx.y * TM;
     const int n0 = cb * 128;
     const int g = threadIdx.x & 7;              // which 8-wide m chunk
-    const int nr = threadIdx.x >> 3;            // 0..31: n row within a pass
+    const int nr = threadIdx.x >> 3;            // 0..31: this thread reads n rows 4*nr .. 4*nr+3
     const int warp = threadIdx.x >> 5;
 
     float v[4][8];
     const int m = m0 + g * 8;
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
-        const int n = n0 + p * 32 + nr;
+        const int n = n0 + nr * 4 + p;
         if (n < N && m < M) {
-            Elem<T>::load8(x + (int64_t)n * L + m, v[p]);
+            unpack_raw8<T>(load_raw8<T>(x + (int64_t)n * L + m), v[p]);
         } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[p][i] = 0.0f;
@@ -206,15 +256,13 @@ quant_row_transposed_kernel(const T* __restrict__ x, int64_t L, uint8_t* __restr
         for (int i = 0; i < 8; ++i)
             if (m + i < M) scales[(int64_t)(m + i) * nb + cb] = sc[i];
     }
+    // four consecutive n of one logical row -> one 32-bit word
 #pragma unroll
-    for (int p = 0; p < 4; ++p) {
-        const int nl = p * 32 + nr;
-#pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-            const uint16_t two = cvt_e4m3x2(scaled_clamped<DIV>(v[p][i], sc[i]), scaled_clamped<DIV>(v[p][i + 1], sc[i + 1]));
-            s_out[(g * 8 + i) * PITCH + nl] = (uint8_t)(two & 0xff);
-            s_out[(g * 8 + i + 1) * PITCH + nl] = (uint8_t)(two >> 8);
-        }
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t word = cvt_e4m3x4(scaled_clamped<DIV>(v[0][i], sc[i]), scaled_clamped<DIV>(v[1][i], sc[i]),
+                                         scaled_clamped<DIV>(v[2][i], sc[i]), scaled_clamped<DIV>(v[3][i], sc[i]));
+        const int ml = g * 8 + i;
+        s_out[ml * 32 + ((((nr >> 2) ^ g) & 7) << 2) + (nr & 3)] = word;
     }
     __syncthreads();
     // 64 rows x 8 chunks of 16 bytes
@@ -224,8 +272,8 @@ quant_row_transposed_kernel(const T* __restrict__ x, int64_t L, uint8_t* __restr
         const int ml = idx >> 3, ch = idx & 7;
         const int mm = m0 + ml, n = n0 + ch * 16;
         if (mm < M && n < N) {
-            const uint4 val = *reinterpret_cast<const uint4*>(&s_out[ml * PITCH + ch * 16]);
-            *reinterpret_cast<uint4*>(q + (int64_t)mm * N + n) = val;
+            const uint4 val = *reinterpret_cast<const uint4*>(&s_out[ml * 32 + (((ch ^ (ml >> 3)) & 7) << 2)]);
+            __stcs(reinterpret_cast<uint4*>(q + (int64_t)mm * N + n), val);
         }
     }
 }
@@ -443,11 +491,13 @@ static int launch_rowwise(const T* x, int64_t M, int64_t N, int64_t ld_m, int64_
     if (tiles == 0) return CINN_OK;
     const int sms = sm_count();
     if (block == 128 && ld_n == 1 && N % 8 == 0 && ld_m % 8 == 0 && aligned16(x) && aligned16(q)) {
-        constexpr int UNROLL = 4;
+        constexpr int UNROLL = 2;
         int64_t blocks = (tiles + 16 * UNROLL - 1) / (16 * UNROLL);
         const int64_t cap = (int64_t)sms * 8;
         if (blocks > cap) blocks = cap;
-        quant_row_vec_kernel<T, DIV, ROUND, UNROLL><<<(unsigned)blocks, 256, 0, st>>>(x, ld_m, q, scales, (int)N, nb, tiles);
+        const int64_t n_hw = blocks * 16;
+        quant_row_vec_kernel<T, DIV, ROUND, UNROLL><<<(unsigned)blocks, 256, 0, st>>>(
+            x, ld_m, q, scales, (int)N, nb, tiles, (int)(n_hw / nb), (int)(n_hw % nb));
     } else if (block == 128 && ld_m == 1 && ld_n >= M && M % 8 == 0 && ld_n % 8 == 0 && N % 16 == 0 && aligned16(x) &&
                aligned16(q) && M > 1) {
         dim3 grid((unsigned)nb, (unsigned)((M + 63) / 64));

@@ -171,15 +171,18 @@ def requantize_rowwise_to_blockwise(x_fp8: torch.Tensor, x_scale: torch.Tensor, 
 # -----------------------------------------------------------------------------
 # GEMM (reference: src/kernels.py:667-702)
 # -----------------------------------------------------------------------------
-def _gemm(a, a_scales, b, b_layout, sb, sb_stride_k, sb_stride_n, M, N, K, out_dtype):
+def _gemm(a, a_scales, b, b_layout, sb, sb_stride_k, sb_stride_n, M, N, K, out_dtype, bf16_rounded=False):
+    """``bf16_rounded`` (fp32 output only): store the result rounded to bf16, i.e. exactly what a
+    bf16 result cast to fp32 would hold."""
     with torch.cuda.device(a.device):
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        tag = _lib.F32_BF16 if (bf16_rounded and out_dtype == torch.float32) else _DTYPE_TAG[out_dtype]
         ev = None
         if gemm_events is not None:
             ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
             ev[0].record()
         _lib.check(_L.cinn_fp8_gemm(_ptr(a), _ptr(a_scales), a_scales.stride(0), _ptr(b), _ptr(sb), sb_stride_k,
-                                    sb_stride_n, _ptr(out), M, N, K, b_layout, _DTYPE_TAG[out_dtype], _stream(a)),
+                                    sb_stride_n, _ptr(out), M, N, K, b_layout, tag, _stream(a)),
                    "cinn_fp8_gemm")
         if ev is not None:
             ev[1].record()
@@ -257,6 +260,7 @@ class FP8MatmulFunction(torch.autograd.Function):
         ctx.save_for_backward(x_fp8, x_scale, w_fp8, w_scale)
         ctx.x_shape = x_shape
         ctx.round_scale = round_scale
+        ctx.weight_dtype = weight.dtype
         return out.reshape(*x_shape[:-1], -1)
 
     @staticmethod
@@ -283,8 +287,12 @@ class FP8MatmulFunction(torch.autograd.Function):
             x_scale = torch.nn.functional.pad(x_scale, (0, 0, 0, Mp - M), value=1.0)
         grad_fp8_t, grad_scale_t = quantize_fp8_rowwise(grad_flat.t(), block_size=128, round_scale=round_scale)
         x_fp8_block, x_scale_block = requantize_rowwise_to_blockwise(x_fp8, x_scale)
+        # the reference returns a bf16 grad_weight which autograd then casts to the fp32 master
+        # weight's dtype (:788, :794); the GEMM writes those same values as fp32 directly
+        ctx_w_fp32 = ctx.weight_dtype == torch.float32
         grad_weight = _gemm(grad_fp8_t, grad_scale_t, x_fp8_block, _lib.B_KN, x_scale_block, x_scale_block.stride(0),
-                            x_scale_block.stride(1), N, K, Mp, torch.bfloat16)
+                            x_scale_block.stride(1), N, K, Mp, torch.float32 if ctx_w_fp32 else torch.bfloat16,
+                            bf16_rounded=True)
         return grad_x.reshape(x_shape), grad_weight, None
 
 

@@ -31,6 +31,8 @@ extern "C" {
 #define CINN_BF16 0
 #define CINN_F32 1
 #define CINN_F16 2
+#define CINN_F32_BF16 3 /* GEMM output only: the bf16-rounded result stored as fp32 (what autograd makes of a bf16
+                           gradient for an fp32 parameter, without the separate cast kernel) */
 
 /* fp32 division flavour used for amax/448 and x/scale */
 #define CINN_DIV_FULL 0 /* PTX div.full.f32: what Triton emits for the reference kernels on a GPU */
@@ -78,7 +80,7 @@ int cinn_transpose_bytes(const void* in, int64_t ld_in, void* out, int64_t R, in
  * Replaces fp8_gemm_kernel + fp8_matmul_dsv3 (src/kernels.py:588-664, 667-702).
  * A: (M, K) e4m3, K contiguous.  sA: (M, ceil(K/128)) fp32, row pitch ld_sa.
  * B: e4m3 in the layout named by b_layout.  sB: element (kb, nb) at sB[kb*sb_stride_k + nb*sb_stride_n].
- * C: (M, N) contiguous, out_dtype CINN_BF16 (what the reference returns) or CINN_F32.
+ * C: (M, N) contiguous, out_dtype CINN_BF16 (what the reference returns), CINN_F16, CINN_F32 or CINN_F32_BF16.
  * K must be a multiple of 16; N a multiple of 8 for bf16 output, 4 for fp32 output. */
 int cinn_fp8_gemm(const void* A, const float* sA, int64_t ld_sa, const void* B, const float* sB,
                   int64_t sb_stride_k, int64_t sb_stride_n, void* C, int64_t M, int64_t N, int64_t K,
