@@ -8,7 +8,7 @@ from __future__ import annotations
 import ctypes
 import os
 
-from .build import LIB_PATH
+from .build import LIB_PATH as _DEFAULT_LIB_PATH
 
 OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE = 0, 1, 2, 3, 4
 BF16, F32, F16, F32_BF16 = 0, 1, 2, 3
@@ -37,6 +37,7 @@ class LibraryError(RuntimeError):
 
 
 def _load() -> ctypes.CDLL:
+    LIB_PATH = os.environ.get("CINN_LIB_PATH") or _DEFAULT_LIB_PATH    # override: an alternative build of the library
     if not os.path.exists(LIB_PATH):
         raise LibraryError(
             f"{LIB_PATH} is missing: build it with `python -m cinnamon_b200.build` "

@@ -25,14 +25,34 @@ constexpr int BK = 128;            // bytes (= e4m3 elements) per K block: one s
 constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK;   // 16 KiB
 constexpr int B_BYTES = BN * BK;   // 32 KiB
-constexpr int EPI_WARPS = 8;
-constexpr int THREADS = (EPI_WARPS + 4) * 32;   // warps 8-11: producer, MMA, two idle (a full warpgroup for setmaxnreg)
+#ifndef CINN_EPI_WARPS
+#define CINN_EPI_WARPS 8
+#endif
+constexpr int EPI_WARPS = CINN_EPI_WARPS;       // 8 or 16: four TMEM lane quarters x 2 or 4 column groups
+constexpr int WCOLS = BN / (EPI_WARPS / 4);     // accumulator columns per epilogue warp
+constexpr int THREADS = (EPI_WARPS + 2) * 32;
 constexpr int TMEM_COLS = 512;
 constexpr int MAX_EXPERTS = 2048;
 constexpr int GROUP_M = 16;        // rasterisation: m-tiles per L2 group (dense)
 
 // device status word: 0 = fine, otherwise (role << 8) | reason
 __device__ int g_device_status = 0;
+
+// Optional cycle accounting of the waits of each role (builds with -DCINN_GEMM_PROFILE only):
+// [0] producer waits for a free stage, [1] MMA waits for TMEM, [2] MMA waits for operands,
+// [3] epilogue (warp 0) waits for a partial tile, [4] epilogue busy, [5] CTA lifetime, [6] K blocks
+#ifdef CINN_GEMM_PROFILE
+__device__ unsigned long long g_prof[8];
+#define PROF_T0() const long long _pt0 = clock64()
+#define PROF_ADD(i) _prof[i] += (unsigned long long)(clock64() - _pt0)
+#define PROF_DECL() unsigned long long _prof[5] = {0, 0, 0, 0, 0}
+#define PROF_FLUSH(i) atomicAdd(&g_prof[i], _prof[i])
+#else
+#define PROF_T0()
+#define PROF_ADD(i)
+#define PROF_DECL()
+#define PROF_FLUSH(i)
+#endif
 
 struct GemmParams {
     const float* sA; int64_t sa_stride_m, sa_stride_k;
@@ -91,6 +111,13 @@ __device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint32_t bar
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
 
+// fp32 load through the read-only path, pinned in program order
+__device__ __forceinline__ float ld_scale(const float* p) {
+    float v;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -119,20 +146,6 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
-
-// 32 lanes x 32 consecutive fp32 columns, not yet waited for
-__device__ __forceinline__ void tc_ld32_nowait(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// register budget: the kernel starts with 168 registers per thread (384 threads); the
-// epilogue warpgroups grow to 232 once the producer / MMA warpgroup has shrunk to 40
-__device__ __forceinline__ void reg_grow() { asm volatile("setmaxnreg.inc.sync.aligned.u32 232;"); }
-__device__ __forceinline__ void reg_shrink() { asm volatile("setmaxnreg.dec.sync.aligned.u32 40;"); }
 
 // Shared-memory matrix descriptor, 128-byte swizzle, Blackwell descriptor version 1.
 // lbo / sbo in bytes.
@@ -309,9 +322,12 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
     const int KB = (p.K + BK - 1) / BK;
     const int n_total = total_tiles<GROUPED>(p, cum);
+#ifdef CINN_GEMM_PROFILE
+    const long long _cta_t0 = clock64();
+#endif
 
+    PROF_DECL();
     if (warp >= EPI_WARPS) {
-      reg_shrink();
       if (warp == EPI_WARPS) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
@@ -323,7 +339,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
+                    { PROF_T0();
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, (1 << 8) | 1)) { alive = false; break; }
+                    PROF_ADD(0); }
                     const uint32_t fb = full0 + 8 * s;
                     mbar_expect_tx(fb, A_BYTES + B_BYTES);
                     tma_load_2d(&tmA, fb, smem_u32(smem_a + s * A_BYTES), kb * BK, ti.m0);
@@ -357,8 +375,14 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     const uint32_t b = it & 1, bph = (it >> 1) & 1;
-                    if (!mbar_wait(tempty0 + 8 * b, bph ^ 1, abort_flag, (2 << 8) | 2)) { alive = false; break; }
+                    // operands first (they landed long ago: this costs one barrier probe, taken while
+                    // the epilogue still works on the buffer), then the TMEM buffer
+                    { PROF_T0();
                     if (!mbar_wait(full0 + 8 * s, ph, abort_flag, (2 << 8) | 1)) { alive = false; break; }
+                    PROF_ADD(2); }
+                    { PROF_T0();
+                    if (!mbar_wait(tempty0 + 8 * b, bph ^ 1, abort_flag, (2 << 8) | 2)) { alive = false; break; }
+                    PROF_ADD(1); }
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem_a + s * A_BYTES);
                     const uint32_t b_addr = smem_u32(smem_b + s * B_BYTES);
@@ -374,10 +398,11 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     tc_commit(tfull0 + 8 * b);      // and the partial tile is ready for promotion
                 }
             }
+            // every MMA issued above must have retired before tensor memory is freed
+            if (alive && it > 0) mbar_wait(tfull0 + 8 * ((it - 1) & 1), ((it - 1) >> 1) & 1, abort_flag, (2 << 8) | 3);
         }
       }
     } else {
-        reg_grow();
         // ------------------------------ epilogue ------------------------------
         const int q = warp & 3, h = warp >> 2;
         uint32_t it = 0;
@@ -387,45 +412,49 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const TileInfo ti = tile_info<GROUPED>(p, cum, t);
             const int row = ti.m0 + q * 32 + lane;
             const bool rvalid = row < ti.m_end;
-            const int col0 = ti.n0 + h * 128;
+            const int col0 = ti.n0 + h * WCOLS;
             const bool cvalid = col0 < p.N;
             const float* sa_ptr = p.sA + (int64_t)(rvalid ? row : ti.m0) * p.sa_stride_m;
             const float* sb_ptr = p.sB + (int64_t)ti.expert * p.sb_stride_e + (int64_t)(cvalid ? col0 / 128 : 0) * p.sb_stride_n;
-            float acc[128];
+            float acc[WCOLS];
 #pragma unroll
-            for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
-            float sa_n = __ldg(sa_ptr), sb_n = __ldg(sb_ptr);
+            for (int i = 0; i < WCOLS; ++i) acc[i] = 0.0f;
+            // scales are fetched three K blocks ahead with loads the compiler may not move
+            // (a load sunk to its use would expose a full L2 round trip in every K block)
+            float sa0 = ld_scale(sa_ptr), sb0 = ld_scale(sb_ptr);
+            float sa1 = 0.f, sb1 = 0.f, sa2 = 0.f, sb2 = 0.f;
+            if (KB > 1) { sa1 = ld_scale(sa_ptr + p.sa_stride_k); sb1 = ld_scale(sb_ptr + p.sb_stride_k); }
+            if (KB > 2) { sa2 = ld_scale(sa_ptr + 2 * p.sa_stride_k); sb2 = ld_scale(sb_ptr + 2 * p.sb_stride_k); }
             for (int kb = 0; kb < KB; ++kb, ++it) {
-                const float s = sa_n * sb_n;
-                if (kb + 1 < KB) {
-                    sa_n = __ldg(sa_ptr + (int64_t)(kb + 1) * p.sa_stride_k);
-                    sb_n = __ldg(sb_ptr + (int64_t)(kb + 1) * p.sb_stride_k);
+                const float s = sa0 * sb0;
+                sa0 = sa1; sb0 = sb1; sa1 = sa2; sb1 = sb2;
+                if (kb + 3 < KB) {
+                    sa2 = ld_scale(sa_ptr + (int64_t)(kb + 3) * p.sa_stride_k);
+                    sb2 = ld_scale(sb_ptr + (int64_t)(kb + 3) * p.sb_stride_k);
                 }
                 const uint32_t b = it & 1, bph = (it >> 1) & 1;
+                { PROF_T0();
                 if (!mbar_wait(tfull0 + 8 * b, bph, abort_flag, (3 << 8) | 1)) { alive = false; break; }
+                if (threadIdx.x == 0) { PROF_ADD(3); } }
+                PROF_T0();
                 tc_fence_after();
-                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * BN + h * 128;
-                // two loads of 64 columns: one TMEM round trip per 64 FMAs; the buffer is handed
-                // back to the MMA warp as soon as the second half sits in registers
-                uint32_t r[64];
-                tc_ld32_nowait(taddr, r);
-                tc_ld32_nowait(taddr + 32, r + 32);
-                tc_wait_ld();
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * BN + h * WCOLS;
 #pragma unroll
-                for (int j = 0; j < 64; ++j) acc[j] = fmaf(__uint_as_float(r[j]), s, acc[j]);
-                tc_ld32_nowait(taddr + 64, r);
-                tc_ld32_nowait(taddr + 96, r + 32);
-                tc_wait_ld();
+                for (int c = 0; c < WCOLS / 16; ++c) {
+                    float v[16];
+                    tc_ld16(taddr + c * 16, v);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) acc[c * 16 + j] = fmaf(v[j], s, acc[c * 16 + j]);
+                }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty0 + 8 * b);
-#pragma unroll
-                for (int j = 0; j < 64; ++j) acc[64 + j] = fmaf(__uint_as_float(r[j]), s, acc[64 + j]);
+                if (threadIdx.x == 0) { PROF_ADD(4); }
             }
             if (alive && rvalid && cvalid) {
                 const int64_t base = (int64_t)row * p.ldc + col0;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
+                for (int j = 0; j < WCOLS / 8; ++j) {
                     const int ncols = p.N - (col0 + j * 8);
                     if (ncols > 0) store8<OUT>(p.C, base + j * 8, &acc[j * 8], vec_ok, ncols);
                 }
@@ -433,6 +462,17 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
     }
 
+#ifdef CINN_GEMM_PROFILE
+    if (warp == EPI_WARPS && lane == 0) { PROF_FLUSH(0); }
+    if (warp == EPI_WARPS + 1 && lane == 0) { PROF_FLUSH(1); PROF_FLUSH(2); }
+    if (threadIdx.x == 0) { PROF_FLUSH(3); PROF_FLUSH(4); }
+    if (threadIdx.x == 0) {
+        atomicAdd(&g_prof[5], (unsigned long long)(clock64() - _cta_t0));
+        unsigned long long nk = 0;
+        for (int t = blockIdx.x; t < n_total; t += gridDim.x) nk += KB;
+        atomicAdd(&g_prof[6], nk);
+    }
+#endif
     tc_fence_before();
     __syncthreads();
     if (warp == EPI_WARPS + 1) {
@@ -580,3 +620,14 @@ int read_device_status(int* out, int reset) {
 }
 
 }  // namespace cinn
+
+#ifdef CINN_GEMM_PROFILE
+extern "C" int cinn_debug_profile(unsigned long long* out8, int reset) {
+    if (cudaMemcpyFromSymbol(out8, cinn::g_prof, 8 * sizeof(unsigned long long)) != cudaSuccess) return CINN_ERR_CUDA;
+    if (reset) {
+        unsigned long long z[8] = {};
+        if (cudaMemcpyToSymbol(cinn::g_prof, z, sizeof(z)) != cudaSuccess) return CINN_ERR_CUDA;
+    }
+    return CINN_OK;
+}
+#endif
