@@ -35,6 +35,8 @@ int requant_row_to_block(const void* xq, const float* xs, int64_t M, int64_t K, 
 int dequantize(const void* q, const float* scales, void* out, int out_dtype, int64_t M, int64_t N, int bm, int bn,
                cudaStream_t st);
 int transpose_bytes(const void* in, int64_t ld_in, void* out, int64_t R, int64_t C, cudaStream_t st);
+int swiglu_quant_rowwise(const void* h12, int dtype, int64_t T_rows, int64_t I, void* q, float* scales, int div_mode,
+                         cudaStream_t st);
 int fp8_gemm(const void* A, const float* sA, int64_t ld_sa, const void* B, const float* sB, int64_t sbk, int64_t sbn,
              void* C, int64_t M, int64_t N, int64_t K, int b_layout, int out_dtype, cudaStream_t st);
 int fp8_grouped_gemm(const void* A, const float* sA, const void* W, const float* sW, const int64_t* starts,
@@ -71,6 +73,11 @@ int cinn_requant_row_to_block(const void* xq, const float* xs, int64_t M, int64_
 int cinn_dequant(const void* q, const float* scales, void* out, int out_dtype, int64_t M, int64_t N, int block_m,
                  int block_n, void* stream) {
     return cinn::dequantize(q, scales, out, out_dtype, M, N, block_m, block_n, (cudaStream_t)stream);
+}
+
+int cinn_swiglu_quant_rowwise(const void* h12, int dtype, int64_t T, int64_t I, void* q, float* scales, int div_mode,
+                              void* stream) {
+    return cinn::swiglu_quant_rowwise(h12, dtype, T, I, q, scales, div_mode, (cudaStream_t)stream);
 }
 
 int cinn_transpose_bytes(const void* in, int64_t ld_in, void* out, int64_t R, int64_t C, void* stream) {

@@ -435,6 +435,56 @@ requant_row_to_block_kernel(const uint8_t* __restrict__ xq, const float* __restr
 }
 
 // ---------------------------------------------------------------------------
+// SwiGLU + row-wise quantisation in one pass: h12 is (T, 2*I) with the gate half first
+// (GroupedExperts keeps w12 = [w1; w2], src/layers.py:47-49, 71-73); h = silu(h1) * h2 is
+// formed in fp32, rounded to the activation dtype as the reference does before its second
+// grouped GEMM (src/layers.py:74), and quantised in 1x128 tiles.  The fp32 h never reaches HBM.
+// A half-warp owns one 128-wide tile.
+// ---------------------------------------------------------------------------
+template <typename T, int DIV>
+__global__ void __launch_bounds__(256)
+swiglu_quant_row_kernel(const T* __restrict__ h12, uint8_t* __restrict__ q, float* __restrict__ scales,
+                        int I, int nb, int64_t total_tiles) {
+    const int sub = threadIdx.x & 15;
+    const int64_t hw = (int64_t)blockIdx.x * 16 + (threadIdx.x >> 4);
+    const int64_t n_hw = (int64_t)gridDim.x * 16;
+    for (int64_t tw = hw & ~(int64_t)1; tw < total_tiles; tw += n_hw) {
+        const int64_t t = tw + (hw & 1);
+        const int64_t row = t / nb;
+        const int col = (int)(t - row * nb) * 128 + sub * 8;
+        const bool inb = t < total_tiles && col < I;
+        float a[8], b[8], v[8];
+        if (inb) {
+            unpack_raw8<T>(load_raw8<T>(h12 + row * 2 * (int64_t)I + col), a);
+            unpack_raw8<T>(load_raw8<T>(h12 + row * 2 * (int64_t)I + I + col), b);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float h = (a[i] / (1.0f + expf(-a[i]))) * b[i];
+                if constexpr (std::is_same<T, __nv_bfloat16>::value) v[i] = __bfloat162float(__float2bfloat16_rn(h));
+                else if constexpr (std::is_same<T, __half>::value) v[i] = __half2float(__float2half_rn(h));
+                else v[i] = h;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const float s = scale_from_amax<DIV, false>(amax);
+        if (inb) {
+            uint2 o2;
+            o2.x = cvt_e4m3x4(scaled_clamped<DIV>(v[0], s), scaled_clamped<DIV>(v[1], s), scaled_clamped<DIV>(v[2], s), scaled_clamped<DIV>(v[3], s));
+            o2.y = cvt_e4m3x4(scaled_clamped<DIV>(v[4], s), scaled_clamped<DIV>(v[5], s), scaled_clamped<DIV>(v[6], s), scaled_clamped<DIV>(v[7], s));
+            *reinterpret_cast<uint2*>(q + row * (int64_t)I + col) = o2;
+        }
+        if (sub == 0 && t < total_tiles) scales[t] = s;
+    }
+}
+
+// ---------------------------------------------------------------------------
 // De-quantisers
 // ---------------------------------------------------------------------------
 // out[r, c] = e4m3(q[r, c]) * scales[(r / bm) * ncb + c / bn]; OUT = bf16 or fp32.
@@ -599,6 +649,35 @@ int dequantize(const void* q, const float* scales, void* out, int out_dtype, int
     else { set_error("dequantise: output dtype must be bf16 or fp32"); return CINN_ERR_INVALID; }
     CINN_CHECK_LAUNCH();
     return CINN_OK;
+}
+
+template <typename T>
+static int launch_swiglu(const T* h12, int64_t T_rows, int64_t I, uint8_t* q, float* scales, int div_mode, cudaStream_t st) {
+    const int nb = (int)((I + 127) / 128);
+    const int64_t tiles = T_rows * nb;
+    int64_t blocks = (tiles + 15) / 16;
+    const int64_t cap = (int64_t)sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    if (div_mode == CINN_DIV_FULL) swiglu_quant_row_kernel<T, CINN_DIV_FULL><<<(unsigned)blocks, 256, 0, st>>>(h12, q, scales, (int)I, nb, tiles);
+    else swiglu_quant_row_kernel<T, CINN_DIV_RN><<<(unsigned)blocks, 256, 0, st>>>(h12, q, scales, (int)I, nb, tiles);
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+int swiglu_quant_rowwise(const void* h12, int dtype, int64_t T_rows, int64_t I, void* q, float* scales, int div_mode,
+                         cudaStream_t st) {
+    CINN_CHECK_ARG(T_rows >= 0 && I >= 0, "swiglu_quant: negative shape");
+    if (T_rows == 0 || I == 0) return CINN_OK;
+    CINN_CHECK_ARG(h12 && q && scales, "swiglu_quant: null pointer");
+    CINN_CHECK_ARG(I % 8 == 0 && I < (1LL << 30), "swiglu_quant: the hidden width (%lld) must be a multiple of 8", (long long)I);
+    CINN_CHECK_ARG(aligned16(h12) && (reinterpret_cast<uintptr_t>(q) & 7) == 0, "swiglu_quant: buffers must be 16-byte aligned");
+    CINN_CHECK_ARG(div_mode == CINN_DIV_FULL || div_mode == CINN_DIV_RN, "swiglu_quant: unknown div_mode %d", div_mode);
+    switch (dtype) {
+        case CINN_BF16: return launch_swiglu((const __nv_bfloat16*)h12, T_rows, I, (uint8_t*)q, scales, div_mode, st);
+        case CINN_F16: return launch_swiglu((const __half*)h12, T_rows, I, (uint8_t*)q, scales, div_mode, st);
+        case CINN_F32: return launch_swiglu((const float*)h12, T_rows, I, (uint8_t*)q, scales, div_mode, st);
+        default: set_error("swiglu_quant: unknown dtype tag %d", dtype); return CINN_ERR_INVALID;
+    }
 }
 
 int transpose_bytes(const void* in, int64_t ld_in, void* out, int64_t R, int64_t C, cudaStream_t st) {

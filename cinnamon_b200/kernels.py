@@ -399,6 +399,23 @@ def fp8_grouped_gemm(x_fp8, x_scale, w_fp8, w_scale, expert_starts, expert_ends,
     return out
 
 
+def swiglu_quantize_rowwise(h12: torch.Tensor):
+    """``h = (silu(h1) * h2).to(h12.dtype)`` with ``h1, h2 = h12.float().chunk(2, -1)`` (reference
+    src/layers.py:72-74), quantised row-wise in 1x128 tiles, in one pass.
+    Returns ``(h_fp8 [T, I], scales [T, ceil(I/128)])``."""
+    assert h12.is_cuda and h12.ndim == 2 and h12.shape[1] % 2 == 0
+    h12 = h12.contiguous()
+    T, I2 = h12.shape
+    I = I2 // 2
+    with torch.cuda.device(h12.device):
+        q = torch.empty((T, I), dtype=torch.float8_e4m3fn, device=h12.device)
+        s = torch.empty((T, (I + 127) // 128), dtype=torch.float32, device=h12.device)
+        _lib.check(_L.cinn_swiglu_quant_rowwise(_ptr(h12), _DTYPE_TAG[h12.dtype], T, I, _ptr(q), _ptr(s), _DIV_MODE,
+                                                _stream(h12)), "cinn_swiglu_quant_rowwise")
+    _count()
+    return q, s
+
+
 def moe_grouped_gemm(sorted_x: torch.Tensor, weights: torch.Tensor, expert_starts: torch.Tensor,
                      expert_ends: torch.Tensor, max_expert_tokens: int = None,
                      dtype: torch.dtype = torch.float16) -> torch.Tensor:

@@ -1,0 +1,201 @@
+"""Routed-expert MoE layer with FP8 grouped GEMMs and expert parallelism.
+
+The reference replicates every expert on every rank (src/layers.py:89-179); its routed
+path is: route -> sort pairs by expert -> gather tokens -> grouped SwiGLU (two grouped
+GEMMs, src/layers.py:69-75) -> gate -> scatter-add.  This module keeps that arithmetic
+and adds the partitioning the reference lacks:
+
+  * experts are sharded contiguously, ``E / G`` per rank; every rank routes its own tokens;
+  * dispatch: one all-to-all of e4m3 rows and one of their fp32 1x128 scales (tokens are
+    quantised once, before the exchange, so 1 byte per element crosses NVLink);
+  * each rank runs the two grouped GEMMs over the ragged per-expert ranges it received
+    (offsets stay on the device; nothing is padded);
+  * combine: one all-to-all of bf16 rows back to the owners, then the gate-weighted
+    scatter-add of the reference (src/layers.py:157-160).
+
+The exchange plan (who sends how many rows to whom, and the permutations on both sides)
+is plain torch + ``torch.distributed`` and works on any backend, so it is tested with
+gloo on CPU; the expert computation is a callable (the FP8 one needs a B200).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+
+# ---------------------------------------------------------------------------------------
+# routing (src/layers.py:122-148)
+# ---------------------------------------------------------------------------------------
+@dataclass
+class Routing:
+    token_indices: torch.Tensor    # (T*k,) source token of each sorted pair
+    sorted_scores: torch.Tensor    # (T*k,) normalised gate of each sorted pair
+    sorted_experts: torch.Tensor   # (T*k,) global expert id, ascending
+    counts: torch.Tensor           # (E,) pairs per expert
+
+
+def route(x: torch.Tensor, router_weight: torch.Tensor, expert_bias: torch.Tensor, top_k: int) -> Routing:
+    """Router of ``MoE.forward`` (src/layers.py:122-148): sigmoid scores, top-k on
+    scores + bias, gates normalised over the selected experts, pairs sorted by expert."""
+    n_experts = router_weight.shape[0]
+    scores = torch.sigmoid(torch.nn.functional.linear(x.float(), router_weight.float()))
+    _, top_idx = (scores + expert_bias).topk(top_k, dim=-1)
+    top_scores = scores.gather(-1, top_idx)
+    top_scores = top_scores / (top_scores.sum(dim=-1, keepdim=True) + 1e-9)
+    expanded = top_idx.reshape(-1)
+    sorted_experts, order = expanded.sort(stable=True)
+    return Routing(token_indices=order // top_k, sorted_scores=top_scores.reshape(-1)[order],
+                   sorted_experts=sorted_experts, counts=torch.bincount(expanded, minlength=n_experts))
+
+
+def offsets_from_counts(counts: torch.Tensor):
+    ends = counts.cumsum(0)
+    return ends - counts, ends
+
+
+# ---------------------------------------------------------------------------------------
+# expert computation
+# ---------------------------------------------------------------------------------------
+class FP8Experts:
+    """Stacked SwiGLU experts with cached e4m3 weights: w12 (E, 2*I, d), w3 (E, d, I)
+    (the layout of ``GroupedExperts``, src/layers.py:47-50)."""
+
+    def __init__(self, w12: torch.Tensor, w3: torch.Tensor):
+        from . import kernels as K
+        self.K = K
+        self.n_experts, two_i, self.d_model = w12.shape
+        self.hidden = two_i // 2
+        self.requantize(w12, w3)
+
+    def requantize(self, w12: torch.Tensor, w3: torch.Tensor) -> None:
+        """Quantise the master weights in 128x128 blocks (once per optimiser step, not per call)."""
+        self.w12_q, self.w12_s = self.K.quantize_expert_weights(w12)
+        self.w3_q, self.w3_s = self.K.quantize_expert_weights(w3)
+
+    def __call__(self, x_q: torch.Tensor, x_s: torch.Tensor, starts: torch.Tensor, ends: torch.Tensor,
+                 out_dtype=torch.bfloat16) -> torch.Tensor:
+        """x_q (R, d) e4m3 rows grouped by expert, x_s (R, d/128) -> (R, d) ``out_dtype``.
+        Rows outside [starts[0], ends[-1]) are not written."""
+        K = self.K
+        h12 = K.fp8_grouped_gemm(x_q, x_s, self.w12_q, self.w12_s, starts, ends, out_dtype=torch.bfloat16)
+        h_q, h_s = K.swiglu_quantize_rowwise(h12)
+        return K.fp8_grouped_gemm(h_q, h_s, self.w3_q, self.w3_s, starts, ends, out_dtype=out_dtype)
+
+
+# ---------------------------------------------------------------------------------------
+# exchange plan
+# ---------------------------------------------------------------------------------------
+@dataclass
+class DispatchPlan:
+    send_splits: list              # rows this rank sends to each rank
+    recv_splits: list              # rows this rank receives from each rank
+    recv_counts: torch.Tensor      # (G, E_local) rows received from rank g for local expert e
+    perm: torch.Tensor             # received order (by source rank, then expert) -> grouped by expert
+    starts: torch.Tensor           # (E_local,) int64, device
+    ends: torch.Tensor             # (E_local,) int64, device
+
+
+def make_plan(counts: torch.Tensor, group=None) -> DispatchPlan:
+    """``counts``: (E,) pairs this rank routed to every global expert.  Exchanges the counts
+    (one small all-to-all) and derives split sizes, the regrouping permutation and the
+    per-expert row ranges on the receiving side."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    n_experts = counts.numel()
+    assert n_experts % world == 0, "experts must divide evenly over ranks"
+    e_local = n_experts // world
+    send_counts = counts.reshape(world, e_local).to(torch.int64).contiguous()
+    recv_counts = torch.empty_like(send_counts)
+    if world > 1:
+        dist.all_to_all_single(recv_counts, send_counts, group=group)
+    else:
+        recv_counts.copy_(send_counts)
+    send_splits = send_counts.sum(1).tolist()           # host synchronisation: split sizes are Python ints
+    recv_splits = recv_counts.sum(1).tolist()
+    # received rows arrive ordered by (source rank, local expert); regroup to (local expert, source rank)
+    flat = recv_counts.reshape(-1)
+    expert_of_segment = torch.arange(e_local, device=counts.device).repeat(world)
+    row_expert = torch.repeat_interleave(expert_of_segment, flat)
+    perm = torch.sort(row_expert, stable=True).indices
+    per_expert = recv_counts.sum(0)
+    starts, ends = offsets_from_counts(per_expert)
+    return DispatchPlan(send_splits, recv_splits, recv_counts, perm, starts.contiguous(), ends.contiguous())
+
+
+def all_to_all_rows(rows: torch.Tensor, send_splits, recv_splits, group=None) -> torch.Tensor:
+    """Variable-size all-to-all of the rows of a 2-D tensor (any dtype; e4m3 travels as bytes)."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        return rows
+    view = rows.view(torch.uint8) if rows.dtype == torch.float8_e4m3fn else rows
+    out = torch.empty((sum(recv_splits), view.shape[1]), dtype=view.dtype, device=view.device)
+    dist.all_to_all_single(out, view.contiguous(), output_split_sizes=list(recv_splits),
+                           input_split_sizes=list(send_splits), group=group)
+    return out.view(rows.dtype) if rows.dtype == torch.float8_e4m3fn else out
+
+
+# ---------------------------------------------------------------------------------------
+# the layer
+# ---------------------------------------------------------------------------------------
+def moe_forward(x: torch.Tensor, routing: Routing, experts: Callable, quantize: Optional[Callable],
+                group=None, timings: Optional[dict] = None) -> torch.Tensor:
+    """Routed part of ``MoE.forward`` for this rank's tokens ``x`` (T, d).
+
+    ``experts(rows_q, rows_s, starts, ends)`` computes the expert SwiGLU for rows grouped by
+    local expert; ``quantize(x) -> (q, s)`` is the row-wise quantiser (``None`` = rows travel
+    unquantised and ``experts`` receives ``(rows, None, starts, ends)``: the CPU test path).
+    Returns the gate-weighted sum over each token's experts, fp32 (T, d).
+    """
+    T, d = x.shape
+    plan = make_plan(routing.counts, group)
+    if quantize is not None:
+        x_q, x_s = quantize(x)
+        send_q = x_q.view(torch.uint8).index_select(0, routing.token_indices).view(x_q.dtype)
+        send_s = x_s.index_select(0, routing.token_indices)
+        recv_q = all_to_all_rows(send_q, plan.send_splits, plan.recv_splits, group)
+        recv_s = all_to_all_rows(send_s, plan.send_splits, plan.recv_splits, group)
+        if len(plan.recv_splits) > 1:
+            recv_q = recv_q.view(torch.uint8).index_select(0, plan.perm).view(x_q.dtype)
+            recv_s = recv_s.index_select(0, plan.perm)
+        out_rows = experts(recv_q, recv_s, plan.starts, plan.ends)
+    else:
+        send = x.index_select(0, routing.token_indices)
+        recv = all_to_all_rows(send, plan.send_splits, plan.recv_splits, group)
+        if len(plan.recv_splits) > 1:
+            recv = recv.index_select(0, plan.perm)
+        out_rows = experts(recv, None, plan.starts, plan.ends)
+    # back to arrival order, then home
+    if len(plan.recv_splits) > 1:
+        back = torch.empty_like(out_rows)
+        back.index_copy_(0, plan.perm, out_rows)
+        out_rows = all_to_all_rows(back, plan.recv_splits, plan.send_splits, group)
+    weighted = out_rows.float() * routing.sorted_scores[:, None]
+    y = torch.zeros(T, d, dtype=torch.float32, device=x.device)
+    y.index_add_(0, routing.token_indices, weighted)            # src/layers.py:157-160
+    return y
+
+
+class ExpertParallelMoE(torch.nn.Module):
+    """Inference/forward module: router + FP8 routed experts sharded over ``group``.
+
+    Holds this rank's slice of the expert weights: ``w12`` (E/G, 2*I, d), ``w3`` (E/G, d, I).
+    """
+
+    def __init__(self, router_weight: torch.Tensor, expert_bias: torch.Tensor, w12_local: torch.Tensor,
+                 w3_local: torch.Tensor, top_k: int, group=None):
+        super().__init__()
+        from . import kernels as K
+        self.K = K
+        self.register_buffer("router_weight", router_weight)
+        self.register_buffer("expert_bias", expert_bias)
+        self.top_k = top_k
+        self.group = group
+        self.experts = FP8Experts(w12_local, w3_local)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        flat = x.reshape(-1, x.shape[-1])
+        r = route(flat, self.router_weight, self.expert_bias, self.top_k)
+        y = moe_forward(flat, r, self.experts, self.K.quantize_fp8_rowwise, self.group)
+        return y.reshape(x.shape)

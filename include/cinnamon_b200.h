@@ -72,6 +72,13 @@ int cinn_requant_row_to_block(const void* xq, const float* xs, int64_t M, int64_
 int cinn_dequant(const void* q, const float* scales, void* out, int out_dtype, int64_t M, int64_t N,
                  int block_m, int block_n, void* stream);
 
+/* h = silu(h12[:, :I]) * h12[:, I:] in fp32, rounded to the dtype of h12, then quantised row-wise (1x128) to e4m3.
+ * Replaces the torch ops between the two grouped GEMMs of GroupedExperts.forward (src/layers.py:72-74:
+ * `h12.float().chunk(2)`, `F.silu(h1) * h2`, `.to(dtype)`) fused with the quantisation of the second GEMM's input.
+ * h12: (T, 2*I), contiguous.  q: (T, I) bytes.  scales: (T, ceil(I/128)).  I must be a multiple of 8. */
+int cinn_swiglu_quant_rowwise(const void* h12, int dtype, int64_t T, int64_t I, void* q, float* scales, int div_mode,
+                              void* stream);
+
 /* out (C, R) = in (R, C; row pitch ld_in) transposed, bytes.  Replaces the `.t().contiguous()` copies of
  * e4m3 operands (src/kernels.py:748). */
 int cinn_transpose_bytes(const void* in, int64_t ld_in, void* out, int64_t R, int64_t C, void* stream);
