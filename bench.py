@@ -170,6 +170,92 @@ def reference_arm(args):
 
 
 # ---------------------------------------------------------------------------------------
+# MoE layer (expert parallel where N > 1): reported beside the dense line
+# ---------------------------------------------------------------------------------------
+MOE = dict(E=256, d=7168, I=2048, tokens=32768, top_k=8, shared_hidden=2048)
+
+
+def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label):
+    """256 routed experts (SwiGLU 7168 -> 2x2048 -> 7168) + 1 shared expert, 32768 tokens, top-8 with
+    sigmoid scores + per-expert bias.  Strong scaling: tokens and experts are both split over the ranks.
+    Returns a dict (rank 0) with whole-layer tokens/s, the grouped-GEMM rate and the load imbalance."""
+    import torch.distributed as dist
+    from cinnamon_b200 import moe
+    c = MOE
+    E_local, T_local = c["E"] // world, c["tokens"] // world
+    g = torch.Generator(device=dev).manual_seed(1004)
+    router = torch.randn(c["E"], c["d"], generator=g, device=dev) * 0.02
+    bias = torch.randn(c["E"], generator=g, device=dev) * bias_scale
+    gw = torch.Generator(device=dev).manual_seed(2004 + rank)
+    w12 = (torch.randn(E_local, 2 * c["I"], c["d"], generator=gw, device=dev) * 0.02).to(torch.bfloat16)
+    w3 = (torch.randn(E_local, c["d"], c["I"], generator=gw, device=dev) * 0.02).to(torch.bfloat16)
+    x = torch.randn(T_local, c["d"], generator=gw, device=dev).to(torch.bfloat16)
+    shared = [Kmod.FP8Linear(c["d"], c["shared_hidden"]).to(dev), Kmod.FP8Linear(c["d"], c["shared_hidden"]).to(dev),
+              Kmod.FP8Linear(c["shared_hidden"], c["d"]).to(dev)]
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    experts = moe.FP8Experts(w12, w3)
+    t1.record()
+    torch.cuda.synchronize()
+    wq_ms = t0.elapsed_time(t1)
+    del w12, w3
+
+    def layer():
+        with torch.no_grad():
+            r = moe.route(x, router, bias, c["top_k"])
+            y = moe.moe_forward(x, r, experts, Kmod.quantize_fp8_rowwise)
+            sh = shared[2](torch.nn.functional.silu(shared[0](x)) * shared[1](x))
+            return y + sh.float(), r
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        _, r = layer()
+    sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        layer()
+    e1.record()
+    sync()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+    # grouped GEMMs alone, on the rows this rank received in the last step
+    plan = moe.make_plan(r.counts)
+    rows = int(plan.ends[-1])
+    xq = torch.empty(rows, c["d"], dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+    xs = torch.ones(rows, c["d"] // 128, device=dev)
+    for _ in range(2):
+        experts(xq, xs, plan.starts, plan.ends)
+    sync()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record()
+    for _ in range(steps):
+        experts(xq, xs, plan.starts, plan.ends)
+    g1.record()
+    sync()
+    gms = torch.tensor([g0.elapsed_time(g1) / steps], device=dev, dtype=torch.float64)
+    load = torch.tensor([float(rows)], device=dev, dtype=torch.float64)
+    total = load.clone()
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(gms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(load, op=dist.ReduceOp.MAX)
+        dist.all_reduce(total, op=dist.ReduceOp.SUM)
+    active = int((r.counts > 0).sum())
+    del experts
+    torch.cuda.empty_cache()
+    flop = float(total.item()) * 2.0 * c["d"] * 3 * c["I"]
+    return {"workload": f"moe_layer E=256 d=7168 I=2048 tokens=32768 top8 {label}", "tokens_per_s": c["tokens"] / (ms.item() * 1e-3),
+            "ms_per_layer": ms.item(), "grouped_gemm_ms": gms.item(), "grouped_gemm_tflops": flop / (gms.item() * 1e-3) / 1e12,
+            "expert_weight_quant_ms": wq_ms, "max_rank_rows": int(load.item()), "mean_rank_rows": total.item() / world,
+            "active_experts_rank0_view": active, "scaling": "strong", "n_gpus": world}
+
+
+# ---------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------
 def main():
@@ -179,6 +265,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-moe", action="store_true", help="skip the MoE layer measurements")
     ap.add_argument("--shape", default=None, help="M,K,N of a smaller case (profiling captures); default is the FFN workload")
     args = ap.parse_args()
     if args.shape:
@@ -284,6 +371,14 @@ def main():
     h2d = x_h.numel() * 2 + dy_h.numel() * 2
     d2h = out_h.numel() * 2 + gx_h.numel() * 2 + gw_h.numel() * 4
 
+    moe_lines = []
+    if not args.no_moe and not args.shape:
+        del x, w, dy, out_h, gx_h, gw_h
+        torch.cuda.empty_cache()
+        for scale, label in ((1.0, "bias~N(0,1) as specified"), (0.1, "mild skew: bias~N(0,0.1)")):
+            moe_lines.append(bench_moe(Kmod, dev, rank, world, steps=5, warmup=3, bias_scale=scale, label=label))
+        assert Kmod.device_status() == 0, "a kernel reported a device-side failure in the MoE layer"
+
     if rank == 0:
         peaks, peak_kind = measured_peaks()
         ms_per_step = ms_max / args.steps
@@ -309,6 +404,8 @@ def main():
             "gpu_launches": launches,
             "clocks": clocks,
         }
+        if moe_lines:
+            line["moe"] = moe_lines
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"], _ = run_cpu_baseline(256, repeats=1)
         print(json.dumps(line), flush=True)
