@@ -16,6 +16,7 @@
 #include "common.cuh"
 #include <cuda.h>
 #include <mutex>
+#include <cstdlib>
 
 namespace cinn {
 
@@ -30,7 +31,7 @@ constexpr int B_BYTES = BN * BK;   // 32 KiB
 #endif
 constexpr int EPI_WARPS = CINN_EPI_WARPS;       // 8 or 16: four TMEM lane quarters x 2 or 4 column groups
 constexpr int WCOLS = BN / (EPI_WARPS / 4);     // accumulator columns per epilogue warp
-constexpr int THREADS = (EPI_WARPS + 2) * 32;
+constexpr int THREADS = (EPI_WARPS + 3) * 32;     // + TMA producer + two MMA issuers
 constexpr int TMEM_COLS = 512;
 constexpr int MAX_EXPERTS = 2048;
 constexpr int GROUP_M = 16;        // rasterisation: m-tiles per L2 group (dense)
@@ -38,20 +39,16 @@ constexpr int GROUP_M = 16;        // rasterisation: m-tiles per L2 group (dense
 // device status word: 0 = fine, otherwise (role << 8) | reason
 __device__ int g_device_status = 0;
 
-// Optional cycle accounting of the waits of each role (builds with -DCINN_GEMM_PROFILE only):
-// [0] producer waits for a free stage, [1] MMA waits for TMEM, [2] MMA waits for operands,
-// [3] epilogue (warp 0) waits for a partial tile, [4] epilogue busy, [5] CTA lifetime, [6] K blocks
+// Optional time-line trace (builds with -DCINN_GEMM_PROFILE only): CTA 0 records 32-bit clock stamps of
+// K blocks 128..191 in shared memory (a store costs a few cycles) and dumps them when it finishes.
+// Slots: 0 MMA has operands, 1 MMA has a TMEM buffer, 2 MMAs issued and committed,
+//        8+w epilogue warp w sees the partial tile, 16+w epilogue warp w has released the buffer.
 #ifdef CINN_GEMM_PROFILE
-__device__ unsigned long long g_prof[8];
-#define PROF_T0() const long long _pt0 = clock64()
-#define PROF_ADD(i) _prof[i] += (unsigned long long)(clock64() - _pt0)
-#define PROF_DECL() unsigned long long _prof[5] = {0, 0, 0, 0, 0}
-#define PROF_FLUSH(i) atomicAdd(&g_prof[i], _prof[i])
+__device__ unsigned int g_trace[64 * 24];
+__device__ __forceinline__ unsigned int clock32() { unsigned int c; asm volatile("mov.u32 %0, %%clock;" : "=r"(c)); return c; }
+#define STRACE(slot) do { if (it >= 128u && it < 192u) trace[(it - 128u) * 24 + (slot)] = clock32(); } while (0)
 #else
-#define PROF_T0()
-#define PROF_ADD(i)
-#define PROF_DECL()
-#define PROF_FLUSH(i)
+#define STRACE(slot)
 #endif
 
 struct GemmParams {
@@ -276,6 +273,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* cum = reinterpret_cast<int*>(tmem_slot + 2);          // grouped: E + 1 prefix counts of m-tiles
+#ifdef CINN_GEMM_PROFILE
+    unsigned int* trace = reinterpret_cast<unsigned int*>(cum + (GROUPED ? p.E + 2 : 2));
+#endif
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
@@ -326,7 +326,6 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const long long _cta_t0 = clock64();
 #endif
 
-    PROF_DECL();
     if (warp >= EPI_WARPS) {
       if (warp == EPI_WARPS) {
         // ------------------------------ TMA producer ------------------------------
@@ -339,9 +338,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
-                    { PROF_T0();
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, (1 << 8) | 1)) { alive = false; break; }
-                    PROF_ADD(0); }
                     const uint32_t fb = full0 + 8 * s;
                     mbar_expect_tx(fb, A_BYTES + B_BYTES);
                     tma_load_2d(&tmA, fb, smem_u32(smem_a + s * A_BYTES), kb * BK, ti.m0);
@@ -364,25 +361,29 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
             }
         }
-    } else if (warp == EPI_WARPS + 1) {
-        // ------------------------------ MMA issuer ------------------------------
+    } else {
+        // ------------------------------ MMA issuers ------------------------------
+        // Two warps take alternate K blocks (one TMEM buffer each).  Issuing a block's MMAs blocks the
+        // issuing thread for about as long as they execute, and every barrier probe costs a few
+        // hundred cycles next to a busy tensor pipe; with two issuers one probes while the other feeds.
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(B_MN);
-            uint32_t it = 0;
+            const uint32_t mine = (uint32_t)(warp - (EPI_WARPS + 1));
+            uint32_t it = 0, last = 0xffffffffu;
             bool alive = true;
             for (int t = blockIdx.x; t < n_total && alive; t += gridDim.x) {
                 for (int kb = 0; kb < KB; ++kb, ++it) {
+                    if ((it & 1u) != mine) continue;
+                    last = it;
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     const uint32_t b = it & 1, bph = (it >> 1) & 1;
                     // operands first (they landed long ago: this costs one barrier probe, taken while
                     // the epilogue still works on the buffer), then the TMEM buffer
-                    { PROF_T0();
                     if (!mbar_wait(full0 + 8 * s, ph, abort_flag, (2 << 8) | 1)) { alive = false; break; }
-                    PROF_ADD(2); }
-                    { PROF_T0();
+                    STRACE(0);
                     if (!mbar_wait(tempty0 + 8 * b, bph ^ 1, abort_flag, (2 << 8) | 2)) { alive = false; break; }
-                    PROF_ADD(1); }
+                    STRACE(1);
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem_a + s * A_BYTES);
                     const uint32_t b_addr = smem_u32(smem_b + s * B_BYTES);
@@ -396,10 +397,11 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     }
                     tc_commit(empty0 + 8 * s);      // the stage may be refilled once these MMAs retire
                     tc_commit(tfull0 + 8 * b);      // and the partial tile is ready for promotion
+                    STRACE(2);
                 }
             }
             // every MMA issued above must have retired before tensor memory is freed
-            if (alive && it > 0) mbar_wait(tfull0 + 8 * ((it - 1) & 1), ((it - 1) >> 1) & 1, abort_flag, (2 << 8) | 3);
+            if (alive && last != 0xffffffffu) mbar_wait(tfull0 + 8 * (last & 1), (last >> 1) & 1, abort_flag, (2 << 8) | 3);
         }
       }
     } else {
@@ -433,10 +435,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     sb2 = ld_scale(sb_ptr + (int64_t)(kb + 3) * p.sb_stride_k);
                 }
                 const uint32_t b = it & 1, bph = (it >> 1) & 1;
-                { PROF_T0();
                 if (!mbar_wait(tfull0 + 8 * b, bph, abort_flag, (3 << 8) | 1)) { alive = false; break; }
-                if (threadIdx.x == 0) { PROF_ADD(3); } }
-                PROF_T0();
+                if (lane == 0) STRACE(8 + warp);
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * BN + h * WCOLS;
 #pragma unroll
@@ -446,10 +446,12 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
                     for (int j = 0; j < 16; ++j) acc[c * 16 + j] = fmaf(v[j], s, acc[c * 16 + j]);
                 }
+                // (Measured alternatives, all slower on B200: wider TMEM loads with a larger register budget,
+                // double-buffered loads, packed fp32x2 FMAs, sixteen promotion warps.)
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty0 + 8 * b);
-                if (threadIdx.x == 0) { PROF_ADD(4); }
+                if (lane == 0) STRACE(16 + warp);
             }
             if (alive && rvalid && cvalid) {
                 const int64_t base = (int64_t)row * p.ldc + col0;
@@ -463,15 +465,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
 
 #ifdef CINN_GEMM_PROFILE
-    if (warp == EPI_WARPS && lane == 0) { PROF_FLUSH(0); }
-    if (warp == EPI_WARPS + 1 && lane == 0) { PROF_FLUSH(1); PROF_FLUSH(2); }
-    if (threadIdx.x == 0) { PROF_FLUSH(3); PROF_FLUSH(4); }
-    if (threadIdx.x == 0) {
-        atomicAdd(&g_prof[5], (unsigned long long)(clock64() - _cta_t0));
-        unsigned long long nk = 0;
-        for (int t = blockIdx.x; t < n_total; t += gridDim.x) nk += KB;
-        atomicAdd(&g_prof[6], nk);
-    }
+    __syncthreads();
+    if (blockIdx.x == 0) for (int i = threadIdx.x; i < 64 * 24; i += THREADS) g_trace[i] = trace[i];
 #endif
     tc_fence_before();
     __syncthreads();
@@ -480,6 +475,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
+
+#include "gemm_pair.cuh"
 
 // ---------------------------------------------------------------------------
 // host side
@@ -522,7 +519,11 @@ static int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t
 }
 
 static size_t smem_bytes(int E) {
-    return (size_t)STAGES * (A_BYTES + B_BYTES) + 1024 + (2 * STAGES + 4) * 8 + 16 + 4 * (size_t)(E + 2);
+    size_t n = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024 + (2 * STAGES + 4) * 8 + 16 + 4 * (size_t)(E + 2);
+#ifdef CINN_GEMM_PROFILE
+    n += 64 * 24 * 4;
+#endif
+    return n;
 }
 
 template <bool B_MN, bool GROUPED, int OUT>
@@ -553,6 +554,55 @@ static int launch_out(const CUtensorMap& ta, const CUtensorMap& tb, const GemmPa
     }
 }
 
+template <bool B_MN, int OUT>
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int clusters, cudaStream_t st) {
+    auto kern = pair::fp8_gemm_pair_kernel<B_MN, OUT>;
+    const size_t smem = (size_t)pair::PSTAGES * (pair::PA_BYTES + pair::PB_BYTES) + 1024 + (2 * pair::PSTAGES + 4) * 8 + 16;
+    static thread_local bool configured[64] = {};
+    int dev = 0;
+    CINN_CHECK_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        CINN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * clusters, 1, 1);
+    cfg.blockDim = dim3(pair::PTHREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CINN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, p));
+    return CINN_OK;
+}
+
+template <bool B_MN>
+static int launch_pair_out(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int out_dtype, int clusters,
+                           cudaStream_t st) {
+    switch (out_dtype) {
+        case CINN_BF16: return launch_pair<B_MN, CINN_BF16>(ta, tb, p, clusters, st);
+        case CINN_F32: return launch_pair<B_MN, CINN_F32>(ta, tb, p, clusters, st);
+        case CINN_F16: return launch_pair<B_MN, CINN_F16>(ta, tb, p, clusters, st);
+        case CINN_F32_BF16: return launch_pair<B_MN, CINN_F32_BF16>(ta, tb, p, clusters, st);
+        default: set_error("GEMM: unknown output dtype tag %d", out_dtype); return CINN_ERR_INVALID;
+    }
+}
+
+// 0 = one-SM kernel only, 1 = two-SM pairs for problems with at least one 256 x 256 tile per pair of SMs
+static int pair_mode() {
+    static int mode = -1;
+    if (mode < 0) {
+        const char* e = getenv("CINN_GEMM_PAIR");
+        mode = (e && e[0] == '1') ? 1 : 0;
+    }
+    return mode;
+}
+
 static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 int fp8_gemm(const void* A, const float* sA, int64_t ld_sa, const void* B, const float* sB, int64_t sbk, int64_t sbn,
@@ -566,10 +616,12 @@ int fp8_gemm(const void* A, const float* sA, int64_t ld_sa, const void* B, const
     CINN_CHECK_ARG(al16(A) && al16(B) && al16(C), "fp8_gemm: A, B and C must be 16-byte aligned");
     CINN_CHECK_ARG(b_layout == 0 || b_layout == 1, "fp8_gemm: unknown B layout %d", b_layout);
     CINN_CHECK_ARG(b_layout == 0 || N % 16 == 0, "fp8_gemm: B stored (K, N) needs N %% 16 == 0");
+    const int64_t pair_tiles = ((M + pair::PM - 1) / pair::PM) * ((N + pair::PN - 1) / pair::PN);
+    const bool use_pair = pair_mode() == 1 && pair_tiles >= sm_count() / 2;
     CUtensorMap ta, tb;
     int rc = make_map(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)K, BK, BM);
     if (rc) return rc;
-    if (b_layout == 0) rc = make_map(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, BN);
+    if (b_layout == 0) rc = make_map(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, use_pair ? 128 : BN);
     else rc = make_map(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)N, 128, BK);
     if (rc) return rc;
     GemmParams p{};
@@ -577,6 +629,11 @@ int fp8_gemm(const void* A, const float* sA, int64_t ld_sa, const void* B, const
     p.sB = sB; p.sb_stride_k = sbk; p.sb_stride_n = sbn; p.sb_stride_e = 0;
     p.C = C; p.ldc = N; p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.starts = nullptr; p.ends = nullptr; p.E = 1; p.b_rows_per_expert = 0;
+    if (use_pair) {
+        const int clusters = (int)(pair_tiles < sm_count() / 2 ? pair_tiles : sm_count() / 2);
+        return b_layout == 0 ? launch_pair_out<false>(ta, tb, p, out_dtype, clusters, st)
+                             : launch_pair_out<true>(ta, tb, p, out_dtype, clusters, st);
+    }
     const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     return b_layout == 0 ? launch_out<false, false>(ta, tb, p, out_dtype, grid, st)
@@ -622,12 +679,7 @@ int read_device_status(int* out, int reset) {
 }  // namespace cinn
 
 #ifdef CINN_GEMM_PROFILE
-extern "C" int cinn_debug_profile(unsigned long long* out8, int reset) {
-    if (cudaMemcpyFromSymbol(out8, cinn::g_prof, 8 * sizeof(unsigned long long)) != cudaSuccess) return CINN_ERR_CUDA;
-    if (reset) {
-        unsigned long long z[8] = {};
-        if (cudaMemcpyToSymbol(cinn::g_prof, z, sizeof(z)) != cudaSuccess) return CINN_ERR_CUDA;
-    }
-    return CINN_OK;
+extern "C" int cinn_debug_trace(unsigned int* out1536) {
+    return cudaMemcpyFromSymbol(out1536, cinn::g_trace, 1536 * sizeof(unsigned int)) == cudaSuccess ? CINN_OK : CINN_ERR_CUDA;
 }
 #endif
