@@ -5,12 +5,12 @@
 // [128 r, 128 r + 128) of B in its own shared memory and the 128 x 256 accumulator rows
 // in its own tensor memory.  Each SM therefore stages 32 KiB per K block instead of 48 KiB
 // and the tensor pipe reads a third less shared memory per MMA.  One thread of the even
-// (leader) CTA issues the MMAs for the pair; completion is signalled to both CTAs with a
-// multicast commit.  TMA loads are plain (no multicast): each CTA fetches only its own
-// halves and reports the bytes to the leader's "operands landed" barrier.
+// (leader) CTA issues the MMAs for the pair; completion is signalled to a barrier in each
+// CTA.  TMA loads are plain per-CTA loads: each CTA fetches only its own halves and reports
+// the bytes to the leader's "operands landed" barrier.
 //
-// Roles per CTA (10 warps): 0-7 promotion/epilogue, 8 TMA producer, 9 TMEM allocation
-// (+ MMA issue in the leader).  All waits are bounded exactly as in the one-SM kernel.
+// Roles per CTA (11 warps): 0-7 promotion/epilogue, 8 TMA producer, 9 TMEM allocation;
+// warps 9 and 10 of the leader issue the MMAs of alternate K blocks.  All waits are bounded exactly as in the one-SM kernel.
 #pragma once
 
 namespace pair {
@@ -20,7 +20,7 @@ constexpr int PN = 256;                 // columns of the pair's tile
 constexpr int PSTAGES = 6;
 constexpr int PA_BYTES = 128 * BK;      // A rows of this CTA: 16 KiB
 constexpr int PB_BYTES = 128 * BK;      // B columns of this CTA: 16 KiB
-constexpr int PTHREADS = 10 * 32;
+constexpr int PTHREADS = 11 * 32;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -37,8 +37,11 @@ __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Arrival on a barrier of the other CTA.  Relaxed: the barrier hands over a tensor-memory buffer whose reads
+// are already complete (tcgen05.wait::ld + tcgen05.fence), no generic-memory data is published by it, and a
+// cluster-scope release here costs over a thousand cycles per K block.
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // TMA load into this CTA's shared memory whose byte count is reported to a barrier that may live in
 // the other CTA of the pair
@@ -47,10 +50,12 @@ __device__ __forceinline__ void tma_load_2d_pair(const CUtensorMap* map, uint32_
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(x), "r"(y) : "memory");
 }
+// Completion of the pair's MMAs issued so far is reported to the barrier at the same offset in BOTH CTAs:
+// one commit per CTA, each naming that CTA's barrier by its cluster address.
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
-    asm volatile(
-        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-        ::"r"(bar), "h"((uint16_t)3) : "memory");
+    const uint32_t own = mapa(bar, 0), peer = mapa(bar, 1);
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(own) : "memory");
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(peer) : "memory");
 }
 __device__ __forceinline__ void tc_mma_f8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -145,14 +150,17 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                 while (clock64() - t0 < 2000000LL) { }
             }
         }
-    } else if (warp == 9) {
-        // ------------------------------ MMA issuer (leader only) ------------------------------
+    } else if (warp >= 9) {
+        // ------------------------------ MMA issuers (leader only) ------------------------------
         if (lane == 0 && rank == 0) {
             constexpr uint32_t idesc = make_idesc_pair(B_MN);
-            uint32_t it = 0;
+            const uint32_t mine = (uint32_t)(warp - 9);
+            uint32_t it = 0, last = 0xffffffffu;
             bool alive = true;
             for (int t = cluster_id; t < n_total && alive; t += n_clusters) {
                 for (int kb = 0; kb < KB; ++kb, ++it) {
+                    if ((it & 1u) != mine) continue;
+                    last = it;
                     const int s = it % PSTAGES;
                     const uint32_t ph = (it / PSTAGES) & 1;
                     const uint32_t b = it & 1, bph = (it >> 1) & 1;
@@ -173,7 +181,7 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                     tc_commit_pair(tfull0 + 8 * b);
                 }
             }
-            if (alive && it > 0) mbar_wait(tfull0 + 8 * ((it - 1) & 1), ((it - 1) >> 1) & 1, abort_flag, (2 << 8) | 3);
+            if (alive && last != 0xffffffffu) mbar_wait(tfull0 + 8 * (last & 1), (last >> 1) & 1, abort_flag, (2 << 8) | 3);
         }
     } else {
         // ------------------------------ promotion / epilogue (both CTAs) ------------------------------
