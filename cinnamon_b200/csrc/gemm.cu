@@ -26,16 +26,9 @@ constexpr int BK = 128;            // bytes (= e4m3 elements) per K block: one s
 constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK;   // 16 KiB
 constexpr int B_BYTES = BN * BK;   // 32 KiB
-#ifndef CINN_EPI_WARPS
-#define CINN_EPI_WARPS 8
-#endif
-constexpr int EPI_WARPS = CINN_EPI_WARPS;       // 8 or 16: four TMEM lane quarters x 2 or 4 column groups
+constexpr int EPI_WARPS = 8;                    // four TMEM lane quarters x two column groups
 constexpr int WCOLS = BN / (EPI_WARPS / 4);     // accumulator columns per epilogue warp
-#ifdef CINN_EPI_WIDE
-constexpr int THREADS = (EPI_WARPS + 4) * 32;     // + TMA producer + two MMA issuers + one idle (full warpgroup)
-#else
 constexpr int THREADS = (EPI_WARPS + 3) * 32;     // + TMA producer + two MMA issuers
-#endif
 constexpr int TMEM_COLS = 512;
 constexpr int MAX_EXPERTS = 2048;
 constexpr int GROUP_M = 16;        // rasterisation: m-tiles per L2 group (dense)
@@ -147,20 +140,6 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
-
-#ifdef CINN_EPI_WIDE
-__device__ __forceinline__ void tc_ld32_nowait(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-#endif
 
 // Shared-memory matrix descriptor, 128-byte swizzle, Blackwell descriptor version 1.
 // lbo / sbo in bytes.
@@ -345,9 +324,6 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #endif
 
     if (warp >= EPI_WARPS) {
-#ifdef CINN_EPI_WIDE
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-#endif
       if (warp == EPI_WARPS) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
@@ -426,9 +402,6 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
       }
     } else {
-#ifdef CINN_EPI_WIDE
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
-#endif
         // ------------------------------ epilogue ------------------------------
         const int q = warp & 3, h = warp >> 2;
         uint32_t it = 0;
@@ -463,24 +436,6 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 if (lane == 0) STRACE(8 + warp);
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * BN + h * WCOLS;
-#ifdef CINN_EPI_WIDE
-                {
-                    uint32_t r[64];
-                    tc_ld32_nowait(taddr, r);
-                    tc_ld32_nowait(taddr + 32, r + 32);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int j = 0; j < 64; ++j) acc[j] = fmaf(__uint_as_float(r[j]), s, acc[j]);
-                    tc_ld32_nowait(taddr + 64, r);
-                    tc_ld32_nowait(taddr + 96, r + 32);
-                    tc_wait_ld();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(tempty0 + 8 * b);
-#pragma unroll
-                    for (int j = 0; j < 64; ++j) acc[64 + j] = fmaf(__uint_as_float(r[j]), s, acc[64 + j]);
-                }
-#else
 #pragma unroll
                 for (int c = 0; c < WCOLS / 16; ++c) {
                     float v[16];
@@ -493,7 +448,6 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty0 + 8 * b);
-#endif
                 if (lane == 0) STRACE(16 + warp);
             }
             if (alive && rvalid && cvalid) {

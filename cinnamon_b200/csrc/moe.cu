@@ -1,0 +1,87 @@
+// MoE combine: y[t, :] = sum_j gate[t, j] * rows[pos[t, j], :]   (fp32 result)
+//
+// Replaces the three torch passes at the end of cinnamon's MoE.forward (src/layers.py:157-160:
+// `sorted_out * sorted_scores[:, None]`, `torch.zeros`, `scatter_add_`) by one gather-style pass
+// without atomics: every token reads the rows of its own (token, expert) pairs.  With the
+// positions of a token given in ascending order the fp32 sum has the order of the reference's
+// scatter-add over the sorted pairs.
+#include "common.cuh"
+
+namespace cinn {
+
+template <typename T>
+__device__ __forceinline__ void load8f(const T* p, float (&v)[8]);
+template <>
+__device__ __forceinline__ void load8f<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+}
+template <>
+__device__ __forceinline__ void load8f<__half>(const __half* p, float (&v)[8]) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+template <>
+__device__ __forceinline__ void load8f<float>(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+constexpr int kMaxTopK = 32;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const T* __restrict__ rows, const int64_t* __restrict__ pos, const float* __restrict__ gates,
+                   float* __restrict__ y, int64_t n_rows, int top_k, int d) {
+    __shared__ int64_t s_pos[kMaxTopK];
+    __shared__ float s_gate[kMaxTopK];
+    const int64_t t = blockIdx.x;
+    if (threadIdx.x < top_k) {
+        const int64_t p = pos[t * top_k + threadIdx.x];
+        s_pos[threadIdx.x] = (p >= 0 && p < n_rows) ? p : -1;
+        s_gate[threadIdx.x] = gates[t * top_k + threadIdx.x];
+    }
+    __syncthreads();
+    for (int c = threadIdx.x * 8; c < d; c += 256 * 8) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int j = 0; j < top_k; ++j) {
+            const int64_t p = s_pos[j];
+            if (p < 0) continue;
+            float v[8];
+            load8f<T>(rows + p * d + c, v);
+            const float g = s_gate[j];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(v[i], g));   // product then sum, as the reference
+        }
+        float4* out = reinterpret_cast<float4*>(y + t * d + c);
+        out[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        out[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+}
+
+int moe_combine(const void* rows, int dtype, const int64_t* pos, const float* gates, void* y, int64_t n_tokens,
+                int64_t n_rows, int top_k, int64_t d, cudaStream_t st) {
+    CINN_CHECK_ARG(n_tokens >= 0 && n_rows >= 0 && d >= 0, "moe_combine: negative shape");
+    if (n_tokens == 0 || d == 0) return CINN_OK;
+    CINN_CHECK_ARG(pos && gates && y && (rows || n_rows == 0), "moe_combine: null pointer");
+    CINN_CHECK_ARG(top_k >= 1 && top_k <= kMaxTopK, "moe_combine: top_k must be in [1, %d]", kMaxTopK);
+    CINN_CHECK_ARG(d % 8 == 0 && d < (1LL << 31), "moe_combine: the row width (%lld) must be a multiple of 8", (long long)d);
+    CINN_CHECK_ARG((reinterpret_cast<uintptr_t>(rows) & 15) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0,
+                   "moe_combine: rows and y must be 16-byte aligned");
+    CINN_CHECK_ARG(n_tokens < (1LL << 31), "moe_combine: too many tokens");
+    const unsigned grid = (unsigned)n_tokens;
+    switch (dtype) {
+        case CINN_BF16: moe_combine_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)rows, pos, gates, (float*)y, n_rows, top_k, (int)d); break;
+        case CINN_F16: moe_combine_kernel<__half><<<grid, 256, 0, st>>>((const __half*)rows, pos, gates, (float*)y, n_rows, top_k, (int)d); break;
+        case CINN_F32: moe_combine_kernel<float><<<grid, 256, 0, st>>>((const float*)rows, pos, gates, (float*)y, n_rows, top_k, (int)d); break;
+        default: set_error("moe_combine: unknown dtype tag %d", dtype); return CINN_ERR_INVALID;
+    }
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+}  // namespace cinn

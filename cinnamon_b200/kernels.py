@@ -416,6 +416,24 @@ def swiglu_quantize_rowwise(h12: torch.Tensor):
     return q, s
 
 
+def moe_combine(rows: torch.Tensor, pos: torch.Tensor, gates: torch.Tensor) -> torch.Tensor:
+    """``y[t] = sum_j gates[t, j] * rows[pos[t, j]]`` in fp32: the gate multiply + scatter-add of
+    ``MoE.forward`` (reference src/layers.py:157-160) as one gather pass without atomics.
+    rows (R, d) bf16/fp16/fp32, pos (T, k) int64 (negative = skip), gates (T, k) fp32."""
+    assert rows.is_cuda and pos.is_cuda and gates.is_cuda, "Inputs must be on CUDA"
+    T, k = pos.shape
+    rows = rows.contiguous()
+    pos = pos.to(torch.int64).contiguous()
+    gates = gates.float().contiguous()
+    d = rows.shape[1]
+    with torch.cuda.device(rows.device):
+        y = torch.empty((T, d), dtype=torch.float32, device=rows.device)
+        _lib.check(_L.cinn_moe_combine(_ptr(rows), _DTYPE_TAG[rows.dtype], _ptr(pos), _ptr(gates), _ptr(y), T,
+                                       rows.shape[0], k, d, _stream(rows)), "cinn_moe_combine")
+    _count()
+    return y
+
+
 def moe_grouped_gemm(sorted_x: torch.Tensor, weights: torch.Tensor, expert_starts: torch.Tensor,
                      expert_ends: torch.Tensor, max_expert_tokens: int = None,
                      dtype: torch.dtype = torch.float16) -> torch.Tensor:

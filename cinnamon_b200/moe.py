@@ -35,20 +35,32 @@ class Routing:
     sorted_scores: torch.Tensor    # (T*k,) normalised gate of each sorted pair
     sorted_experts: torch.Tensor   # (T*k,) global expert id, ascending
     counts: torch.Tensor           # (E,) pairs per expert
+    pair_pos: torch.Tensor = None  # (T, k) sorted position of each of a token's pairs, ascending
+    pair_gate: torch.Tensor = None  # (T, k) the gates in the same order
 
 
 def route(x: torch.Tensor, router_weight: torch.Tensor, expert_bias: torch.Tensor, top_k: int) -> Routing:
     """Router of ``MoE.forward`` (src/layers.py:122-148): sigmoid scores, top-k on
     scores + bias, gates normalised over the selected experts, pairs sorted by expert."""
     n_experts = router_weight.shape[0]
-    scores = torch.sigmoid(torch.nn.functional.linear(x.float(), router_weight.float()))
+    if x.dtype in (torch.bfloat16, torch.float16):
+        # the reference's router is an nn.Linear under autocast: a 16-bit GEMM, scores in fp32 afterwards
+        logits = torch.nn.functional.linear(x, router_weight.to(x.dtype)).float()
+    else:
+        logits = torch.nn.functional.linear(x.float(), router_weight.float())
+    scores = torch.sigmoid(logits)
     _, top_idx = (scores + expert_bias).topk(top_k, dim=-1)
     top_scores = scores.gather(-1, top_idx)
     top_scores = top_scores / (top_scores.sum(dim=-1, keepdim=True) + 1e-9)
     expanded = top_idx.reshape(-1)
     sorted_experts, order = expanded.sort(stable=True)
+    # where each (token, slot) pair sits in the sorted order, per token in ascending position
+    pos = torch.empty_like(order)
+    pos[order] = torch.arange(order.numel(), device=order.device)
+    pair_pos, perm = pos.view(-1, top_k).sort(dim=1)
     return Routing(token_indices=order // top_k, sorted_scores=top_scores.reshape(-1)[order],
-                   sorted_experts=sorted_experts, counts=torch.bincount(expanded, minlength=n_experts))
+                   sorted_experts=sorted_experts, counts=torch.bincount(expanded, minlength=n_experts),
+                   pair_pos=pair_pos, pair_gate=top_scores.gather(1, perm))
 
 
 def offsets_from_counts(counts: torch.Tensor):
@@ -171,9 +183,12 @@ def moe_forward(x: torch.Tensor, routing: Routing, experts: Callable, quantize: 
         back = torch.empty_like(out_rows)
         back.index_copy_(0, plan.perm, out_rows)
         out_rows = all_to_all_rows(back, plan.recv_splits, plan.send_splits, group)
-    weighted = out_rows.float() * routing.sorted_scores[:, None]
+    if out_rows.is_cuda:
+        from . import kernels as K
+        return K.moe_combine(out_rows, routing.pair_pos, routing.pair_gate)      # src/layers.py:157-160, fused
+    weighted = out_rows.float() * routing.sorted_scores[:, None]                 # host-logic tests (CPU ranks)
     y = torch.zeros(T, d, dtype=torch.float32, device=x.device)
-    y.index_add_(0, routing.token_indices, weighted)            # src/layers.py:157-160
+    y.index_add_(0, routing.token_indices, weighted)
     return y
 
 

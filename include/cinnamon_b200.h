@@ -104,6 +104,14 @@ int cinn_fp8_grouped_gemm(const void* A, const float* sA, const void* W, const f
                           const int64_t* starts, const int64_t* ends, int64_t E, int64_t T, int64_t d_in,
                           int64_t d_out, void* C, int out_dtype, void* stream);
 
+/* y[t, :] = sum_j gates[t, j] * rows[pos[t, j], :]  for t < n_tokens, j < top_k; fp32 result, no atomics.
+ * Replaces the gate multiply, torch.zeros and scatter_add_ at the end of MoE.forward (src/layers.py:157-160).
+ * rows: (n_rows, d) bf16 / fp16 / fp32.  pos: (n_tokens, top_k) int64 row indices (negative = skip), ascending per
+ * token to reproduce the summation order of the reference.  gates: (n_tokens, top_k) fp32.  y: (n_tokens, d) fp32.
+ * d must be a multiple of 8, top_k at most 32. */
+int cinn_moe_combine(const void* rows, int dtype, const int64_t* pos, const float* gates, void* y, int64_t n_tokens,
+                     int64_t n_rows, int top_k, int64_t d, void* stream);
+
 /* Reads (and with reset != 0 clears) the device-side status word of the current device into the HOST int
  * *out.  0 means no kernel of this library has given up on a bounded wait since the last reset; any other
  * value is (role << 8) | reason.  This call synchronises with the device.  No counterpart in the reference,

@@ -69,6 +69,52 @@ def test_gemm_layout_kn(K, M, N, Kd):
     assert err <= TOL and err <= 2e-5
 
 
+PAIR_SCRIPT = r"""
+import sys, torch
+sys.path.insert(0, sys.argv[1])
+from cinnamon_b200 import kernels as K
+from oracle import fp8_oracle as O
+M, N, Kd = 2304, 2560, 640          # 9 x 10 tiles of 256 x 256: enough for the two-SM kernel, ragged against nothing
+xq, xs = O.quantize_rowwise(O.make_linear_case(M, Kd, N, 77)[0], 128)
+w = O.make_linear_case(M, Kd, N, 77)[1]
+wq, ws = O.quantize_blockwise(w.float(), 128, 128)
+f8 = lambda t: t.cuda().view(torch.float8_e4m3fn)
+nk = K.fp8_matmul_dsv3(f8(xq), f8(wq).t(), xs.cuda(), ws.cuda().t(), out_dtype=torch.float32)
+b = wq.t().contiguous(); bs = ws.t().contiguous()
+kn = K.fp8_matmul_dsv3(f8(xq), f8(b), xs.cuda(), bs.cuda(), out_dtype=torch.float32)
+torch.cuda.synchronize()
+assert K.device_status() == 0
+torch.save({"nk": nk.cpu(), "kn": kn.cpu()}, sys.argv[2])
+"""
+
+
+def test_two_sm_and_one_sm_kernels_agree(K, tmp_path):
+    """CINN_GEMM_PAIR=0 forces the one-SM kernel, =2 the two-SM (cta_group::2) kernel for both B layouts."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "pair.py"
+    script.write_text(PAIR_SCRIPT)
+    outs = {}
+    for mode in ("0", "2"):
+        out = tmp_path / f"out{mode}.pt"
+        subprocess.check_call([sys.executable, str(script), root, str(out)], env=dict(os.environ, CINN_GEMM_PAIR=mode),
+                              timeout=300)
+        outs[mode] = torch.load(out)
+    M, N, Kd = 2304, 2560, 640
+    x, w, _ = O.make_linear_case(M, Kd, N, 77)
+    xq, xs = O.quantize_rowwise(x, 128)
+    wq, ws = O.quantize_blockwise(w.float(), 128, 128)
+    ref = O.fp8_matmul_f64(xq, wq.t(), xs, ws.t())
+    for mode in ("0", "2"):
+        for layout in ("nk", "kn"):
+            err = rel_fro(outs[mode][layout], ref)
+            assert err <= TOL and err <= 2e-5, (mode, layout, err)
+    assert rel_fro(outs["2"]["nk"], outs["0"]["nk"].double()) < 1e-6
+    assert rel_fro(outs["2"]["kn"], outs["0"]["kn"].double()) < 1e-6
+
+
 def test_gemm_is_deterministic(K):
     xq, xs, wq, ws = _operands(512, 1024, 1024, seed=5)
     a = K.fp8_matmul_dsv3(_f8(xq), _f8(wq).t(), xs.cuda(), ws.cuda().t(), out_dtype=torch.float32)

@@ -50,6 +50,22 @@ def test_swiglu_quantiser(K, dtype, T, I):
     assert torch.all((deq - h_cpu.float()).abs() <= tol)
 
 
+def test_combine_kernel_matches_scatter_add(K):
+    g = torch.Generator().manual_seed(8)
+    T, k, d = 77, 4, 264
+    rows = torch.randn(T * k + 5, d, generator=g).bfloat16()
+    pos = torch.stack([torch.randperm(T * k, generator=g)[:k].sort().values for _ in range(T)])
+    pos[3, 1] = -1                                                     # a skipped pair
+    gates = torch.rand(T, k, generator=g)
+    y = K.moe_combine(rows.cuda(), pos.cuda(), gates.cuda())
+    ref = torch.zeros(T, d)
+    for t in range(T):
+        for j in range(k):
+            if pos[t, j] >= 0:
+                ref[t] += rows[pos[t, j]].float() * gates[t, j]
+    assert torch.equal(y.cpu(), ref)                                   # same products, same order of sums
+
+
 def _moe_case(E, d, I, T, top_k, seed):
     g = torch.Generator().manual_seed(seed)
     x = torch.randn(T, d, generator=g).bfloat16()
