@@ -204,76 +204,84 @@ quant_row_generic_kernel(const T* __restrict__ x, int64_t ld_m, int64_t ld_n, ui
 template <typename T, int DIV, bool ROUND>
 __global__ void __launch_bounds__(256)
 quant_row_transposed_kernel(const T* __restrict__ x, int64_t L, uint8_t* __restrict__ q,
-                            float* __restrict__ scales, int M, int N, int nb) {
+                            float* __restrict__ scales, int M, int N, int nb, int tiles_per_cta) {
     constexpr int TM = 64;            // logical rows per CTA
-    __shared__ float s_amax[8][TM];
+    __shared__ float s_amax[2][8][TM];
     // staged output: 64 logical rows x 128 bytes; the 16-byte chunk index of a row is XOR-ed
     // with (row / 8) so that the 4-byte stores of a warp fall into 32 different banks
-    __shared__ __align__(16) uint32_t s_out[TM * 32];
+    __shared__ __align__(16) uint32_t s_out[2][TM * 32];
 
-    const int cb = blockIdx.x;                  // tile index along n
-    const int m0 = blockIdx.y * TM;
-    const int n0 = cb * 128;
+    // blockIdx.x runs along m: CTAs that are scheduled together read neighbouring 128-byte pieces of the
+    // same memory rows, which keeps DRAM pages open
+    const int m0 = blockIdx.x * TM;
     const int g = threadIdx.x & 7;              // which 8-wide m chunk
     const int nr = threadIdx.x >> 3;            // 0..31: this thread reads n rows 4*nr .. 4*nr+3
     const int warp = threadIdx.x >> 5;
-
-    float v[4][8];
     const int m = m0 + g * 8;
+    const int cb_first = blockIdx.y * tiles_per_cta;
+    const int cb_last = min(cb_first + tiles_per_cta, nb);
+
+    // raw vectors of the next tile are fetched before the current one is converted
+    Raw8<T> nxt[4];
+    auto fetch = [&](int cb) {
 #pragma unroll
-    for (int p = 0; p < 4; ++p) {
-        const int n = n0 + nr * 4 + p;
-        if (n < N && m < M) {
-            unpack_raw8<T>(load_raw8<T>(x + (int64_t)n * L + m), v[p]);
-        } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[p][i] = 0.0f;
+        for (int p = 0; p < 4; ++p) {
+            const int n = cb * 128 + nr * 4 + p;
+            nxt[p] = (cb < cb_last && n < N && m < M) ? load_raw8<T>(x + (int64_t)n * L + m) : zero_raw8<T>();
         }
-    }
-    float am[8];
+    };
+    fetch(cb_first);
+    for (int cb = cb_first, buf = 0; cb < cb_last; ++cb, buf ^= 1) {
+        const int n0 = cb * 128;
+        float v[4][8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        float a = fmaxf(fmaxf(fabsf(v[0][i]), fabsf(v[1][i])), fmaxf(fabsf(v[2][i]), fabsf(v[3][i])));
-        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 8));
-        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 16));
-        am[i] = a;
-    }
-    if ((threadIdx.x & 31) < 8) {
+        for (int p = 0; p < 4; ++p) unpack_raw8<T>(nxt[p], v[p]);
+        fetch(cb + 1);
+        float am[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) s_amax[warp][g * 8 + i] = am[i];
-    }
-    __syncthreads();
-    float sc[8];
+        for (int i = 0; i < 8; ++i) {
+            float a = fmaxf(fmaxf(fabsf(v[0][i]), fabsf(v[1][i])), fmaxf(fabsf(v[2][i]), fabsf(v[3][i])));
+            a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 8));
+            a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 16));
+            am[i] = a;
+        }
+        if ((threadIdx.x & 31) < 8) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        float a = 0.0f;
+            for (int i = 0; i < 8; ++i) s_amax[buf][warp][g * 8 + i] = am[i];
+        }
+        __syncthreads();                        // (also: everyone is done reading s_out[buf] of two tiles ago)
+        float sc[8];
 #pragma unroll
-        for (int w = 0; w < 8; ++w) a = fmaxf(a, s_amax[w][g * 8 + i]);
-        sc[i] = scale_from_amax<DIV, ROUND>(a);
-    }
-    if (nr == 0) {
+        for (int i = 0; i < 8; ++i) {
+            float a = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-            if (m + i < M) scales[(int64_t)(m + i) * nb + cb] = sc[i];
-    }
-    // four consecutive n of one logical row -> one 32-bit word
+            for (int w = 0; w < 8; ++w) a = fmaxf(a, s_amax[buf][w][g * 8 + i]);
+            sc[i] = scale_from_amax<DIV, ROUND>(a);
+        }
+        if (nr == 0) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const uint32_t word = cvt_e4m3x4(scaled_clamped<DIV>(v[0][i], sc[i]), scaled_clamped<DIV>(v[1][i], sc[i]),
-                                         scaled_clamped<DIV>(v[2][i], sc[i]), scaled_clamped<DIV>(v[3][i], sc[i]));
-        const int ml = g * 8 + i;
-        s_out[ml * 32 + ((((nr >> 2) ^ g) & 7) << 2) + (nr & 3)] = word;
-    }
-    __syncthreads();
-    // 64 rows x 8 chunks of 16 bytes
+            for (int i = 0; i < 8; ++i)
+                if (m + i < M) scales[(int64_t)(m + i) * nb + cb] = sc[i];
+        }
+        // four consecutive n of one logical row -> one 32-bit word
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const int idx = threadIdx.x + r * 256;
-        const int ml = idx >> 3, ch = idx & 7;
-        const int mm = m0 + ml, n = n0 + ch * 16;
-        if (mm < M && n < N) {
-            const uint4 val = *reinterpret_cast<const uint4*>(&s_out[ml * 32 + (((ch ^ (ml >> 3)) & 7) << 2)]);
-            __stcs(reinterpret_cast<uint4*>(q + (int64_t)mm * N + n), val);
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t word = cvt_e4m3x4(scaled_clamped<DIV>(v[0][i], sc[i]), scaled_clamped<DIV>(v[1][i], sc[i]),
+                                             scaled_clamped<DIV>(v[2][i], sc[i]), scaled_clamped<DIV>(v[3][i], sc[i]));
+            const int ml = g * 8 + i;
+            s_out[buf][ml * 32 + ((((nr >> 2) ^ g) & 7) << 2) + (nr & 3)] = word;
+        }
+        __syncthreads();
+        // 64 rows x 8 chunks of 16 bytes
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int idx = threadIdx.x + r * 256;
+            const int ml = idx >> 3, ch = idx & 7;
+            const int mm = m0 + ml, n = n0 + ch * 16;
+            if (mm < M && n < N) {
+                const uint4 val = *reinterpret_cast<const uint4*>(&s_out[buf][ml * 32 + (((ch ^ (ml >> 3)) & 7) << 2)]);
+                __stcs(reinterpret_cast<uint4*>(q + (int64_t)mm * N + n), val);
+            }
         }
     }
 }
@@ -550,8 +558,13 @@ static int launch_rowwise(const T* x, int64_t M, int64_t N, int64_t ld_m, int64_
             x, ld_m, q, scales, (int)N, nb, tiles, (int)(n_hw / nb), (int)(n_hw % nb));
     } else if (block == 128 && ld_m == 1 && ld_n >= M && M % 8 == 0 && ld_n % 8 == 0 && N % 16 == 0 && aligned16(x) &&
                aligned16(q) && M > 1) {
-        dim3 grid((unsigned)nb, (unsigned)((M + 63) / 64));
-        quant_row_transposed_kernel<T, DIV, ROUND><<<grid, 256, 0, st>>>(x, ld_n, q, scales, (int)M, (int)N, nb);
+        // enough CTAs to fill the GPU several times over, each walking a few tiles with prefetch
+        const int64_t slabs = (M + 63) / 64;
+        int per = 4;
+        while (per > 1 && slabs * ((nb + per - 1) / per) < (int64_t)sms * 8) per >>= 1;
+        CINN_CHECK_ARG((nb + per - 1) / per <= 65535, "row-wise quantiser: too many tiles along the strided axis");
+        dim3 grid((unsigned)slabs, (unsigned)((nb + per - 1) / per));
+        quant_row_transposed_kernel<T, DIV, ROUND><<<grid, 256, 0, st>>>(x, ld_n, q, scales, (int)M, (int)N, nb, per);
     } else {
         int64_t blocks = (tiles + 7) / 8;
         const int64_t cap = (int64_t)sms * 16;
