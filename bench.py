@@ -171,6 +171,74 @@ def reference_arm(args):
 
 
 # ---------------------------------------------------------------------------------------
+# per-kernel figures: every kernel of the step alone, plus the other benchmark configurations
+# ---------------------------------------------------------------------------------------
+def _time_kernel(fn, iters=10, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def bench_kernels(Kmod, dev, x, w, dy, peaks):
+    """Each kernel of the step on the FFN shapes (inputs larger than L2, so every launch streams from HBM),
+    against the roof that bounds it: measured copy bandwidth for the quantisers, 2 x measured bf16 burst for
+    the GEMMs (kernels timed alone).  Then the GEMM shapes of the other configurations (single Linear
+    4096x512 -> 2048; MLA projections at 16384 tokens)."""
+    hbm = float(peaks["hbm_gbs"])
+    fp8_peak = 2.0 * float(peaks["bf16_tflops"])
+    out = []
+
+    def quant_line(name, fn, nbytes):
+        ms = _time_kernel(fn)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out.append({"kernel": name, "ms": ms, "bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm})
+
+    def gemm_line(name, fn, flop):
+        ms = _time_kernel(fn)
+        tf = flop / (ms * 1e-3) / 1e12
+        out.append({"kernel": name, "ms": ms, "bound": "tensor", "achieved": tf, "peak": fp8_peak, "unit": "TFLOP/s",
+                    "frac": tf / fp8_peak})
+
+    xd, wd = x.detach(), w.detach()
+    nkb, nnb = (K + 127) // 128, (N + 127) // 128
+    quant_line("quant_row_vec x[16384,7168] bf16", lambda: Kmod.quantize_fp8_rowwise(xd), M * K * 3 + 4 * M * nkb)
+    quant_line("quant_row_vec dy[16384,18432] bf16", lambda: Kmod.quantize_fp8_rowwise(dy), M * N * 3 + 4 * M * nnb)
+    quant_line("quant_row_transposed dy^T (tiles along tokens)", lambda: Kmod.quantize_fp8_rowwise(dy.t()),
+               M * N * 3 + 4 * N * (M // 128))
+    quant_line("quant_block_vec W[18432,7168] fp32", lambda: Kmod.quantize_fp8_blockwise(wd), N * K * 5 + 4 * nnb * nkb)
+    xq, xs = Kmod.quantize_fp8_rowwise(xd)
+    quant_line("requant_row_to_block x e4m3", lambda: Kmod.requantize_rowwise_to_blockwise(xq, xs),
+               M * K * 2 + 4 * M * nkb + 4 * (M // 128) * nkb)
+    wq, ws = Kmod.quantize_fp8_blockwise(wd)
+    dq, ds = Kmod.quantize_fp8_rowwise(dy)
+    dtq, dts = Kmod.quantize_fp8_rowwise(dy.t())
+    xbq, xbs = Kmod.requantize_rowwise_to_blockwise(xq, xs)
+    flop = 2.0 * M * N * K
+    gemm_line("gemm forward  16384x18432x7168 (B K-major, two-SM)", lambda: Kmod.fp8_matmul_dsv3(xq, wq.t(), xs, ws.t()), flop)
+    gemm_line("gemm dgrad    16384x7168x18432 (B MN-major)", lambda: Kmod.fp8_matmul_dsv3(dq, wq, ds, ws), flop)
+    gemm_line("gemm wgrad    18432x7168x16384 (B MN-major)", lambda: Kmod.fp8_matmul_dsv3(dtq, xbq, dts, xbs), flop)
+    del dq, ds, dtq, dts, xbq, xbs, wq, ws
+    # other configurations: (tokens, in, out)
+    g = torch.Generator(device=dev).manual_seed(1003)
+    for name, (m, k, n) in {"config 1 Linear 4096x512->2048": (4096, 512, 2048),
+                            "MLA W_dq 7168->1536": (16384, 7168, 1536), "MLA W_dkv 7168->576": (16384, 7168, 576),
+                            "MLA W_uq 1536->24576": (16384, 1536, 24576), "MLA W_uk/W_uv 512->16384": (16384, 512, 16384)}.items():
+        a = torch.randn(m, k, generator=g, device=dev).to(torch.bfloat16)
+        b = (torch.randn(n, k, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        aq, as_ = Kmod.quantize_fp8_rowwise(a)
+        bq, bs = Kmod.quantize_fp8_blockwise(b)
+        gemm_line(f"gemm {name} ({m} tokens)", lambda: Kmod.fp8_matmul_dsv3(aq, bq.t(), as_, bs.t()), 2.0 * m * n * k)
+    return out
+
+
+# ---------------------------------------------------------------------------------------
 # MoE layer (expert parallel where N > 1): reported beside the dense line
 # ---------------------------------------------------------------------------------------
 MOE = dict(E=256, d=7168, I=2048, tokens=32768, top_k=8, shared_hidden=2048)
@@ -423,6 +491,9 @@ def main():
     h2d = x_h.numel() * 2 + dy_h.numel() * 2
     d2h = out_h.numel() * 2 + gx_h.numel() * 2 + gw_h.numel() * 4
 
+    kernel_lines = []
+    if rank == 0 and world == 1 and not args.shape and not args.no_moe:
+        kernel_lines = bench_kernels(Kmod, dev, x, w, dy, measured_peaks()[0])
     moe_lines = []
     if not args.no_moe and not args.shape:
         del x, w, dy, out_h, gx_h, gw_h
@@ -459,6 +530,8 @@ def main():
             "gpu_launches": launches,
             "clocks": clocks,
         }
+        if kernel_lines:
+            line["kernels"] = kernel_lines
         if moe_lines:
             line["moe"] = moe_lines
         if world == 1 and not args.no_cpu_baseline:

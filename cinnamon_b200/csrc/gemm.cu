@@ -255,6 +255,53 @@ __device__ __forceinline__ void store8(void* C, int64_t off, const float* a, boo
     }
 }
 
+// Tile store through shared memory.  Each promotion thread owns one output row; storing it directly would
+// make every warp-wide store touch 32 different rows (32 cache lines per instruction).  Instead the warp
+// stages 64 bytes of each of its 32 rows (XOR-swizzled 16-byte slots, conflict-free both ways) and writes
+// them back out as 8 rows x 64 contiguous bytes per instruction.  `stage` is this warp's 2 KiB.
+template <int OUT>
+__device__ __forceinline__ uint4 pack16(const float* a) {
+    uint4 v;
+    if constexpr (OUT == CINN_F32) {
+        v = make_uint4(__float_as_uint(a[0]), __float_as_uint(a[1]), __float_as_uint(a[2]), __float_as_uint(a[3]));
+    } else if constexpr (OUT == CINN_F32_BF16) {
+        v = make_uint4(__float_as_uint(__bfloat162float(__float2bfloat16_rn(a[0]))), __float_as_uint(__bfloat162float(__float2bfloat16_rn(a[1]))),
+                       __float_as_uint(__bfloat162float(__float2bfloat16_rn(a[2]))), __float_as_uint(__bfloat162float(__float2bfloat16_rn(a[3]))));
+    } else if constexpr (OUT == CINN_BF16) {
+        __nv_bfloat162 t0 = __floats2bfloat162_rn(a[0], a[1]), t1 = __floats2bfloat162_rn(a[2], a[3]);
+        __nv_bfloat162 t2 = __floats2bfloat162_rn(a[4], a[5]), t3 = __floats2bfloat162_rn(a[6], a[7]);
+        v = make_uint4(*reinterpret_cast<uint32_t*>(&t0), *reinterpret_cast<uint32_t*>(&t1), *reinterpret_cast<uint32_t*>(&t2), *reinterpret_cast<uint32_t*>(&t3));
+    } else {
+        __half2 t0 = __floats2half2_rn(a[0], a[1]), t1 = __floats2half2_rn(a[2], a[3]);
+        __half2 t2 = __floats2half2_rn(a[4], a[5]), t3 = __floats2half2_rn(a[6], a[7]);
+        v = make_uint4(*reinterpret_cast<uint32_t*>(&t0), *reinterpret_cast<uint32_t*>(&t1), *reinterpret_cast<uint32_t*>(&t2), *reinterpret_cast<uint32_t*>(&t3));
+    }
+    return v;
+}
+
+template <int OUT, int NCOLS>
+__device__ __forceinline__ void store_rows_staged(const float* acc, uint8_t* stage, void* C, int64_t ldc, int row0, int m_end,
+                                                  int col0, int N, int lane) {
+    using T = typename OutT<OUT>::type;
+    constexpr int PER16 = 16 / (int)sizeof(T);      // elements per 16-byte slot
+    constexpr int PER64 = 4 * PER16;                // elements per staged row piece
+#pragma unroll
+    for (int ps = 0; ps < NCOLS / PER64; ++ps) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            *reinterpret_cast<uint4*>(stage + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4)) = pack16<OUT>(&acc[ps * PER64 + c * PER16]);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = i * 8 + (lane >> 2), c = lane & 3;
+            const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 64 + ((c ^ ((r >> 1) & 3)) << 4));
+            const int grow = row0 + r, gcol = col0 + ps * PER64 + c * PER16;
+            if (grow < m_end && gcol < N) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(C) + (int64_t)grow * ldc + gcol) = v;
+        }
+        __syncwarp();
+    }
+}
+
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
@@ -269,7 +316,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem full, [2S+2..2S+4) tmem empty
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    int* cum = reinterpret_cast<int*>(tmem_slot + 2);          // grouped: E + 1 prefix counts of m-tiles
+    uint8_t* store_stage = smem + STAGES * (A_BYTES + B_BYTES) + 256;      // 2 KiB per promotion warp
+    int* cum = reinterpret_cast<int*>(store_stage + EPI_WARPS * 2048);     // grouped: E + 1 prefix counts of m-tiles
 #ifdef CINN_GEMM_PROFILE
     unsigned int* trace = reinterpret_cast<unsigned int*>(cum + (GROUPED ? p.E + 2 : 2));
 #endif
@@ -407,23 +455,36 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         uint32_t it = 0;
         bool alive = true;
         const bool vec_ok = (OUT == CINN_F32 || OUT == CINN_F32_BF16) ? (p.ldc % 4 == 0) : (p.ldc % 8 == 0);
+        // The first three scale pairs of a tile are fetched while the previous tile is being stored, so that
+        // a tile does not start with an exposed round trip to L2 (it matters when K is only a few blocks).
+        float sa0 = 0.f, sb0 = 0.f, sa1 = 0.f, sb1 = 0.f, sa2 = 0.f, sb2 = 0.f;
+        auto scale_ptrs = [&](const TileInfo& ti, const float*& sa_ptr, const float*& sb_ptr) {
+            const int row = ti.m0 + q * 32 + lane;
+            const int col0 = ti.n0 + h * WCOLS;
+            sa_ptr = p.sA + (int64_t)(row < ti.m_end ? row : ti.m0) * p.sa_stride_m;
+            sb_ptr = p.sB + (int64_t)ti.expert * p.sb_stride_e + (int64_t)(col0 < p.N ? col0 / 128 : 0) * p.sb_stride_n;
+        };
+        auto prefetch_scales = [&](const TileInfo& ti) {
+            const float *sa_ptr, *sb_ptr;
+            scale_ptrs(ti, sa_ptr, sb_ptr);
+            sa0 = ld_scale(sa_ptr); sb0 = ld_scale(sb_ptr);
+            if (KB > 1) { sa1 = ld_scale(sa_ptr + p.sa_stride_k); sb1 = ld_scale(sb_ptr + p.sb_stride_k); }
+            if (KB > 2) { sa2 = ld_scale(sa_ptr + 2 * p.sa_stride_k); sb2 = ld_scale(sb_ptr + 2 * p.sb_stride_k); }
+        };
+        if ((int)blockIdx.x < n_total) prefetch_scales(tile_info<GROUPED>(p, cum, blockIdx.x));
         for (int t = blockIdx.x; t < n_total && alive; t += gridDim.x) {
             const TileInfo ti = tile_info<GROUPED>(p, cum, t);
             const int row = ti.m0 + q * 32 + lane;
             const bool rvalid = row < ti.m_end;
             const int col0 = ti.n0 + h * WCOLS;
             const bool cvalid = col0 < p.N;
-            const float* sa_ptr = p.sA + (int64_t)(rvalid ? row : ti.m0) * p.sa_stride_m;
-            const float* sb_ptr = p.sB + (int64_t)ti.expert * p.sb_stride_e + (int64_t)(cvalid ? col0 / 128 : 0) * p.sb_stride_n;
+            const float *sa_ptr, *sb_ptr;
+            scale_ptrs(ti, sa_ptr, sb_ptr);
             float acc[WCOLS];
 #pragma unroll
             for (int i = 0; i < WCOLS; ++i) acc[i] = 0.0f;
-            // scales are fetched three K blocks ahead with loads the compiler may not move
+            // within a tile scales are fetched three K blocks ahead with loads the compiler may not move
             // (a load sunk to its use would expose a full L2 round trip in every K block)
-            float sa0 = ld_scale(sa_ptr), sb0 = ld_scale(sb_ptr);
-            float sa1 = 0.f, sb1 = 0.f, sa2 = 0.f, sb2 = 0.f;
-            if (KB > 1) { sa1 = ld_scale(sa_ptr + p.sa_stride_k); sb1 = ld_scale(sb_ptr + p.sb_stride_k); }
-            if (KB > 2) { sa2 = ld_scale(sa_ptr + 2 * p.sa_stride_k); sb2 = ld_scale(sb_ptr + 2 * p.sb_stride_k); }
             for (int kb = 0; kb < KB; ++kb, ++it) {
                 const float s = sa0 * sb0;
                 sa0 = sa1; sb0 = sb1; sa1 = sa2; sb1 = sb2;
@@ -450,12 +511,16 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 if (lane == 0) mbar_arrive(tempty0 + 8 * b);
                 if (lane == 0) STRACE(16 + warp);
             }
-            if (alive && rvalid && cvalid) {
+            if (alive && t + (int)gridDim.x < n_total) prefetch_scales(tile_info<GROUPED>(p, cum, t + gridDim.x));
+            if (alive && vec_ok) {
+                // warp-uniform: every lane takes part in the staging even if its own row is past the end
+                if (cvalid) store_rows_staged<OUT, WCOLS>(acc, store_stage + warp * 2048, p.C, p.ldc, ti.m0 + q * 32, ti.m_end, col0, p.N, lane);
+            } else if (alive && rvalid && cvalid) {
                 const int64_t base = (int64_t)row * p.ldc + col0;
 #pragma unroll
                 for (int j = 0; j < WCOLS / 8; ++j) {
                     const int ncols = p.N - (col0 + j * 8);
-                    if (ncols > 0) store8<OUT>(p.C, base + j * 8, &acc[j * 8], vec_ok, ncols);
+                    if (ncols > 0) store8<OUT>(p.C, base + j * 8, &acc[j * 8], false, ncols);
                 }
             }
         }
@@ -516,7 +581,7 @@ static int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t
 }
 
 static size_t smem_bytes(int E) {
-    size_t n = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024 + (2 * STAGES + 4) * 8 + 16 + 4 * (size_t)(E + 2);
+    size_t n = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024 + 256 + EPI_WARPS * 2048 + 4 * (size_t)(E + 2);
 #ifdef CINN_GEMM_PROFILE
     n += 64 * 24 * 4;
 #endif
@@ -554,7 +619,7 @@ static int launch_out(const CUtensorMap& ta, const CUtensorMap& tb, const GemmPa
 template <bool B_MN, int OUT>
 static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int clusters, cudaStream_t st) {
     auto kern = pair::fp8_gemm_pair_kernel<B_MN, OUT>;
-    const size_t smem = (size_t)pair::PSTAGES * (pair::PA_BYTES + pair::PB_BYTES) + 1024 + (2 * pair::PSTAGES + 4) * 8 + 16;
+    const size_t smem = pair::PSMEM_BYTES;
     static thread_local bool configured[64] = {};
     int dev = 0;
     CINN_CHECK_CUDA(cudaGetDevice(&dev));

@@ -21,6 +21,14 @@ constexpr int PSTAGES = 6;
 constexpr int PA_BYTES = 128 * BK;      // A rows of this CTA: 16 KiB
 constexpr int PB_BYTES = 128 * BK;      // B columns of this CTA: 16 KiB
 constexpr int PTHREADS = 11 * 32;
+// dynamic shared memory: stages | 256 B of barriers and flags | 2 KiB of store staging per promotion warp
+// (| trace in profiling builds), plus 1 KiB of slack to align the stages to 1024 bytes
+constexpr int PSTAGE_OFF = PSTAGES * (PA_BYTES + PB_BYTES) + 256;
+#ifdef CINN_GEMM_PROFILE
+constexpr size_t PSMEM_BYTES = (size_t)PSTAGE_OFF + 8 * 2048 + 64 * 24 * 4 + 1024;
+#else
+constexpr size_t PSMEM_BYTES = (size_t)PSTAGE_OFF + 8 * 2048 + 1024;
+#endif
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -98,6 +106,7 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     // [0, S) full (used in the leader), [S, 2S) empty, [2S, 2S+2) tmem full, [2S+2, 2S+4) tmem empty (leader)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * PSTAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    uint8_t* store_stage = smem + PSTAGE_OFF;                                   // 2 KiB per promotion warp
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();           // 0 = leader
@@ -227,12 +236,15 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                 __syncwarp();
                 if (lane == 0) mbar_arrive_remote(tempty_leader + 8 * b);
             }
-            if (alive && rvalid && cvalid) {
+            if (alive && vec_ok) {
+                if (cvalid) store_rows_staged<OUT, 128>(acc, store_stage + warp * 2048, p.C, p.ldc, ti.m0 + 128 * (int)rank + q * 32,
+                                                        p.M, col0, p.N, lane);
+            } else if (alive && rvalid && cvalid) {
                 const int64_t base = (int64_t)row * p.ldc + col0;
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const int ncols = p.N - (col0 + j * 8);
-                    if (ncols > 0) store8<OUT>(p.C, base + j * 8, &acc[j * 8], vec_ok, ncols);
+                    if (ncols > 0) store8<OUT>(p.C, base + j * 8, &acc[j * 8], false, ncols);
                 }
             }
         }

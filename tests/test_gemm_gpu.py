@@ -218,3 +218,26 @@ def test_config2_full_size_sampled(K):
     # linearity in the activation scales: doubling sA doubles the result exactly
     out2 = K.fp8_matmul_dsv3(xq, wq.t(), xs * 2, ws.t(), out_dtype=torch.float32)
     assert torch.equal(out2, out * 2)
+
+
+@pytest.mark.parametrize("k_in,n_out", [(7168, 1536), (7168, 576), (1536, 24576), (512, 16384)])
+def test_mla_projection_shapes_sampled(K, k_in, n_out):
+    """Tall-skinny / small-N / small-K GEMMs of the MLA projections at 16384 tokens (quantised on the GPU,
+    float64 check on sampled rows)."""
+    Mt = 16384
+    g = torch.Generator().manual_seed(1003 + n_out)
+    x = torch.randn(Mt, k_in, generator=g).bfloat16().cuda()
+    w = (torch.randn(n_out, k_in, generator=g) * 0.02).bfloat16().cuda()
+    xq, xs = K.quantize_fp8_rowwise(x)
+    wq, ws = K.quantize_fp8_blockwise(w)
+    out = K.fp8_matmul_dsv3(xq, wq.t(), xs, ws.t(), out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert K.device_status() == 0
+    rows = torch.tensor([0, 127, 128, 4097, 9999, 16383])
+    ref = O.fp8_matmul_f64(xq[rows.cuda()].view(torch.uint8).cpu(), wq.view(torch.uint8).cpu().t(),
+                           xs[rows.cuda()].cpu(), ws.cpu().t())
+    err = rel_fro(out[rows.cuda()], ref)
+    print(f"MLA {k_in}->{n_out}: rel-Fro {err:.3e}")
+    assert err <= TOL and err <= 2e-5
+    out16 = K.fp8_matmul_dsv3(xq, wq.t(), xs, ws.t())
+    assert_bf16_close(out16[rows.cuda()], ref, "bf16 output")
