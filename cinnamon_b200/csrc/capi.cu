@@ -44,6 +44,9 @@ int fp8_grouped_gemm(const void* A, const float* sA, const void* W, const float*
                      cudaStream_t st);
 
 int read_device_status(int* out, int reset);
+int fp8_grouped_gemm_dgrad(const void* dY, const float* sdY, const void* W, const float* sW, const int64_t* starts,
+                           const int64_t* ends, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* dX, int out_dtype,
+                           cudaStream_t st);
 int moe_combine(const void* rows, int dtype, const int64_t* pos, const float* gates, void* y, int64_t n_tokens,
                 int64_t n_rows, int top_k, int64_t d, cudaStream_t st);
 
@@ -97,6 +100,12 @@ int cinn_fp8_grouped_gemm(const void* A, const float* sA, const void* W, const f
                           const int64_t* ends, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* C,
                           int out_dtype, void* stream) {
     return cinn::fp8_grouped_gemm(A, sA, W, sW, starts, ends, E, T, d_in, d_out, C, out_dtype, (cudaStream_t)stream);
+}
+
+int cinn_fp8_grouped_gemm_dgrad(const void* dY, const float* sdY, const void* W, const float* sW, const int64_t* starts,
+                                const int64_t* ends, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* dX,
+                                int out_dtype, void* stream) {
+    return cinn::fp8_grouped_gemm_dgrad(dY, sdY, W, sW, starts, ends, E, T, d_in, d_out, dX, out_dtype, (cudaStream_t)stream);
 }
 
 int cinn_moe_combine(const void* rows, int dtype, const int64_t* pos, const float* gates, void* y, int64_t n_tokens,

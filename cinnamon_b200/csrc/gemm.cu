@@ -730,6 +730,37 @@ int fp8_grouped_gemm(const void* A, const float* sA, const void* W, const float*
     return launch_out<false, true>(ta, tb, p, out_dtype, sm_count(), st);
 }
 
+// Input gradient of the grouped GEMM: dX[starts[e]:ends[e], :] = dY[starts[e]:ends[e], :] @ W[e]
+// (W[e] is (d_out, d_in); its bytes are read MN-major, exactly as the dense dgrad reads a weight).
+int fp8_grouped_gemm_dgrad(const void* dY, const float* sdY, const void* W, const float* sW, const int64_t* starts,
+                           const int64_t* ends, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* dX, int out_dtype,
+                           cudaStream_t st) {
+    CINN_CHECK_ARG(E >= 0 && T >= 0 && d_in >= 0 && d_out >= 0, "grouped_gemm_dgrad: negative shape");
+    if (E == 0 || T == 0 || d_in == 0) return CINN_OK;
+    CINN_CHECK_ARG(dY && sdY && W && sW && starts && ends && dX, "grouped_gemm_dgrad: null pointer");
+    CINN_CHECK_ARG(E <= MAX_EXPERTS, "grouped_gemm_dgrad: at most %d experts are supported (got %lld)", MAX_EXPERTS, (long long)E);
+    CINN_CHECK_ARG(d_out > 0 && d_out % 16 == 0 && d_in % 16 == 0,
+                   "grouped_gemm_dgrad: d_out (%lld) and d_in (%lld) must be multiples of 16", (long long)d_out, (long long)d_in);
+    CINN_CHECK_ARG(T < (1LL << 31) && d_out < (1LL << 31) && d_in < (1LL << 31) && E * d_out < (1LL << 31),
+                   "grouped_gemm_dgrad: dimension too large");
+    CINN_CHECK_ARG(al16(dY) && al16(W) && al16(dX), "grouped_gemm_dgrad: dY, W and dX must be 16-byte aligned");
+    CUtensorMap ta, tb;
+    int rc = make_map(&ta, dY, (uint64_t)d_out, (uint64_t)T, (uint64_t)d_out, BK, BM);
+    if (rc) return rc;
+    // W viewed as (E * d_out) reduction rows of d_in output bytes: boxes of 128 output columns x 128 reduction rows.
+    // A K block that runs past an expert's d_out rows meets zero-filled columns of dY, so the neighbour's bytes it
+    // reads contribute nothing (quantised weights hold no NaN codes).
+    rc = make_map(&tb, W, (uint64_t)d_in, (uint64_t)(E * d_out), (uint64_t)d_in, 128, BK);
+    if (rc) return rc;
+    const int64_t nkb_in = (d_in + 127) / 128, nob = (d_out + 127) / 128;
+    GemmParams p{};
+    p.sA = sdY; p.sa_stride_m = nob; p.sa_stride_k = 1;
+    p.sB = sW; p.sb_stride_k = nkb_in; p.sb_stride_n = 1; p.sb_stride_e = nob * nkb_in;
+    p.C = dX; p.ldc = d_in; p.M = (int)T; p.N = (int)d_in; p.K = (int)d_out;
+    p.starts = starts; p.ends = ends; p.E = (int)E; p.b_rows_per_expert = (int)d_out;
+    return launch_out<true, true>(ta, tb, p, out_dtype, sm_count(), st);
+}
+
 int read_device_status(int* out, int reset) {
     int v = 0;
     CINN_CHECK_CUDA(cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)));

@@ -434,6 +434,70 @@ def moe_combine(rows: torch.Tensor, pos: torch.Tensor, gates: torch.Tensor) -> t
     return y
 
 
+def fp8_grouped_gemm_dgrad(dy_fp8, dy_scale, w_fp8, w_scale, expert_starts, expert_ends, out_dtype=torch.bfloat16):
+    """``dX[starts[e]:ends[e]] = dY[starts[e]:ends[e]] @ W[e]`` on quantised operands (one launch, ragged ranges)."""
+    T, d_out = dy_fp8.shape
+    E, _, d_in = w_fp8.shape
+    starts = expert_starts.to(torch.int64).contiguous()
+    ends = expert_ends.to(torch.int64).contiguous()
+    with torch.cuda.device(dy_fp8.device):
+        dx = torch.zeros((T, d_in), dtype=out_dtype, device=dy_fp8.device)     # rows of no expert get no gradient
+        _lib.check(_L.cinn_fp8_grouped_gemm_dgrad(_ptr(dy_fp8), _ptr(dy_scale), _ptr(w_fp8), _ptr(w_scale), _ptr(starts),
+                                                  _ptr(ends), E, T, d_in, d_out, _ptr(dx), _DTYPE_TAG[out_dtype],
+                                                  _stream(dy_fp8)), "cinn_fp8_grouped_gemm_dgrad")
+    _count()
+    return dx
+
+
+class MoEGroupedGemmFunction(torch.autograd.Function):
+    """Differentiable grouped GEMM.  The reference's ``moe_grouped_gemm`` is a plain function (src/kernels.py:526-581),
+    so on CUDA no gradient reaches the routed experts there; this function gives the grouped GEMM the backward of
+    ``FP8MatmulFunction`` (src/kernels.py:763-794) expert by expert:
+
+      dX[e rows] = rowwise(dY[e rows]) @ W_q[e]                                 one grouped launch
+      dW[e]      = rowwise(dY[e rows]^T) @ blockwise(dequant_rowwise(x_q[e rows]))   per non-empty expert
+
+    The weight gradient walks the experts on the host (their row counts are read back once per backward)."""
+
+    @staticmethod
+    def forward(ctx, sorted_x, weights, expert_starts, expert_ends, out_dtype):
+        x = sorted_x if sorted_x.stride(-1) == 1 else sorted_x.contiguous()
+        x_fp8, x_scale = quantize_fp8_rowwise(x, block_size=128)
+        w_fp8, w_scale = quantize_expert_weights(weights)
+        out = fp8_grouped_gemm(x_fp8, x_scale, w_fp8, w_scale, expert_starts, expert_ends, out_dtype=out_dtype)
+        ctx.save_for_backward(x_fp8, x_scale, w_fp8, w_scale, expert_starts, expert_ends)
+        ctx.x_dtype, ctx.w_dtype = sorted_x.dtype, weights.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x_fp8, x_scale, w_fp8, w_scale, starts, ends = ctx.saved_tensors
+        E, d_out, d_in = w_fp8.shape
+        g = grad_out if grad_out.is_contiguous() else grad_out.contiguous()
+        g_fp8, g_scale = quantize_fp8_rowwise(g, block_size=128)
+        dx_dtype = ctx.x_dtype if ctx.x_dtype in _DTYPE_TAG else torch.float32
+        grad_x = fp8_grouped_gemm_dgrad(g_fp8, g_scale, w_fp8, w_scale, starts, ends, out_dtype=dx_dtype)
+        w_dtype = ctx.w_dtype if ctx.w_dtype in (torch.float32, torch.bfloat16) else torch.float32
+        grad_w = torch.zeros((E, d_out, d_in), dtype=w_dtype, device=g.device)
+        bounds = torch.stack([starts, ends]).tolist()              # one host read-back per backward
+        for e, (s, t) in enumerate(zip(*bounds)):
+            n = t - s
+            if n <= 0:
+                continue
+            ge, xq, xs = g[s:t], x_fp8[s:t], x_scale[s:t]
+            npad = (n + 15) // 16 * 16                             # the reduction axis in multiples of 16 (zero rows)
+            if npad != n:
+                ge = torch.nn.functional.pad(ge, (0, 0, 0, npad - n))
+                xq = torch.nn.functional.pad(xq.view(torch.uint8), (0, 0, 0, npad - n)).view(torch.float8_e4m3fn)
+                xs = torch.nn.functional.pad(xs, (0, 0, 0, npad - n), value=1.0)
+            gt_fp8, gt_scale = quantize_fp8_rowwise(ge.t(), block_size=128)
+            xb_fp8, xb_scale = requantize_rowwise_to_blockwise(xq.contiguous(), xs.contiguous())
+            grad_w[e] = _gemm(gt_fp8, gt_scale, xb_fp8, _lib.B_KN, xb_scale, xb_scale.stride(0), xb_scale.stride(1),
+                              d_out, d_in, npad, torch.float32 if w_dtype == torch.float32 else torch.bfloat16,
+                              bf16_rounded=True)
+        return grad_x.to(ctx.x_dtype), grad_w.to(ctx.w_dtype), None, None, None
+
+
 def moe_grouped_gemm(sorted_x: torch.Tensor, weights: torch.Tensor, expert_starts: torch.Tensor,
                      expert_ends: torch.Tensor, max_expert_tokens: int = None,
                      dtype: torch.dtype = torch.float16) -> torch.Tensor:
@@ -443,8 +507,11 @@ def moe_grouped_gemm(sorted_x: torch.Tensor, weights: torch.Tensor, expert_start
     ``expert_starts`` / ``expert_ends`` are read on the device; ``max_expert_tokens`` is
     accepted for signature compatibility and ignored (no grid depends on it, so the
     caller's ``.item()`` synchronisation is unnecessary).  Tokens and weights are quantised
-    to e4m3 on the fly; returns fp16 like the reference unless ``dtype`` says otherwise."""
+    to e4m3 on the fly; returns fp16 like the reference unless ``dtype`` says otherwise.
+    Unlike the reference it is differentiable (``MoEGroupedGemmFunction``)."""
     assert sorted_x.is_cuda and weights.is_cuda, "Inputs must be on CUDA"
+    if torch.is_grad_enabled() and (sorted_x.requires_grad or weights.requires_grad):
+        return MoEGroupedGemmFunction.apply(sorted_x, weights, expert_starts, expert_ends, dtype)
     x = sorted_x if sorted_x.stride(-1) == 1 else sorted_x.contiguous()
     x_fp8, x_scale = quantize_fp8_rowwise(x, block_size=128)
     w_fp8, w_scale = quantize_expert_weights(weights)

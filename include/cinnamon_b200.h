@@ -104,6 +104,15 @@ int cinn_fp8_grouped_gemm(const void* A, const float* sA, const void* W, const f
                           const int64_t* starts, const int64_t* ends, int64_t E, int64_t T, int64_t d_in,
                           int64_t d_out, void* C, int out_dtype, void* stream);
 
+/* Input gradient of the grouped GEMM:  dX[starts[e]:ends[e], :] = dY[starts[e]:ends[e], :] @ W[e].
+ * No counterpart in the reference: its moe_grouped_gemm is not differentiable (src/kernels.py:526-581 is a plain
+ * function), so routed experts receive no gradient there; the arithmetic mirrors the dense dgrad
+ * (src/kernels.py:771-774).  dY: (T, d_out) e4m3 with scales (T, ceil(d_out/128)); W, sW as in
+ * cinn_fp8_grouped_gemm (the weight bytes are read as stored, never transposed); dX: (T, d_in). */
+int cinn_fp8_grouped_gemm_dgrad(const void* dY, const float* sdY, const void* W, const float* sW, const int64_t* starts,
+                                const int64_t* ends, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* dX,
+                                int out_dtype, void* stream);
+
 /* y[t, :] = sum_j gates[t, j] * rows[pos[t, j], :]  for t < n_tokens, j < top_k; fp32 result, no atomics.
  * Replaces the gate multiply, torch.zeros and scatter_add_ at the end of MoE.forward (src/layers.py:157-160).
  * rows: (n_rows, d) bf16 / fp16 / fp32.  pos: (n_tokens, top_k) int64 row indices (negative = skip), ascending per

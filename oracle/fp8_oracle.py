@@ -311,6 +311,26 @@ def grouped_gemm_fp8_f64(sorted_x: torch.Tensor, weights: torch.Tensor, starts, 
     return out
 
 
+def grouped_gemm_fp8_backward_f64(sorted_x: torch.Tensor, weights: torch.Tensor, starts, ends, grad_out: torch.Tensor):
+    """Backward of the FP8 grouped GEMM, expert by expert with the arithmetic of
+    FP8MatmulFunction.backward (src/kernels.py:763-794); the reference itself defines no
+    backward for its grouped GEMM.  Returns (dX float64 [T, d_in], dW float64 [E, d_out, d_in])."""
+    T, d_in = sorted_x.shape
+    E, d_out, _ = weights.shape
+    x_q, x_s = quantize_rowwise(sorted_x, 128, False)
+    dx = torch.zeros(T, d_in, dtype=torch.float64)
+    dw = torch.zeros(E, d_out, d_in, dtype=torch.float64)
+    for e in range(E):
+        s, t = int(starts[e]), int(ends[e])
+        if t <= s:
+            continue
+        w_q, w_s = quantize_blockwise(weights[e].float(), 128, 128)
+        gx, gw = fp8_linear_backward(grad_out[s:t], (x_q[s:t], x_s[s:t], w_q, w_s), False)
+        dx[s:t] = gx
+        dw[e] = gw
+    return dx, dw
+
+
 # ----------------------------------------------------------------------------
 # MoE routing (src/layers.py:118-160), used by the expert-parallel tests
 # ----------------------------------------------------------------------------

@@ -241,3 +241,26 @@ def test_mla_projection_shapes_sampled(K, k_in, n_out):
     assert err <= TOL and err <= 2e-5
     out16 = K.fp8_matmul_dsv3(xq, wq.t(), xs, ws.t())
     assert_bf16_close(out16[rows.cuda()], ref, "bf16 output")
+
+
+@pytest.mark.parametrize("name", ["ragged", "empty_first_last", "wide_k"])
+def test_grouped_gemm_backward(K, name):
+    """moe_grouped_gemm is differentiable here (it is not in the reference): grouped dgrad in one launch,
+    weight gradient per expert, both with the arithmetic of the dense backward."""
+    E, d_in, d_out, counts = GROUPED[name]
+    x, w, starts, ends = _grouped_case(E, d_in, d_out, counts, seed=40 + len(name))
+    g = torch.Generator().manual_seed(41)
+    dy = torch.randn(x.shape[0], d_out, generator=g).bfloat16()
+    ref_dx, ref_dw = O.grouped_gemm_fp8_backward_f64(x, w, starts, ends, dy)
+    xg = x.cuda().requires_grad_(True)
+    wg = w.float().cuda().requires_grad_(True)
+    out = K.moe_grouped_gemm(xg, wg, starts.cuda(), ends.cuda(), dtype=torch.bfloat16)
+    out.backward(dy.cuda())
+    torch.cuda.synchronize()
+    assert K.device_status() == 0
+    assert xg.grad.dtype == torch.bfloat16 and wg.grad.dtype == torch.float32
+    assert_bf16_close(xg.grad, ref_dx, "grouped dgrad")
+    assert_bf16_close(wg.grad.to(torch.bfloat16), ref_dw, "grouped wgrad")
+    for e, c in enumerate(counts):
+        if c == 0:
+            assert torch.all(wg.grad[e] == 0)
