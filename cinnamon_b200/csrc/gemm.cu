@@ -23,30 +23,21 @@ namespace cinn {
 constexpr int BM = 128;            // tile rows
 constexpr int BN = 256;            // tile columns (two 128-column scale blocks)
 constexpr int BK = 128;            // bytes (= e4m3 elements) per K block: one scale block, one swizzle row
-constexpr int STAGES = 4;
+constexpr int STAGES = 4;             // even: each of the two MMA issuers then always meets the same stages, so it
+                                      // sees every phase of their barriers (a parity wait cannot skip a phase)
+constexpr int C_SLOT_BYTES = BM * 128;   // one TMA-store box: 128 rows x 64 columns of a 2-byte type
+constexpr int C_STAGE_BYTES = 2 * C_SLOT_BYTES;   // one slot per column group of promotion warps
 constexpr int A_BYTES = BM * BK;   // 16 KiB
 constexpr int B_BYTES = BN * BK;   // 32 KiB
 constexpr int EPI_WARPS = 8;                    // four TMEM lane quarters x two column groups
 constexpr int WCOLS = BN / (EPI_WARPS / 4);     // accumulator columns per epilogue warp
 constexpr int THREADS = (EPI_WARPS + 3) * 32;     // + TMA producer + two MMA issuers
 constexpr int TMEM_COLS = 512;
-constexpr int MAX_EXPERTS = 2048;
+constexpr int MAX_EXPERTS = 384;      // bounded by the shared memory left for the per-expert prefix sums
 constexpr int GROUP_M = 16;        // rasterisation: m-tiles per L2 group (dense)
 
 // device status word: 0 = fine, otherwise (role << 8) | reason
 __device__ int g_device_status = 0;
-
-// Optional time-line trace (builds with -DCINN_GEMM_PROFILE only): CTA 0 records 32-bit clock stamps of
-// K blocks 128..191 in shared memory (a store costs a few cycles) and dumps them when it finishes.
-// Slots: 0 MMA has operands, 1 MMA has a TMEM buffer, 2 MMAs issued and committed,
-//        8+w epilogue warp w sees the partial tile, 16+w epilogue warp w has released the buffer.
-#ifdef CINN_GEMM_PROFILE
-__device__ unsigned int g_trace[64 * 24];
-__device__ __forceinline__ unsigned int clock32() { unsigned int c; asm volatile("mov.u32 %0, %%clock;" : "=r"(c)); return c; }
-#define STRACE(slot) do { if (it >= 128u && it < 192u) trace[(it - 128u) * 24 + (slot)] = clock32(); } while (0)
-#else
-#define STRACE(slot)
-#endif
 
 struct GemmParams {
     const float* sA; int64_t sa_stride_m, sa_stride_k;
@@ -54,6 +45,7 @@ struct GemmParams {
     void* C; int64_t ldc;
     int M, N, K;                   // dense: A is (M, K); grouped: M = total rows T
     const int64_t* starts; const int64_t* ends; int E; int b_rows_per_expert;
+    int tma_out;                   // 1: finished tiles leave through TMA stores (2-byte outputs, N % 8 == 0)
 };
 
 // ---------------------------------------------------------------------------
@@ -99,11 +91,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// The same wait taken by a whole warp, with one verdict for all its lanes: the promotion warps execute
+// warp-collective tcgen05.ld next, so no lane may leave the wait on its own.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    const bool ok = mbar_wait(bar, parity, abort_flag, code);
+    return __all_sync(0xffffffffu, ok);
+}
+
 __device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint32_t bar, uint32_t dst, int x, int y) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+
+// TMA store of one box from shared memory (bulk async-group completion)
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // fp32 load through the read-only path, pinned in program order
 __device__ __forceinline__ float ld_scale(const float* p) {
@@ -307,29 +316,31 @@ __device__ __forceinline__ void store_rows_staged(const float* acc, uint8_t* sta
 // ---------------------------------------------------------------------------
 template <bool B_MN, bool GROUPED, int OUT>
 __global__ void __launch_bounds__(THREADS, 1)
-fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    // layout: operand stages | output staging (32 KiB, 1024-aligned) | barriers and flags (256 B) | expert prefix sums
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + STAGES * A_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_BYTES + B_BYTES));
-    // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem full, [2S+2..2S+4) tmem empty
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    uint8_t* c_stage = smem + STAGES * (A_BYTES + B_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(c_stage + C_STAGE_BYTES);
+    // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem full, [2S+2..2S+4) tmem empty, then slot free / slot full x 2
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    uint8_t* store_stage = smem + STAGES * (A_BYTES + B_BYTES) + 256;      // 2 KiB per promotion warp
-    int* cum = reinterpret_cast<int*>(store_stage + EPI_WARPS * 2048);     // grouped: E + 1 prefix counts of m-tiles
-#ifdef CINN_GEMM_PROFILE
-    unsigned int* trace = reinterpret_cast<unsigned int*>(cum + (GROUPED ? p.E + 2 : 2));
-#endif
+    uint8_t* store_stage = c_stage;                                        // 2 KiB per promotion warp (non-TMA path)
+    int* cum = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 256);   // grouped: E + 1 prefix counts of m-tiles
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
     const uint32_t tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
+    const uint32_t gfree0 = smem_u32(bars + 2 * STAGES + 4), gfull0 = smem_u32(bars + 2 * STAGES + 6);
 
     if (threadIdx.x == 0) *abort_flag = 0;
     if (warp == EPI_WARPS && lane == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, EPI_WARPS); }
+        for (int g = 0; g < 2; ++g) { mbar_init(gfree0 + 8 * g, 4); mbar_init(gfull0 + 8 * g, 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == EPI_WARPS + 1) {
@@ -367,9 +378,6 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
     const int KB = (p.K + BK - 1) / BK;
     const int n_total = total_tiles<GROUPED>(p, cum);
-#ifdef CINN_GEMM_PROFILE
-    const long long _cta_t0 = clock64();
-#endif
 
     if (warp >= EPI_WARPS) {
       if (warp == EPI_WARPS) {
@@ -426,9 +434,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     // operands first (they landed long ago: this costs one barrier probe, taken while
                     // the epilogue still works on the buffer), then the TMEM buffer
                     if (!mbar_wait(full0 + 8 * s, ph, abort_flag, (2 << 8) | 1)) { alive = false; break; }
-                    STRACE(0);
                     if (!mbar_wait(tempty0 + 8 * b, bph ^ 1, abort_flag, (2 << 8) | 2)) { alive = false; break; }
-                    STRACE(1);
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem_a + s * A_BYTES);
                     const uint32_t b_addr = smem_u32(smem_b + s * B_BYTES);
@@ -442,7 +448,6 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     }
                     tc_commit(empty0 + 8 * s);      // the stage may be refilled once these MMAs retire
                     tc_commit(tfull0 + 8 * b);      // and the partial tile is ready for promotion
-                    STRACE(2);
                 }
             }
             // every MMA issued above must have retired before tensor memory is freed
@@ -457,6 +462,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const bool vec_ok = (OUT == CINN_F32 || OUT == CINN_F32_BF16) ? (p.ldc % 4 == 0) : (p.ldc % 8 == 0);
         // The first three scale pairs of a tile are fetched while the previous tile is being stored, so that
         // a tile does not start with an exposed round trip to L2 (it matters when K is only a few blocks).
+        uint32_t n_rounds = 0;                   // staging rounds of this column group so far (two per TMA tile)
         float sa0 = 0.f, sb0 = 0.f, sa1 = 0.f, sb1 = 0.f, sa2 = 0.f, sb2 = 0.f;
         auto scale_ptrs = [&](const TileInfo& ti, const float*& sa_ptr, const float*& sb_ptr) {
             const int row = ti.m0 + q * 32 + lane;
@@ -493,8 +499,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     sb2 = ld_scale(sb_ptr + (int64_t)(kb + 3) * p.sb_stride_k);
                 }
                 const uint32_t b = it & 1, bph = (it >> 1) & 1;
-                if (!mbar_wait(tfull0 + 8 * b, bph, abort_flag, (3 << 8) | 1)) { alive = false; break; }
-                if (lane == 0) STRACE(8 + warp);
+                if (!mbar_wait_warp(tfull0 + 8 * b, bph, abort_flag, (3 << 8) | 1)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * BN + h * WCOLS;
 #pragma unroll
@@ -509,10 +514,48 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty0 + 8 * b);
-                if (lane == 0) STRACE(16 + warp);
             }
             if (alive && t + (int)gridDim.x < n_total) prefetch_scales(tile_info<GROUPED>(p, cum, t + gridDim.x));
-            if (alive && vec_ok) {
+            constexpr bool TMA_OUT = (OUT == CINN_BF16 || OUT == CINN_F16);
+            // A tile whose 128 rows all belong to it leaves through TMA stores.  Each column group of four
+            // promotion warps owns one 16 KiB slot: its threads drop 64 columns of their rows into it (16-byte
+            // chunks, 128-byte swizzle), one thread hands the box to the TMA unit, and the group repeats for its
+            // other 64 columns once the unit has read the slot.  Storing one row per thread straight from
+            // registers costs thousands of cycles per tile, and so do shared-memory round trips next to a busy
+            // tensor pipe.
+            const bool whole = !GROUPED || ti.m0 + BM <= ti.m_end;
+            if (TMA_OUT && alive && p.tma_out && whole) {
+                const bool elected = (warp == h * 4) && lane == 0;
+                const uint32_t slot = smem_u32(c_stage) + h * C_SLOT_BYTES;
+                const int rl = q * 32 + lane;
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    const uint32_t par = n_rounds & 1u;
+                    if (elected) tma_store_wait_read();               // the unit has finished reading this slot
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(gfree0 + 8 * h);
+                    if (!mbar_wait_warp(gfree0 + 8 * h, par, abort_flag, (3 << 8) | 2)) { alive = false; break; }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint4 v = pack16<OUT>(&acc[r * 64 + j * 8]);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(slot + rl * 128 + ((j ^ (rl & 7)) << 4)),
+                                     "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+                    }
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(gfull0 + 8 * h);
+                    if (elected) {
+                        const int col = col0 + r * 64;
+                        if (mbar_wait(gfull0 + 8 * h, par, abort_flag, (3 << 8) | 3)) {
+                            if (col < p.N) tma_store_2d(&tmC, slot, col, ti.m0);
+                            tma_store_commit();
+                        }
+                    }
+                    __syncwarp();   // the elected lane rejoins its warp before the next warp-collective instruction
+                    ++n_rounds;
+                }
+                if (!alive) break;
+            } else if (alive && vec_ok && !(TMA_OUT && p.tma_out)) {
                 // warp-uniform: every lane takes part in the staging even if its own row is past the end
                 if (cvalid) store_rows_staged<OUT, WCOLS>(acc, store_stage + warp * 2048, p.C, p.ldc, ti.m0 + q * 32, ti.m_end, col0, p.N, lane);
             } else if (alive && rvalid && cvalid) {
@@ -520,16 +563,13 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
                 for (int j = 0; j < WCOLS / 8; ++j) {
                     const int ncols = p.N - (col0 + j * 8);
-                    if (ncols > 0) store8<OUT>(p.C, base + j * 8, &acc[j * 8], false, ncols);
+                    if (ncols > 0) store8<OUT>(p.C, base + j * 8, &acc[j * 8], vec_ok, ncols);
                 }
             }
         }
+        if (lane == 0 && (warp & 3) == 0) tma_store_wait_all();      // this group's boxes have reached global memory
     }
 
-#ifdef CINN_GEMM_PROFILE
-    __syncthreads();
-    if (blockIdx.x == 0) for (int i = threadIdx.x; i < 64 * 24; i += THREADS) g_trace[i] = trace[i];
-#endif
     tc_fence_before();
     __syncthreads();
     if (warp == EPI_WARPS + 1) {
@@ -560,16 +600,16 @@ static EncodeFn get_encode() {
     return fn;
 }
 
-// 2-D byte tensor: inner extent `inner` bytes (contiguous), `rows` rows of pitch `pitch` bytes
+// 2-D tensor: inner extent `inner` elements (contiguous), `rows` rows of pitch `pitch` BYTES
 static int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows, uint64_t pitch, uint32_t box_inner,
-                    uint32_t box_rows) {
+                    uint32_t box_rows, CUtensorMapDataType dtype = CU_TENSOR_MAP_DATA_TYPE_UINT8) {
     EncodeFn enc = get_encode();
     if (!enc) { set_error("cuTensorMapEncodeTiled is not available from the CUDA driver"); return CINN_ERR_CUDA; }
     cuuint64_t dims[2] = {inner, rows};
     cuuint64_t strides[1] = {pitch};
     cuuint32_t box[2] = {box_inner, box_rows};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+    CUresult r = enc(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -581,15 +621,27 @@ static int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t
 }
 
 static size_t smem_bytes(int E) {
-    size_t n = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024 + 256 + EPI_WARPS * 2048 + 4 * (size_t)(E + 2);
-#ifdef CINN_GEMM_PROFILE
-    n += 64 * 24 * 4;
-#endif
+    size_t n = (size_t)STAGES * (A_BYTES + B_BYTES) + C_STAGE_BYTES + 1024 + 256 + 4 * (size_t)(E + 2);
     return n;
 }
 
+// Output map for the TMA-store epilogue: (rows, N) of a 2-byte type, boxes of 64 columns x 128 rows, 128-byte swizzle.
+// Sets p.tma_out; when the output cannot go through TMA the (unused) operand map is passed in its place.
+static int make_out_map(CUtensorMap* tc, const CUtensorMap& fallback, GemmParams& p, int out_dtype, int64_t rows) {
+    p.tma_out = 0;
+    *tc = fallback;
+    if ((out_dtype == CINN_BF16 || out_dtype == CINN_F16) && p.N % 8 == 0) {
+        int rc = make_map(tc, p.C, (uint64_t)p.N, (uint64_t)rows, (uint64_t)p.ldc * 2, 64, BM,
+                          out_dtype == CINN_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+        if (rc) return rc;
+        p.tma_out = 1;
+    }
+    return CINN_OK;
+}
+
 template <bool B_MN, bool GROUPED, int OUT>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid,
+                  cudaStream_t st) {
     auto kern = fp8_gemm_kernel<B_MN, GROUPED, OUT>;
     const size_t smem = smem_bytes(GROUPED ? p.E : 0);
     static thread_local size_t configured[64] = {};   // per instantiation, per thread, per device
@@ -599,19 +651,22 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
         CINN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         if (dev >= 0 && dev < 64) configured[dev] = smem;
     }
-    kern<<<grid, THREADS, smem, st>>>(ta, tb, p);
+    kern<<<grid, THREADS, smem, st>>>(ta, tb, tc, p);
     CINN_CHECK_LAUNCH();
     return CINN_OK;
 }
 
 template <bool B_MN, bool GROUPED>
-static int launch_out(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int out_dtype, int grid,
+static int launch_out(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, int out_dtype, int grid,
                       cudaStream_t st) {
+    CUtensorMap tc;
+    int rc = make_out_map(&tc, ta, p, out_dtype, p.M);
+    if (rc) return rc;
     switch (out_dtype) {
-        case CINN_BF16: return launch<B_MN, GROUPED, CINN_BF16>(ta, tb, p, grid, st);
-        case CINN_F32: return launch<B_MN, GROUPED, CINN_F32>(ta, tb, p, grid, st);
-        case CINN_F16: return launch<B_MN, GROUPED, CINN_F16>(ta, tb, p, grid, st);
-        case CINN_F32_BF16: return launch<B_MN, GROUPED, CINN_F32_BF16>(ta, tb, p, grid, st);
+        case CINN_BF16: return launch<B_MN, GROUPED, CINN_BF16>(ta, tb, tc, p, grid, st);
+        case CINN_F32: return launch<B_MN, GROUPED, CINN_F32>(ta, tb, tc, p, grid, st);
+        case CINN_F16: return launch<B_MN, GROUPED, CINN_F16>(ta, tb, tc, p, grid, st);
+        case CINN_F32_BF16: return launch<B_MN, GROUPED, CINN_F32_BF16>(ta, tb, tc, p, grid, st);
         default: set_error("GEMM: unknown output dtype tag %d", out_dtype); return CINN_ERR_INVALID;
     }
 }
@@ -774,8 +829,3 @@ int read_device_status(int* out, int reset) {
 
 }  // namespace cinn
 
-#ifdef CINN_GEMM_PROFILE
-extern "C" int cinn_debug_trace(unsigned int* out1536) {
-    return cudaMemcpyFromSymbol(out1536, cinn::g_trace, 1536 * sizeof(unsigned int)) == cudaSuccess ? CINN_OK : CINN_ERR_CUDA;
-}
-#endif

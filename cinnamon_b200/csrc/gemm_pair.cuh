@@ -21,14 +21,10 @@ constexpr int PSTAGES = 6;
 constexpr int PA_BYTES = 128 * BK;      // A rows of this CTA: 16 KiB
 constexpr int PB_BYTES = 128 * BK;      // B columns of this CTA: 16 KiB
 constexpr int PTHREADS = 11 * 32;
-// dynamic shared memory: stages | 256 B of barriers and flags | 2 KiB of store staging per promotion warp
-// (| trace in profiling builds), plus 1 KiB of slack to align the stages to 1024 bytes
+// dynamic shared memory: stages | 256 B of barriers and flags | 2 KiB of store staging per promotion warp,
+// plus 1 KiB of slack to align the stages to 1024 bytes
 constexpr int PSTAGE_OFF = PSTAGES * (PA_BYTES + PB_BYTES) + 256;
-#ifdef CINN_GEMM_PROFILE
-constexpr size_t PSMEM_BYTES = (size_t)PSTAGE_OFF + 8 * 2048 + 64 * 24 * 4 + 1024;
-#else
 constexpr size_t PSMEM_BYTES = (size_t)PSTAGE_OFF + 8 * 2048 + 1024;
-#endif
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -222,7 +218,7 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                     sb2 = ld_scale(sb_ptr + (int64_t)(kb + 3) * p.sb_stride_k);
                 }
                 const uint32_t b = it & 1, bph = (it >> 1) & 1;
-                if (!mbar_wait(tfull0 + 8 * b, bph, abort_flag, (3 << 8) | 1)) { alive = false; break; }
+                if (!mbar_wait_warp(tfull0 + 8 * b, bph, abort_flag, (3 << 8) | 1)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * PN + h * 128;
 #pragma unroll
