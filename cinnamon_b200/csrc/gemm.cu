@@ -672,7 +672,8 @@ static int launch_out(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& 
 }
 
 template <bool B_MN, int OUT>
-static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int clusters, cudaStream_t st) {
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int clusters,
+                       cudaStream_t st) {
     auto kern = pair::fp8_gemm_pair_kernel<B_MN, OUT>;
     const size_t smem = pair::PSMEM_BYTES;
     static thread_local bool configured[64] = {};
@@ -694,18 +695,21 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    CINN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, p));
+    CINN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p));
     return CINN_OK;
 }
 
 template <bool B_MN>
-static int launch_pair_out(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int out_dtype, int clusters,
+static int launch_pair_out(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, int out_dtype, int clusters,
                            cudaStream_t st) {
+    CUtensorMap tc;
+    int rc = make_out_map(&tc, ta, p, out_dtype, p.M);
+    if (rc) return rc;
     switch (out_dtype) {
-        case CINN_BF16: return launch_pair<B_MN, CINN_BF16>(ta, tb, p, clusters, st);
-        case CINN_F32: return launch_pair<B_MN, CINN_F32>(ta, tb, p, clusters, st);
-        case CINN_F16: return launch_pair<B_MN, CINN_F16>(ta, tb, p, clusters, st);
-        case CINN_F32_BF16: return launch_pair<B_MN, CINN_F32_BF16>(ta, tb, p, clusters, st);
+        case CINN_BF16: return launch_pair<B_MN, CINN_BF16>(ta, tb, tc, p, clusters, st);
+        case CINN_F32: return launch_pair<B_MN, CINN_F32>(ta, tb, tc, p, clusters, st);
+        case CINN_F16: return launch_pair<B_MN, CINN_F16>(ta, tb, tc, p, clusters, st);
+        case CINN_F32_BF16: return launch_pair<B_MN, CINN_F32_BF16>(ta, tb, tc, p, clusters, st);
         default: set_error("GEMM: unknown output dtype tag %d", out_dtype); return CINN_ERR_INVALID;
     }
 }

@@ -21,10 +21,10 @@ constexpr int PSTAGES = 6;
 constexpr int PA_BYTES = 128 * BK;      // A rows of this CTA: 16 KiB
 constexpr int PB_BYTES = 128 * BK;      // B columns of this CTA: 16 KiB
 constexpr int PTHREADS = 11 * 32;
-// dynamic shared memory: stages | 256 B of barriers and flags | 2 KiB of store staging per promotion warp,
-// plus 1 KiB of slack to align the stages to 1024 bytes
-constexpr int PSTAGE_OFF = PSTAGES * (PA_BYTES + PB_BYTES) + 256;
-constexpr size_t PSMEM_BYTES = (size_t)PSTAGE_OFF + 8 * 2048 + 1024;
+// dynamic shared memory: operand stages | two 16 KiB output slots (TMA-store boxes; also the 2 KiB-per-warp staging of
+// the non-TMA path) | 256 B of barriers and flags, plus 1 KiB of slack to align the stages to 1024 bytes
+constexpr int PSTAGE_OFF = PSTAGES * (PA_BYTES + PB_BYTES);
+constexpr size_t PSMEM_BYTES = (size_t)PSTAGE_OFF + C_STAGE_BYTES + 256 + 1024;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -93,26 +93,30 @@ __device__ __forceinline__ PairTile pair_tile(const GemmParams& p, int t) {
 
 template <bool B_MN, int OUT>
 __global__ void __launch_bounds__(PTHREADS, 1)
-fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + PSTAGES * PA_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PSTAGES * (PA_BYTES + PB_BYTES));
+    uint8_t* c_stage = smem + PSTAGE_OFF;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(c_stage + C_STAGE_BYTES);
     // [0, S) full (used in the leader), [S, 2S) empty, [2S, 2S+2) tmem full, [2S+2, 2S+4) tmem empty (leader)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * PSTAGES + 4);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * PSTAGES + 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    uint8_t* store_stage = smem + PSTAGE_OFF;                                   // 2 KiB per promotion warp
+    uint8_t* store_stage = c_stage;                                             // 2 KiB per promotion warp (non-TMA path)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();           // 0 = leader
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + PSTAGES);
     const uint32_t tfull0 = smem_u32(bars + 2 * PSTAGES), tempty0 = smem_u32(bars + 2 * PSTAGES + 2);
+    const uint32_t gfree0 = smem_u32(bars + 2 * PSTAGES + 4), gfull0 = smem_u32(bars + 2 * PSTAGES + 6);
 
     if (threadIdx.x == 0) *abort_flag = 0;
     if (warp == 8 && lane == 0) {
         for (int s = 0; s < PSTAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 16); }
+        for (int g = 0; g < 2; ++g) { mbar_init(gfree0 + 8 * g, 4); mbar_init(gfull0 + 8 * g, 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 9) {
@@ -192,7 +196,7 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         // ------------------------------ promotion / epilogue (both CTAs) ------------------------------
         const int q = warp & 3, h = warp >> 2;
         const uint32_t tempty_leader = mapa(tempty0, 0);
-        uint32_t it = 0;
+        uint32_t it = 0, n_rounds = 0;
         bool alive = true;
         const bool vec_ok = (OUT == CINN_F32 || OUT == CINN_F32_BF16) ? (p.ldc % 4 == 0) : (p.ldc % 8 == 0);
         for (int t = cluster_id; t < n_total && alive; t += n_clusters) {
@@ -232,7 +236,41 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                 __syncwarp();
                 if (lane == 0) mbar_arrive_remote(tempty_leader + 8 * b);
             }
-            if (alive && vec_ok) {
+            constexpr bool TMA_OUT = (OUT == CINN_BF16 || OUT == CINN_F16);
+            if (TMA_OUT && alive && p.tma_out) {
+                // as in the one-SM kernel: each column group of four promotion warps stages 64 columns of its rows
+                // in its own 16 KiB slot and one thread hands the box to the TMA unit, twice per tile
+                const bool elected = (warp == h * 4) && lane == 0;
+                const uint32_t slot = smem_u32(c_stage) + h * C_SLOT_BYTES;
+                const int rl = q * 32 + lane;
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    const uint32_t par = n_rounds & 1u;
+                    if (elected) tma_store_wait_read();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(gfree0 + 8 * h);
+                    if (!mbar_wait_warp(gfree0 + 8 * h, par, abort_flag, (3 << 8) | 2)) { alive = false; break; }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint4 v = pack16<OUT>(&acc[r * 64 + j * 8]);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(slot + rl * 128 + ((j ^ (rl & 7)) << 4)),
+                                     "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+                    }
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(gfull0 + 8 * h);
+                    if (elected) {
+                        const int col = col0 + r * 64;
+                        if (mbar_wait(gfull0 + 8 * h, par, abort_flag, (3 << 8) | 3)) {
+                            if (col < p.N) tma_store_2d(&tmC, slot, col, ti.m0 + 128 * (int)rank);
+                            tma_store_commit();
+                        }
+                    }
+                    __syncwarp();
+                    ++n_rounds;
+                }
+                if (!alive) break;
+            } else if (alive && vec_ok) {
                 if (cvalid) store_rows_staged<OUT, 128>(acc, store_stage + warp * 2048, p.C, p.ldc, ti.m0 + 128 * (int)rank + q * 32,
                                                         p.M, col0, p.N, lane);
             } else if (alive && rvalid && cvalid) {
@@ -244,6 +282,7 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                 }
             }
         }
+        if (lane == 0 && (warp & 3) == 0) tma_store_wait_all();      // this group's boxes have reached global memory
     }
 
     // nobody leaves while the other CTA may still read this CTA's shared memory or signal its barriers
