@@ -17,14 +17,16 @@ namespace pair {
 
 constexpr int PM = 256;                 // rows of the pair's tile
 constexpr int PN = 256;                 // columns of the pair's tile
-constexpr int PSTAGES = 6;
+constexpr int PSTAGES = 4;               // even (see the one-SM kernel); leaves room for a whole output tile
 constexpr int PA_BYTES = 128 * BK;      // A rows of this CTA: 16 KiB
 constexpr int PB_BYTES = 128 * BK;      // B columns of this CTA: 16 KiB
 constexpr int PTHREADS = 11 * 32;
-// dynamic shared memory: operand stages | two 16 KiB output slots (TMA-store boxes; also the 2 KiB-per-warp staging of
-// the non-TMA path) | 256 B of barriers and flags, plus 1 KiB of slack to align the stages to 1024 bytes
+// dynamic shared memory: operand stages | four 16 KiB output slots = the CTA's whole 128 x 256 tile of a 2-byte type
+// (TMA-store boxes; also the 2 KiB-per-warp staging of the non-TMA path) | 256 B of barriers and flags, plus 1 KiB of
+// slack to align the stages to 1024 bytes
 constexpr int PSTAGE_OFF = PSTAGES * (PA_BYTES + PB_BYTES);
-constexpr size_t PSMEM_BYTES = (size_t)PSTAGE_OFF + C_STAGE_BYTES + 256 + 1024;
+constexpr int PC_BYTES = 4 * C_SLOT_BYTES;
+constexpr size_t PSMEM_BYTES = (size_t)PSTAGE_OFF + PC_BYTES + 256 + 1024;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -100,7 +102,7 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + PSTAGES * PA_BYTES;
     uint8_t* c_stage = smem + PSTAGE_OFF;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(c_stage + C_STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(c_stage + PC_BYTES);
     // [0, S) full (used in the leader), [S, 2S) empty, [2S, 2S+2) tmem full, [2S+2, 2S+4) tmem empty (leader)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * PSTAGES + 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -238,38 +240,37 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             }
             constexpr bool TMA_OUT = (OUT == CINN_BF16 || OUT == CINN_F16);
             if (TMA_OUT && alive && p.tma_out) {
-                // as in the one-SM kernel: each column group of four promotion warps stages 64 columns of its rows
-                // in its own 16 KiB slot and one thread hands the box to the TMA unit, twice per tile
+                // The whole tile has room in shared memory here: each column group of four promotion warps drops its
+                // 128 columns into its two 16 KiB slots (16-byte chunks, 128-byte swizzle) and one thread hands both
+                // boxes to the TMA unit; nobody waits for the unit until the next tile is ready to be staged.
                 const bool elected = (warp == h * 4) && lane == 0;
-                const uint32_t slot = smem_u32(c_stage) + h * C_SLOT_BYTES;
+                const uint32_t slot = smem_u32(c_stage) + h * 2 * C_SLOT_BYTES;
                 const int rl = q * 32 + lane;
+                const uint32_t par = n_rounds & 1u;
+                if (elected) tma_store_wait_read();                   // the previous tile has left the slots
+                __syncwarp();
+                if (lane == 0) mbar_arrive(gfree0 + 8 * h);
+                if (!mbar_wait_warp(gfree0 + 8 * h, par, abort_flag, (3 << 8) | 2)) { alive = false; break; }
 #pragma unroll
-                for (int r = 0; r < 2; ++r) {
-                    const uint32_t par = n_rounds & 1u;
-                    if (elected) tma_store_wait_read();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(gfree0 + 8 * h);
-                    if (!mbar_wait_warp(gfree0 + 8 * h, par, abort_flag, (3 << 8) | 2)) { alive = false; break; }
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const uint4 v = pack16<OUT>(&acc[r * 64 + j * 8]);
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(slot + rl * 128 + ((j ^ (rl & 7)) << 4)),
-                                     "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-                    }
-                    fence_async_smem();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(gfull0 + 8 * h);
-                    if (elected) {
-                        const int col = col0 + r * 64;
-                        if (mbar_wait(gfull0 + 8 * h, par, abort_flag, (3 << 8) | 3)) {
-                            if (col < p.N) tma_store_2d(&tmC, slot, col, ti.m0 + 128 * (int)rank);
-                            tma_store_commit();
-                        }
-                    }
-                    __syncwarp();
-                    ++n_rounds;
+                for (int j = 0; j < 16; ++j) {
+                    const uint4 v = pack16<OUT>(&acc[j * 8]);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                 ::"r"(slot + (j >> 3) * C_SLOT_BYTES + rl * 128 + (((j & 7) ^ (rl & 7)) << 4)),
+                                   "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
                 }
-                if (!alive) break;
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(gfull0 + 8 * h);
+                if (elected) {
+                    if (mbar_wait(gfull0 + 8 * h, par, abort_flag, (3 << 8) | 3)) {
+#pragma unroll
+                        for (int r = 0; r < 2; ++r)
+                            if (col0 + r * 64 < p.N) tma_store_2d(&tmC, slot + r * C_SLOT_BYTES, col0 + r * 64, ti.m0 + 128 * (int)rank);
+                        tma_store_commit();
+                    }
+                }
+                __syncwarp();       // the elected lane rejoins its warp before the next warp-collective instruction
+                ++n_rounds;
             } else if (alive && vec_ok) {
                 if (cvalid) store_rows_staged<OUT, 128>(acc, store_stage + warp * 2048, p.C, p.ldc, ti.m0 + 128 * (int)rank + q * 32,
                                                         p.M, col0, p.N, lane);
