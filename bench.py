@@ -212,6 +212,8 @@ def bench_kernels(Kmod, dev, x, w, dy, peaks):
     quant_line("quant_row_vec dy[16384,18432] bf16", lambda: Kmod.quantize_fp8_rowwise(dy), M * N * 3 + 4 * M * nnb)
     quant_line("quant_row_transposed dy^T (tiles along tokens)", lambda: Kmod.quantize_fp8_rowwise(dy.t()),
                M * N * 3 + 4 * N * (M // 128))
+    quant_line("quant_row_dual dy (tiles along features + tiles along tokens, one pass)",
+               lambda: Kmod.quantize_fp8_rowwise_dual(dy), M * N * 4 + 4 * (M * nnb + N * (M // 128)))
     quant_line("quant_block_vec W[18432,7168] fp32", lambda: Kmod.quantize_fp8_blockwise(wd), N * K * 5 + 4 * nnb * nkb)
     xq, xs = Kmod.quantize_fp8_rowwise(xd)
     quant_line("requant_row_to_block x e4m3", lambda: Kmod.requantize_rowwise_to_blockwise(xq, xs),

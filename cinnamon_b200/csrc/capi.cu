@@ -30,6 +30,8 @@ int sm_count() {
 
 int quantize(bool blockwise, const void* x, int dtype, int64_t M, int64_t N, int64_t ld_m, int64_t ld_n, void* q,
              float* scales, int bm, int bn, int round_scale, int div_mode, cudaStream_t st);
+int quantize_dual(const void* x, int dtype, int64_t M, int64_t N, int64_t ld, void* q_row, float* s_row, void* q_col,
+                  float* s_col, int round_scale, int div_mode, cudaStream_t st);
 int requant_row_to_block(const void* xq, const float* xs, int64_t M, int64_t K, void* out, float* scales,
                          int transpose_out, int div_mode, cudaStream_t st);
 int dequantize(const void* q, const float* scales, void* out, int out_dtype, int64_t M, int64_t N, int bm, int bn,
@@ -68,6 +70,11 @@ int cinn_quant_blockwise(const void* x, int x_dtype, int64_t M, int64_t N, int64
                          float* scales, int block_m, int block_n, int round_scale, int div_mode, void* stream) {
     return cinn::quantize(true, x, x_dtype, M, N, ld_m, ld_n, q, scales, block_m, block_n, round_scale, div_mode,
                           (cudaStream_t)stream);
+}
+
+int cinn_quant_rowwise_dual(const void* x, int x_dtype, int64_t M, int64_t N, int64_t ld, void* q_row, float* s_row,
+                            void* q_col, float* s_col, int round_scale, int div_mode, void* stream) {
+    return cinn::quantize_dual(x, x_dtype, M, N, ld, q_row, s_row, q_col, s_col, round_scale, div_mode, (cudaStream_t)stream);
 }
 
 int cinn_requant_row_to_block(const void* xq, const float* xs, int64_t M, int64_t K, void* out, float* scales,

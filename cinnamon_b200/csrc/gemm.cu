@@ -14,6 +14,7 @@
 // Every wait is bounded: when one runs out the kernel records a code in a device status
 // word, every role leaves its loop, TMEM is freed and the kernel returns.
 #include "common.cuh"
+#include "tma.cuh"
 #include <cuda.h>
 #include <mutex>
 #include <cstdlib>
@@ -49,29 +50,8 @@ struct GemmParams {
 };
 
 // ---------------------------------------------------------------------------
-// PTX wrappers
+// bounded waits
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;   // about two seconds
 
 // Bounded wait.  Returns false when the kernel is being abandoned.
@@ -97,22 +77,6 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
     const bool ok = mbar_wait(bar, parity, abort_flag, code);
     return __all_sync(0xffffffffu, ok);
 }
-
-__device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint32_t bar, uint32_t dst, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-
-// TMA store of one box from shared memory (bulk async-group completion)
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                 ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // fp32 load through the read-only path, pinned in program order
 __device__ __forceinline__ float ld_scale(const float* p) {
@@ -600,24 +564,35 @@ static EncodeFn get_encode() {
     return fn;
 }
 
-// 2-D tensor: inner extent `inner` elements (contiguous), `rows` rows of pitch `pitch` BYTES
-static int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows, uint64_t pitch, uint32_t box_inner,
-                    uint32_t box_rows, CUtensorMapDataType dtype = CU_TENSOR_MAP_DATA_TYPE_UINT8) {
+int encode_map_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows, uint64_t pitch_bytes,
+                  uint32_t box_inner, uint32_t box_rows, CUtensorMapDataType dtype, CUtensorMapSwizzle swizzle) {
     EncodeFn enc = get_encode();
     if (!enc) { set_error("cuTensorMapEncodeTiled is not available from the CUDA driver"); return CINN_ERR_CUDA; }
     cuuint64_t dims[2] = {inner, rows};
-    cuuint64_t strides[1] = {pitch};
+    cuuint64_t strides[1] = {pitch_bytes};
     cuuint32_t box[2] = {box_inner, box_rows};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = enc(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_ERROR_INVALID_CONTEXT || r == CUDA_ERROR_NOT_INITIALIZED) {
+        // a thread that has made no runtime call yet (an autograd worker, say) has no context bound:
+        // let the runtime bind the device's primary context, then encode again
+        cudaFree(nullptr);
+        r = enc(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
     if (r != CUDA_SUCCESS) {
         set_error("cuTensorMapEncodeTiled failed with CUresult %d (base %p inner %llu rows %llu pitch %llu)", (int)r, base,
-                  (unsigned long long)inner, (unsigned long long)rows, (unsigned long long)pitch);
+                  (unsigned long long)inner, (unsigned long long)rows, (unsigned long long)pitch_bytes);
         return CINN_ERR_CUDA;
     }
     return CINN_OK;
+}
+
+// GEMM operands and outputs: 128-byte swizzle; `pitch` in BYTES
+static int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows, uint64_t pitch, uint32_t box_inner,
+                    uint32_t box_rows, CUtensorMapDataType dtype = CU_TENSOR_MAP_DATA_TYPE_UINT8) {
+    return encode_map_2d(map, base, inner, rows, pitch, box_inner, box_rows, dtype, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 static size_t smem_bytes(int E) {
@@ -820,14 +795,19 @@ int fp8_grouped_gemm_dgrad(const void* dY, const float* sdY, const void* W, cons
     return launch_out<true, true>(ta, tb, p, out_dtype, sm_count(), st);
 }
 
+int read_quant_status(int* out, int reset);
+
+// One word for the caller: the GEMM's code if it has one, else the quantisers'.
 int read_device_status(int* out, int reset) {
-    int v = 0;
+    int v = 0, q = 0;
     CINN_CHECK_CUDA(cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)));
     if (reset && v != 0) {
         int z = 0;
         CINN_CHECK_CUDA(cudaMemcpyToSymbol(g_device_status, &z, sizeof(int)));
     }
-    *out = v;
+    int rc = read_quant_status(&q, reset);
+    if (rc) return rc;
+    *out = v != 0 ? v : q;
     return CINN_OK;
 }
 

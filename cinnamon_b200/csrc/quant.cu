@@ -10,7 +10,9 @@
 // Layout: every kernel moves 16-byte vectors per lane where alignment allows,
 // reduces amax with warp shuffles, and writes packed e4m3 (4-16 bytes per lane).
 #include "common.cuh"
+#include "tma.cuh"
 #include <type_traits>
+#include <mutex>
 
 namespace cinn {
 
@@ -283,6 +285,206 @@ quant_row_transposed_kernel(const T* __restrict__ x, int64_t L, uint8_t* __restr
                 __stcs(reinterpret_cast<uint4*>(q + (int64_t)mm * N + n), val);
             }
         }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Both 1x128 quantisations of one matrix in a single pass: tiles along n (what the input
+// gradient needs, src/kernels.py:771) and tiles along m of the transpose (what the weight
+// gradient needs, src/kernels.py:781-783).  One CTA holds a 128 x 128 piece in registers:
+// thread (hw, sub) keeps rows hw*8 .. +7 and columns sub*8 .. +7, so a row tile is reduced
+// inside a half-warp and a column tile across the 16 half-warps (one shuffle + shared memory).
+// The transposed bytes leave through a 16 KiB staging tile whose 16-byte chunks are XOR-ed
+// with (n / 8) so that the 8-byte stores of a warp spread over all banks.
+// ---------------------------------------------------------------------------
+// One 128 x 128 piece held as v[i][j] = x[mt + i][n + j].  `ok` is this thread's verdict on its input (a
+// bounded wait that ran out makes it false); the CTA leaves together when any thread says so.  `after_sync`
+// runs once every thread has taken its input out of shared memory.
+template <int DIV, bool ROUND, typename AfterSync>
+__device__ __forceinline__ bool dual_tile(float (&v)[8][8], float (*s_amax)[128], uint8_t* s_out, bool ok,
+                                          uint8_t* __restrict__ q_row, float* __restrict__ s_row,
+                                          uint8_t* __restrict__ q_col, float* __restrict__ s_col, int M, int N, int nb_n,
+                                          int nb_m, int bm, int bn, AfterSync&& after_sync) {
+    const int sub = threadIdx.x & 15, hw = threadIdx.x >> 4, warp = threadIdx.x >> 5;
+    const int m0 = bm * 128, n0 = bn * 128;
+    const int n = n0 + sub * 8;
+    const int mt = m0 + hw * 8;
+
+    // column tiles first: their reduction needs the barrier, the row tiles fill the wait
+    float cam[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        float a = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a = fmaxf(a, fabsf(v[i][j]));
+        cam[j] = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 16));
+    }
+    if ((threadIdx.x & 31) < 16) {
+        *reinterpret_cast<float4*>(&s_amax[warp][sub * 8]) = make_float4(cam[0], cam[1], cam[2], cam[3]);
+        *reinterpret_cast<float4*>(&s_amax[warp][sub * 8 + 4]) = make_float4(cam[4], cam[5], cam[6], cam[7]);
+    }
+    if (!__syncthreads_and(ok)) return false;
+    after_sync();
+
+    // row tiles: amax inside the half-warp, bytes straight to global memory
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float a = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a = fmaxf(a, fabsf(v[i][j]));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+        const float s = scale_from_amax<DIV, ROUND>(a);
+        if (mt + i < M && n < N) {
+            uint2 o2;
+            o2.x = cvt_e4m3x4(scaled_clamped<DIV>(v[i][0], s), scaled_clamped<DIV>(v[i][1], s),
+                              scaled_clamped<DIV>(v[i][2], s), scaled_clamped<DIV>(v[i][3], s));
+            o2.y = cvt_e4m3x4(scaled_clamped<DIV>(v[i][4], s), scaled_clamped<DIV>(v[i][5], s),
+                              scaled_clamped<DIV>(v[i][6], s), scaled_clamped<DIV>(v[i][7], s));
+            __stcs(reinterpret_cast<uint2*>(q_row + (int64_t)(mt + i) * N + n), o2);
+            if (sub == 0) s_row[(int64_t)(mt + i) * nb_n + bn] = s;
+        }
+    }
+
+    // column tiles: every half-warp derives the same 8 scales for its columns
+    float sc[8];
+    {
+        float4 lo = *reinterpret_cast<const float4*>(&s_amax[0][sub * 8]);
+        float4 hi = *reinterpret_cast<const float4*>(&s_amax[0][sub * 8 + 4]);
+#pragma unroll
+        for (int w = 1; w < 8; ++w) {
+            const float4 a = *reinterpret_cast<const float4*>(&s_amax[w][sub * 8]);
+            const float4 b = *reinterpret_cast<const float4*>(&s_amax[w][sub * 8 + 4]);
+            lo.x = fmaxf(lo.x, a.x); lo.y = fmaxf(lo.y, a.y); lo.z = fmaxf(lo.z, a.z); lo.w = fmaxf(lo.w, a.w);
+            hi.x = fmaxf(hi.x, b.x); hi.y = fmaxf(hi.y, b.y); hi.z = fmaxf(hi.z, b.z); hi.w = fmaxf(hi.w, b.w);
+        }
+        const float am[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sc[j] = scale_from_amax<DIV, ROUND>(am[j]);
+    }
+    if (hw == 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (n + j < N) s_col[(int64_t)(n + j) * nb_m + bm] = sc[j];
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        uint2 o2;
+        o2.x = cvt_e4m3x4(scaled_clamped<DIV>(v[0][j], sc[j]), scaled_clamped<DIV>(v[1][j], sc[j]),
+                          scaled_clamped<DIV>(v[2][j], sc[j]), scaled_clamped<DIV>(v[3][j], sc[j]));
+        o2.y = cvt_e4m3x4(scaled_clamped<DIV>(v[4][j], sc[j]), scaled_clamped<DIV>(v[5][j], sc[j]),
+                          scaled_clamped<DIV>(v[6][j], sc[j]), scaled_clamped<DIV>(v[7][j], sc[j]));
+        const int nl = sub * 8 + j;
+        *reinterpret_cast<uint2*>(&s_out[nl * 128 + ((((hw >> 1) ^ sub) & 7) << 4) + ((hw & 1) << 3)]) = o2;
+    }
+    __syncthreads();
+    // 128 transposed rows x 8 chunks of 16 bytes (16 consecutive m)
+#pragma unroll
+    for (int rep = 0; rep < 4; ++rep) {
+        const int idx = threadIdx.x + rep * 256;
+        const int nl = idx >> 3, ch = idx & 7;
+        const int nn = n0 + nl, mm = m0 + ch * 16;
+        if (nn < N && mm < M) {
+            const uint4 val = *reinterpret_cast<const uint4*>(&s_out[nl * 128 + (((ch ^ (nl >> 3)) & 7) << 4)]);
+            __stcs(reinterpret_cast<uint4*>(q_col + (int64_t)nn * M + mm), val);
+        }
+    }
+    return true;
+}
+
+// One CTA per piece, loads straight into registers (4-byte inputs, and rows whose pitch a tensor map cannot take).
+template <typename T, int DIV, bool ROUND>
+__global__ void __launch_bounds__(256, 2)
+quant_row_dual_kernel(const T* __restrict__ x, int64_t ld, uint8_t* __restrict__ q_row, float* __restrict__ s_row,
+                      uint8_t* __restrict__ q_col, float* __restrict__ s_col, int M, int N, int nb_n, int nb_m) {
+    __shared__ __align__(16) float s_amax[8][128];
+    __shared__ __align__(16) uint8_t s_out[128 * 128];
+    const int sub = threadIdx.x & 15, hw = threadIdx.x >> 4;
+    const int n = blockIdx.x * 128 + sub * 8;
+    const int mt = blockIdx.y * 128 + hw * 8;
+    Raw8<T> raw[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        raw[i] = (mt + i < M && n < N) ? load_raw8<T>(x + (int64_t)(mt + i) * ld + n) : zero_raw8<T>();
+    float v[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) unpack_raw8<T>(raw[i], v[i]);
+    dual_tile<DIV, ROUND>(v, s_amax, s_out, true, q_row, s_row, q_col, s_col, M, N, nb_n, nb_m, (int)blockIdx.y,
+                          (int)blockIdx.x, [] {});
+}
+
+// Persistent CTAs fed by TMA (2-byte inputs): the 128 x 128 pieces arrive in a ring of shared-memory stages
+// (out-of-range elements arrive as zeros, which is the reference's mask), so the loads of the next pieces are
+// in flight while this one is converted.  A stage is handed back to the TMA unit right after every thread has
+// copied its part into registers.
+constexpr int DUAL_STAGES = 2;
+constexpr int DUAL_STAGE_BYTES = 128 * 128 * 2;
+constexpr int DUAL_SMEM_BYTES = DUAL_STAGES * DUAL_STAGE_BYTES + 128 * 128 + 8 * 128 * 4 + 64;
+constexpr long long QUANT_WAIT_LIMIT_CYCLES = 4000000000LL;   // about two seconds
+
+__device__ int g_quant_status = 0;     // 0 = fine, otherwise (4 << 8) | reason
+
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t spin = 1;; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 255u) == 0 && clock64() - t0 > QUANT_WAIT_LIMIT_CYCLES) return false;
+    }
+}
+
+template <typename T, int DIV, bool ROUND>
+__global__ void __launch_bounds__(256, 2)
+quant_row_dual_tma_kernel(const __grid_constant__ CUtensorMap tmX, uint8_t* __restrict__ q_row, float* __restrict__ s_row,
+                          uint8_t* __restrict__ q_col, float* __restrict__ s_col, int M, int N, int nb_n, int nb_m,
+                          int total) {
+    static_assert(sizeof(T) == 2, "the TMA-fed path takes 2-byte inputs");
+    extern __shared__ __align__(128) uint8_t dsm[];
+    uint8_t* stages = dsm;
+    uint8_t* s_out = dsm + DUAL_STAGES * DUAL_STAGE_BYTES;
+    float (*s_amax)[128] = reinterpret_cast<float (*)[128]>(s_out + 128 * 128);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_out + 128 * 128 + 8 * 128 * 4);
+    const uint32_t full0 = smem_u32(bars);
+    const int sub = threadIdx.x & 15, hw = threadIdx.x >> 4;
+    const int stride = gridDim.x;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < DUAL_STAGES; ++s) mbar_init(full0 + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    auto issue = [&](int t, int s) {                     // one elected thread
+        mbar_expect_tx(full0 + 8 * s, DUAL_STAGE_BYTES);
+        tma_load_2d(&tmX, full0 + 8 * s, smem_u32(stages + s * DUAL_STAGE_BYTES), (t % nb_n) * 128, (t / nb_n) * 128);
+    };
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < DUAL_STAGES; ++s)
+            if ((int)blockIdx.x + s * stride < total) issue(blockIdx.x + s * stride, s);
+    }
+    int k = 0;
+    int t = blockIdx.x;
+    bool alive = true;
+    for (; t < total; t += stride, ++k) {
+        const int s = k % DUAL_STAGES;
+        const bool ok = mbar_wait_bounded(full0 + 8 * s, (k / DUAL_STAGES) & 1);
+        const uint8_t* src = stages + s * DUAL_STAGE_BYTES + (hw * 8) * 256 + sub * 16;
+        float v[8][8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            Raw8<T> r;
+            r.a = *reinterpret_cast<const uint4*>(src + i * 256);
+            unpack_raw8<T>(r, v[i]);
+        }
+        const int tn = t + DUAL_STAGES * stride;
+        alive = dual_tile<DIV, ROUND>(v, s_amax, s_out, ok, q_row, s_row, q_col, s_col, M, N, nb_n, nb_m, t / nb_n, t % nb_n,
+                                      [&] { if (threadIdx.x == 0 && tn < total) issue(tn, s); });
+        if (!alive) break;
+    }
+    if (!alive && threadIdx.x == 0) {
+        atomicCAS(&g_quant_status, 0, (4 << 8) | 1);
+        // loads still in flight target this CTA's shared memory: give them their (bounded) time before leaving
+        for (int j = 1; j < DUAL_STAGES; ++j)
+            if (t + j * stride < total) mbar_wait_bounded(full0 + 8 * ((k + j) % DUAL_STAGES), ((k + j) / DUAL_STAGES) & 1);
     }
 }
 
@@ -617,6 +819,79 @@ int quantize(bool blockwise, const void* x, int dtype, int64_t M, int64_t N, int
         case CINN_F16:  return dispatch_quant(blockwise, (const __half*)x, M, N, ld_m, ld_n, (uint8_t*)q, scales, bm, bn, round_scale, div_mode, st);
         case CINN_F32:  return dispatch_quant(blockwise, (const float*)x, M, N, ld_m, ld_n, (uint8_t*)q, scales, bm, bn, round_scale, div_mode, st);
         default: set_error("quantise: unknown dtype tag %d", dtype); return CINN_ERR_INVALID;
+    }
+}
+
+template <typename T>
+static int dispatch_dual(const T* x, int64_t M, int64_t N, int64_t ld, uint8_t* q_row, float* s_row, uint8_t* q_col,
+                         float* s_col, int round_scale, int div_mode, cudaStream_t st) {
+    const int nb_n = (int)((N + 127) / 128), nb_m = (int)((M + 127) / 128);
+    const bool fused = M % 16 == 0 && N % 8 == 0 && ld % 8 == 0 && nb_m <= 65535 && aligned16(x) && aligned16(q_row) &&
+                       aligned16(q_col);
+    if (!fused) {
+        // ragged shapes: the two single-output quantisers, reading x twice
+        int rc = dispatch_quant(false, x, M, N, ld, (int64_t)1, q_row, s_row, 1, 128, round_scale, div_mode, st);
+        if (rc) return rc;
+        return dispatch_quant(false, x, N, M, (int64_t)1, ld, q_col, s_col, 1, 128, round_scale, div_mode, st);
+    }
+    if constexpr (sizeof(T) == 2) {
+        // 2-byte inputs: persistent CTAs fed by TMA
+        CUtensorMap tm;
+        int rc = encode_map_2d(&tm, x, (uint64_t)N, (uint64_t)M, (uint64_t)ld * 2, 128, 128, CU_TENSOR_MAP_DATA_TYPE_UINT16,
+                               CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc) return rc;
+        const int64_t total = (int64_t)nb_n * nb_m;
+        CINN_CHECK_ARG(total < (1LL << 31), "dual quantiser: too many tiles");
+        const int grid = (int)(total < 2 * (int64_t)sm_count() ? total : 2 * (int64_t)sm_count());
+#define CINN_D(DIV, RND)                                                                                              \
+    do {                                                                                                              \
+        auto kern = quant_row_dual_tma_kernel<T, DIV, RND>;                                                           \
+        static std::once_flag once;                                                                                   \
+        static cudaError_t attr_err = cudaSuccess;                                                                    \
+        std::call_once(once, [&] {                                                                                    \
+            attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);      \
+        });                                                                                                           \
+        CINN_CHECK_CUDA(attr_err);                                                                                    \
+        kern<<<grid, 256, DUAL_SMEM_BYTES, st>>>(tm, q_row, s_row, q_col, s_col, (int)M, (int)N, nb_n, nb_m, (int)total); \
+    } while (0)
+        if (div_mode == CINN_DIV_FULL) { if (round_scale) CINN_D(CINN_DIV_FULL, true); else CINN_D(CINN_DIV_FULL, false); }
+        else                           { if (round_scale) CINN_D(CINN_DIV_RN, true);   else CINN_D(CINN_DIV_RN, false); }
+#undef CINN_D
+    } else {
+        dim3 grid((unsigned)nb_n, (unsigned)nb_m);
+#define CINN_D(DIV, RND) quant_row_dual_kernel<T, DIV, RND><<<grid, 256, 0, st>>>(x, ld, q_row, s_row, q_col, s_col, (int)M, (int)N, nb_n, nb_m)
+        if (div_mode == CINN_DIV_FULL) { if (round_scale) CINN_D(CINN_DIV_FULL, true); else CINN_D(CINN_DIV_FULL, false); }
+        else                           { if (round_scale) CINN_D(CINN_DIV_RN, true);   else CINN_D(CINN_DIV_RN, false); }
+#undef CINN_D
+    }
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+int read_quant_status(int* out, int reset) {
+    int v = 0;
+    CINN_CHECK_CUDA(cudaMemcpyFromSymbol(&v, g_quant_status, sizeof(int)));
+    if (reset && v != 0) {
+        int z = 0;
+        CINN_CHECK_CUDA(cudaMemcpyToSymbol(g_quant_status, &z, sizeof(int)));
+    }
+    *out = v;
+    return CINN_OK;
+}
+
+int quantize_dual(const void* x, int dtype, int64_t M, int64_t N, int64_t ld, void* q_row, float* s_row, void* q_col,
+                  float* s_col, int round_scale, int div_mode, cudaStream_t st) {
+    CINN_CHECK_ARG(M >= 0 && N >= 0, "dual quantiser: negative shape (%lld, %lld)", (long long)M, (long long)N);
+    if (M == 0 || N == 0) return CINN_OK;
+    CINN_CHECK_ARG(x && q_row && s_row && q_col && s_col, "dual quantiser: null pointer");
+    CINN_CHECK_ARG(N < (1LL << 31) && M < (1LL << 31), "dual quantiser: dimension too large");
+    CINN_CHECK_ARG(ld >= N, "dual quantiser: row pitch %lld below the row length %lld", (long long)ld, (long long)N);
+    CINN_CHECK_ARG(div_mode == CINN_DIV_FULL || div_mode == CINN_DIV_RN, "dual quantiser: unknown div_mode %d", div_mode);
+    switch (dtype) {
+        case CINN_BF16: return dispatch_dual((const __nv_bfloat16*)x, M, N, ld, (uint8_t*)q_row, s_row, (uint8_t*)q_col, s_col, round_scale, div_mode, st);
+        case CINN_F16:  return dispatch_dual((const __half*)x, M, N, ld, (uint8_t*)q_row, s_row, (uint8_t*)q_col, s_col, round_scale, div_mode, st);
+        case CINN_F32:  return dispatch_dual((const float*)x, M, N, ld, (uint8_t*)q_row, s_row, (uint8_t*)q_col, s_col, round_scale, div_mode, st);
+        default: set_error("dual quantiser: unknown dtype tag %d", dtype); return CINN_ERR_INVALID;
     }
 }
 

@@ -105,6 +105,29 @@ def quantize_fp8_rowwise(x: torch.Tensor, block_size: int = 128, round_scale: bo
     return q, s
 
 
+def quantize_fp8_rowwise_dual(x: torch.Tensor, round_scale: bool = False):
+    """``quantize_fp8_rowwise(x)`` and ``quantize_fp8_rowwise(x.t())`` (1 x 128 tiles) from one pass over
+    ``x``: the two quantisations of the output gradient in ``FP8MatmulFunction.backward`` (reference
+    src/kernels.py:771 and :781-783).  Returns ``(q_row, s_row, q_col, s_col)`` with ``q_row`` (M, N),
+    ``q_col`` (N, M); bit-identical to the two separate calls."""
+    assert x.is_cuda, "Input must be on CUDA"
+    assert x.ndim == 2, "Input must be 2D for now"
+    x = _as_quant_input(x)
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    M, N = x.shape
+    with torch.cuda.device(x.device):
+        q_row = torch.empty((M, N), dtype=torch.float8_e4m3fn, device=x.device)
+        s_row = torch.empty((M, (N + 127) // 128), dtype=torch.float32, device=x.device)
+        q_col = torch.empty((N, M), dtype=torch.float8_e4m3fn, device=x.device)
+        s_col = torch.empty((N, (M + 127) // 128), dtype=torch.float32, device=x.device)
+        _lib.check(_L.cinn_quant_rowwise_dual(_ptr(x), _DTYPE_TAG[x.dtype], M, N, x.stride(0), _ptr(q_row), _ptr(s_row),
+                                              _ptr(q_col), _ptr(s_col), int(bool(round_scale)), _DIV_MODE, _stream(x)),
+                   "cinn_quant_rowwise_dual")
+    _count()
+    return q_row, s_row, q_col, s_col
+
+
 def quantize_fp8_blockwise(x: torch.Tensor, block_m: int = 128, block_n: int = 128, round_scale: bool = False):
     """Block-wise block_m x block_n quantisation (reference src/kernels.py:219-259).
 
@@ -273,19 +296,19 @@ class FP8MatmulFunction(torch.autograd.Function):
         if grad_flat.stride(1) != 1:
             grad_flat = grad_flat.contiguous()
         M = grad_flat.shape[0]
-        # dgrad (:771-774): dy (M, N) @ W (N, K); W is the B operand stored (reduction, output)
-        grad_fp8, grad_scale = quantize_fp8_rowwise(grad_flat, block_size=128, round_scale=round_scale)
-        grad_x = _gemm(grad_fp8, grad_scale, w_fp8, _lib.B_KN, w_scale, w_scale.stride(0), w_scale.stride(1), M, K, N,
-                       torch.bfloat16)
-        # wgrad (:781-788): dy^T quantised along tokens, x re-quantised in 128x128 blocks.
-        # The token axis is the reduction axis here; the GEMM wants it in multiples of 16, so a
-        # ragged token count is padded with zero rows (they change neither an amax nor a sum).
+        # The token axis is the reduction axis of the weight gradient; the GEMM wants it in multiples
+        # of 16, so a ragged token count is padded with zero rows (they change neither an amax nor a sum).
         Mp = (M + 15) // 16 * 16
         if Mp != M:
             grad_flat = torch.nn.functional.pad(grad_flat, (0, 0, 0, Mp - M))
             x_fp8 = torch.nn.functional.pad(x_fp8.view(torch.uint8), (0, 0, 0, Mp - M)).view(torch.float8_e4m3fn)
             x_scale = torch.nn.functional.pad(x_scale, (0, 0, 0, Mp - M), value=1.0)
-        grad_fp8_t, grad_scale_t = quantize_fp8_rowwise(grad_flat.t(), block_size=128, round_scale=round_scale)
+        # dy quantised along features for dgrad (:771) and along tokens for wgrad (:781-783), one pass over dy
+        grad_fp8, grad_scale, grad_fp8_t, grad_scale_t = quantize_fp8_rowwise_dual(grad_flat, round_scale=round_scale)
+        # dgrad (:771-774): dy (M, N) @ W (N, K); W is the B operand stored (reduction, output)
+        grad_x = _gemm(grad_fp8, grad_scale, w_fp8, _lib.B_KN, w_scale, w_scale.stride(0), w_scale.stride(1), M, K, N,
+                       torch.bfloat16)
+        # wgrad (:781-788): x re-quantised in 128x128 blocks
         x_fp8_block, x_scale_block = requantize_rowwise_to_blockwise(x_fp8, x_scale)
         # the reference returns a bf16 grad_weight which autograd then casts to the fp32 master
         # weight's dtype (:788, :794); the GEMM writes those same values as fp32 directly

@@ -52,6 +52,14 @@ const char* cinn_last_error(void);
 int cinn_quant_rowwise(const void* x, int x_dtype, int64_t M, int64_t N, int64_t ld_m, int64_t ld_n,
                        void* q, float* scales, int block_size, int round_scale, int div_mode, void* stream);
 
+/* Both 1 x 128 quantisations of one (M, N) matrix with contiguous rows of pitch ld, in one pass over it:
+ *   q_row (M, N), s_row (M, ceil(N/128)): tiles along N, as cinn_quant_rowwise(x);
+ *   q_col (N, M), s_col (N, ceil(M/128)): tiles along M of the transpose, as cinn_quant_rowwise(x^T).
+ * Replaces the two quantize_fp8_rowwise calls of FP8MatmulFunction.backward on grad_flat and on
+ * grad_flat.t() (src/kernels.py:771 and :781-783); the results are bit-identical to those two calls. */
+int cinn_quant_rowwise_dual(const void* x, int x_dtype, int64_t M, int64_t N, int64_t ld, void* q_row, float* s_row,
+                            void* q_col, float* s_col, int round_scale, int div_mode, void* stream);
+
 /* Block-wise block_m x block_n quantisation.
  * Replaces quantize_fp8_blockwise_kernel + quantize_fp8_blockwise (src/kernels.py:74-132, 219-259).
  * scales: (ceil(M/block_m), ceil(N/block_n)). */

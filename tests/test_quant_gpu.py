@@ -66,6 +66,38 @@ def test_transposed_view_ragged(K):
     assert_quant_equal(q, s, *O.quantize_rowwise(base.t().contiguous(), 128, True), what="ragged transposed 272")
 
 
+@pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
+@pytest.mark.parametrize("rs", [False, True])
+def test_dual_rowwise_bit_exact(K, case, rs):
+    """One pass, two quantisations: tiles along the columns and tiles along the rows of the transpose."""
+    name, seed, M, N, dtype, std, special = case
+    x = gen_input(seed, M, N, dtype, std, special)
+    q_row, s_row, q_col, s_col = K.quantize_fp8_rowwise_dual(x.cuda(), rs)
+    assert q_col.shape == (N, M) and s_col.shape == (N, (M + 127) // 128)
+    assert_quant_equal(q_row, s_row, *O.quantize_rowwise(x, 128, rs), what=name + " rows")
+    assert_quant_equal(q_col, s_col, *O.quantize_rowwise(x.t().contiguous(), 128, rs), what=name + " columns")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("shape", [(256, 384), (144, 136), (16, 8), (400, 1000), (130, 264), (77, 200)])
+def test_dual_rowwise_shapes(K, dtype, shape):
+    """Fused path (rows a multiple of 16, columns of 8) and the ragged fallback, on a pitched view too."""
+    M, N = shape
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    base = (torch.randn(M, N + 16, generator=g) * torch.logspace(-3, 2, N + 16)[None, :]).to(dtype)
+    base[M // 2, :] = 0                                               # an all-zero tile: floor 1e-4
+    xc = base.cuda()
+    for what, view, ref in (("contiguous", xc[:, :N].contiguous(), base[:, :N]), ("pitched", xc[:, 8:N + 8], base[:, 8:N + 8])):
+        q_row, s_row, q_col, s_col = K.quantize_fp8_rowwise_dual(view, False)
+        assert_quant_equal(q_row, s_row, *O.quantize_rowwise(ref.contiguous(), 128, False), what=what + " rows")
+        assert_quant_equal(q_col, s_col, *O.quantize_rowwise(ref.t().contiguous(), 128, False), what=what + " columns")
+        # and the same bytes as the two single-output calls
+        q1, s1 = K.quantize_fp8_rowwise(view, 128, False)
+        q2, s2 = K.quantize_fp8_rowwise(view.t(), 128, False)
+        assert torch.equal(q1.view(torch.uint8), q_row.view(torch.uint8)) and torch.equal(s1, s_row)
+        assert torch.equal(q2.view(torch.uint8), q_col.view(torch.uint8)) and torch.equal(s2, s_col)
+
+
 @pytest.mark.parametrize("rs", [False, True])
 def test_every_bf16_amax(K, rs):
     """For bf16 input the scale is a function of the tile's amax alone: sweep every
