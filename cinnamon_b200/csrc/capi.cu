@@ -32,6 +32,7 @@ int quantize(bool blockwise, const void* x, int dtype, int64_t M, int64_t N, int
              float* scales, int bm, int bn, int round_scale, int div_mode, cudaStream_t st);
 int quantize_dual(const void* x, int dtype, int64_t M, int64_t N, int64_t ld, void* q_row, float* s_row, void* q_col,
                   float* s_col, int round_scale, int div_mode, cudaStream_t st);
+int selfcheck_division(unsigned long long* mismatches, cudaStream_t st);
 int requant_row_to_block(const void* xq, const float* xs, int64_t M, int64_t K, void* out, float* scales,
                          int transpose_out, int div_mode, cudaStream_t st);
 int dequantize(const void* q, const float* scales, void* out, int out_dtype, int64_t M, int64_t N, int bm, int bn,
@@ -75,6 +76,10 @@ int cinn_quant_blockwise(const void* x, int x_dtype, int64_t M, int64_t N, int64
 int cinn_quant_rowwise_dual(const void* x, int x_dtype, int64_t M, int64_t N, int64_t ld, void* q_row, float* s_row,
                             void* q_col, float* s_col, int round_scale, int div_mode, void* stream) {
     return cinn::quantize_dual(x, x_dtype, M, N, ld, q_row, s_row, q_col, s_col, round_scale, div_mode, (cudaStream_t)stream);
+}
+
+int cinn_selfcheck_division(unsigned long long* mismatches, void* stream) {
+    return cinn::selfcheck_division(mismatches, (cudaStream_t)stream);
 }
 
 int cinn_requant_row_to_block(const void* xq, const float* xs, int64_t M, int64_t K, void* out, float* scales,

@@ -82,9 +82,28 @@ __device__ __forceinline__ float scale_from_amax(float amax) {
     return s;
 }
 
+// Many elements are divided by one scale.  In the div.full.f32 flavour the quotient x / s is formed as
+// x * rcp.approx(s) with the reciprocal taken once per scale: for every divisor in [2^-126, 2^126] (all scales these
+// kernels produce: the amax has a floor of 1e-4 and is finite) that product has the very bits of
+// div.full.f32(x, s), which cinn_selfcheck_division confirms on the GPU at hand for every 16-bit x and every
+// scale a 16-bit amax can give.  The IEEE flavour divides element by element.
 template <int DIV>
-__device__ __forceinline__ float scaled_clamped(float x, float s) {
-    float y = div_f32<DIV>(x, s);
+__device__ __forceinline__ float divisor_of(float s) {
+    if constexpr (DIV == CINN_DIV_FULL) {
+        float r;
+        asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(s));
+        return r;
+    } else {
+        return s;
+    }
+}
+
+// x / s (d = divisor_of(s)), clamped from below.
+template <int DIV>
+__device__ __forceinline__ float scaled_clamped(float x, float d) {
+    float y;
+    if constexpr (DIV == CINN_DIV_FULL) y = __fmul_rn(x, d);
+    else y = __fdiv_rn(x, d);
     // The reference clamps with max(y, -448) then min(., 448), both dropping a NaN operand.
     // Only the max is kept: it turns NaN into -448 as the reference does; the upper (and lower)
     // clamp is what the saturating e4m3 conversion that always follows does anyway.

@@ -156,9 +156,10 @@ quant_row_vec_kernel(const T* __restrict__ x, int64_t ld, uint8_t* __restrict__ 
 #pragma unroll
             for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
             const float s = scale_from_amax<DIV, ROUND>(amax);
+            const float d = divisor_of<DIV>(s);
             float y[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) y[i] = scaled_clamped<DIV>(v[i], s);
+            for (int i = 0; i < 8; ++i) y[i] = scaled_clamped<DIV>(v[i], d);
             if (off[u] >= 0) {
                 uint2 o2;
                 o2.x = cvt_e4m3x4(y[0], y[1], y[2], y[3]);
@@ -188,8 +189,9 @@ quant_row_generic_kernel(const T* __restrict__ x, int64_t ld_m, int64_t ld_n, ui
         for (int c = c0 + lane; c < c1; c += 32) amax = fmaxf(amax, fabsf(Elem<T>::to_f(x[row * ld_m + c * ld_n])));
         amax = warp_max(amax);
         const float s = scale_from_amax<DIV, ROUND>(amax);
+        const float d = divisor_of<DIV>(s);
         for (int c = c0 + lane; c < c1; c += 32) {
-            const float y = scaled_clamped<DIV>(Elem<T>::to_f(x[row * ld_m + c * ld_n]), s);
+            const float y = scaled_clamped<DIV>(Elem<T>::to_f(x[row * ld_m + c * ld_n]), d);
             q[row * (int64_t)N + c] = (uint8_t)(cvt_e4m3x2(y, 0.0f) & 0xff);
         }
         if (lane == 0) scales[t] = s;
@@ -252,13 +254,14 @@ quant_row_transposed_kernel(const T* __restrict__ x, int64_t L, uint8_t* __restr
             for (int i = 0; i < 8; ++i) s_amax[buf][warp][g * 8 + i] = am[i];
         }
         __syncthreads();                        // (also: everyone is done reading s_out[buf] of two tiles ago)
-        float sc[8];
+        float sc[8], dv[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             float a = 0.0f;
 #pragma unroll
             for (int w = 0; w < 8; ++w) a = fmaxf(a, s_amax[buf][w][g * 8 + i]);
             sc[i] = scale_from_amax<DIV, ROUND>(a);
+            dv[i] = divisor_of<DIV>(sc[i]);
         }
         if (nr == 0) {
 #pragma unroll
@@ -268,8 +271,8 @@ quant_row_transposed_kernel(const T* __restrict__ x, int64_t L, uint8_t* __restr
         // four consecutive n of one logical row -> one 32-bit word
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const uint32_t word = cvt_e4m3x4(scaled_clamped<DIV>(v[0][i], sc[i]), scaled_clamped<DIV>(v[1][i], sc[i]),
-                                             scaled_clamped<DIV>(v[2][i], sc[i]), scaled_clamped<DIV>(v[3][i], sc[i]));
+            const uint32_t word = cvt_e4m3x4(scaled_clamped<DIV>(v[0][i], dv[i]), scaled_clamped<DIV>(v[1][i], dv[i]),
+                                             scaled_clamped<DIV>(v[2][i], dv[i]), scaled_clamped<DIV>(v[3][i], dv[i]));
             const int ml = g * 8 + i;
             s_out[buf][ml * 32 + ((((nr >> 2) ^ g) & 7) << 2) + (nr & 3)] = word;
         }
@@ -335,19 +338,20 @@ __device__ __forceinline__ bool dual_tile(float (&v)[8][8], float (*s_amax)[128]
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
         const float s = scale_from_amax<DIV, ROUND>(a);
+        const float d = divisor_of<DIV>(s);
         if (mt + i < M && n < N) {
             uint2 o2;
-            o2.x = cvt_e4m3x4(scaled_clamped<DIV>(v[i][0], s), scaled_clamped<DIV>(v[i][1], s),
-                              scaled_clamped<DIV>(v[i][2], s), scaled_clamped<DIV>(v[i][3], s));
-            o2.y = cvt_e4m3x4(scaled_clamped<DIV>(v[i][4], s), scaled_clamped<DIV>(v[i][5], s),
-                              scaled_clamped<DIV>(v[i][6], s), scaled_clamped<DIV>(v[i][7], s));
+            o2.x = cvt_e4m3x4(scaled_clamped<DIV>(v[i][0], d), scaled_clamped<DIV>(v[i][1], d),
+                              scaled_clamped<DIV>(v[i][2], d), scaled_clamped<DIV>(v[i][3], d));
+            o2.y = cvt_e4m3x4(scaled_clamped<DIV>(v[i][4], d), scaled_clamped<DIV>(v[i][5], d),
+                              scaled_clamped<DIV>(v[i][6], d), scaled_clamped<DIV>(v[i][7], d));
             __stcs(reinterpret_cast<uint2*>(q_row + (int64_t)(mt + i) * N + n), o2);
             if (sub == 0) s_row[(int64_t)(mt + i) * nb_n + bn] = s;
         }
     }
 
     // column tiles: every half-warp derives the same 8 scales for its columns
-    float sc[8];
+    float sc[8], dv[8];
     {
         float4 lo = *reinterpret_cast<const float4*>(&s_amax[0][sub * 8]);
         float4 hi = *reinterpret_cast<const float4*>(&s_amax[0][sub * 8 + 4]);
@@ -360,7 +364,7 @@ __device__ __forceinline__ bool dual_tile(float (&v)[8][8], float (*s_amax)[128]
         }
         const float am[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
-        for (int j = 0; j < 8; ++j) sc[j] = scale_from_amax<DIV, ROUND>(am[j]);
+        for (int j = 0; j < 8; ++j) { sc[j] = scale_from_amax<DIV, ROUND>(am[j]); dv[j] = divisor_of<DIV>(sc[j]); }
     }
     if (hw == 0) {
 #pragma unroll
@@ -370,10 +374,10 @@ __device__ __forceinline__ bool dual_tile(float (&v)[8][8], float (*s_amax)[128]
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         uint2 o2;
-        o2.x = cvt_e4m3x4(scaled_clamped<DIV>(v[0][j], sc[j]), scaled_clamped<DIV>(v[1][j], sc[j]),
-                          scaled_clamped<DIV>(v[2][j], sc[j]), scaled_clamped<DIV>(v[3][j], sc[j]));
-        o2.y = cvt_e4m3x4(scaled_clamped<DIV>(v[4][j], sc[j]), scaled_clamped<DIV>(v[5][j], sc[j]),
-                          scaled_clamped<DIV>(v[6][j], sc[j]), scaled_clamped<DIV>(v[7][j], sc[j]));
+        o2.x = cvt_e4m3x4(scaled_clamped<DIV>(v[0][j], dv[j]), scaled_clamped<DIV>(v[1][j], dv[j]),
+                          scaled_clamped<DIV>(v[2][j], dv[j]), scaled_clamped<DIV>(v[3][j], dv[j]));
+        o2.y = cvt_e4m3x4(scaled_clamped<DIV>(v[4][j], dv[j]), scaled_clamped<DIV>(v[5][j], dv[j]),
+                          scaled_clamped<DIV>(v[6][j], dv[j]), scaled_clamped<DIV>(v[7][j], dv[j]));
         const int nl = sub * 8 + j;
         *reinterpret_cast<uint2*>(&s_out[nl * 128 + ((((hw >> 1) ^ sub) & 7) << 4) + ((hw & 1) << 3)]) = o2;
     }
@@ -522,13 +526,14 @@ quant_block_vec_kernel(const T* __restrict__ x, int64_t ld, uint8_t* __restrict_
 #pragma unroll
     for (int w = 1; w < 8; ++w) amax = fmaxf(amax, s_red[w]);
     const float s = scale_from_amax<DIV, ROUND>(amax);
+    const float d = divisor_of<DIV>(s);
     if (threadIdx.x == 0) scales[(int64_t)blockIdx.y * nb + blockIdx.x] = s;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
         const int r = r0 + warp + i * 8;
         if (r < M && c < N) {
-            const uint32_t o = cvt_e4m3x4(scaled_clamped<DIV>(v[i][0], s), scaled_clamped<DIV>(v[i][1], s),
-                                          scaled_clamped<DIV>(v[i][2], s), scaled_clamped<DIV>(v[i][3], s));
+            const uint32_t o = cvt_e4m3x4(scaled_clamped<DIV>(v[i][0], d), scaled_clamped<DIV>(v[i][1], d),
+                                          scaled_clamped<DIV>(v[i][2], d), scaled_clamped<DIV>(v[i][3], d));
             *reinterpret_cast<uint32_t*>(q + (int64_t)r * N + c) = o;
         }
     }
@@ -555,10 +560,11 @@ quant_block_generic_kernel(const T* __restrict__ x, int64_t ld_m, int64_t ld_n, 
 #pragma unroll
     for (int w = 1; w < 8; ++w) amax = fmaxf(amax, s_red[w]);
     const float s = scale_from_amax<DIV, ROUND>(amax);
+    const float d = divisor_of<DIV>(s);
     if (threadIdx.x == 0) scales[(int64_t)blockIdx.y * nb + blockIdx.x] = s;
     for (int i = threadIdx.x; i < count; i += 256) {
         const int r = r0 + i / cols, c = c0 + i % cols;
-        const float y = scaled_clamped<DIV>(Elem<T>::to_f(x[(int64_t)r * ld_m + (int64_t)c * ld_n]), s);
+        const float y = scaled_clamped<DIV>(Elem<T>::to_f(x[(int64_t)r * ld_m + (int64_t)c * ld_n]), d);
         q[(int64_t)r * N + c] = (uint8_t)(cvt_e4m3x2(y, 0.0f) & 0xff);
     }
 }
@@ -611,6 +617,7 @@ requant_row_to_block_kernel(const uint8_t* __restrict__ xq, const float* __restr
 #pragma unroll
     for (int w = 1; w < 8; ++w) amax = fmaxf(amax, s_red[w]);
     const float s = scale_from_amax<DIV, false>(amax);
+    const float d = divisor_of<DIV>(s);
     if (threadIdx.x == 0) scales[(int64_t)blockIdx.y * nb + blockIdx.x] = s;
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
@@ -619,8 +626,8 @@ requant_row_to_block_kernel(const uint8_t* __restrict__ xq, const float* __restr
         uint32_t o[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-            o[j] = cvt_e4m3x4(scaled_clamped<DIV>(v[p][4 * j], s), scaled_clamped<DIV>(v[p][4 * j + 1], s),
-                              scaled_clamped<DIV>(v[p][4 * j + 2], s), scaled_clamped<DIV>(v[p][4 * j + 3], s));
+            o[j] = cvt_e4m3x4(scaled_clamped<DIV>(v[p][4 * j], d), scaled_clamped<DIV>(v[p][4 * j + 1], d),
+                              scaled_clamped<DIV>(v[p][4 * j + 2], d), scaled_clamped<DIV>(v[p][4 * j + 3], d));
         if constexpr (!TRANSPOSE_OUT) {
             if (r < M && c < K) *reinterpret_cast<uint4*>(out + (int64_t)r * K + c) = make_uint4(o[0], o[1], o[2], o[3]);
         } else {
@@ -684,10 +691,11 @@ swiglu_quant_row_kernel(const T* __restrict__ h12, uint8_t* __restrict__ q, floa
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
         const float s = scale_from_amax<DIV, false>(amax);
+        const float d = divisor_of<DIV>(s);
         if (inb) {
             uint2 o2;
-            o2.x = cvt_e4m3x4(scaled_clamped<DIV>(v[0], s), scaled_clamped<DIV>(v[1], s), scaled_clamped<DIV>(v[2], s), scaled_clamped<DIV>(v[3], s));
-            o2.y = cvt_e4m3x4(scaled_clamped<DIV>(v[4], s), scaled_clamped<DIV>(v[5], s), scaled_clamped<DIV>(v[6], s), scaled_clamped<DIV>(v[7], s));
+            o2.x = cvt_e4m3x4(scaled_clamped<DIV>(v[0], d), scaled_clamped<DIV>(v[1], d), scaled_clamped<DIV>(v[2], d), scaled_clamped<DIV>(v[3], d));
+            o2.y = cvt_e4m3x4(scaled_clamped<DIV>(v[4], d), scaled_clamped<DIV>(v[5], d), scaled_clamped<DIV>(v[6], d), scaled_clamped<DIV>(v[7], d));
             *reinterpret_cast<uint2*>(q + row * (int64_t)I + col) = o2;
         }
         if (sub == 0 && t < total_tiles) scales[t] = s;
@@ -865,6 +873,48 @@ static int dispatch_dual(const T* x, int64_t M, int64_t N, int64_t ld, uint8_t* 
 #undef CINN_D
     }
     CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Self-check of the hoisted reciprocal: for every positive 16-bit amax pattern (bf16 and fp16, infinity
+// included) and both kinds of scale (amax / 448 and its power-of-two rounding), compares
+// div.full.f32(x, s) with x * rcp.approx(s) for all 65536 16-bit x of that type and for 65536 fp32 bit
+// patterns spread over the whole range, and counts the pairs whose bits differ (two NaNs count as equal:
+// the clamp that follows maps both to -448).
+// ---------------------------------------------------------------------------
+__device__ unsigned long long g_div_mismatches;
+
+__global__ void __launch_bounds__(256)
+selfcheck_division_kernel(int fp16) {
+    const uint32_t abits = blockIdx.x + 1;
+    float amax = fp16 ? __half2float(__ushort_as_half((unsigned short)abits)) : __uint_as_float(abits << 16);
+    unsigned long long bad = 0;
+    for (int kind = 0; kind < 2; ++kind) {
+        const float s = kind == 0 ? scale_from_amax<CINN_DIV_FULL, false>(amax) : scale_from_amax<CINN_DIV_FULL, true>(amax);
+        const float d = divisor_of<CINN_DIV_FULL>(s);
+        for (uint32_t i = threadIdx.x; i < 2 * 65536u; i += 256) {
+            float x;
+            if (i < 65536u) x = fp16 ? __half2float(__ushort_as_half((unsigned short)i)) : __uint_as_float(i << 16);
+            else x = __uint_as_float((i - 65536u) * 65537u + abits * 40503u);
+            const float a = div_f32<CINN_DIV_FULL>(x, s);
+            const float b = __fmul_rn(x, d);
+            if (__float_as_uint(a) != __float_as_uint(b) && !(a != a && b != b)) ++bad;
+        }
+    }
+    if (bad) atomicAdd(&g_div_mismatches, bad);
+}
+
+int selfcheck_division(unsigned long long* mismatches, cudaStream_t st) {
+    CINN_CHECK_ARG(mismatches != nullptr, "selfcheck_division: null pointer");
+    const unsigned long long zero = 0;
+    CINN_CHECK_CUDA(cudaMemcpyToSymbolAsync(g_div_mismatches, &zero, sizeof(zero), 0, cudaMemcpyHostToDevice, st));
+    selfcheck_division_kernel<<<0x7f80, 256, 0, st>>>(0);      // bf16: patterns 0x0001 .. 0x7f80 (+inf)
+    CINN_CHECK_LAUNCH();
+    selfcheck_division_kernel<<<0x7c00, 256, 0, st>>>(1);      // fp16: patterns 0x0001 .. 0x7c00 (+inf)
+    CINN_CHECK_LAUNCH();
+    CINN_CHECK_CUDA(cudaMemcpyFromSymbolAsync(mismatches, g_div_mismatches, sizeof(zero), 0, cudaMemcpyDeviceToHost, st));
+    CINN_CHECK_CUDA(cudaStreamSynchronize(st));
     return CINN_OK;
 }
 

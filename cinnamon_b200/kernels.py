@@ -73,6 +73,19 @@ def device_status(reset: bool = True) -> int:
     return out.value
 
 
+def selfcheck_division(device=None) -> int:
+    """Number of (x, scale) pairs for which ``x * rcp.approx(scale)`` (what the ``full`` flavour computes, one
+    reciprocal per scale) differs in bits from ``div.full.f32(x, scale)`` (what Triton emits for the reference's
+    ``x / scale``, src/kernels.py:60, :121), over every positive bf16/fp16 amax, both scale kinds, every 16-bit
+    x and 65536 fp32 patterns per scale.  0 on a GPU where the hoisting is exact."""
+    n = ctypes.c_ulonglong(0)
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        _lib.check(_L.cinn_selfcheck_division(ctypes.byref(n), stream), "cinn_selfcheck_division")
+    _count(2)
+    return int(n.value)
+
+
 def _as_quant_input(x: torch.Tensor) -> torch.Tensor:
     if x.dtype not in _DTYPE_TAG:
         x = x.float()

@@ -60,6 +60,14 @@ int cinn_quant_rowwise(const void* x, int x_dtype, int64_t M, int64_t N, int64_t
 int cinn_quant_rowwise_dual(const void* x, int x_dtype, int64_t M, int64_t N, int64_t ld, void* q_row, float* s_row,
                             void* q_col, float* s_col, int round_scale, int div_mode, void* stream);
 
+/* Diagnostic (no reference counterpart).  With CINN_DIV_FULL the quantisers form x / scale as
+ * x * rcp.approx(scale), the reciprocal taken once per scale.  This call checks on the current GPU that the
+ * product has the bits of div.full.f32(x, scale) - the instruction Triton emits for the reference kernels
+ * (src/kernels.py:60, :121) - for every positive bf16 and fp16 amax (both scale kinds), every 16-bit x and
+ * 65536 fp32 patterns per scale, and writes the number of differing pairs to *mismatches (host memory).
+ * Synchronises the stream. */
+int cinn_selfcheck_division(unsigned long long* mismatches, void* stream);
+
 /* Block-wise block_m x block_n quantisation.
  * Replaces quantize_fp8_blockwise_kernel + quantize_fp8_blockwise (src/kernels.py:74-132, 219-259).
  * scales: (ceil(M/block_m), ceil(N/block_n)). */

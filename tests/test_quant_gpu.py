@@ -184,6 +184,12 @@ def test_reference_suite_cases(K):
     assert not torch.isnan(rec).any() and not torch.isinf(rec).any()
 
 
+def test_hoisted_reciprocal_equals_div_full(K):
+    """The default flavour multiplies by one rcp.approx per scale; on this GPU that product must have the bits of
+    div.full.f32 for every 16-bit input and every scale a 16-bit amax can produce."""
+    assert K.selfcheck_division() == 0
+
+
 def test_full_division_flavour_is_close(K):
     """div.full.f32 (what Triton emits for the reference on a GPU) is a <= 2 ulp division:
     scales stay within 2 ulp of the IEEE ones and a byte moves by at most one e4m3 step."""
