@@ -261,23 +261,25 @@ def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label):
     w12 = (torch.randn(E_local, 2 * c["I"], c["d"], generator=gw, device=dev) * 0.02).to(torch.bfloat16)
     w3 = (torch.randn(E_local, c["d"], c["I"], generator=gw, device=dev) * 0.02).to(torch.bfloat16)
     x = torch.randn(T_local, c["d"], generator=gw, device=dev).to(torch.bfloat16)
-    shared = [Kmod.FP8Linear(c["d"], c["shared_hidden"]).to(dev), Kmod.FP8Linear(c["d"], c["shared_hidden"]).to(dev),
-              Kmod.FP8Linear(c["shared_hidden"], c["d"]).to(dev)]
+    gs = torch.Generator(device=dev).manual_seed(3004)
+    sw = [torch.randn(c["shared_hidden"], c["d"], generator=gs, device=dev) * 0.02,
+          torch.randn(c["shared_hidden"], c["d"], generator=gs, device=dev) * 0.02,
+          torch.randn(c["d"], c["shared_hidden"], generator=gs, device=dev) * 0.02]
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
     t0.record()
-    experts = moe.FP8Experts(w12, w3)
+    # the layer as a user builds it: router + this rank's routed experts + the shared expert (round_scale on the
+    # shared expert's input, as the reference's converted model has it)
+    module = moe.ExpertParallelMoE(router, bias, w12, w3, c["top_k"], shared=moe.FP8SwiGLU(*sw, round_scale=True))
     t1.record()
     torch.cuda.synchronize()
     wq_ms = t0.elapsed_time(t1)
-    del w12, w3
+    experts = module.experts
+    del w12, w3, sw
 
     def layer():
         with torch.no_grad():
-            r = moe.route(x, router, bias, c["top_k"])
-            y = moe.moe_forward(x, r, experts, Kmod.quantize_fp8_rowwise)
-            sh = shared[2](torch.nn.functional.silu(shared[0](x)) * shared[1](x))
-            return y + sh.float(), r
+            return module(x)
 
     def sync():
         if world > 1:
@@ -285,7 +287,7 @@ def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label):
         torch.cuda.synchronize()
 
     for _ in range(warmup):
-        _, r = layer()
+        layer()
     sync()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -295,6 +297,8 @@ def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label):
     sync()
     ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
     # grouped GEMMs alone, on the rows this rank received in the last step
+    with torch.no_grad():
+        r = moe.route(x, router, bias, c["top_k"])
     plan = moe.make_plan(r.counts)
     rows = int(plan.ends[-1])
     xq = torch.empty(rows, c["d"], dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
@@ -317,7 +321,7 @@ def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label):
         dist.all_reduce(load, op=dist.ReduceOp.MAX)
         dist.all_reduce(total, op=dist.ReduceOp.SUM)
     active = int((r.counts > 0).sum())
-    del experts
+    del experts, module
     torch.cuda.empty_cache()
     flop = float(total.item()) * 2.0 * c["d"] * 3 * c["I"]
     return {"workload": f"moe_layer E=256 d=7168 I=2048 tokens=32768 top8 {label}", "tokens_per_s": c["tokens"] / (ms.item() * 1e-3),

@@ -32,6 +32,9 @@ SIGNATURES = {
     "cinn_fp8_gemm": [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _i32, _i32, _vp],
     "cinn_fp8_grouped_gemm_dgrad": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32, _vp],
     "cinn_moe_combine": [_vp, _i32, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _vp],
+    "cinn_moe_route_workspace_ints": [_i64, _i32],
+    "cinn_moe_route": [_vp, _vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+    "cinn_moe_combine_add": [_vp, _i32, _vp, _vp, _vp, _i32, _vp, _i64, _i64, _i32, _i64, _vp],
     "cinn_device_status": [ctypes.POINTER(ctypes.c_int), _i32],
     "cinn_fp8_grouped_gemm": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32, _vp],
 }
@@ -51,7 +54,8 @@ def _load() -> ctypes.CDLL:
     for name, argtypes in SIGNATURES.items():
         fn = getattr(lib, name)            # AttributeError if the symbol is not exported
         fn.argtypes = argtypes
-        fn.restype = ctypes.c_char_p if name == "cinn_last_error" else ctypes.c_int
+        fn.restype = (ctypes.c_char_p if name == "cinn_last_error"
+                      else ctypes.c_int64 if name == "cinn_moe_route_workspace_ints" else ctypes.c_int)
     return lib
 
 

@@ -50,8 +50,12 @@ int read_device_status(int* out, int reset);
 int fp8_grouped_gemm_dgrad(const void* dY, const float* sdY, const void* W, const float* sW, const int64_t* starts,
                            const int64_t* ends, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* dX, int out_dtype,
                            cudaStream_t st);
-int moe_combine(const void* rows, int dtype, const int64_t* pos, const float* gates, void* y, int64_t n_tokens,
-                int64_t n_rows, int top_k, int64_t d, cudaStream_t st);
+int64_t moe_route_workspace_ints(int64_t T, int E);
+int moe_route(const float* logits, const float* bias, int64_t T, int E, int top_k, int* workspace, int* top_experts,
+              float* top_gates, int64_t* token_indices, float* sorted_scores, int64_t* sorted_experts, int64_t* counts,
+              int64_t* pair_pos, float* pair_gate, cudaStream_t st);
+int moe_combine(const void* rows, int dtype, const int64_t* pos, const float* gates, const void* addend, int addend_dtype,
+                void* y, int64_t n_tokens, int64_t n_rows, int top_k, int64_t d, cudaStream_t st);
 
 }  // namespace cinn
 
@@ -122,7 +126,24 @@ int cinn_fp8_grouped_gemm_dgrad(const void* dY, const float* sdY, const void* W,
 
 int cinn_moe_combine(const void* rows, int dtype, const int64_t* pos, const float* gates, void* y, int64_t n_tokens,
                      int64_t n_rows, int top_k, int64_t d, void* stream) {
-    return cinn::moe_combine(rows, dtype, pos, gates, y, n_tokens, n_rows, top_k, d, (cudaStream_t)stream);
+    return cinn::moe_combine(rows, dtype, pos, gates, nullptr, 0, y, n_tokens, n_rows, top_k, d, (cudaStream_t)stream);
+}
+
+int cinn_moe_combine_add(const void* rows, int dtype, const int64_t* pos, const float* gates, const void* addend,
+                         int addend_dtype, void* y, int64_t n_tokens, int64_t n_rows, int top_k, int64_t d, void* stream) {
+    return cinn::moe_combine(rows, dtype, pos, gates, addend, addend_dtype, y, n_tokens, n_rows, top_k, d,
+                             (cudaStream_t)stream);
+}
+
+int64_t cinn_moe_route_workspace_ints(int64_t n_tokens, int n_experts) {
+    return cinn::moe_route_workspace_ints(n_tokens, n_experts);
+}
+
+int cinn_moe_route(const float* logits, const float* bias, int64_t n_tokens, int n_experts, int top_k, int* workspace,
+                   int* top_experts, float* top_gates, int64_t* token_indices, float* sorted_scores,
+                   int64_t* sorted_experts, int64_t* counts, int64_t* pair_pos, float* pair_gate, void* stream) {
+    return cinn::moe_route(logits, bias, n_tokens, n_experts, top_k, workspace, top_experts, top_gates, token_indices,
+                           sorted_scores, sorted_experts, counts, pair_pos, pair_gate, (cudaStream_t)stream);
 }
 
 int cinn_device_status(int* out, int reset) {

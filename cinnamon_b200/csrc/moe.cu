@@ -36,7 +36,8 @@ constexpr int kMaxTopK = 32;
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const T* __restrict__ rows, const int64_t* __restrict__ pos, const float* __restrict__ gates,
-                   float* __restrict__ y, int64_t n_rows, int top_k, int d) {
+                   const void* __restrict__ addend, int addend_dtype, float* __restrict__ y, int64_t n_rows, int top_k,
+                   int d) {
     __shared__ int64_t s_pos[kMaxTopK];
     __shared__ float s_gate[kMaxTopK];
     const int64_t t = blockIdx.x;
@@ -57,14 +58,22 @@ moe_combine_kernel(const T* __restrict__ rows, const int64_t* __restrict__ pos, 
 #pragma unroll
             for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(v[i], g));   // product then sum, as the reference
         }
+        if (addend != nullptr) {                   // shared-expert output + routed sum (src/layers.py:179)
+            float a[8];
+            if (addend_dtype == CINN_BF16) load8f<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(addend) + t * d + c, a);
+            else if (addend_dtype == CINN_F16) load8f<__half>(reinterpret_cast<const __half*>(addend) + t * d + c, a);
+            else load8f<float>(reinterpret_cast<const float*>(addend) + t * d + c, a);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(a[i], acc[i]);
+        }
         float4* out = reinterpret_cast<float4*>(y + t * d + c);
         out[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
         out[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
 }
 
-int moe_combine(const void* rows, int dtype, const int64_t* pos, const float* gates, void* y, int64_t n_tokens,
-                int64_t n_rows, int top_k, int64_t d, cudaStream_t st) {
+int moe_combine(const void* rows, int dtype, const int64_t* pos, const float* gates, const void* addend, int addend_dtype,
+                void* y, int64_t n_tokens, int64_t n_rows, int top_k, int64_t d, cudaStream_t st) {
     CINN_CHECK_ARG(n_tokens >= 0 && n_rows >= 0 && d >= 0, "moe_combine: negative shape");
     if (n_tokens == 0 || d == 0) return CINN_OK;
     CINN_CHECK_ARG(pos && gates && y && (rows || n_rows == 0), "moe_combine: null pointer");
@@ -73,11 +82,14 @@ int moe_combine(const void* rows, int dtype, const int64_t* pos, const float* ga
     CINN_CHECK_ARG((reinterpret_cast<uintptr_t>(rows) & 15) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0,
                    "moe_combine: rows and y must be 16-byte aligned");
     CINN_CHECK_ARG(n_tokens < (1LL << 31), "moe_combine: too many tokens");
+    CINN_CHECK_ARG(addend == nullptr || addend_dtype == CINN_BF16 || addend_dtype == CINN_F16 || addend_dtype == CINN_F32,
+                   "moe_combine: unknown addend dtype tag %d", addend_dtype);
+    CINN_CHECK_ARG((reinterpret_cast<uintptr_t>(addend) & 15) == 0, "moe_combine: the addend must be 16-byte aligned");
     const unsigned grid = (unsigned)n_tokens;
     switch (dtype) {
-        case CINN_BF16: moe_combine_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)rows, pos, gates, (float*)y, n_rows, top_k, (int)d); break;
-        case CINN_F16: moe_combine_kernel<__half><<<grid, 256, 0, st>>>((const __half*)rows, pos, gates, (float*)y, n_rows, top_k, (int)d); break;
-        case CINN_F32: moe_combine_kernel<float><<<grid, 256, 0, st>>>((const float*)rows, pos, gates, (float*)y, n_rows, top_k, (int)d); break;
+        case CINN_BF16: moe_combine_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)rows, pos, gates, addend, addend_dtype, (float*)y, n_rows, top_k, (int)d); break;
+        case CINN_F16: moe_combine_kernel<__half><<<grid, 256, 0, st>>>((const __half*)rows, pos, gates, addend, addend_dtype, (float*)y, n_rows, top_k, (int)d); break;
+        case CINN_F32: moe_combine_kernel<float><<<grid, 256, 0, st>>>((const float*)rows, pos, gates, addend, addend_dtype, (float*)y, n_rows, top_k, (int)d); break;
         default: set_error("moe_combine: unknown dtype tag %d", dtype); return CINN_ERR_INVALID;
     }
     CINN_CHECK_LAUNCH();

@@ -422,6 +422,7 @@ quant_row_dual_kernel(const T* __restrict__ x, int64_t ld, uint8_t* __restrict__
 // in flight while this one is converted.  A stage is handed back to the TMA unit right after every thread has
 // copied its part into registers.
 constexpr int DUAL_STAGES = 2;
+constexpr int DUAL_GROUP_M = 8;
 constexpr int DUAL_STAGE_BYTES = 128 * 128 * 2;
 constexpr int DUAL_SMEM_BYTES = DUAL_STAGES * DUAL_STAGE_BYTES + 128 * 128 + 8 * 128 * 4 + 64;
 constexpr long long QUANT_WAIT_LIMIT_CYCLES = 4000000000LL;   // about two seconds
@@ -457,9 +458,21 @@ quant_row_dual_tma_kernel(const __grid_constant__ CUtensorMap tmX, uint8_t* __re
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    // Pieces are walked in bands of DUAL_GROUP_M row blocks, down the band first: the CTAs running at one time
+    // then touch long runs of every input row and DUAL_GROUP_M neighbouring 128-byte pieces of every transposed
+    // output row, so both sides keep DRAM pages open.
+    auto coords = [&](int t, int& bm, int& bn) {
+        const int band = t / (DUAL_GROUP_M * nb_n);
+        const int r = t - band * (DUAL_GROUP_M * nb_n);
+        const int rows = min(DUAL_GROUP_M, nb_m - band * DUAL_GROUP_M);
+        bn = r / rows;
+        bm = band * DUAL_GROUP_M + (r - bn * rows);
+    };
     auto issue = [&](int t, int s) {                     // one elected thread
+        int bm, bn;
+        coords(t, bm, bn);
         mbar_expect_tx(full0 + 8 * s, DUAL_STAGE_BYTES);
-        tma_load_2d(&tmX, full0 + 8 * s, smem_u32(stages + s * DUAL_STAGE_BYTES), (t % nb_n) * 128, (t / nb_n) * 128);
+        tma_load_2d(&tmX, full0 + 8 * s, smem_u32(stages + s * DUAL_STAGE_BYTES), bn * 128, bm * 128);
     };
     if (threadIdx.x == 0) {
         for (int s = 0; s < DUAL_STAGES; ++s)
@@ -480,7 +493,9 @@ quant_row_dual_tma_kernel(const __grid_constant__ CUtensorMap tmX, uint8_t* __re
             unpack_raw8<T>(r, v[i]);
         }
         const int tn = t + DUAL_STAGES * stride;
-        alive = dual_tile<DIV, ROUND>(v, s_amax, s_out, ok, q_row, s_row, q_col, s_col, M, N, nb_n, nb_m, t / nb_n, t % nb_n,
+        int bm, bn;
+        coords(t, bm, bn);
+        alive = dual_tile<DIV, ROUND>(v, s_amax, s_out, ok, q_row, s_row, q_col, s_col, M, N, nb_n, nb_m, bm, bn,
                                       [&] { if (threadIdx.x == 0 && tn < total) issue(tn, s); });
         if (!alive) break;
     }

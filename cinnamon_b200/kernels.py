@@ -452,10 +452,12 @@ def swiglu_quantize_rowwise(h12: torch.Tensor):
     return q, s
 
 
-def moe_combine(rows: torch.Tensor, pos: torch.Tensor, gates: torch.Tensor) -> torch.Tensor:
+def moe_combine(rows: torch.Tensor, pos: torch.Tensor, gates: torch.Tensor, addend: torch.Tensor = None) -> torch.Tensor:
     """``y[t] = sum_j gates[t, j] * rows[pos[t, j]]`` in fp32: the gate multiply + scatter-add of
     ``MoE.forward`` (reference src/layers.py:157-160) as one gather pass without atomics.
-    rows (R, d) bf16/fp16/fp32, pos (T, k) int64 (negative = skip), gates (T, k) fp32."""
+    rows (R, d) bf16/fp16/fp32, pos (T, k) int64 (negative = skip), gates (T, k) fp32.
+    ``addend`` (T, d), optional: the shared experts' output, added to the routed sum in the same pass
+    (``shared_out + routed_out``, src/layers.py:179)."""
     assert rows.is_cuda and pos.is_cuda and gates.is_cuda, "Inputs must be on CUDA"
     T, k = pos.shape
     rows = rows.contiguous()
@@ -464,10 +466,51 @@ def moe_combine(rows: torch.Tensor, pos: torch.Tensor, gates: torch.Tensor) -> t
     d = rows.shape[1]
     with torch.cuda.device(rows.device):
         y = torch.empty((T, d), dtype=torch.float32, device=rows.device)
-        _lib.check(_L.cinn_moe_combine(_ptr(rows), _DTYPE_TAG[rows.dtype], _ptr(pos), _ptr(gates), _ptr(y), T,
-                                       rows.shape[0], k, d, _stream(rows)), "cinn_moe_combine")
+        if addend is None:
+            _lib.check(_L.cinn_moe_combine(_ptr(rows), _DTYPE_TAG[rows.dtype], _ptr(pos), _ptr(gates), _ptr(y), T,
+                                           rows.shape[0], k, d, _stream(rows)), "cinn_moe_combine")
+        else:
+            assert addend.shape == (T, d), f"addend must be ({T}, {d})"
+            if addend.dtype not in _DTYPE_TAG:
+                addend = addend.float()
+            addend = addend.contiguous()
+            _lib.check(_L.cinn_moe_combine_add(_ptr(rows), _DTYPE_TAG[rows.dtype], _ptr(pos), _ptr(gates), _ptr(addend),
+                                               _DTYPE_TAG[addend.dtype], _ptr(y), T, rows.shape[0], k, d, _stream(rows)),
+                       "cinn_moe_combine_add")
     _count()
     return y
+
+
+def moe_route(logits: torch.Tensor, bias: torch.Tensor, top_k: int):
+    """Routing of ``MoE.forward`` (reference src/layers.py:122-148) from the router's fp32 logits, on the
+    device and without a host synchronisation: sigmoid scores, top-k of score + bias, normalised gates, and the
+    (token, expert) pairs in the order of a stable sort by expert.  Returns a dict of tensors:
+    ``top_experts`` (T, k) int32, ``top_gates`` (T, k), ``token_indices`` / ``sorted_scores`` /
+    ``sorted_experts`` (T*k), ``counts`` (E) int64, ``pair_pos`` / ``pair_gate`` (T, k)."""
+    assert logits.is_cuda and bias.is_cuda, "Inputs must be on CUDA"
+    assert logits.ndim == 2, "logits must be (tokens, experts)"
+    logits = logits.float().contiguous()
+    bias = bias.float().contiguous()
+    T, E = logits.shape
+    dev = logits.device
+    with torch.cuda.device(dev):
+        ws = torch.empty(max(1, int(_L.cinn_moe_route_workspace_ints(T, E))), dtype=torch.int32, device=dev)
+        out = {
+            "top_experts": torch.empty((T, top_k), dtype=torch.int32, device=dev),
+            "top_gates": torch.empty((T, top_k), dtype=torch.float32, device=dev),
+            "token_indices": torch.empty(T * top_k, dtype=torch.int64, device=dev),
+            "sorted_scores": torch.empty(T * top_k, dtype=torch.float32, device=dev),
+            "sorted_experts": torch.empty(T * top_k, dtype=torch.int64, device=dev),
+            "counts": torch.empty(E, dtype=torch.int64, device=dev),
+            "pair_pos": torch.empty((T, top_k), dtype=torch.int64, device=dev),
+            "pair_gate": torch.empty((T, top_k), dtype=torch.float32, device=dev),
+        }
+        _lib.check(_L.cinn_moe_route(_ptr(logits), _ptr(bias), T, E, top_k, _ptr(ws), _ptr(out["top_experts"]),
+                                     _ptr(out["top_gates"]), _ptr(out["token_indices"]), _ptr(out["sorted_scores"]),
+                                     _ptr(out["sorted_experts"]), _ptr(out["counts"]), _ptr(out["pair_pos"]),
+                                     _ptr(out["pair_gate"]), _stream(logits)), "cinn_moe_route")
+    _count(3)
+    return out
 
 
 def fp8_grouped_gemm_dgrad(dy_fp8, dy_scale, w_fp8, w_scale, expert_starts, expert_ends, out_dtype=torch.bfloat16):

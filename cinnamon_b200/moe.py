@@ -39,15 +39,33 @@ class Routing:
     pair_gate: torch.Tensor = None  # (T, k) the gates in the same order
 
 
+def router_logits(x: torch.Tensor, router_weight: torch.Tensor) -> torch.Tensor:
+    """The reference's router is an ``nn.Linear`` under autocast (src/layers.py:122): a 16-bit GEMM for 16-bit
+    activations, scores in fp32 afterwards."""
+    if x.dtype in (torch.bfloat16, torch.float16):
+        w = router_weight if router_weight.dtype == x.dtype else router_weight.to(x.dtype)
+        return torch.nn.functional.linear(x, w).float()
+    return torch.nn.functional.linear(x.float(), router_weight.float())
+
+
 def route(x: torch.Tensor, router_weight: torch.Tensor, expert_bias: torch.Tensor, top_k: int) -> Routing:
     """Router of ``MoE.forward`` (src/layers.py:122-148): sigmoid scores, top-k on
-    scores + bias, gates normalised over the selected experts, pairs sorted by expert."""
+    scores + bias, gates normalised over the selected experts, pairs sorted by expert.
+    On a GPU everything after the router GEMM is three kernel launches (``kernels.moe_route``) with no host
+    synchronisation; on the CPU (host-logic tests) it is the reference's chain of torch calls."""
     n_experts = router_weight.shape[0]
-    if x.dtype in (torch.bfloat16, torch.float16):
-        # the reference's router is an nn.Linear under autocast: a 16-bit GEMM, scores in fp32 afterwards
-        logits = torch.nn.functional.linear(x, router_weight.to(x.dtype)).float()
-    else:
-        logits = torch.nn.functional.linear(x.float(), router_weight.float())
+    logits = router_logits(x, router_weight)
+    if logits.is_cuda:
+        from . import kernels as K
+        r = K.moe_route(logits, expert_bias, top_k)
+        return Routing(token_indices=r["token_indices"], sorted_scores=r["sorted_scores"],
+                       sorted_experts=r["sorted_experts"], counts=r["counts"], pair_pos=r["pair_pos"],
+                       pair_gate=r["pair_gate"])
+    return route_torch(logits, expert_bias, top_k, n_experts)
+
+
+def route_torch(logits: torch.Tensor, expert_bias: torch.Tensor, top_k: int, n_experts: int) -> Routing:
+    """The routing arithmetic as the reference writes it (src/layers.py:122-148), in torch."""
     scores = torch.sigmoid(logits)
     _, top_idx = (scores + expert_bias).topk(top_k, dim=-1)
     top_scores = scores.gather(-1, top_idx)
@@ -97,6 +115,45 @@ class FP8Experts:
         return K.fp8_grouped_gemm(h_q, h_s, self.w3_q, self.w3_s, starts, ends, out_dtype=out_dtype)
 
 
+class FP8SwiGLU:
+    """A shared expert: the ``SwiGLU`` block (src/layers.py:15-32) after ``convert_to_fp8`` turned its three
+    linears into FP8 ones, with the work the three separate layers repeat done once:
+
+      * the weights are quantised when they change, not on every call;
+      * w1 and w2 share their input, so x is quantised once and [w1; w2] is one GEMM of width 2 * hidden
+        (the layout ``GroupedExperts`` uses for the routed experts, src/layers.py:47-49);
+      * SiLU, the product and the quantisation of w3's input are one pass over that GEMM's output.
+
+    ``round_scale`` is the power-of-two scale option of w1 / w2's input quantisation."""
+
+    def __init__(self, w1: torch.Tensor, w2: torch.Tensor, w3: torch.Tensor, round_scale: bool = False):
+        from . import kernels as K
+        self.K = K
+        self.round_scale = bool(round_scale)
+        self.hidden, self.d_model = w1.shape
+        self.requantize(w1, w2, w3)
+
+    def requantize(self, w1: torch.Tensor, w2: torch.Tensor, w3: torch.Tensor) -> None:
+        K = self.K
+        w12 = torch.cat([w1, w2], dim=0)
+        self.w12_q, self.w12_s = K.quantize_fp8_blockwise(w12 if w12.dtype in (torch.bfloat16, torch.float32, torch.float16)
+                                                          else w12.float())
+        self.w3_q, self.w3_s = K.quantize_fp8_blockwise(w3 if w3.dtype in (torch.bfloat16, torch.float32, torch.float16)
+                                                        else w3.float())
+
+    def __call__(self, x: torch.Tensor, x_q: torch.Tensor = None, x_s: torch.Tensor = None) -> torch.Tensor:
+        """x (T, d) -> (T, d) bf16.  ``x_q, x_s``: an existing 1x128 quantisation of x to reuse."""
+        K = self.K
+        T = x.shape[0]
+        if x_q is None:
+            x_q, x_s = K.quantize_fp8_rowwise(x, 128, self.round_scale)
+        h12 = K._gemm(x_q, x_s, self.w12_q, K._lib.B_NK, self.w12_s, self.w12_s.stride(1), self.w12_s.stride(0), T,
+                      2 * self.hidden, self.d_model, torch.bfloat16)
+        h_q, h_s = K.swiglu_quantize_rowwise(h12)
+        return K._gemm(h_q, h_s, self.w3_q, K._lib.B_NK, self.w3_s, self.w3_s.stride(1), self.w3_s.stride(0), T,
+                       self.d_model, self.hidden, torch.bfloat16)
+
+
 # ---------------------------------------------------------------------------------------
 # exchange plan
 # ---------------------------------------------------------------------------------------
@@ -110,26 +167,30 @@ class DispatchPlan:
     ends: torch.Tensor             # (E_local,) int64, device
 
 
-def make_plan(counts: torch.Tensor, group=None) -> DispatchPlan:
+def make_plan(counts: torch.Tensor, group=None, n_pairs: Optional[int] = None) -> DispatchPlan:
     """``counts``: (E,) pairs this rank routed to every global expert.  Exchanges the counts
     (one small all-to-all) and derives split sizes, the regrouping permutation and the
-    per-expert row ranges on the receiving side."""
+    per-expert row ranges on the receiving side.  With one rank nothing is exchanged or permuted, and when the
+    caller passes the number of pairs (tokens x top_k) nothing is read back to the host either."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     n_experts = counts.numel()
     assert n_experts % world == 0, "experts must divide evenly over ranks"
     e_local = n_experts // world
     send_counts = counts.reshape(world, e_local).to(torch.int64).contiguous()
+    if world == 1:
+        ends = send_counts[0].cumsum(0)
+        starts = ends - send_counts[0]
+        n = int(n_pairs) if n_pairs is not None else int(ends[-1])
+        return DispatchPlan([n], [n], send_counts, None, starts.contiguous(), ends.contiguous())
     recv_counts = torch.empty_like(send_counts)
-    if world > 1:
-        dist.all_to_all_single(recv_counts, send_counts, group=group)
-    else:
-        recv_counts.copy_(send_counts)
-    send_splits = send_counts.sum(1).tolist()           # host synchronisation: split sizes are Python ints
-    recv_splits = recv_counts.sum(1).tolist()
+    dist.all_to_all_single(recv_counts, send_counts, group=group)
+    # the one host read-back of the layer: the collective wants its split sizes as Python ints
+    splits = torch.stack([send_counts.sum(1), recv_counts.sum(1)]).tolist()
+    send_splits, recv_splits = splits[0], splits[1]
     # received rows arrive ordered by (source rank, local expert); regroup to (local expert, source rank)
     flat = recv_counts.reshape(-1)
     expert_of_segment = torch.arange(e_local, device=counts.device).repeat(world)
-    row_expert = torch.repeat_interleave(expert_of_segment, flat)
+    row_expert = torch.repeat_interleave(expert_of_segment, flat, output_size=sum(recv_splits))
     perm = torch.sort(row_expert, stable=True).indices
     per_expert = recv_counts.sum(0)
     starts, ends = offsets_from_counts(per_expert)
@@ -152,16 +213,18 @@ def all_to_all_rows(rows: torch.Tensor, send_splits, recv_splits, group=None) ->
 # the layer
 # ---------------------------------------------------------------------------------------
 def moe_forward(x: torch.Tensor, routing: Routing, experts: Callable, quantize: Optional[Callable],
-                group=None, timings: Optional[dict] = None) -> torch.Tensor:
+                group=None, addend: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Routed part of ``MoE.forward`` for this rank's tokens ``x`` (T, d).
 
     ``experts(rows_q, rows_s, starts, ends)`` computes the expert SwiGLU for rows grouped by
     local expert; ``quantize(x) -> (q, s)`` is the row-wise quantiser (``None`` = rows travel
     unquantised and ``experts`` receives ``(rows, None, starts, ends)``: the CPU test path).
-    Returns the gate-weighted sum over each token's experts, fp32 (T, d).
+    ``addend`` (T, d), optional: the shared experts' output, folded into the combine pass
+    (``shared_out + routed_out``, src/layers.py:179).
+    Returns the gate-weighted sum over each token's experts (plus ``addend``), fp32 (T, d).
     """
     T, d = x.shape
-    plan = make_plan(routing.counts, group)
+    plan = make_plan(routing.counts, group, n_pairs=routing.token_indices.numel())
     if quantize is not None:
         x_q, x_s = quantize(x)
         send_q = x_q.view(torch.uint8).index_select(0, routing.token_indices).view(x_q.dtype)
@@ -185,32 +248,46 @@ def moe_forward(x: torch.Tensor, routing: Routing, experts: Callable, quantize: 
         out_rows = all_to_all_rows(back, plan.recv_splits, plan.send_splits, group)
     if out_rows.is_cuda:
         from . import kernels as K
-        return K.moe_combine(out_rows, routing.pair_pos, routing.pair_gate)      # src/layers.py:157-160, fused
+        return K.moe_combine(out_rows, routing.pair_pos, routing.pair_gate, addend)   # src/layers.py:157-160, fused
     weighted = out_rows.float() * routing.sorted_scores[:, None]                 # host-logic tests (CPU ranks)
     y = torch.zeros(T, d, dtype=torch.float32, device=x.device)
     y.index_add_(0, routing.token_indices, weighted)
-    return y
+    return y if addend is None else addend.float() + y
 
 
 class ExpertParallelMoE(torch.nn.Module):
-    """Inference/forward module: router + FP8 routed experts sharded over ``group``.
+    """Inference/forward module: router + FP8 routed experts sharded over ``group`` (+ an optional shared expert
+    whose output is added in the combine pass, ``shared_out + routed_out``, src/layers.py:179).
 
     Holds this rank's slice of the expert weights: ``w12`` (E/G, 2*I, d), ``w3`` (E/G, d, I).
     """
 
     def __init__(self, router_weight: torch.Tensor, expert_bias: torch.Tensor, w12_local: torch.Tensor,
-                 w3_local: torch.Tensor, top_k: int, group=None):
+                 w3_local: torch.Tensor, top_k: int, group=None, shared: Optional[FP8SwiGLU] = None):
         super().__init__()
         from . import kernels as K
         self.K = K
         self.register_buffer("router_weight", router_weight)
         self.register_buffer("expert_bias", expert_bias)
+        self._router_cache = (None, None)
         self.top_k = top_k
         self.group = group
         self.experts = FP8Experts(w12_local, w3_local)
+        self.shared = shared
+
+    def _router_as(self, dtype: torch.dtype) -> torch.Tensor:
+        """The router weight in the activations' 16-bit type, converted when the weight changes, not per call."""
+        w = self.router_weight
+        if w.dtype == dtype or dtype not in (torch.bfloat16, torch.float16):
+            return w
+        key = (dtype, w._version, w.data_ptr())
+        if self._router_cache[0] != key:
+            self._router_cache = (key, w.to(dtype))
+        return self._router_cache[1]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         flat = x.reshape(-1, x.shape[-1])
-        r = route(flat, self.router_weight, self.expert_bias, self.top_k)
-        y = moe_forward(flat, r, self.experts, self.K.quantize_fp8_rowwise, self.group)
+        r = route(flat, self._router_as(flat.dtype), self.expert_bias, self.top_k)
+        sh = self.shared(flat) if self.shared is not None else None
+        y = moe_forward(flat, r, self.experts, self.K.quantize_fp8_rowwise, self.group, addend=sh)
         return y.reshape(x.shape)

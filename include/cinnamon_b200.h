@@ -137,6 +137,29 @@ int cinn_fp8_grouped_gemm_dgrad(const void* dY, const float* sdY, const void* W,
 int cinn_moe_combine(const void* rows, int dtype, const int64_t* pos, const float* gates, void* y, int64_t n_tokens,
                      int64_t n_rows, int top_k, int64_t d, void* stream);
 
+/* The same with the shared experts' output folded in: y[t, :] = addend[t, :] + sum_j ...  (the
+ * `shared_out + routed_out` of MoE.forward, src/layers.py:179).  addend: (n_tokens, d) bf16 / fp16 / fp32, or
+ * NULL for the plain combine. */
+int cinn_moe_combine_add(const void* rows, int dtype, const int64_t* pos, const float* gates, const void* addend,
+                         int addend_dtype, void* y, int64_t n_tokens, int64_t n_rows, int top_k, int64_t d, void* stream);
+
+/* Routing of MoE.forward (src/layers.py:122-148) on the device: scores = sigmoid(logits), the top_k experts of
+ * scores + bias per token (ties: the lower expert id), gates = score / (sum of the k scores + 1e-9), and the
+ * (token, expert) pairs sorted by expert in the order of a stable sort.
+ *   logits (n_tokens, n_experts) fp32: the router's output; bias (n_experts) fp32.
+ *   workspace: cinn_moe_route_workspace_ints(n_tokens, n_experts) ints of device memory, contents irrelevant.
+ *   top_experts / top_gates (n_tokens, top_k): the selection in descending order of score + bias.
+ *   token_indices / sorted_scores / sorted_experts (n_tokens * top_k): source token, gate and expert of every row
+ *   of the sorted order (`sort_order // top_k`, `expanded_scores[sort_order]`, `sorted_idx`, :135-142).
+ *   counts (n_experts) int64: rows per expert (`torch.bincount`, :145).
+ *   pair_pos / pair_gate (n_tokens, top_k): per token its rows in ascending order with their gates: the input of
+ *   cinn_moe_combine.
+ * n_experts <= 1024, top_k <= min(32, n_experts), n_tokens * top_k < 2^31.  No host synchronisation. */
+int64_t cinn_moe_route_workspace_ints(int64_t n_tokens, int n_experts);
+int cinn_moe_route(const float* logits, const float* bias, int64_t n_tokens, int n_experts, int top_k, int* workspace,
+                   int* top_experts, float* top_gates, int64_t* token_indices, float* sorted_scores,
+                   int64_t* sorted_experts, int64_t* counts, int64_t* pair_pos, float* pair_gate, void* stream);
+
 /* Reads (and with reset != 0 clears) the device-side status word of the current device into the HOST int
  * *out.  0 means no kernel of this library has given up on a bounded wait since the last reset; any other
  * value is (role << 8) | reason.  This call synchronises with the device.  No counterpart in the reference,

@@ -100,7 +100,8 @@ def test_plan_single_process():
     plan = moe.make_plan(counts)
     assert plan.send_splits == [9] and plan.recv_splits == [9]
     assert plan.starts.tolist() == [0, 3, 3, 8] and plan.ends.tolist() == [3, 3, 8, 9]
-    assert plan.perm.tolist() == list(range(9))
+    assert plan.perm is None                       # one rank: rows already arrive grouped by expert
+    assert moe.make_plan(counts, n_pairs=9).send_splits == [9]      # no host read-back when the caller knows the total
 
 
 def test_two_ranks_match_single_rank():

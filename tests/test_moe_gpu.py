@@ -64,6 +64,41 @@ def test_combine_kernel_matches_scatter_add(K):
             if pos[t, j] >= 0:
                 ref[t] += rows[pos[t, j]].float() * gates[t, j]
     assert torch.equal(y.cpu(), ref)                                   # same products, same order of sums
+    # with the shared experts' output folded in: shared_out + routed_out (src/layers.py:179)
+    for dt in (torch.bfloat16, torch.float32, torch.float16):
+        shared = torch.randn(T, d, generator=g).to(dt)
+        y2 = K.moe_combine(rows.cuda(), pos.cuda(), gates.cuda(), addend=shared.cuda())
+        assert torch.equal(y2.cpu(), shared.float() + ref), dt
+
+
+@pytest.mark.parametrize("T,E,k", [(1000, 256, 8), (128, 16, 2), (1, 8, 3), (777, 257, 5), (4096, 64, 6), (300, 1024, 32)])
+def test_route_kernel_matches_torch(K, T, E, k):
+    """Device routing (three launches) against the reference's chain of torch calls (src/layers.py:122-148) on
+    the same logits: same experts, same stable order, gates to fp32 rounding."""
+    from cinnamon_b200 import moe
+    g = torch.Generator().manual_seed(T + E + k)
+    logits = (torch.randn(T, E, generator=g) * 2.0).cuda()
+    bias = (torch.randn(E, generator=g) * 0.5).cuda()
+    got = K.moe_route(logits, bias, k)
+    ref = moe.route_torch(logits, bias, k, E)
+    assert torch.equal(got["counts"], ref.counts)
+    assert torch.equal(got["sorted_experts"], ref.sorted_experts)
+    assert torch.equal(got["token_indices"], ref.token_indices)
+    assert torch.equal(got["pair_pos"], ref.pair_pos)
+    torch.testing.assert_close(got["sorted_scores"], ref.sorted_scores, rtol=2e-6, atol=1e-8)
+    torch.testing.assert_close(got["pair_gate"], ref.pair_gate, rtol=2e-6, atol=1e-8)
+    sel = torch.sigmoid(logits) + bias
+    assert torch.equal(got["top_experts"].long(), sel.topk(k, dim=-1).indices)
+    torch.testing.assert_close(got["top_gates"].sum(1), torch.ones(T, device="cuda"), rtol=1e-5, atol=1e-6)
+    # the same call again gives the same bits (no atomics decide an order)
+    again = K.moe_route(logits, bias, k)
+    for key in got:
+        assert torch.equal(got[key], again[key]), key
+
+
+def test_route_empty(K):
+    got = K.moe_route(torch.empty(0, 32, device="cuda"), torch.zeros(32, device="cuda"), 4)
+    assert got["counts"].tolist() == [0] * 32 and got["token_indices"].numel() == 0
 
 
 def _moe_case(E, d, I, T, top_k, seed):
@@ -109,6 +144,32 @@ def test_fp8_moe_single_gpu(K):
     layer = moe.ExpertParallelMoE(router.cuda(), bias.cuda(), w12.cuda(), w3.cuda(), k)
     y2 = layer(xc.view(3, 100, d))
     assert y2.shape == (3, 100, d) and rel_fro(y2.reshape(T, d), ref) < 5e-3
+
+
+@pytest.mark.parametrize("rs", [False, True])
+def test_shared_expert_and_combined_layer(K, rs):
+    """FP8SwiGLU (w1|w2 as one GEMM, fused SiLU-product-quantise, w3) against the oracle's FP8 linears, and the
+    layer output shared + routed from the one combine pass."""
+    from cinnamon_b200 import moe
+    E, d, I, T, k, H = 8, 512, 256, 300, 2, 384
+    x, router, bias, w12, w3 = _moe_case(E, d, I, T, k, seed=23)
+    g = torch.Generator().manual_seed(24)
+    s1, s2, s3 = (torch.randn(H, d, generator=g) * 0.02, torch.randn(H, d, generator=g) * 0.02,
+                  torch.randn(d, H, generator=g) * 0.02)
+    shared = moe.FP8SwiGLU(s1.cuda(), s2.cuda(), s3.cuda(), round_scale=rs)
+    got = shared(x.cuda())
+    h12_ref, _ = O.fp8_linear_forward(x, torch.cat([s1, s2]), rs)
+    h_ref = _oracle_swiglu(h12_ref.to(torch.bfloat16))
+    sh_ref, _ = O.fp8_linear_forward(h_ref, s3, False)
+    err = rel_fro(got.float(), sh_ref)
+    print(f"shared expert: rel-Fro {err:.3e}")
+    assert got.dtype == torch.bfloat16 and err < 5e-3
+    layer = moe.ExpertParallelMoE(router.cuda(), bias.cuda(), w12.cuda(), w3.cuda(), k, shared=shared)
+    y = layer(x.cuda())
+    r = moe.route(x.cuda(), router.cuda(), bias.cuda(), k)
+    routed = moe.moe_forward(x.cuda(), r, layer.experts, K.quantize_fp8_rowwise)
+    assert torch.equal(y, got.float() + routed)                       # one pass, same sums
+    assert K.device_status() == 0
 
 
 EP_WORKER = r'''
