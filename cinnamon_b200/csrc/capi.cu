@@ -54,6 +54,10 @@ int64_t moe_route_workspace_ints(int64_t T, int E);
 int moe_route(const float* logits, const float* bias, int64_t T, int E, int top_k, int* workspace, int* top_experts,
               float* top_gates, int64_t* token_indices, float* sorted_scores, int64_t* sorted_experts, int64_t* counts,
               int64_t* pair_pos, float* pair_gate, cudaStream_t st);
+int64_t moe_route_static_max_ints();
+int moe_route_static(const float* logits, const float* bias, int64_t T, int E, int top_k, int* top_experts, float* top_gates,
+                     int64_t* token_indices, float* sorted_scores, int64_t* sorted_experts, int64_t* counts,
+                     int64_t* pair_pos, float* pair_gate, cudaStream_t st);
 int moe_combine(const void* rows, int dtype, const int64_t* pos, const float* gates, const void* addend, int addend_dtype,
                 void* y, int64_t n_tokens, int64_t n_rows, int top_k, int64_t d, cudaStream_t st);
 
@@ -144,6 +148,15 @@ int cinn_moe_route(const float* logits, const float* bias, int64_t n_tokens, int
                    int64_t* sorted_experts, int64_t* counts, int64_t* pair_pos, float* pair_gate, void* stream) {
     return cinn::moe_route(logits, bias, n_tokens, n_experts, top_k, workspace, top_experts, top_gates, token_indices,
                            sorted_scores, sorted_experts, counts, pair_pos, pair_gate, (cudaStream_t)stream);
+}
+
+int64_t cinn_moe_route_static_max_ints(void) { return cinn::moe_route_static_max_ints(); }
+
+int cinn_moe_route_static(const float* logits, const float* bias, int64_t n_tokens, int n_experts, int top_k,
+                          int* top_experts, float* top_gates, int64_t* token_indices, float* sorted_scores,
+                          int64_t* sorted_experts, int64_t* counts, int64_t* pair_pos, float* pair_gate, void* stream) {
+    return cinn::moe_route_static(logits, bias, n_tokens, n_experts, top_k, top_experts, top_gates, token_indices,
+                                  sorted_scores, sorted_experts, counts, pair_pos, pair_gate, (cudaStream_t)stream);
 }
 
 int cinn_device_status(int* out, int reset) {

@@ -15,6 +15,7 @@
 //
 // The workspace (ceil(T / 128) * E ints) is the only memory beyond inputs and outputs.
 #include "common.cuh"
+#include <mutex>
 
 namespace cinn {
 
@@ -205,6 +206,55 @@ int moe_route(const float* logits, const float* bias, int64_t T, int E, int top_
                                                  sorted_scores, sorted_experts, pair_pos, pair_gate);
     CINN_CHECK_LAUNCH();
     return CINN_OK;
+}
+
+// ---------------------------------------------------------------------------
+// The same routing for callers that cannot hand over a workspace.  The scratch lives in a fixed array inside
+// the library image: every GPU that loads the library holds these 2 MiB until the process exits.  All calls on
+// a device share it, so two calls that overlap on that GPU (different streams, different threads) race; the
+// routing kernels overwrite every word they later read, so nothing has to be cleared between calls.
+// ---------------------------------------------------------------------------
+constexpr int64_t ROUTE_STATIC_MAX_INTS = 1 << 19;                     // 2 MiB
+static __device__ __align__(256) int g_route_scratch[ROUTE_STATIC_MAX_INTS];
+
+constexpr int ROUTE_MAX_DEVICES = 64;
+static std::mutex g_route_scratch_mutex;
+static int* g_route_scratch_ptr[ROUTE_MAX_DEVICES] = {};               // device address of the array, per device
+
+// In host code `g_route_scratch` is only a handle for the symbol, not an address a kernel can use; the device
+// address is asked for once per device, with that device current.
+static int route_scratch_address(int** out) {
+    int dev = -1;
+    CINN_CHECK_CUDA(cudaGetDevice(&dev));
+    CINN_CHECK_ARG(dev >= 0 && dev < ROUTE_MAX_DEVICES, "moe_route_static: device ordinal %d is beyond %d", dev,
+                   ROUTE_MAX_DEVICES);
+    std::lock_guard<std::mutex> lock(g_route_scratch_mutex);
+    if (g_route_scratch_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        CINN_CHECK_CUDA(cudaGetSymbolAddress(&p, g_route_scratch));
+        g_route_scratch_ptr[dev] = static_cast<int*>(p);
+    }
+    *out = g_route_scratch_ptr[dev];
+    return CINN_OK;
+}
+
+int64_t moe_route_static_max_ints() { return ROUTE_STATIC_MAX_INTS; }
+
+int moe_route_static(const float* logits, const float* bias, int64_t T, int E, int top_k, int* top_experts, float* top_gates,
+                     int64_t* token_indices, float* sorted_scores, int64_t* sorted_experts, int64_t* counts,
+                     int64_t* pair_pos, float* pair_gate, cudaStream_t st) {
+    CINN_CHECK_ARG(T >= 0 && E >= 1 && E <= ROUTE_MAX_EXPERTS, "moe_route_static: 1 <= E <= %d experts (got %d)",
+                   ROUTE_MAX_EXPERTS, E);
+    const int64_t need = moe_route_workspace_ints(T, E);
+    CINN_CHECK_ARG(need <= ROUTE_STATIC_MAX_INTS,
+                   "moe_route_static: %lld tokens x %d experts need %lld ints of scratch, the built-in array holds %lld; "
+                   "use cinn_moe_route with a workspace of your own",
+                   (long long)T, E, (long long)need, (long long)ROUTE_STATIC_MAX_INTS);
+    int* scratch = nullptr;
+    int rc = route_scratch_address(&scratch);
+    if (rc) return rc;
+    return moe_route(logits, bias, T, E, top_k, scratch, top_experts, top_gates, token_indices, sorted_scores,
+                     sorted_experts, counts, pair_pos, pair_gate, st);
 }
 
 }  // namespace cinn

@@ -160,6 +160,24 @@ int cinn_moe_route(const float* logits, const float* bias, int64_t n_tokens, int
                    int* top_experts, float* top_gates, int64_t* token_indices, float* sorted_scores,
                    int64_t* sorted_experts, int64_t* counts, int64_t* pair_pos, float* pair_gate, void* stream);
 
+/* cinn_moe_route for callers that have no device memory to give as a workspace and may not allocate any: a
+ * serving process that handed all of HBM to its own arena at start-up, a job running at the memory limit, a
+ * latency-bound loop that cannot afford the device-wide synchronisation an allocation can imply.  This entry
+ * point has no counterpart in the reference; it is an addition of this library.
+ * The scratch is a fixed 2 MiB array inside the library (every GPU that loads the library holds it until the
+ * process exits); inputs and outputs are still the caller's.  It allocates and frees nothing.
+ *   - Limit: cinn_moe_route_workspace_ints(n_tokens, n_experts) <= cinn_moe_route_static_max_ints() (524288),
+ *     e.g. 262016 tokens at 256 experts; larger problems are refused with CINN_ERR_INVALID and a message.
+ *   - The first call on each device looks up the array's device address (with that device current); make that
+ *     first call before any stream capture begins.
+ *   - All calls on one device share the array: calls that overlap on the GPU race, so keep them on one stream
+ *     (or otherwise ordered).  Nothing needs clearing between calls; the kernels overwrite what they read.
+ * Arguments and results are exactly those of cinn_moe_route, without `workspace`. */
+int64_t cinn_moe_route_static_max_ints(void);
+int cinn_moe_route_static(const float* logits, const float* bias, int64_t n_tokens, int n_experts, int top_k,
+                          int* top_experts, float* top_gates, int64_t* token_indices, float* sorted_scores,
+                          int64_t* sorted_experts, int64_t* counts, int64_t* pair_pos, float* pair_gate, void* stream);
+
 /* Reads (and with reset != 0 clears) the device-side status word of the current device into the HOST int
  * *out.  0 means no kernel of this library has given up on a bounded wait since the last reset; any other
  * value is (role << 8) | reason.  This call synchronises with the device.  No counterpart in the reference,
