@@ -50,6 +50,14 @@ int read_device_status(int* out, int reset);
 int fp8_grouped_gemm_dgrad(const void* dY, const float* sdY, const void* W, const float* sW, const int64_t* starts,
                            const int64_t* ends, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* dX, int out_dtype,
                            cudaStream_t st);
+int gather_rows(const void* q, const float* s, const int64_t* idx, void* out_q, float* out_s, int64_t n_out, int64_t n_src,
+                int64_t d, int64_t ns, cudaStream_t st);
+int sparse_attn_fwd(const void* q, const void* k, const void* v, int dtype, const int64_t* idx, float* out, float* lse,
+                    float* attn_w, int64_t B, int64_t H, int64_t L, int64_t K, int64_t Dqk, int64_t Dv, float scale,
+                    cudaStream_t st);
+int sparse_attn_bwd(const void* d_out, int grad_dtype, const float* out, const float* lse, const void* q, const void* k,
+                    const void* v, int dtype, const int64_t* idx, float* dq, float* dk, float* dv, int64_t B, int64_t H,
+                    int64_t L, int64_t K, int64_t Dqk, int64_t Dv, float scale, cudaStream_t st);
 int64_t moe_route_workspace_ints(int64_t T, int E);
 int moe_route(const float* logits, const float* bias, int64_t T, int E, int top_k, int* workspace, int* top_experts,
               float* top_gates, int64_t* token_indices, float* sorted_scores, int64_t* sorted_experts, int64_t* counts,
@@ -137,6 +145,25 @@ int cinn_moe_combine_add(const void* rows, int dtype, const int64_t* pos, const 
                          int addend_dtype, void* y, int64_t n_tokens, int64_t n_rows, int top_k, int64_t d, void* stream) {
     return cinn::moe_combine(rows, dtype, pos, gates, addend, addend_dtype, y, n_tokens, n_rows, top_k, d,
                              (cudaStream_t)stream);
+}
+
+int cinn_gather_rows(const void* q, const float* scales, const int64_t* idx, void* out_q, float* out_scales, int64_t n_out,
+                     int64_t n_src, int64_t d, int64_t n_scales, void* stream) {
+    return cinn::gather_rows(q, scales, idx, out_q, out_scales, n_out, n_src, d, n_scales, (cudaStream_t)stream);
+}
+
+int cinn_sparse_attn_fwd(const void* q, const void* k, const void* v, int dtype, const int64_t* idx, float* out, float* lse,
+                         float* attn_weights, int64_t B, int64_t H, int64_t L, int64_t K, int64_t d_qk, int64_t d_v,
+                         float scale, void* stream) {
+    return cinn::sparse_attn_fwd(q, k, v, dtype, idx, out, lse, attn_weights, B, H, L, K, d_qk, d_v, scale, (cudaStream_t)stream);
+}
+
+int cinn_sparse_attn_bwd(const void* grad_out, int grad_dtype, const float* out, const float* lse, const void* q,
+                         const void* k, const void* v, int dtype, const int64_t* idx, float* grad_q, float* grad_k,
+                         float* grad_v, int64_t B, int64_t H, int64_t L, int64_t K, int64_t d_qk, int64_t d_v, float scale,
+                         void* stream) {
+    return cinn::sparse_attn_bwd(grad_out, grad_dtype, out, lse, q, k, v, dtype, idx, grad_q, grad_k, grad_v, B, H, L, K, d_qk,
+                                 d_v, scale, (cudaStream_t)stream);
 }
 
 int64_t cinn_moe_route_workspace_ints(int64_t n_tokens, int n_experts) {

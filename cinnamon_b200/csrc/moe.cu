@@ -96,4 +96,44 @@ int moe_combine(const void* rows, int dtype, const int64_t* pos, const float* ga
     return CINN_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Dispatch gather: out_q[r, :] = q[idx[r], :] (e4m3 bytes) and out_s[r, :] = s[idx[r], :] (their 1x128 scales)
+// in one pass: the `flat_x[token_indices]` of MoE.forward (src/layers.py:140) applied to tokens that were
+// quantised once, before the gather.  One warp per output row, 16-byte vectors.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint8_t* __restrict__ q, const float* __restrict__ s, const int64_t* __restrict__ idx,
+                   uint8_t* __restrict__ out_q, float* __restrict__ out_s, int64_t n_out, int64_t n_src, int d, int ns) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int64_t n_warps = (int64_t)gridDim.x * 8;
+    const int vecs = d >> 4;
+    for (int64_t r = warp; r < n_out; r += n_warps) {
+        const int64_t src = idx[r];
+        if (src < 0 || src >= n_src) continue;                                    // rows outside the source stay untouched
+        const uint4* in = reinterpret_cast<const uint4*>(q + src * d);
+        uint4* out = reinterpret_cast<uint4*>(out_q + r * d);
+        for (int v = lane; v < vecs; v += 32) __stcs(out + v, __ldg(in + v));
+        for (int c = lane; c < ns; c += 32) out_s[r * ns + c] = s[src * ns + c];
+    }
+}
+
+int gather_rows(const void* q, const float* s, const int64_t* idx, void* out_q, float* out_s, int64_t n_out, int64_t n_src,
+                int64_t d, int64_t ns, cudaStream_t st) {
+    CINN_CHECK_ARG(n_out >= 0 && n_src >= 0 && d >= 0 && ns >= 0, "gather_rows: negative shape");
+    if (n_out == 0 || d == 0) return CINN_OK;
+    CINN_CHECK_ARG(q && s && idx && out_q && out_s, "gather_rows: null pointer");
+    CINN_CHECK_ARG(d % 16 == 0 && d < (1LL << 31) && ns < (1LL << 31), "gather_rows: the row width (%lld) must be a multiple of 16",
+                   (long long)d);
+    CINN_CHECK_ARG((reinterpret_cast<uintptr_t>(q) & 15) == 0 && (reinterpret_cast<uintptr_t>(out_q) & 15) == 0,
+                   "gather_rows: byte buffers must be 16-byte aligned");
+    int64_t blocks = (n_out + 7) / 8;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    gather_rows_kernel<<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)q, s, idx, (uint8_t*)out_q, out_s, n_out, n_src, (int)d,
+                                                        (int)ns);
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
 }  // namespace cinn

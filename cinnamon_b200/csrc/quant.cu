@@ -680,18 +680,36 @@ swiglu_quant_row_kernel(const T* __restrict__ h12, uint8_t* __restrict__ q, floa
     const int sub = threadIdx.x & 15;
     const int64_t hw = (int64_t)blockIdx.x * 16 + (threadIdx.x >> 4);
     const int64_t n_hw = (int64_t)gridDim.x * 16;
+    // the raw vectors of the next tile are in flight while this one is converted
+    Raw8<T> na = zero_raw8<T>(), nb8 = zero_raw8<T>();
+    auto fetch = [&](int64_t t) {
+        const int64_t row = t / nb;
+        const int col = (int)(t - row * nb) * 128 + sub * 8;
+        if (t < total_tiles && col < I) {
+            na = load_raw8<T>(h12 + row * 2 * (int64_t)I + col);
+            nb8 = load_raw8<T>(h12 + row * 2 * (int64_t)I + I + col);
+        }
+    };
+    fetch((hw & ~(int64_t)1) + (hw & 1));
     for (int64_t tw = hw & ~(int64_t)1; tw < total_tiles; tw += n_hw) {
         const int64_t t = tw + (hw & 1);
         const int64_t row = t / nb;
         const int col = (int)(t - row * nb) * 128 + sub * 8;
         const bool inb = t < total_tiles && col < I;
+        const Raw8<T> ca = na, cb = nb8;
+        fetch(t + n_hw);
         float a[8], b[8], v[8];
         if (inb) {
-            unpack_raw8<T>(load_raw8<T>(h12 + row * 2 * (int64_t)I + col), a);
-            unpack_raw8<T>(load_raw8<T>(h12 + row * 2 * (int64_t)I + I + col), b);
+            unpack_raw8<T>(ca, a);
+            unpack_raw8<T>(cb, b);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const float h = (a[i] / (1.0f + expf(-a[i]))) * b[i];
+                // 16-bit activations: silu to a few fp32 ulp (ex2.approx and div.approx), far inside the rounding to
+                // the activation type that follows; the IEEE sequences would make this pass instruction-bound
+                // instead of HBM-bound.  fp32 activations are not rounded afterwards and take the exact sequences.
+                float h;
+                if constexpr (sizeof(T) == 4) h = (a[i] / (1.0f + expf(-a[i]))) * b[i];
+                else h = __fdividef(a[i], 1.0f + __expf(-a[i])) * b[i];
                 if constexpr (std::is_same<T, __nv_bfloat16>::value) v[i] = __bfloat162float(__float2bfloat16_rn(h));
                 else if constexpr (std::is_same<T, __half>::value) v[i] = __half2float(__float2half_rn(h));
                 else v[i] = h;
@@ -711,7 +729,7 @@ swiglu_quant_row_kernel(const T* __restrict__ h12, uint8_t* __restrict__ q, floa
             uint2 o2;
             o2.x = cvt_e4m3x4(scaled_clamped<DIV>(v[0], d), scaled_clamped<DIV>(v[1], d), scaled_clamped<DIV>(v[2], d), scaled_clamped<DIV>(v[3], d));
             o2.y = cvt_e4m3x4(scaled_clamped<DIV>(v[4], d), scaled_clamped<DIV>(v[5], d), scaled_clamped<DIV>(v[6], d), scaled_clamped<DIV>(v[7], d));
-            *reinterpret_cast<uint2*>(q + row * (int64_t)I + col) = o2;
+            __stcs(reinterpret_cast<uint2*>(q + row * (int64_t)I + col), o2);
         }
         if (sub == 0 && t < total_tiles) scales[t] = s;
     }

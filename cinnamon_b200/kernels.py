@@ -27,8 +27,8 @@ import os
 import torch
 
 from . import _lib
-from ._compat_ops import (SparseAttentionFunction, lightning_indexer_fused,  # noqa: F401
-                          sparse_attention)
+from ._compat_ops import lightning_indexer_fused  # noqa: F401
+from .sparse_attention import SparseAttentionFunction, sparse_attention  # noqa: F401
 
 _L = _lib.lib
 FP8_E4M3_MAX = 448.0
@@ -479,6 +479,25 @@ def moe_combine(rows: torch.Tensor, pos: torch.Tensor, gates: torch.Tensor, adde
                        "cinn_moe_combine_add")
     _count()
     return y
+
+
+def gather_quantized_rows(x_fp8: torch.Tensor, x_scale: torch.Tensor, idx: torch.Tensor):
+    """``(x_fp8[idx], x_scale[idx])`` in one pass: the dispatch gather of ``MoE.forward``
+    (reference src/layers.py:140) on tokens quantised once before the gather."""
+    assert x_fp8.is_cuda and x_scale.is_cuda and idx.is_cuda, "Inputs must be on CUDA"
+    n_src, d = x_fp8.shape
+    x_fp8, x_scale = x_fp8.contiguous(), x_scale.float().contiguous()
+    idx = idx.to(torch.int64).contiguous()
+    n_out, ns = idx.numel(), x_scale.shape[1]
+    if d % 16 != 0:
+        return x_fp8.view(torch.uint8).index_select(0, idx).view(x_fp8.dtype), x_scale.index_select(0, idx)
+    with torch.cuda.device(x_fp8.device):
+        out_q = torch.empty((n_out, d), dtype=x_fp8.dtype, device=x_fp8.device)
+        out_s = torch.empty((n_out, ns), dtype=torch.float32, device=x_fp8.device)
+        _lib.check(_L.cinn_gather_rows(_ptr(x_fp8), _ptr(x_scale), _ptr(idx), _ptr(out_q), _ptr(out_s), n_out, n_src, d, ns,
+                                       _stream(x_fp8)), "cinn_gather_rows")
+    _count()
+    return out_q, out_s
 
 
 def moe_route(logits: torch.Tensor, bias: torch.Tensor, top_k: int):

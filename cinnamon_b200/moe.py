@@ -213,27 +213,26 @@ def all_to_all_rows(rows: torch.Tensor, send_splits, recv_splits, group=None) ->
 # the layer
 # ---------------------------------------------------------------------------------------
 def moe_forward(x: torch.Tensor, routing: Routing, experts: Callable, quantize: Optional[Callable],
-                group=None, addend: Optional[torch.Tensor] = None) -> torch.Tensor:
+                group=None, addend: Optional[torch.Tensor] = None, before_combine: Optional[Callable] = None) -> torch.Tensor:
     """Routed part of ``MoE.forward`` for this rank's tokens ``x`` (T, d).
 
     ``experts(rows_q, rows_s, starts, ends)`` computes the expert SwiGLU for rows grouped by
     local expert; ``quantize(x) -> (q, s)`` is the row-wise quantiser (``None`` = rows travel
     unquantised and ``experts`` receives ``(rows, None, starts, ends)``: the CPU test path).
     ``addend`` (T, d), optional: the shared experts' output, folded into the combine pass
-    (``shared_out + routed_out``, src/layers.py:179).
+    (``shared_out + routed_out``, src/layers.py:179); ``before_combine`` is called right before that pass.
     Returns the gate-weighted sum over each token's experts (plus ``addend``), fp32 (T, d).
     """
     T, d = x.shape
     plan = make_plan(routing.counts, group, n_pairs=routing.token_indices.numel())
     if quantize is not None:
         x_q, x_s = quantize(x)
-        send_q = x_q.view(torch.uint8).index_select(0, routing.token_indices).view(x_q.dtype)
-        send_s = x_s.index_select(0, routing.token_indices)
+        from . import kernels as K
+        send_q, send_s = K.gather_quantized_rows(x_q, x_s, routing.token_indices)
         recv_q = all_to_all_rows(send_q, plan.send_splits, plan.recv_splits, group)
         recv_s = all_to_all_rows(send_s, plan.send_splits, plan.recv_splits, group)
         if len(plan.recv_splits) > 1:
-            recv_q = recv_q.view(torch.uint8).index_select(0, plan.perm).view(x_q.dtype)
-            recv_s = recv_s.index_select(0, plan.perm)
+            recv_q, recv_s = K.gather_quantized_rows(recv_q, recv_s, plan.perm)
         out_rows = experts(recv_q, recv_s, plan.starts, plan.ends)
     else:
         send = x.index_select(0, routing.token_indices)
@@ -246,6 +245,8 @@ def moe_forward(x: torch.Tensor, routing: Routing, experts: Callable, quantize: 
         back = torch.empty_like(out_rows)
         back.index_copy_(0, plan.perm, out_rows)
         out_rows = all_to_all_rows(back, plan.recv_splits, plan.send_splits, group)
+    if before_combine is not None:
+        before_combine()                       # e.g. join the stream that produced ``addend``
     if out_rows.is_cuda:
         from . import kernels as K
         return K.moe_combine(out_rows, routing.pair_pos, routing.pair_gate, addend)   # src/layers.py:157-160, fused
@@ -274,6 +275,7 @@ class ExpertParallelMoE(torch.nn.Module):
         self.group = group
         self.experts = FP8Experts(w12_local, w3_local)
         self.shared = shared
+        self._side = None
 
     def _router_as(self, dtype: torch.dtype) -> torch.Tensor:
         """The router weight in the activations' 16-bit type, converted when the weight changes, not per call."""
@@ -288,6 +290,22 @@ class ExpertParallelMoE(torch.nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         flat = x.reshape(-1, x.shape[-1])
         r = route(flat, self._router_as(flat.dtype), self.expert_bias, self.top_k)
-        sh = self.shared(flat) if self.shared is not None else None
-        y = moe_forward(flat, r, self.experts, self.K.quantize_fp8_rowwise, self.group, addend=sh)
+        sh = None
+        world = dist.get_world_size(self.group) if dist.is_initialized() else 1
+        if self.shared is not None and world > 1 and flat.is_cuda:
+            # the shared expert needs nothing from the exchange: it runs on a second stream, under the
+            # all-to-alls and the host read-back of the split sizes, and is joined before the combine pass
+            cur = torch.cuda.current_stream(flat.device)
+            if self._side is None:
+                self._side = torch.cuda.Stream(flat.device)
+            self._side.wait_stream(cur)
+            with torch.cuda.stream(self._side):
+                sh = self.shared(flat)
+            sh.record_stream(cur)
+            y = moe_forward(flat, r, self.experts, self.K.quantize_fp8_rowwise, self.group, addend=sh,
+                            before_combine=lambda: cur.wait_stream(self._side))
+        else:
+            if self.shared is not None:
+                sh = self.shared(flat)
+            y = moe_forward(flat, r, self.experts, self.K.quantize_fp8_rowwise, self.group, addend=sh)
         return y.reshape(x.shape)

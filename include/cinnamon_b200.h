@@ -143,6 +143,32 @@ int cinn_moe_combine(const void* rows, int dtype, const int64_t* pos, const floa
 int cinn_moe_combine_add(const void* rows, int dtype, const int64_t* pos, const float* gates, const void* addend,
                          int addend_dtype, void* y, int64_t n_tokens, int64_t n_rows, int top_k, int64_t d, void* stream);
 
+/* Sparse attention over per-query index lists, forward.
+ * Replaces sparse_attention_fwd_kernel + SparseAttentionFunction.forward (src/kernels.py:913-1052, 1194-1245).
+ * q, k: (B, H, L, d_qk), v: (B, H, L, d_v) of `dtype`, contiguous; idx: (B, L, K) int64, shared by the heads.
+ * Key idx[b, t, j] takes part in query t when 0 <= idx <= t.  out: (B, H, L, d_v) fp32; lse: (B, H, L) fp32;
+ * attn_weights: (B, H, L, K) fp32 probabilities (0 for keys that do not take part; a query without any valid
+ * key gets all-zero weights, zero output and lse 0). */
+int cinn_sparse_attn_fwd(const void* q, const void* k, const void* v, int dtype, const int64_t* idx, float* out, float* lse,
+                         float* attn_weights, int64_t B, int64_t H, int64_t L, int64_t K, int64_t d_qk, int64_t d_v,
+                         float scale, void* stream);
+
+/* Backward of the above.  Replaces sparse_attention_bwd_kernel + SparseAttentionFunction.backward
+ * (src/kernels.py:1055-1186, 1247-1289).  grad_out: (B, H, L, d_v) of `grad_dtype` (the inputs' type or fp32);
+ * out, lse: as saved by the forward.  grad_q is written; grad_k and grad_v (fp32, same shapes as k and v) are
+ * ACCUMULATED into with fp32 atomics, so the caller zeroes them first, as the reference does (:1257-1259). */
+int cinn_sparse_attn_bwd(const void* grad_out, int grad_dtype, const float* out, const float* lse, const void* q,
+                         const void* k, const void* v, int dtype, const int64_t* idx, float* grad_q, float* grad_k,
+                         float* grad_v, int64_t B, int64_t H, int64_t L, int64_t K, int64_t d_qk, int64_t d_v, float scale,
+                         void* stream);
+
+/* Dispatch gather of quantised tokens: out_q[r, :] = q[idx[r], :], out_scales[r, :] = scales[idx[r], :] for
+ * r < n_out, in one pass (the `flat_x[token_indices]` of MoE.forward, src/layers.py:140, on tokens that were
+ * quantised once before the gather).  q: (n_src, d) e4m3 bytes, d a multiple of 16; scales: (n_src, n_scales)
+ * fp32; idx: (n_out) int64, entries outside [0, n_src) leave their output row untouched. */
+int cinn_gather_rows(const void* q, const float* scales, const int64_t* idx, void* out_q, float* out_scales, int64_t n_out,
+                     int64_t n_src, int64_t d, int64_t n_scales, void* stream);
+
 /* Routing of MoE.forward (src/layers.py:122-148) on the device: scores = sigmoid(logits), the top_k experts of
  * scores + bias per token (ties: the lower expert id), gates = score / (sum of the k scores + 1e-9), and the
  * (token, expert) pairs sorted by expert in the order of a stable sort.

@@ -96,6 +96,17 @@ def test_route_kernel_matches_torch(K, T, E, k):
         assert torch.equal(got[key], again[key]), key
 
 
+def test_gather_quantized_rows(K):
+    g = torch.Generator().manual_seed(5)
+    q = torch.randint(0, 256, (300, 512), generator=g, dtype=torch.uint8).cuda().view(torch.float8_e4m3fn)
+    s = torch.rand(300, 4, generator=g).cuda()
+    idx = torch.randint(0, 300, (1000,), generator=g).cuda()
+    out_q, out_s = K.gather_quantized_rows(q, s, idx)
+    assert torch.equal(out_q.view(torch.uint8), q.view(torch.uint8)[idx]) and torch.equal(out_s, s[idx])
+    out_q, out_s = K.gather_quantized_rows(q[:, :72].contiguous(), s[:, :1].contiguous(), idx)   # width not a multiple of 16
+    assert torch.equal(out_q.view(torch.uint8), q.view(torch.uint8)[:, :72][idx]) and torch.equal(out_s, s[:, :1][idx])
+
+
 def test_route_empty(K):
     got = K.moe_route(torch.empty(0, 32, device="cuda"), torch.zeros(32, device="cuda"), 4)
     assert got["counts"].tolist() == [0] * 32 and got["token_indices"].numel() == 0
@@ -189,7 +200,13 @@ x = torch.randn(T, d, generator=torch.Generator().manual_seed(50 + rank)).bfloat
 r = moe.route(x, router, bias, k)
 lo, hi = rank * E // world, (rank + 1) * E // world
 y_ep = moe.moe_forward(x, r, moe.FP8Experts(w12[lo:hi], w3[lo:hi]), K.quantize_fp8_rowwise)
-torch.save({"y_ep": y_ep.cpu(), "x": x.cpu(), "status": K.device_status()}, os.path.join(sys.argv[2], f"ep_{rank}.pt"))
+# the whole layer: the shared expert runs on a second stream under the exchange
+s1, s2, s3 = [(torch.randn(*shape, generator=g) * 0.02).cuda() for shape in ((384, d), (384, d), (d, 384))]
+layer = moe.ExpertParallelMoE(router, bias, w12[lo:hi], w3[lo:hi], k, shared=moe.FP8SwiGLU(s1, s2, s3))
+y_layer = [layer(x) for _ in range(3)][-1]
+torch.cuda.synchronize()
+torch.save({"y_ep": y_ep.cpu(), "y_layer": y_layer.cpu(), "x": x.cpu(), "status": K.device_status()},
+           os.path.join(sys.argv[2], f"ep_{rank}.pt"))
 dist.barrier(); dist.destroy_process_group()
 '''
 
@@ -213,12 +230,15 @@ def test_expert_parallel_two_gpus_match_one(K, tmp_path):
     w12 = (torch.randn(E, 2 * I, d, generator=g) * 0.02).bfloat16().cuda()
     w3 = (torch.randn(E, d, I, generator=g) * 0.02).bfloat16().cuda()
     experts = moe.FP8Experts(w12, w3)
+    s1, s2, s3 = [(torch.randn(*shape, generator=g) * 0.02).cuda() for shape in ((384, d), (384, d), (d, 384))]
+    shared = moe.FP8SwiGLU(s1, s2, s3)
     for rank in range(2):
         got = torch.load(tmp_path / f"ep_{rank}.pt")
         assert got["status"] == 0
         x = got["x"].cuda()
         r = moe.route(x, router, bias, k)
         y_one = moe.moe_forward(x, r, experts, K.quantize_fp8_rowwise)
+        assert rel_fro(got["y_layer"], (shared(x).float() + y_one).cpu().double()) < 1e-6
         # same e4m3 payloads and the same per-row arithmetic: only the fp32 summation order of a token's
         # experts could differ, and index_add_ keeps it
         assert rel_fro(got["y_ep"], y_one.cpu().double()) < 1e-6
