@@ -237,6 +237,52 @@ def bench_kernels(Kmod, dev, x, w, dy, peaks):
         aq, as_ = Kmod.quantize_fp8_rowwise(a)
         bq, bs = Kmod.quantize_fp8_blockwise(b)
         gemm_line(f"gemm {name} ({m} tokens)", lambda: Kmod.fp8_matmul_dsv3(aq, bq.t(), as_, bs.t()), 2.0 * m * n * k)
+    del a, b, aq, as_, bq, bs
+    # MoE plumbing at the C4 sizes (32768 tokens, top-8, d = 7168, I = 2048): HBM-bound passes
+    T, E, k8, d, I = MOE["tokens"], MOE["E"], MOE["top_k"], MOE["d"], MOE["I"]
+    logits = torch.randn(T, E, generator=g, device=dev)
+    bias = torch.randn(E, generator=g, device=dev)
+    quant_line("moe_route 32768 tokens x 256 experts, top-8 (3 launches)", lambda: Kmod.moe_route(logits, bias, k8),
+               T * E * 4 + T * k8 * (4 + 4 + 8 + 4 + 8 + 8 + 4))
+    r = Kmod.moe_route(logits, bias, k8)
+    tq, ts = Kmod.quantize_fp8_rowwise(torch.randn(T, d, generator=g, device=dev).to(torch.bfloat16))
+    quant_line("gather_rows e4m3 [262144,7168] + scales", lambda: Kmod.gather_quantized_rows(tq, ts, r["token_indices"]),
+               T * k8 * (d + 4 * (d // 128)) * 2)
+    del tq, ts
+    h12 = torch.randn(T * k8 // 2, 2 * I, generator=g, device=dev).to(torch.bfloat16)
+    quant_line("swiglu_quant_row h12[131072,4096] bf16", lambda: Kmod.swiglu_quantize_rowwise(h12),
+               (T * k8 // 2) * (2 * I * 2 + I + 4 * (I // 128)))
+    del h12
+    rows = torch.randn(T * k8, d, generator=g, device=dev).to(torch.bfloat16)
+    shared = torch.randn(T, d, generator=g, device=dev).to(torch.bfloat16)
+    quant_line("moe_combine + shared [262144,7168] bf16 -> [32768,7168] fp32",
+               lambda: Kmod.moe_combine(rows, r["pair_pos"], r["pair_gate"], shared), T * k8 * d * 2 + T * d * (2 + 4))
+    del rows, shared, logits
+    # sparse attention at the model's sizes (PoPE: 192-wide queries/keys, 64-wide values, 128 selected keys); the bound
+    # is the L2 -> SM gather traffic, reported as such (no measured peak for it)
+    Bs, Hs, Ls, Ks, Dq, Dvv = 32, 8, 1024, 128, 192, 64
+    qa = torch.randn(Bs, Hs, Ls, Dq, generator=g, device=dev).to(torch.bfloat16).requires_grad_(True)
+    ka = torch.randn(Bs, Hs, Ls, Dq, generator=g, device=dev).to(torch.bfloat16).requires_grad_(True)
+    va = torch.randn(Bs, Hs, Ls, Dvv, generator=g, device=dev).to(torch.bfloat16).requires_grad_(True)
+    pos = torch.arange(Ls, device=dev).view(1, Ls, 1)
+    idx = (torch.rand(Bs, Ls, Ks, generator=g, device=dev) * (pos + 1)).long().clamp(max=Ls - 1)
+    go = torch.randn(Bs, Hs, Ls, Dvv, generator=g, device=dev).to(torch.bfloat16)
+    gathered = Bs * Hs * Ls * Ks * (Dq + Dvv) * 2
+
+    def attn_fwd():
+        with torch.no_grad():
+            Kmod.sparse_attention(qa, ka, va, idx)
+
+    def attn_fwd_bwd():
+        o, _ = Kmod.sparse_attention(qa, ka, va, idx)
+        o.backward(go)
+        qa.grad = ka.grad = va.grad = None
+
+    for name, fn, nbytes in (("sparse_attention forward B32 H8 L1024 K128 d192/64 bf16", attn_fwd, gathered),
+                             ("sparse_attention forward+backward (same)", attn_fwd_bwd, 3 * gathered)):
+        ms = _time_kernel(fn)
+        out.append({"kernel": name, "ms": ms, "bound": "l2 gather", "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": None,
+                    "unit": "GB/s gathered", "frac": None})
     return out
 
 
