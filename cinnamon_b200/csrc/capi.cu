@@ -58,6 +58,9 @@ int sparse_attn_fwd(const void* q, const void* k, const void* v, int dtype, cons
 int sparse_attn_bwd(const void* d_out, int grad_dtype, const float* out, const float* lse, const void* q, const void* k,
                     const void* v, int dtype, const int64_t* idx, float* dq, float* dk, float* dv, int64_t B, int64_t H,
                     int64_t L, int64_t K, int64_t Dqk, int64_t Dv, float scale, cudaStream_t st);
+int lightning_indexer(const void* q, const void* k, const void* w, int dtype, void* out, int64_t B, int64_t Lq, int64_t Lk,
+                      int64_t H, int64_t d, const int64_t* q_strides, const int64_t* k_strides, const int64_t* w_strides,
+                      cudaStream_t st);
 int64_t moe_route_workspace_ints(int64_t T, int E);
 int moe_route(const float* logits, const float* bias, int64_t T, int E, int top_k, int* workspace, int* top_experts,
               float* top_gates, int64_t* token_indices, float* sorted_scores, int64_t* sorted_experts, int64_t* counts,
@@ -164,6 +167,12 @@ int cinn_sparse_attn_bwd(const void* grad_out, int grad_dtype, const float* out,
                          void* stream) {
     return cinn::sparse_attn_bwd(grad_out, grad_dtype, out, lse, q, k, v, dtype, idx, grad_q, grad_k, grad_v, B, H, L, K, d_qk,
                                  d_v, scale, (cudaStream_t)stream);
+}
+
+int cinn_lightning_indexer(const void* q, const void* k, const void* w, int dtype, void* out, int64_t B, int64_t Lq,
+                           int64_t Lk, int64_t H, int64_t d, const int64_t* q_strides, const int64_t* k_strides,
+                           const int64_t* w_strides, void* stream) {
+    return cinn::lightning_indexer(q, k, w, dtype, out, B, Lq, Lk, H, d, q_strides, k_strides, w_strides, (cudaStream_t)stream);
 }
 
 int64_t cinn_moe_route_workspace_ints(int64_t n_tokens, int n_experts) {

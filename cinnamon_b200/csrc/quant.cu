@@ -676,32 +676,43 @@ requant_row_to_block_kernel(const uint8_t* __restrict__ xq, const float* __restr
 template <typename T, int DIV>
 __global__ void __launch_bounds__(256)
 swiglu_quant_row_kernel(const T* __restrict__ h12, uint8_t* __restrict__ q, float* __restrict__ scales,
-                        int I, int nb, int64_t total_tiles) {
+                        int I, int nb, int64_t total_tiles, int step_rows, int step_cols) {
+    // the n-th tile of this half-warp is hw + n * n_hw; (step_rows, step_cols) = divmod(n_hw, nb): tile
+    // coordinates advance without a division in the loop
     const int sub = threadIdx.x & 15;
     const int64_t hw = (int64_t)blockIdx.x * 16 + (threadIdx.x >> 4);
     const int64_t n_hw = (int64_t)gridDim.x * 16;
+    int64_t t = hw;                                  // next tile to FETCH
+    int row = (int)(hw / nb);
+    int cb = (int)(hw - (int64_t)row * nb);
     // the raw vectors of the next tile are in flight while this one is converted
     Raw8<T> na = zero_raw8<T>(), nb8 = zero_raw8<T>();
-    auto fetch = [&](int64_t t) {
-        const int64_t row = t / nb;
-        const int col = (int)(t - row * nb) * 128 + sub * 8;
-        if (t < total_tiles && col < I) {
-            na = load_raw8<T>(h12 + row * 2 * (int64_t)I + col);
-            nb8 = load_raw8<T>(h12 + row * 2 * (int64_t)I + I + col);
-        }
-    };
-    fetch((hw & ~(int64_t)1) + (hw & 1));
-    for (int64_t tw = hw & ~(int64_t)1; tw < total_tiles; tw += n_hw) {
-        const int64_t t = tw + (hw & 1);
-        const int64_t row = t / nb;
-        const int col = (int)(t - row * nb) * 128 + sub * 8;
-        const bool inb = t < total_tiles && col < I;
-        const Raw8<T> ca = na, cb = nb8;
-        fetch(t + n_hw);
-        float a[8], b[8], v[8];
+    int64_t n_off = -1, n_tile = -1;
+    auto fetch = [&]() {
+        const int col = cb * 128 + sub * 8;
+        const bool live = t < total_tiles;
+        const bool inb = live && col < I;
         if (inb) {
+            const T* p = h12 + (int64_t)row * 2 * I + col;
+            na = load_raw8<T>(p);
+            nb8 = load_raw8<T>(p + I);
+        }
+        n_off = inb ? (int64_t)row * I + col : -1;
+        n_tile = live ? t : -1;
+        t += n_hw;
+        row += step_rows;
+        cb += step_cols;
+        if (cb >= nb) { cb -= nb; row += 1; }
+    };
+    fetch();
+    for (int64_t tw = hw & ~(int64_t)1; tw < total_tiles; tw += n_hw) {
+        const Raw8<T> ca = na, cb_raw = nb8;
+        const int64_t off = n_off, tile = n_tile;
+        fetch();
+        float a[8], b[8], v[8];
+        if (off >= 0) {
             unpack_raw8<T>(ca, a);
-            unpack_raw8<T>(cb, b);
+            unpack_raw8<T>(cb_raw, b);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 // 16-bit activations: silu to a few fp32 ulp (ex2.approx and div.approx), far inside the rounding to
@@ -725,13 +736,13 @@ swiglu_quant_row_kernel(const T* __restrict__ h12, uint8_t* __restrict__ q, floa
         for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
         const float s = scale_from_amax<DIV, false>(amax);
         const float d = divisor_of<DIV>(s);
-        if (inb) {
+        if (off >= 0) {
             uint2 o2;
             o2.x = cvt_e4m3x4(scaled_clamped<DIV>(v[0], d), scaled_clamped<DIV>(v[1], d), scaled_clamped<DIV>(v[2], d), scaled_clamped<DIV>(v[3], d));
             o2.y = cvt_e4m3x4(scaled_clamped<DIV>(v[4], d), scaled_clamped<DIV>(v[5], d), scaled_clamped<DIV>(v[6], d), scaled_clamped<DIV>(v[7], d));
-            __stcs(reinterpret_cast<uint2*>(q + row * (int64_t)I + col), o2);
+            __stcs(reinterpret_cast<uint2*>(q + off), o2);
         }
-        if (sub == 0 && t < total_tiles) scales[t] = s;
+        if (sub == 0 && tile >= 0) scales[tile] = s;
     }
 }
 
@@ -1029,8 +1040,10 @@ static int launch_swiglu(const T* h12, int64_t T_rows, int64_t I, uint8_t* q, fl
     int64_t blocks = (tiles + 15) / 16;
     const int64_t cap = (int64_t)sm_count() * 8;
     if (blocks > cap) blocks = cap;
-    if (div_mode == CINN_DIV_FULL) swiglu_quant_row_kernel<T, CINN_DIV_FULL><<<(unsigned)blocks, 256, 0, st>>>(h12, q, scales, (int)I, nb, tiles);
-    else swiglu_quant_row_kernel<T, CINN_DIV_RN><<<(unsigned)blocks, 256, 0, st>>>(h12, q, scales, (int)I, nb, tiles);
+    const int64_t n_hw = blocks * 16;
+    const int sr = (int)(n_hw / nb), sc = (int)(n_hw % nb);
+    if (div_mode == CINN_DIV_FULL) swiglu_quant_row_kernel<T, CINN_DIV_FULL><<<(unsigned)blocks, 256, 0, st>>>(h12, q, scales, (int)I, nb, tiles, sr, sc);
+    else swiglu_quant_row_kernel<T, CINN_DIV_RN><<<(unsigned)blocks, 256, 0, st>>>(h12, q, scales, (int)I, nb, tiles, sr, sc);
     CINN_CHECK_LAUNCH();
     return CINN_OK;
 }

@@ -23,32 +23,56 @@ template <> __device__ __forceinline__ float to_float<float>(float v) { return v
 template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <> __device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
 
-// dot product of an fp32 vector in shared memory with a row of T in global memory
+// Part of the dot product of an fp32 vector in shared memory with a row of T in global memory: eight lanes share a
+// row, lane l8 of them takes the 16-byte chunks l8, l8 + 8, ... (so the eight lanes read 128 contiguous bytes per
+// step), up to four chunks are fetched before any is used.  The caller adds the eight partial sums.
 template <typename T>
-__device__ __forceinline__ float dot_row(const float* __restrict__ qs, const T* __restrict__ row, int D, bool vec) {
+__device__ __forceinline__ float dot_row_part(const float* __restrict__ qs, const T* __restrict__ row, int D, int l8, bool vec) {
     float acc = 0.0f;
     if (vec) {
         constexpr int PER = 16 / (int)sizeof(T);                // elements per 16-byte load
-        for (int d = 0; d < D; d += PER) {
-            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(row + d));
-            if constexpr (sizeof(T) == 4) {
-                const float4 f = *reinterpret_cast<const float4*>(&raw);
-                const float4 qv = *reinterpret_cast<const float4*>(qs + d);
-                acc = fmaf(f.x, qv.x, acc); acc = fmaf(f.y, qv.y, acc); acc = fmaf(f.z, qv.z, acc); acc = fmaf(f.w, qv.w, acc);
-            } else {
-                const T* e = reinterpret_cast<const T*>(&raw);
-                const float4 q0 = *reinterpret_cast<const float4*>(qs + d);
-                const float4 q1 = *reinterpret_cast<const float4*>(qs + d + 4);
-                acc = fmaf(to_float<T>(e[0]), q0.x, acc); acc = fmaf(to_float<T>(e[1]), q0.y, acc);
-                acc = fmaf(to_float<T>(e[2]), q0.z, acc); acc = fmaf(to_float<T>(e[3]), q0.w, acc);
-                acc = fmaf(to_float<T>(e[4]), q1.x, acc); acc = fmaf(to_float<T>(e[5]), q1.y, acc);
-                acc = fmaf(to_float<T>(e[6]), q1.z, acc); acc = fmaf(to_float<T>(e[7]), q1.w, acc);
+        const int chunks = D / PER;
+        for (int c0 = l8; c0 < chunks; c0 += 32) {
+            uint4 raw[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int c = c0 + 8 * u;
+                raw[u] = c < chunks ? __ldg(reinterpret_cast<const uint4*>(row) + c) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int c = c0 + 8 * u;
+                if (c < chunks) {
+                    const float* qv = qs + c * PER;
+                    if constexpr (sizeof(T) == 4) {
+                        const float4 f = *reinterpret_cast<const float4*>(&raw[u]);
+                        const float4 q0 = *reinterpret_cast<const float4*>(qv);
+                        acc = fmaf(f.x, q0.x, acc); acc = fmaf(f.y, q0.y, acc); acc = fmaf(f.z, q0.z, acc); acc = fmaf(f.w, q0.w, acc);
+                    } else {
+                        const T* e = reinterpret_cast<const T*>(&raw[u]);
+                        const float4 q0 = *reinterpret_cast<const float4*>(qv);
+                        const float4 q1 = *reinterpret_cast<const float4*>(qv + 4);
+                        float a0 = to_float<T>(e[0]) * q0.x, a1 = to_float<T>(e[1]) * q0.y;
+                        a0 = fmaf(to_float<T>(e[2]), q0.z, a0); a1 = fmaf(to_float<T>(e[3]), q0.w, a1);
+                        a0 = fmaf(to_float<T>(e[4]), q1.x, a0); a1 = fmaf(to_float<T>(e[5]), q1.y, a1);
+                        a0 = fmaf(to_float<T>(e[6]), q1.z, a0); a1 = fmaf(to_float<T>(e[7]), q1.w, a1);
+                        acc += a0 + a1;
+                    }
+                }
             }
         }
     } else {
-        for (int d = 0; d < D; ++d) acc = fmaf(to_float<T>(row[d]), qs[d], acc);
+        for (int d = l8; d < D; d += 8) acc = fmaf(to_float<T>(row[d]), qs[d], acc);
     }
     return acc;
+}
+
+// sum over the eight lanes that share a row
+__device__ __forceinline__ float group8_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    return v;
 }
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -95,13 +119,18 @@ sparse_attn_fwd_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
         }
         __syncwarp();
         float mx = -INFINITY;
-        for (int j = lane; j < K; j += 32) {
-            const int i = s_idx[j];
-            float sc = -INFINITY;
-            if (i >= 0) sc = dot_row<T>(s_q, kb + (int64_t)i * Dqk, Dqk, vec_qk) * scale;
-            s_p[j] = sc;
+        const int grp = lane >> 3, l8 = lane & 7;                     // four keys per step, eight lanes per key
+        for (int j0 = 0; j0 < K; j0 += 4) {
+            const int j = j0 + grp;
+            const int i = j < K ? s_idx[j] : -1;
+            float part = 0.0f;
+            if (i >= 0) part = dot_row_part<T>(s_q, kb + (int64_t)i * Dqk, Dqk, l8, vec_qk);
+            const float red = group8_sum(part);                       // every lane takes part in the shuffles
+            const float sc = i >= 0 ? red * scale : -INFINITY;
+            if (l8 == 0 && j < K) s_p[j] = sc;
             mx = fmaxf(mx, sc);
         }
+        __syncwarp();
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
         float sum = 0.0f;
@@ -123,9 +152,9 @@ sparse_attn_fwd_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
         for (int d0 = lane * 2; d0 < Dv; d0 += 64) {
             float a0 = 0.0f, a1 = 0.0f;
             const bool two = d0 + 1 < Dv;
+#pragma unroll 8
             for (int j = 0; j < K; ++j) {
-                const int i = s_idx[j];
-                if (i < 0) continue;
+                const int i = max(s_idx[j], 0);                         // a key that takes no part has p = 0
                 const float p = s_p[j];
                 const T* vr = vb + (int64_t)i * Dv + d0;
                 a0 = fmaf(p, to_float<T>(vr[0]), a0);
@@ -179,18 +208,26 @@ sparse_attn_bwd_kernel(const TG* __restrict__ d_out, const float* __restrict__ o
         }
         __syncwarp();
         const float l = lse[w];
-        for (int j = lane; j < K; j += 32) {
-            const int i = s_idx[j];
-            float p = 0.0f, dp = 0.0f;
+        const int grp = lane >> 3, l8 = lane & 7;                     // four keys per step, eight lanes per key
+        for (int j0 = 0; j0 < K; j0 += 4) {
+            const int j = j0 + grp;
+            const int i = j < K ? s_idx[j] : -1;
+            float qk = 0.0f, dov = 0.0f;
             if (i >= 0) {
-                p = expf(dot_row<T>(s_q, kb + (int64_t)i * Dqk, Dqk, vec_qk) * scale - l);
-                dp = p * (dot_row<T>(s_do, vb + (int64_t)i * Dv, Dv, vec_v) - delta);
+                qk = dot_row_part<T>(s_q, kb + (int64_t)i * Dqk, Dqk, l8, vec_qk);
+                dov = dot_row_part<T>(s_do, vb + (int64_t)i * Dv, Dv, l8, vec_v);
             }
-            s_pp[j] = p;
-            s_p[j] = dp;
+            qk = group8_sum(qk);
+            dov = group8_sum(dov);
+            if (l8 == 0 && j < K) {
+                const float p = i >= 0 ? expf(qk * scale - l) : 0.0f;
+                s_pp[j] = p;
+                s_p[j] = p * (dov - delta);
+            }
         }
         __syncwarp();
         // dq[d] = scale * sum_j dp_j k_j[d];  dk[idx_j][d] += scale * dp_j q[d]
+        const bool pair_qk = (Dqk & 1) == 0, pair_v = (Dv & 1) == 0;     // even widths: 8-byte aligned float2 atomics
         for (int d0 = lane * 2; d0 < Dqk; d0 += 64) {
             float a0 = 0.0f, a1 = 0.0f;
             const bool two = d0 + 1 < Dqk;
@@ -200,11 +237,14 @@ sparse_attn_bwd_kernel(const TG* __restrict__ d_out, const float* __restrict__ o
                 if (i < 0) continue;
                 const float dp = s_p[j] * scale;
                 const T* kr = kb + (int64_t)i * Dqk + d0;
+                float* dst = dkb + (int64_t)i * Dqk + d0;
                 a0 = fmaf(dp, to_float<T>(kr[0]), a0);
-                atomicAdd(dkb + (int64_t)i * Dqk + d0, dp * q0);
-                if (two) {
-                    a1 = fmaf(dp, to_float<T>(kr[1]), a1);
-                    atomicAdd(dkb + (int64_t)i * Dqk + d0 + 1, dp * q1);
+                if (two) a1 = fmaf(dp, to_float<T>(kr[1]), a1);
+                if (pair_qk) {
+                    atomicAdd(reinterpret_cast<float2*>(dst), make_float2(dp * q0, dp * q1));
+                } else {
+                    atomicAdd(dst, dp * q0);
+                    if (two) atomicAdd(dst + 1, dp * q1);
                 }
             }
             dq[w * Dqk + d0] = a0;
@@ -218,8 +258,13 @@ sparse_attn_bwd_kernel(const TG* __restrict__ d_out, const float* __restrict__ o
                 const int i = s_idx[j];
                 if (i < 0) continue;
                 const float p = s_pp[j];
-                atomicAdd(dvb + (int64_t)i * Dv + d0, p * g0);
-                if (two) atomicAdd(dvb + (int64_t)i * Dv + d0 + 1, p * g1);
+                float* dst = dvb + (int64_t)i * Dv + d0;
+                if (pair_v) {
+                    atomicAdd(reinterpret_cast<float2*>(dst), make_float2(p * g0, p * g1));
+                } else {
+                    atomicAdd(dst, p * g0);
+                    if (two) atomicAdd(dst + 1, p * g1);
+                }
             }
         }
         __syncwarp();

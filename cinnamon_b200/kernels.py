@@ -27,7 +27,6 @@ import os
 import torch
 
 from . import _lib
-from ._compat_ops import lightning_indexer_fused  # noqa: F401
 from .sparse_attention import SparseAttentionFunction, sparse_attention  # noqa: F401
 
 _L = _lib.lib
@@ -479,6 +478,26 @@ def moe_combine(rows: torch.Tensor, pos: torch.Tensor, gates: torch.Tensor, adde
                        "cinn_moe_combine_add")
     _count()
     return y
+
+
+def lightning_indexer_fused(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """Lightning indexer logits (reference src/kernels.py:392-433):
+    ``I[b, t, s] = sum_h relu(q[b, t, h] . k[b, s]) * w[b, t, h]``, dot-product operands rounded to fp16,
+    fp32 accumulation, fp16 result.  q (B, Lq, H, d), k (B, Lk, d), w (B, Lq, H), any strides."""
+    assert q.is_cuda and k.is_cuda, "Inputs must be on CUDA"
+    B, Lq, H, d = q.shape
+    Lk = k.shape[1]
+    work = q.dtype if q.dtype in _DTYPE_TAG else torch.float32
+    q, k, w = q.to(work), k.to(work), w.to(work)
+    with torch.cuda.device(q.device):
+        out = torch.empty((B, Lq, Lk), dtype=torch.float16, device=q.device)
+        sq = (ctypes.c_int64 * 4)(*q.stride())
+        sk = (ctypes.c_int64 * 3)(*k.stride())
+        sw = (ctypes.c_int64 * 3)(*w.stride())
+        _lib.check(_L.cinn_lightning_indexer(_ptr(q), _ptr(k), _ptr(w), _DTYPE_TAG[work], _ptr(out), B, Lq, Lk, H, d,
+                                             sq, sk, sw, _stream(q)), "cinn_lightning_indexer")
+    _count()
+    return out
 
 
 def gather_quantized_rows(x_fp8: torch.Tensor, x_scale: torch.Tensor, idx: torch.Tensor):

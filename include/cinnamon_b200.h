@@ -162,6 +162,15 @@ int cinn_sparse_attn_bwd(const void* grad_out, int grad_dtype, const float* out,
                          float* grad_v, int64_t B, int64_t H, int64_t L, int64_t K, int64_t d_qk, int64_t d_v, float scale,
                          void* stream);
 
+/* Lightning indexer logits: out[b, t, s] = sum_h relu(q[b, t, h, :] . k[b, s, :]) * w[b, t, h], fp16.
+ * Replaces lightning_indexer_kernel + lightning_indexer_fused (src/kernels.py:321-433): dot-product operands
+ * rounded to fp16, fp32 accumulation, ReLU and head weights in fp32.  q: (B, Lq, H, d), k: (B, Lk, d),
+ * w: (B, Lq, H) of `dtype`, with element strides q_strides[4], k_strides[3], w_strides[3] (HOST arrays, as the
+ * reference passes .stride(), :419-421); out: (B, Lq, Lk) fp16, contiguous. */
+int cinn_lightning_indexer(const void* q, const void* k, const void* w, int dtype, void* out, int64_t B, int64_t Lq,
+                           int64_t Lk, int64_t H, int64_t d, const int64_t* q_strides, const int64_t* k_strides,
+                           const int64_t* w_strides, void* stream);
+
 /* Dispatch gather of quantised tokens: out_q[r, :] = q[idx[r], :], out_scales[r, :] = scales[idx[r], :] for
  * r < n_out, in one pass (the `flat_x[token_indices]` of MoE.forward, src/layers.py:140, on tokens that were
  * quantised once before the gather).  q: (n_src, d) e4m3 bytes, d a multiple of 16; scales: (n_src, n_scales)

@@ -67,3 +67,11 @@ def backward(q, k, v, idx, scale, grad_out):
         dk[b].index_add_(1, flat, dk_c)
         dv[b].index_add_(1, flat, dv_c)
     return dq, dk, dv
+
+
+def lightning_indexer(q, k, w):
+    """Lightning indexer logits (src/kernels.py:321-433) in float64, rounded to fp16 at the end:
+    I[b, t, s] = sum_h relu(fp16(q[b, t, h]) . fp16(k[b, s])) * w[b, t, h]  (:374, :377, :381)."""
+    qh, kh = q.half().double(), k.half().double()
+    dots = torch.einsum("bthd,bsd->bths", qh, kh).clamp(min=0.0)
+    return torch.einsum("bths,bth->bts", dots, w.double())
