@@ -41,6 +41,8 @@ SIGNATURES = {
     "cinn_sparse_attn_bwd": [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
                              ctypes.c_float, _vp],
     "cinn_lightning_indexer": [_vp, _vp, _vp, _i32, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp],
+    "cinn_scatter_rows": [_vp, _vp, _vp, _i64, _i64, _i64, _vp],
+    "cinn_set_gemm_sm_limit": [_i32],
     "cinn_moe_combine_add": [_vp, _i32, _vp, _vp, _vp, _i32, _vp, _i64, _i64, _i32, _i64, _vp],
     "cinn_device_status": [ctypes.POINTER(ctypes.c_int), _i32],
     "cinn_fp8_grouped_gemm": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32, _vp],

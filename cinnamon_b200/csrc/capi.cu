@@ -61,6 +61,9 @@ int sparse_attn_bwd(const void* d_out, int grad_dtype, const float* out, const f
 int lightning_indexer(const void* q, const void* k, const void* w, int dtype, void* out, int64_t B, int64_t Lq, int64_t Lk,
                       int64_t H, int64_t d, const int64_t* q_strides, const int64_t* k_strides, const int64_t* w_strides,
                       cudaStream_t st);
+int scatter_rows(const void* in, const int64_t* idx, void* out, int64_t n_rows, int64_t n_dst, int64_t row_bytes,
+                 cudaStream_t st);
+int set_gemm_sm_limit(int n);
 int64_t moe_route_workspace_ints(int64_t T, int E);
 int moe_route(const float* logits, const float* bias, int64_t T, int E, int top_k, int* workspace, int* top_experts,
               float* top_gates, int64_t* token_indices, float* sorted_scores, int64_t* sorted_experts, int64_t* counts,
@@ -174,6 +177,13 @@ int cinn_lightning_indexer(const void* q, const void* k, const void* w, int dtyp
                            const int64_t* w_strides, void* stream) {
     return cinn::lightning_indexer(q, k, w, dtype, out, B, Lq, Lk, H, d, q_strides, k_strides, w_strides, (cudaStream_t)stream);
 }
+
+int cinn_scatter_rows(const void* in, const int64_t* idx, void* out, int64_t n_rows, int64_t n_dst, int64_t row_bytes,
+                      void* stream) {
+    return cinn::scatter_rows(in, idx, out, n_rows, n_dst, row_bytes, (cudaStream_t)stream);
+}
+
+int cinn_set_gemm_sm_limit(int n_sms) { return cinn::set_gemm_sm_limit(n_sms); }
 
 int64_t cinn_moe_route_workspace_ints(int64_t n_tokens, int n_experts) {
     return cinn::moe_route_workspace_ints(n_tokens, n_experts);

@@ -17,6 +17,7 @@
 #include "tma.cuh"
 #include <cuda.h>
 #include <mutex>
+#include <atomic>
 #include <cstdlib>
 
 namespace cinn {
@@ -700,6 +701,15 @@ static int pair_mode() {
     return mode;
 }
 
+// The persistent GEMM kernels normally take every SM.  A caller that wants other kernels to run beside them
+// (the send/receive kernels of an all-to-all on another stream) can cap the number of SMs they occupy.
+static std::atomic<int> g_gemm_sm_limit{0};
+static inline int gemm_sms() {
+    const int lim = g_gemm_sm_limit.load(std::memory_order_relaxed), all = sm_count();
+    return (lim > 0 && lim < all) ? lim : all;
+}
+int set_gemm_sm_limit(int n) { return g_gemm_sm_limit.exchange(n < 0 ? 0 : n); }
+
 static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 int fp8_gemm(const void* A, const float* sA, int64_t ld_sa, const void* B, const float* sB, int64_t sbk, int64_t sbn,
@@ -729,12 +739,12 @@ int fp8_gemm(const void* A, const float* sA, int64_t ld_sa, const void* B, const
     p.C = C; p.ldc = N; p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.starts = nullptr; p.ends = nullptr; p.E = 1; p.b_rows_per_expert = 0;
     if (use_pair) {
-        const int clusters = (int)(pair_tiles < sm_count() / 2 ? pair_tiles : sm_count() / 2);
+        const int clusters = (int)(pair_tiles < gemm_sms() / 2 ? pair_tiles : gemm_sms() / 2);
         return b_layout == 0 ? launch_pair_out<false>(ta, tb, p, out_dtype, clusters, st)
                              : launch_pair_out<true>(ta, tb, p, out_dtype, clusters, st);
     }
     const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    const int grid = (int)(tiles < gemm_sms() ? tiles : gemm_sms());
     return b_layout == 0 ? launch_out<false, false>(ta, tb, p, out_dtype, grid, st)
                          : launch_out<true, false>(ta, tb, p, out_dtype, grid, st);
 }
@@ -761,7 +771,7 @@ int fp8_grouped_gemm(const void* A, const float* sA, const void* W, const float*
     p.sB = sW; p.sb_stride_k = 1; p.sb_stride_n = nkb; p.sb_stride_e = nnb * nkb;
     p.C = C; p.ldc = d_out; p.M = (int)T; p.N = (int)d_out; p.K = (int)d_in;
     p.starts = starts; p.ends = ends; p.E = (int)E; p.b_rows_per_expert = (int)d_out;
-    return launch_out<false, true>(ta, tb, p, out_dtype, sm_count(), st);
+    return launch_out<false, true>(ta, tb, p, out_dtype, gemm_sms(), st);
 }
 
 // Input gradient of the grouped GEMM: dX[starts[e]:ends[e], :] = dY[starts[e]:ends[e], :] @ W[e]
@@ -792,7 +802,7 @@ int fp8_grouped_gemm_dgrad(const void* dY, const float* sdY, const void* W, cons
     p.sB = sW; p.sb_stride_k = nkb_in; p.sb_stride_n = 1; p.sb_stride_e = nob * nkb_in;
     p.C = dX; p.ldc = d_in; p.M = (int)T; p.N = (int)d_in; p.K = (int)d_out;
     p.starts = starts; p.ends = ends; p.E = (int)E; p.b_rows_per_expert = (int)d_out;
-    return launch_out<true, true>(ta, tb, p, out_dtype, sm_count(), st);
+    return launch_out<true, true>(ta, tb, p, out_dtype, gemm_sms(), st);
 }
 
 int read_quant_status(int* out, int reset);

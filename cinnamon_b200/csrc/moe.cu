@@ -136,4 +136,41 @@ int gather_rows(const void* q, const float* s, const int64_t* idx, void* out_q, 
     return CINN_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Row scatter: out[idx[r], :] = in[r, :] for rows of `row_bytes` bytes (a multiple of 16).  The way back from the
+// expert-grouped order to the arrival order before the rows travel home (the inverse of the regrouping gather).
+// One warp per row, 16-byte vectors.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+scatter_rows_kernel(const uint4* __restrict__ in, const int64_t* __restrict__ idx, uint4* __restrict__ out, int64_t n_rows,
+                    int64_t n_dst, int vecs) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int64_t n_warps = (int64_t)gridDim.x * 8;
+    for (int64_t r = warp; r < n_rows; r += n_warps) {
+        const int64_t dst = idx[r];
+        if (dst < 0 || dst >= n_dst) continue;
+        const uint4* src = in + r * vecs;
+        uint4* o = out + dst * vecs;
+        for (int v = lane; v < vecs; v += 32) __stcs(o + v, __ldcs(src + v));
+    }
+}
+
+int scatter_rows(const void* in, const int64_t* idx, void* out, int64_t n_rows, int64_t n_dst, int64_t row_bytes,
+                 cudaStream_t st) {
+    CINN_CHECK_ARG(n_rows >= 0 && n_dst >= 0 && row_bytes >= 0, "scatter_rows: negative shape");
+    if (n_rows == 0 || row_bytes == 0) return CINN_OK;
+    CINN_CHECK_ARG(in && idx && out, "scatter_rows: null pointer");
+    CINN_CHECK_ARG(row_bytes % 16 == 0 && row_bytes / 16 < (1LL << 31), "scatter_rows: the row size (%lld bytes) must be a multiple of 16",
+                   (long long)row_bytes);
+    CINN_CHECK_ARG((reinterpret_cast<uintptr_t>(in) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0,
+                   "scatter_rows: buffers must be 16-byte aligned");
+    int64_t blocks = (n_rows + 7) / 8;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    scatter_rows_kernel<<<(unsigned)blocks, 256, 0, st>>>((const uint4*)in, idx, (uint4*)out, n_rows, n_dst, (int)(row_bytes / 16));
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
 }  // namespace cinn

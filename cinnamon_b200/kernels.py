@@ -519,6 +519,30 @@ def gather_quantized_rows(x_fp8: torch.Tensor, x_scale: torch.Tensor, idx: torch
     return out_q, out_s
 
 
+def set_gemm_sm_limit(n_sms: int) -> int:
+    """Caps the SMs the persistent GEMM kernels occupy (0 = all); returns the previous cap."""
+    return int(_L.cinn_set_gemm_sm_limit(int(n_sms)))
+
+
+def scatter_rows(rows: torch.Tensor, idx: torch.Tensor, n_out: int = None) -> torch.Tensor:
+    """``out[idx[r]] = rows[r]`` (``out.index_copy_(0, idx, rows)`` into a fresh tensor) with 16-byte vectors."""
+    assert rows.is_cuda and idx.is_cuda, "Inputs must be on CUDA"
+    rows = rows.contiguous()
+    n, d = rows.shape
+    n_out = n if n_out is None else int(n_out)
+    row_bytes = d * rows.element_size()
+    if row_bytes % 16 != 0:
+        out = torch.empty((n_out, d), dtype=rows.dtype, device=rows.device)
+        return out.index_copy_(0, idx, rows)
+    idx = idx.to(torch.int64).contiguous()
+    with torch.cuda.device(rows.device):
+        out = torch.empty((n_out, d), dtype=rows.dtype, device=rows.device)
+        _lib.check(_L.cinn_scatter_rows(_ptr(rows), _ptr(idx), _ptr(out), n, n_out, row_bytes, _stream(rows)),
+                   "cinn_scatter_rows")
+    _count()
+    return out
+
+
 def moe_route(logits: torch.Tensor, bias: torch.Tensor, top_k: int):
     """Routing of ``MoE.forward`` (reference src/layers.py:122-148) from the router's fp32 logits, on the
     device and without a host synchronisation: sigmoid scores, top-k of score + bias, normalised gates, and the

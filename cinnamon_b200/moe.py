@@ -197,6 +197,34 @@ def make_plan(counts: torch.Tensor, group=None, n_pairs: Optional[int] = None) -
     return DispatchPlan(send_splits, recv_splits, recv_counts, perm, starts.contiguous(), ends.contiguous())
 
 
+def make_plans(counts_list, group=None):
+    """Plans for several token chunks from ONE exchange of counts and ONE host read-back (several ranks).
+    ``counts_list``: per chunk, the (E,) pairs this rank routed to every global expert."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        return [make_plan(c, group) for c in counts_list]
+    n_chunks = len(counts_list)
+    n_experts = counts_list[0].numel()
+    assert n_experts % world == 0, "experts must divide evenly over ranks"
+    e_local = n_experts // world
+    # (world, chunk, local expert): the slice for one destination rank is contiguous
+    send_counts = torch.stack([c.reshape(world, e_local).to(torch.int64) for c in counts_list], dim=1).contiguous()
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts, group=group)
+    splits = torch.stack([send_counts.sum(2), recv_counts.sum(2)]).tolist()         # [2][world][chunk]
+    plans = []
+    expert_of_segment = torch.arange(e_local, device=send_counts.device).repeat(world)
+    for c in range(n_chunks):
+        send_splits = [splits[0][g][c] for g in range(world)]
+        recv_splits = [splits[1][g][c] for g in range(world)]
+        rc = recv_counts[:, c, :].contiguous()
+        row_expert = torch.repeat_interleave(expert_of_segment, rc.reshape(-1), output_size=sum(recv_splits))
+        perm = torch.sort(row_expert, stable=True).indices
+        starts, ends = offsets_from_counts(rc.sum(0))
+        plans.append(DispatchPlan(send_splits, recv_splits, rc, perm, starts.contiguous(), ends.contiguous()))
+    return plans
+
+
 def all_to_all_rows(rows: torch.Tensor, send_splits, recv_splits, group=None) -> torch.Tensor:
     """Variable-size all-to-all of the rows of a 2-D tensor (any dtype; e4m3 travels as bytes)."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -242,8 +270,12 @@ def moe_forward(x: torch.Tensor, routing: Routing, experts: Callable, quantize: 
         out_rows = experts(recv, None, plan.starts, plan.ends)
     # back to arrival order, then home
     if len(plan.recv_splits) > 1:
-        back = torch.empty_like(out_rows)
-        back.index_copy_(0, plan.perm, out_rows)
+        if out_rows.is_cuda:
+            from . import kernels as K
+            back = K.scatter_rows(out_rows, plan.perm)
+        else:
+            back = torch.empty_like(out_rows)
+            back.index_copy_(0, plan.perm, out_rows)
         out_rows = all_to_all_rows(back, plan.recv_splits, plan.send_splits, group)
     if before_combine is not None:
         before_combine()                       # e.g. join the stream that produced ``addend``
@@ -256,6 +288,124 @@ def moe_forward(x: torch.Tensor, routing: Routing, experts: Callable, quantize: 
     return y if addend is None else addend.float() + y
 
 
+def moe_forward_pipelined(x: torch.Tensor, routings, experts: Callable, quantize: Callable, group=None,
+                          addend: Optional[torch.Tensor] = None, before_combine: Optional[Callable] = None,
+                          comm_sms: int = 16) -> torch.Tensor:
+    """``moe_forward`` over token chunks with the exchanges of one chunk under the expert GEMMs of another.
+
+    ``routings``: one ``Routing`` per chunk of ``x`` (chunks = ``torch.tensor_split(x, len(routings))``).  All
+    chunks share one exchange of counts and one host read-back.  On a GPU the all-to-alls are enqueued on a
+    second stream: while chunk c is in the experts, chunk c + 1 is being dispatched and chunk c - 1 is on its
+    way home; the GEMMs leave ``comm_sms`` SMs to the send/receive kernels meanwhile.  The arithmetic per token
+    is that of ``moe_forward``.  Returns fp32 (T, d)."""
+    n = len(routings)
+    chunks = torch.tensor_split(x, n)
+    adds = torch.tensor_split(addend, n) if addend is not None else [None] * n
+    plans = make_plans([r.counts for r in routings], group)
+    cuda = x.is_cuda
+    prev_limit = None
+    if cuda:
+        from . import kernels as K
+        main = torch.cuda.current_stream(x.device)
+        comm = _comm_stream(x.device)
+        comm.wait_stream(main)
+        if len(plans[0].recv_splits) > 1 and comm_sms > 0:
+            # the GEMMs are persistent kernels that would hold every SM: leave a few to the send/receive kernels
+            n_sm = torch.cuda.get_device_properties(x.device).multi_processor_count
+            prev_limit = K.set_gemm_sm_limit(max(n_sm - comm_sms, n_sm // 2))
+    keep = []                                   # every intermediate stays referenced until both streams are joined
+
+    def on_comm(fn, after):
+        """Run ``fn`` on the exchange stream once ``after`` (an event of the compute stream) has happened."""
+        if not cuda:
+            return fn(), None
+        with torch.cuda.stream(comm):
+            comm.wait_event(after)
+            out = fn()
+            done = torch.cuda.Event()
+            done.record(comm)
+        return out, done
+
+    def mark():
+        if not cuda:
+            return None
+        ev = torch.cuda.Event()
+        ev.record(main)
+        return ev
+
+    # stage 1 for every chunk: quantise, gather, dispatch (the exchanges queue up behind one another on `comm`)
+    dispatched = []
+    for c in range(n):
+        r, plan = routings[c], plans[c]
+        if quantize is not None:
+            x_q, x_s = quantize(chunks[c])
+            send_q, send_s = K.gather_quantized_rows(x_q, x_s, r.token_indices)
+            ev = mark()
+            (recv_q, recv_s), done = on_comm(lambda sq=send_q, ss=send_s, p=plan: (
+                all_to_all_rows(sq, p.send_splits, p.recv_splits, group),
+                all_to_all_rows(ss, p.send_splits, p.recv_splits, group)), ev)
+            keep += [x_q, x_s, send_q, send_s, recv_q, recv_s]
+            dispatched.append((recv_q, recv_s, done))
+        else:
+            send = chunks[c].index_select(0, r.token_indices)
+            recv, done = on_comm(lambda sd=send, p=plan: all_to_all_rows(sd, p.send_splits, p.recv_splits, group), mark())
+            dispatched.append((recv, None, done))
+    # stage 2 + 3: experts on the compute stream, the way home on the exchange stream
+    returning = []
+    for c in range(n):
+        plan = plans[c]
+        recv_q, recv_s, done = dispatched[c]
+        if cuda:
+            main.wait_event(done)
+        if len(plan.recv_splits) > 1:
+            if recv_s is not None:
+                recv_q, recv_s = K.gather_quantized_rows(recv_q, recv_s, plan.perm)
+            else:
+                recv_q = recv_q.index_select(0, plan.perm)
+        out_rows = experts(recv_q, recv_s, plan.starts, plan.ends)
+        if len(plan.recv_splits) > 1:
+            if cuda:
+                back = K.scatter_rows(out_rows, plan.perm)
+            else:
+                back = torch.empty_like(out_rows)
+                back.index_copy_(0, plan.perm, out_rows)
+            home, done = on_comm(lambda b=back, p=plan: all_to_all_rows(b, p.recv_splits, p.send_splits, group), mark())
+            keep += [recv_q, recv_s, out_rows, back, home]
+        else:
+            home, done = out_rows, mark()
+        returning.append((home, done))
+    if before_combine is not None:
+        before_combine()
+    ys = []
+    for c in range(n):
+        home, done = returning[c]
+        r = routings[c]
+        if cuda:
+            main.wait_event(done)
+            ys.append(K.moe_combine(home, r.pair_pos, r.pair_gate, adds[c]))
+        else:
+            y = torch.zeros(chunks[c].shape[0], x.shape[1], dtype=torch.float32, device=x.device)
+            y.index_add_(0, r.token_indices, home.float() * r.sorted_scores[:, None])
+            ys.append(y if adds[c] is None else adds[c].float() + y)
+    if cuda:
+        comm.wait_stream(main)                  # the exchange stream outlives none of the buffers it read
+        main.wait_stream(comm)
+        if prev_limit is not None:
+            K.set_gemm_sm_limit(prev_limit)
+    del keep
+    return torch.cat(ys, dim=0)
+
+
+_COMM_STREAMS = {}
+
+
+def _comm_stream(device) -> "torch.cuda.Stream":
+    key = torch.device(device).index
+    if key not in _COMM_STREAMS:
+        _COMM_STREAMS[key] = torch.cuda.Stream(device)
+    return _COMM_STREAMS[key]
+
+
 class ExpertParallelMoE(torch.nn.Module):
     """Inference/forward module: router + FP8 routed experts sharded over ``group`` (+ an optional shared expert
     whose output is added in the combine pass, ``shared_out + routed_out``, src/layers.py:179).
@@ -264,7 +414,7 @@ class ExpertParallelMoE(torch.nn.Module):
     """
 
     def __init__(self, router_weight: torch.Tensor, expert_bias: torch.Tensor, w12_local: torch.Tensor,
-                 w3_local: torch.Tensor, top_k: int, group=None, shared: Optional[FP8SwiGLU] = None):
+                 w3_local: torch.Tensor, top_k: int, group=None, shared: Optional[FP8SwiGLU] = None, n_chunks: int = 1):
         super().__init__()
         from . import kernels as K
         self.K = K
@@ -275,6 +425,7 @@ class ExpertParallelMoE(torch.nn.Module):
         self.group = group
         self.experts = FP8Experts(w12_local, w3_local)
         self.shared = shared
+        self.n_chunks = max(1, int(n_chunks))      # several ranks: token chunks whose exchanges overlap the experts
         self._side = None
 
     def _router_as(self, dtype: torch.dtype) -> torch.Tensor:
@@ -289,9 +440,9 @@ class ExpertParallelMoE(torch.nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         flat = x.reshape(-1, x.shape[-1])
-        r = route(flat, self._router_as(flat.dtype), self.expert_bias, self.top_k)
-        sh = None
+        router = self._router_as(flat.dtype)
         world = dist.get_world_size(self.group) if dist.is_initialized() else 1
+        sh, join = None, None
         if self.shared is not None and world > 1 and flat.is_cuda:
             # the shared expert needs nothing from the exchange: it runs on a second stream, under the
             # all-to-alls and the host read-back of the split sizes, and is joined before the combine pass
@@ -302,10 +453,14 @@ class ExpertParallelMoE(torch.nn.Module):
             with torch.cuda.stream(self._side):
                 sh = self.shared(flat)
             sh.record_stream(cur)
-            y = moe_forward(flat, r, self.experts, self.K.quantize_fp8_rowwise, self.group, addend=sh,
-                            before_combine=lambda: cur.wait_stream(self._side))
+            join = lambda: cur.wait_stream(self._side)                    # noqa: E731
+        elif self.shared is not None:
+            sh = self.shared(flat)
+        if world > 1 and self.n_chunks > 1 and flat.shape[0] >= self.n_chunks:
+            routings = [route(c, router, self.expert_bias, self.top_k) for c in torch.tensor_split(flat, self.n_chunks)]
+            y = moe_forward_pipelined(flat, routings, self.experts, self.K.quantize_fp8_rowwise, self.group, addend=sh,
+                                      before_combine=join)
         else:
-            if self.shared is not None:
-                sh = self.shared(flat)
-            y = moe_forward(flat, r, self.experts, self.K.quantize_fp8_rowwise, self.group, addend=sh)
+            r = route(flat, router, self.expert_bias, self.top_k)
+            y = moe_forward(flat, r, self.experts, self.K.quantize_fp8_rowwise, self.group, addend=sh, before_combine=join)
         return y.reshape(x.shape)

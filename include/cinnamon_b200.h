@@ -178,6 +178,13 @@ int cinn_lightning_indexer(const void* q, const void* k, const void* w, int dtyp
 int cinn_gather_rows(const void* q, const float* scales, const int64_t* idx, void* out_q, float* out_scales, int64_t n_out,
                      int64_t n_src, int64_t d, int64_t n_scales, void* stream);
 
+/* Row scatter: out[idx[r], :] = in[r, :] for r < n_rows; rows of row_bytes bytes (a multiple of 16), out has
+ * n_dst rows, entries of idx outside [0, n_dst) are skipped.  Brings the expert outputs of an expert-parallel
+ * rank from the expert-grouped order back to the order in which the rows arrived, before they travel home
+ * (the reference keeps every expert on every rank, src/layers.py:89-179, and has no such step). */
+int cinn_scatter_rows(const void* in, const int64_t* idx, void* out, int64_t n_rows, int64_t n_dst, int64_t row_bytes,
+                      void* stream);
+
 /* Routing of MoE.forward (src/layers.py:122-148) on the device: scores = sigmoid(logits), the top_k experts of
  * scores + bias per token (ties: the lower expert id), gates = score / (sum of the k scores + 1e-9), and the
  * (token, expert) pairs sorted by expert in the order of a stable sort.
@@ -212,6 +219,12 @@ int64_t cinn_moe_route_static_max_ints(void);
 int cinn_moe_route_static(const float* logits, const float* bias, int64_t n_tokens, int n_experts, int top_k,
                           int* top_experts, float* top_gates, int64_t* token_indices, float* sorted_scores,
                           int64_t* sorted_experts, int64_t* counts, int64_t* pair_pos, float* pair_gate, void* stream);
+
+/* Caps the number of SMs the persistent GEMM kernels (cinn_fp8_gemm, cinn_fp8_grouped_gemm*) occupy from now
+ * on, process-wide; 0 = all of them (the default).  Returns the previous cap.  For callers that run other
+ * kernels beside a GEMM on another stream, e.g. the send/receive kernels of an all-to-all, which otherwise wait
+ * until a GEMM has let go of an SM.  No reference counterpart (the reference's kernels are not persistent). */
+int cinn_set_gemm_sm_limit(int n_sms);
 
 /* Reads (and with reset != 0 clears) the device-side status word of the current device into the HOST int
  * *out.  0 means no kernel of this library has given up on a bounded wait since the last reset; any other

@@ -70,7 +70,10 @@ def _worker(rank, world, port, q, leave_early):
             os._exit(0)
         y = moe.moe_forward(x, r, _plain_experts(w12[lo:hi], w3[lo:hi]), None)
         plan = moe.make_plan(r.counts)
-        q.put((rank, "ok", (y, plan.recv_counts.clone(), r.counts.clone())))
+        # the same tokens in three chunks (uneven: 3 does not divide the token count) through the pipelined path
+        routings = [moe.route(c, router, bias, TOPK) for c in torch.tensor_split(x, 3)]
+        y_chunks = moe.moe_forward_pipelined(x, routings, _plain_experts(w12[lo:hi], w3[lo:hi]), None, addend=x.float())
+        q.put((rank, "ok", (y, plan.recv_counts.clone(), r.counts.clone(), y_chunks - x.float())))
         dist.barrier()
         dist.destroy_process_group()
     except Exception as exc:                     # noqa: BLE001
@@ -109,8 +112,9 @@ def test_two_ranks_match_single_rank():
     for rank in range(2):
         status, payload = res[rank]
         assert status == "ok", payload
-        y, recv_counts, counts = payload
+        y, recv_counts, counts, y_chunks = payload
         torch.testing.assert_close(y, _reference(rank), rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(y_chunks, _reference(rank), rtol=1e-5, atol=1e-5)
     # what rank r received from rank s for its experts is what s routed there
     for r in range(2):
         for s in range(2):

@@ -107,6 +107,15 @@ def test_gather_quantized_rows(K):
     assert torch.equal(out_q.view(torch.uint8), q.view(torch.uint8)[:, :72][idx]) and torch.equal(out_s, s[:, :1][idx])
 
 
+def test_scatter_rows(K):
+    g = torch.Generator().manual_seed(6)
+    rows = torch.randn(500, 264, generator=g).bfloat16().cuda()              # 528-byte rows
+    perm = torch.randperm(500, generator=g).cuda()
+    assert torch.equal(K.scatter_rows(rows, perm), torch.empty_like(rows).index_copy_(0, perm, rows))
+    odd = rows[:, :13].contiguous()                                          # 26-byte rows: the torch path
+    assert torch.equal(K.scatter_rows(odd, perm), torch.empty_like(odd).index_copy_(0, perm, odd))
+
+
 def test_route_empty(K):
     got = K.moe_route(torch.empty(0, 32, device="cuda"), torch.zeros(32, device="cuda"), 4)
     assert got["counts"].tolist() == [0] * 32 and got["token_indices"].numel() == 0
@@ -204,8 +213,11 @@ y_ep = moe.moe_forward(x, r, moe.FP8Experts(w12[lo:hi], w3[lo:hi]), K.quantize_f
 s1, s2, s3 = [(torch.randn(*shape, generator=g) * 0.02).cuda() for shape in ((384, d), (384, d), (d, 384))]
 layer = moe.ExpertParallelMoE(router, bias, w12[lo:hi], w3[lo:hi], k, shared=moe.FP8SwiGLU(s1, s2, s3))
 y_layer = [layer(x) for _ in range(3)][-1]
+# and with the tokens in two chunks whose exchanges run under the other chunk's experts
+layer2 = moe.ExpertParallelMoE(router, bias, w12[lo:hi], w3[lo:hi], k, shared=moe.FP8SwiGLU(s1, s2, s3), n_chunks=2)
+y_chunked = [layer2(x) for _ in range(3)][-1]
 torch.cuda.synchronize()
-torch.save({"y_ep": y_ep.cpu(), "y_layer": y_layer.cpu(), "x": x.cpu(), "status": K.device_status()},
+torch.save({"y_ep": y_ep.cpu(), "y_layer": y_layer.cpu(), "y_chunked": y_chunked.cpu(), "x": x.cpu(), "status": K.device_status()},
            os.path.join(sys.argv[2], f"ep_{rank}.pt"))
 dist.barrier(); dist.destroy_process_group()
 '''
@@ -239,6 +251,7 @@ def test_expert_parallel_two_gpus_match_one(K, tmp_path):
         r = moe.route(x, router, bias, k)
         y_one = moe.moe_forward(x, r, experts, K.quantize_fp8_rowwise)
         assert rel_fro(got["y_layer"], (shared(x).float() + y_one).cpu().double()) < 1e-6
+        assert rel_fro(got["y_chunked"], (shared(x).float() + y_one).cpu().double()) < 1e-6
         # same e4m3 payloads and the same per-row arithmetic: only the fp32 summation order of a token's
         # experts could differ, and index_add_ keeps it
         assert rel_fro(got["y_ep"], y_one.cpu().double()) < 1e-6
