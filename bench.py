@@ -30,7 +30,7 @@ sys.path.insert(0, ROOT)
 M, K, N = 16384, 7168, 18432
 FLOP_PER_STEP = 3 * 2.0 * M * N * K
 WORKLOAD = "fp8_linear_fwd_bwd_ffn M=16384 K=7168 N=18432"
-GEMM_TRAFFIC_BYTES = 4 * (457.6e6 + 443.0e6 + 612.8e6) / 3      # per launch, see profiles/fp8_gemm_kernel_8192x9216x7168.md
+GEMM_TRAFFIC_BYTES = 4 * (462.2e6 + 448.7e6 + 622.4e6) / 3      # per launch, see profiles/fp8_gemm_kernel_8192x9216x7168.md
 
 
 def measured_peaks():
