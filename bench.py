@@ -292,7 +292,7 @@ def bench_kernels(Kmod, dev, x, w, dy, peaks):
 MOE = dict(E=256, d=7168, I=2048, tokens=32768, top_k=8, shared_hidden=2048)
 
 
-def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label, chunks=1):
+def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label, chunks=1, exchange="nccl"):
     """256 routed experts (SwiGLU 7168 -> 2x2048 -> 7168) + 1 shared expert, 32768 tokens, top-8 with
     sigmoid scores + per-expert bias.  Strong scaling: tokens and experts are both split over the ranks.
     Returns a dict (rank 0) with whole-layer tokens/s, the grouped-GEMM rate and the load imbalance."""
@@ -317,7 +317,7 @@ def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label, chunks=1
     # the layer as a user builds it: router + this rank's routed experts + the shared expert (round_scale on the
     # shared expert's input, as the reference's converted model has it)
     module = moe.ExpertParallelMoE(router, bias, w12, w3, c["top_k"], shared=moe.FP8SwiGLU(*sw, round_scale=True),
-                                   n_chunks=chunks)
+                                   n_chunks=chunks, exchange=exchange)
     t1.record()
     torch.cuda.synchronize()
     wq_ms = t0.elapsed_time(t1)
@@ -375,7 +375,7 @@ def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label, chunks=1
             "ms_per_layer": ms.item(), "grouped_gemm_ms": gms.item(), "grouped_gemm_tflops": flop / (gms.item() * 1e-3) / 1e12,
             "expert_weight_quant_ms": wq_ms, "max_rank_rows": int(load.item()), "mean_rank_rows": total.item() / world,
             "active_experts_rank0_view": active, "scaling": "strong", "n_gpus": world,
-            "token_chunks": chunks if world > 1 else 1}
+            "token_chunks": chunks if world > 1 else 1, "exchange": exchange if world > 1 else "none"}
 
 
 # ---------------------------------------------------------------------------------------
@@ -411,6 +411,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-moe", action="store_true", help="skip the MoE layer measurements")
+    ap.add_argument("--moe-exchange", default="nccl", choices=["nccl", "p2p"],
+                    help="expert-parallel exchange (N > 1): all-to-all collectives, or peer stores into symmetric memory")
     ap.add_argument("--moe-chunks", type=int, default=1,
                     help="token chunks of the expert-parallel layer (N > 1): exchanges of one chunk run under the experts of another")
     ap.add_argument("--shape", default=None, help="M,K,N of a smaller case (profiling captures); default is the FFN workload")
@@ -556,7 +558,7 @@ def main():
         torch.cuda.empty_cache()
         for scale, label in ((1.0, "bias~N(0,1) as specified"), (0.1, "mild skew: bias~N(0,0.1)")):
             moe_lines.append(bench_moe(Kmod, dev, rank, world, steps=5, warmup=3, bias_scale=scale, label=label,
-                                       chunks=args.moe_chunks))
+                                       chunks=args.moe_chunks, exchange=args.moe_exchange))
         assert Kmod.device_status() == 0, "a kernel reported a device-side failure in the MoE layer"
 
     if rank == 0:

@@ -64,6 +64,13 @@ int lightning_indexer(const void* q, const void* k, const void* w, int dtype, vo
 int scatter_rows(const void* in, const int64_t* idx, void* out, int64_t n_rows, int64_t n_dst, int64_t row_bytes,
                  cudaStream_t st);
 int set_gemm_sm_limit(int n);
+int p2p_dispatch(const void* q, const float* s, const int64_t* token_indices, const int64_t* sorted_experts,
+                 const int64_t* base_send, const int64_t* my_start, const int64_t* peer_q, const int64_t* peer_s,
+                 int64_t n_pairs, int64_t n_tokens, int64_t d, int64_t ns, int e_local, int n_ranks, int64_t capacity,
+                 cudaStream_t st);
+int p2p_return(const void* rows, const int64_t* seg_start, const int64_t* home_base, const int64_t* peer_home, int64_t n_rows,
+               int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity, cudaStream_t st);
+int p2p_barrier(const int64_t* peer_flags, int me, int n_ranks, unsigned epoch, cudaStream_t st);
 int64_t moe_route_workspace_ints(int64_t T, int E);
 int moe_route(const float* logits, const float* bias, int64_t T, int E, int top_k, int* workspace, int* top_experts,
               float* top_gates, int64_t* token_indices, float* sorted_scores, int64_t* sorted_experts, int64_t* counts,
@@ -184,6 +191,24 @@ int cinn_scatter_rows(const void* in, const int64_t* idx, void* out, int64_t n_r
 }
 
 int cinn_set_gemm_sm_limit(int n_sms) { return cinn::set_gemm_sm_limit(n_sms); }
+
+int cinn_p2p_dispatch(const void* q, const float* scales, const int64_t* token_indices, const int64_t* sorted_experts,
+                      const int64_t* base_send, const int64_t* my_start, const int64_t* peer_q, const int64_t* peer_scales,
+                      int64_t n_pairs, int64_t n_tokens, int64_t d, int64_t n_scales, int experts_per_rank, int n_ranks,
+                      int64_t capacity_rows, void* stream) {
+    return cinn::p2p_dispatch(q, scales, token_indices, sorted_experts, base_send, my_start, peer_q, peer_scales, n_pairs,
+                              n_tokens, d, n_scales, experts_per_rank, n_ranks, capacity_rows, (cudaStream_t)stream);
+}
+
+int cinn_p2p_return(const void* rows, const int64_t* seg_start, const int64_t* home_base, const int64_t* peer_home,
+                    int64_t n_rows, int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity_rows, void* stream) {
+    return cinn::p2p_return(rows, seg_start, home_base, peer_home, n_rows, row_bytes, n_segments, n_ranks, capacity_rows,
+                            (cudaStream_t)stream);
+}
+
+int cinn_p2p_barrier(const int64_t* peer_flags, int rank, int n_ranks, unsigned epoch, void* stream) {
+    return cinn::p2p_barrier(peer_flags, rank, n_ranks, epoch, (cudaStream_t)stream);
+}
 
 int64_t cinn_moe_route_workspace_ints(int64_t n_tokens, int n_experts) {
     return cinn::moe_route_workspace_ints(n_tokens, n_experts);

@@ -806,10 +806,11 @@ int fp8_grouped_gemm_dgrad(const void* dY, const float* sdY, const void* W, cons
 }
 
 int read_quant_status(int* out, int reset);
+int read_moe_status(int* out, int reset);
 
-// One word for the caller: the GEMM's code if it has one, else the quantisers'.
+// One word for the caller: the GEMM's code if it has one, else the quantisers', else the exchange kernels'.
 int read_device_status(int* out, int reset) {
-    int v = 0, q = 0;
+    int v = 0, q = 0, m = 0;
     CINN_CHECK_CUDA(cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)));
     if (reset && v != 0) {
         int z = 0;
@@ -817,7 +818,9 @@ int read_device_status(int* out, int reset) {
     }
     int rc = read_quant_status(&q, reset);
     if (rc) return rc;
-    *out = v != 0 ? v : q;
+    rc = read_moe_status(&m, reset);
+    if (rc) return rc;
+    *out = v != 0 ? v : (q != 0 ? q : m);
     return CINN_OK;
 }
 

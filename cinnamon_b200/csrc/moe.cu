@@ -173,4 +173,165 @@ int scatter_rows(const void* in, const int64_t* idx, void* out, int64_t n_rows, 
     return CINN_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Expert-parallel exchange by peer stores.  Every rank holds receive buffers that the other ranks of the node
+// can address (symmetric memory); `peer_*` are device arrays with one base address per rank (this rank's own
+// buffer included).  The destination row of every source row is a closed formula of the routing counts of all
+// ranks (tables built on the host side, see cinnamon_b200/p2p.py), so no rank needs to be told where to write.
+// Rows whose table entries point outside the buffers are skipped and counted in a device status word.
+// ---------------------------------------------------------------------------
+__device__ int g_moe_status = 0;      // 0 = fine, otherwise (5 << 8) | reason
+
+// Dispatch: pair r of this rank (sorted by expert) -> the rank owning its expert, in that rank's expert-grouped
+// order.  Fuses `flat_x[token_indices]` (src/layers.py:140), the two dispatch all-to-alls and the regrouping.
+__global__ void __launch_bounds__(256)
+p2p_dispatch_kernel(const uint8_t* __restrict__ q, const float* __restrict__ s, const int64_t* __restrict__ token_indices,
+                    const int64_t* __restrict__ sorted_experts, const int64_t* __restrict__ base_send,
+                    const int64_t* __restrict__ my_start, const int64_t* __restrict__ peer_q,
+                    const int64_t* __restrict__ peer_s, int64_t n_pairs, int64_t n_tokens, int d, int ns, int e_local,
+                    int n_ranks, int64_t capacity) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int64_t n_warps = (int64_t)gridDim.x * 8;
+    const int vecs = d >> 4;
+    for (int64_t r = warp; r < n_pairs; r += n_warps) {
+        const int64_t e = sorted_experts[r];
+        const int64_t tok = token_indices[r];
+        bool ok = e >= 0 && e < (int64_t)e_local * n_ranks && tok >= 0 && tok < n_tokens;
+        int64_t dst = 0;
+        int rank = 0;
+        if (ok) {
+            rank = (int)(e / e_local);
+            dst = base_send[e] + (r - my_start[e]);
+            ok = dst >= 0 && dst < capacity;
+        }
+        if (!ok) {
+            if (lane == 0) atomicCAS(&g_moe_status, 0, (5 << 8) | 1);
+            continue;
+        }
+        const uint4* in = reinterpret_cast<const uint4*>(q + tok * d);
+        uint4* out = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(peer_q[rank]) + dst * d);
+        for (int v = lane; v < vecs; v += 32) out[v] = __ldg(in + v);
+        float* so = reinterpret_cast<float*>(peer_s[rank]) + dst * ns;
+        for (int c = lane; c < ns; c += 32) so[c] = s[tok * ns + c];
+    }
+}
+
+// Return: row r of this rank's expert-grouped outputs -> the rank its token lives on, at the position of its
+// pair in that rank's sorted order.  Fuses the inverse permutation and the combine all-to-all.
+__global__ void __launch_bounds__(256)
+p2p_return_kernel(const uint4* __restrict__ rows, const int64_t* __restrict__ seg_start, const int64_t* __restrict__ home_base,
+                  const int64_t* __restrict__ peer_home, int64_t n_rows, int n_segments, int n_ranks, int vecs,
+                  int64_t capacity) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int64_t n_warps = (int64_t)gridDim.x * 8;
+    for (int64_t r = warp; r < n_rows; r += n_warps) {
+        // segment of row r: the first one whose end (the next start) lies beyond r; empty segments are stepped over
+        int lo = 0, hi = n_segments;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (seg_start[mid + 1] > r) hi = mid; else lo = mid + 1;
+        }
+        bool ok = lo < n_segments && seg_start[lo] <= r;
+        int64_t dst = 0;
+        if (ok) {
+            dst = home_base[lo] + (r - seg_start[lo]);
+            ok = dst >= 0 && dst < capacity;
+        }
+        if (!ok) {
+            if (lane == 0) atomicCAS(&g_moe_status, 0, (5 << 8) | 2);
+            continue;
+        }
+        const uint4* in = rows + r * vecs;
+        uint4* out = reinterpret_cast<uint4*>(peer_home[lo % n_ranks]) + dst * vecs;
+        for (int v = lane; v < vecs; v += 32) out[v] = __ldcs(in + v);
+    }
+}
+
+// Barrier over the ranks of one node on flags in symmetric memory: thread g tells rank g that this rank has
+// arrived (release store, system scope, of the epoch into slot `me` of rank g's flag array) and waits until rank g
+// has said the same (acquire loads of slot g of this rank's own array).  Kernels enqueued earlier on the stream
+// have completed, so their peer stores are ordered before the flag.  The wait is bounded (about two seconds):
+// when it runs out the kernel records a code in the status word and returns.  Each rank must own its GPU: ranks
+// that share one could wait for a kernel that cannot run beside them.
+constexpr long long P2P_WAIT_LIMIT_CYCLES = 4000000000LL;
+
+__global__ void __launch_bounds__(64)
+p2p_barrier_kernel(const int64_t* __restrict__ peer_flags, int me, int n_ranks, unsigned epoch) {
+    const int g = threadIdx.x;
+    if (g >= n_ranks) return;
+    __threadfence_system();
+    unsigned* remote = reinterpret_cast<unsigned*>(peer_flags[g]) + me;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+    const unsigned* mine = reinterpret_cast<const unsigned*>(peer_flags[me]) + g;
+    const long long t0 = clock64();
+    for (unsigned spin = 1;; ++spin) {
+        unsigned seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+        if ((int)(seen - epoch) >= 0) break;
+        if ((spin & 63u) == 0 && clock64() - t0 > P2P_WAIT_LIMIT_CYCLES) {
+            atomicCAS(&g_moe_status, 0, (5 << 8) | 3);
+            break;
+        }
+    }
+}
+
+int p2p_barrier(const int64_t* peer_flags, int me, int n_ranks, unsigned epoch, cudaStream_t st) {
+    CINN_CHECK_ARG(peer_flags != nullptr && n_ranks >= 1 && n_ranks <= 64 && me >= 0 && me < n_ranks,
+                   "p2p_barrier: 1 <= ranks <= 64 and 0 <= rank < ranks (got %d, %d)", n_ranks, me);
+    p2p_barrier_kernel<<<1, 64, 0, st>>>(peer_flags, me, n_ranks, epoch);
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+int p2p_dispatch(const void* q, const float* s, const int64_t* token_indices, const int64_t* sorted_experts,
+                 const int64_t* base_send, const int64_t* my_start, const int64_t* peer_q, const int64_t* peer_s,
+                 int64_t n_pairs, int64_t n_tokens, int64_t d, int64_t ns, int e_local, int n_ranks, int64_t capacity,
+                 cudaStream_t st) {
+    CINN_CHECK_ARG(n_pairs >= 0 && n_tokens >= 0 && d >= 0 && ns >= 0 && e_local >= 1 && n_ranks >= 1 && capacity >= 0,
+                   "p2p_dispatch: bad shape");
+    if (n_pairs == 0 || d == 0) return CINN_OK;
+    CINN_CHECK_ARG(q && s && token_indices && sorted_experts && base_send && my_start && peer_q && peer_s,
+                   "p2p_dispatch: null pointer");
+    CINN_CHECK_ARG(d % 16 == 0 && d < (1LL << 31) && ns < (1LL << 31), "p2p_dispatch: the row width (%lld) must be a multiple of 16",
+                   (long long)d);
+    CINN_CHECK_ARG((reinterpret_cast<uintptr_t>(q) & 15) == 0, "p2p_dispatch: q must be 16-byte aligned");
+    int64_t blocks = (n_pairs + 7) / 8;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    p2p_dispatch_kernel<<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)q, s, token_indices, sorted_experts, base_send, my_start,
+                                                         peer_q, peer_s, n_pairs, n_tokens, (int)d, (int)ns, e_local, n_ranks, capacity);
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+int p2p_return(const void* rows, const int64_t* seg_start, const int64_t* home_base, const int64_t* peer_home, int64_t n_rows,
+               int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity, cudaStream_t st) {
+    CINN_CHECK_ARG(n_rows >= 0 && row_bytes >= 0 && n_segments >= 1 && n_ranks >= 1 && capacity >= 0, "p2p_return: bad shape");
+    if (n_rows == 0 || row_bytes == 0) return CINN_OK;
+    CINN_CHECK_ARG(rows && seg_start && home_base && peer_home, "p2p_return: null pointer");
+    CINN_CHECK_ARG(row_bytes % 16 == 0 && row_bytes / 16 < (1LL << 31), "p2p_return: the row size (%lld bytes) must be a multiple of 16",
+                   (long long)row_bytes);
+    CINN_CHECK_ARG((reinterpret_cast<uintptr_t>(rows) & 15) == 0, "p2p_return: rows must be 16-byte aligned");
+    int64_t blocks = (n_rows + 7) / 8;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    p2p_return_kernel<<<(unsigned)blocks, 256, 0, st>>>((const uint4*)rows, seg_start, home_base, peer_home, n_rows, n_segments,
+                                                       n_ranks, (int)(row_bytes / 16), capacity);
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+int read_moe_status(int* out, int reset) {
+    int v = 0;
+    CINN_CHECK_CUDA(cudaMemcpyFromSymbol(&v, g_moe_status, sizeof(int)));
+    if (reset && v != 0) {
+        int z = 0;
+        CINN_CHECK_CUDA(cudaMemcpyToSymbol(g_moe_status, &z, sizeof(int)));
+    }
+    *out = v;
+    return CINN_OK;
+}
+
 }  // namespace cinn

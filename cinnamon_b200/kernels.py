@@ -543,6 +543,33 @@ def scatter_rows(rows: torch.Tensor, idx: torch.Tensor, n_out: int = None) -> to
     return out
 
 
+def p2p_dispatch(x_fp8, x_scale, token_indices, sorted_experts, base_send, my_start, peer_q, peer_s, experts_per_rank: int,
+                 n_ranks: int, capacity_rows: int) -> None:
+    """Writes the quantised rows of this rank's sorted (token, expert) pairs straight into the receive buffers of
+    the ranks that own the experts (``cinn_p2p_dispatch``; tables from ``p2p.exchange_tables``)."""
+    assert x_fp8.is_cuda, "Inputs must be on CUDA"
+    n_tokens, d = x_fp8.shape
+    x_fp8, x_scale = x_fp8.contiguous(), x_scale.float().contiguous()
+    with torch.cuda.device(x_fp8.device):
+        _lib.check(_L.cinn_p2p_dispatch(_ptr(x_fp8), _ptr(x_scale), _ptr(token_indices), _ptr(sorted_experts), _ptr(base_send),
+                                        _ptr(my_start), _ptr(peer_q), _ptr(peer_s), token_indices.numel(), n_tokens, d,
+                                        x_scale.shape[1], experts_per_rank, n_ranks, capacity_rows, _stream(x_fp8)),
+                   "cinn_p2p_dispatch")
+    _count()
+
+
+def p2p_return(rows, seg_start, home_base, peer_home, n_ranks: int, capacity_rows: int) -> None:
+    """Writes this rank's expert outputs straight into the home buffers of the ranks the tokens live on
+    (``cinn_p2p_return``)."""
+    assert rows.is_cuda, "Inputs must be on CUDA"
+    rows = rows.contiguous()
+    with torch.cuda.device(rows.device):
+        _lib.check(_L.cinn_p2p_return(_ptr(rows), _ptr(seg_start), _ptr(home_base), _ptr(peer_home), rows.shape[0],
+                                      rows.shape[1] * rows.element_size(), home_base.numel(), n_ranks, capacity_rows,
+                                      _stream(rows)), "cinn_p2p_return")
+    _count()
+
+
 def moe_route(logits: torch.Tensor, bias: torch.Tensor, top_k: int):
     """Routing of ``MoE.forward`` (reference src/layers.py:122-148) from the router's fp32 logits, on the
     device and without a host synchronisation: sigmoid scores, top-k of score + bias, normalised gates, and the

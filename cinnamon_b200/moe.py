@@ -288,6 +288,42 @@ def moe_forward(x: torch.Tensor, routing: Routing, experts: Callable, quantize: 
     return y if addend is None else addend.float() + y
 
 
+def moe_forward_p2p(x: torch.Tensor, routing: Routing, experts: Callable, quantize: Callable, buffers, group=None,
+                    addend: Optional[torch.Tensor] = None, before_combine: Optional[Callable] = None) -> torch.Tensor:
+    """``moe_forward`` with the exchange done by peer stores over NVLink (``cinnamon_b200/p2p.py``) instead of
+    all-to-all collectives: one small all-gather of the routing counts, then every quantised row is written
+    straight to its place in the expert-grouped buffer of the rank that owns its expert, and every expert output
+    straight to its pair's place on the rank its token lives on.  No gather, regrouping or inverse permutation
+    passes, no send/receive kernels; three stream-ordered barriers order the phases.  One host read-back (the
+    number of rows this rank received).  ``buffers``: a ``p2p.PeerBuffers``.  Same arithmetic per row as
+    ``moe_forward``; returns fp32 (T, d)."""
+    from . import kernels as K
+    from . import p2p
+    world, me = dist.get_world_size(group), dist.get_rank(group)
+    n_experts = routing.counts.numel()
+    e_local = n_experts // world
+    counts_all = torch.empty((world, n_experts), dtype=torch.int64, device=x.device)
+    dist.all_gather_into_tensor(counts_all, routing.counts.to(torch.int64).contiguous(), group=group)
+    t = p2p.exchange_tables(counts_all, me)
+    x_q, x_s = quantize(x)
+    n_pairs = routing.token_indices.numel()
+    buffers.barrier()                                   # every rank is done with the buffers' previous contents
+    K.p2p_dispatch(x_q, x_s, routing.token_indices, routing.sorted_experts, t.base_send, t.my_start, buffers.peer_q,
+                   buffers.peer_s, e_local, world, buffers.capacity_rows)
+    buffers.barrier()                                   # every row has landed
+    rows = int(t.total_rows)                            # the one host read-back: sizes the expert GEMMs' outputs
+    assert rows <= buffers.capacity_rows and n_pairs <= buffers.home_rows, "peer buffers too small"
+    recv_q = buffers.q.view(buffers.capacity_rows, buffers.d)[:rows].view(x_q.dtype)
+    recv_s = buffers.s.view(buffers.capacity_rows, buffers.n_scales)[:rows]
+    out_rows = experts(recv_q, recv_s, t.starts, t.ends)
+    K.p2p_return(out_rows, t.seg_start, t.home_base, buffers.peer_home, world, buffers.home_rows)
+    buffers.barrier()                                   # every expert output is home
+    home = buffers.home.view(buffers.home_rows, buffers.d)[:n_pairs]
+    if before_combine is not None:
+        before_combine()
+    return K.moe_combine(home, routing.pair_pos, routing.pair_gate, addend)
+
+
 def moe_forward_pipelined(x: torch.Tensor, routings, experts: Callable, quantize: Callable, group=None,
                           addend: Optional[torch.Tensor] = None, before_combine: Optional[Callable] = None,
                           comm_sms: int = 16) -> torch.Tensor:
@@ -414,8 +450,12 @@ class ExpertParallelMoE(torch.nn.Module):
     """
 
     def __init__(self, router_weight: torch.Tensor, expert_bias: torch.Tensor, w12_local: torch.Tensor,
-                 w3_local: torch.Tensor, top_k: int, group=None, shared: Optional[FP8SwiGLU] = None, n_chunks: int = 1):
+                 w3_local: torch.Tensor, top_k: int, group=None, shared: Optional[FP8SwiGLU] = None, n_chunks: int = 1,
+                 exchange: str = "nccl"):
         super().__init__()
+        assert exchange in ("nccl", "p2p"), "exchange must be 'nccl' (all-to-all collectives) or 'p2p' (peer stores)"
+        self.exchange = exchange
+        self._peer_buffers = None
         from . import kernels as K
         self.K = K
         self.register_buffer("router_weight", router_weight)
@@ -456,7 +496,16 @@ class ExpertParallelMoE(torch.nn.Module):
             join = lambda: cur.wait_stream(self._side)                    # noqa: E731
         elif self.shared is not None:
             sh = self.shared(flat)
-        if world > 1 and self.n_chunks > 1 and flat.shape[0] >= self.n_chunks:
+        if world > 1 and self.exchange == "p2p" and flat.is_cuda:
+            from . import p2p
+            r = route(flat, router, self.expert_bias, self.top_k)
+            n_pairs, d = flat.shape[0] * self.top_k, flat.shape[1]
+            if self._peer_buffers is None or not self._peer_buffers.fits(n_pairs * world, n_pairs, d, (d + 127) // 128):
+                # worst case: every pair of every rank routed to this rank's experts (all ranks bring equally many tokens)
+                self._peer_buffers = p2p.PeerBuffers(self.group, flat.device, n_pairs * world, n_pairs, d, (d + 127) // 128)
+            y = moe_forward_p2p(flat, r, self.experts, self.K.quantize_fp8_rowwise, self._peer_buffers, self.group, addend=sh,
+                                before_combine=join)
+        elif world > 1 and self.n_chunks > 1 and flat.shape[0] >= self.n_chunks:
             routings = [route(c, router, self.expert_bias, self.top_k) for c in torch.tensor_split(flat, self.n_chunks)]
             y = moe_forward_pipelined(flat, routings, self.experts, self.K.quantize_fp8_rowwise, self.group, addend=sh,
                                       before_combine=join)

@@ -185,6 +185,37 @@ int cinn_gather_rows(const void* q, const float* scales, const int64_t* idx, voi
 int cinn_scatter_rows(const void* in, const int64_t* idx, void* out, int64_t n_rows, int64_t n_dst, int64_t row_bytes,
                       void* stream);
 
+/* Expert-parallel dispatch by peer stores (no reference counterpart: the reference keeps every expert on every
+ * rank, src/layers.py:89-179).  Pair r of this rank, r < n_pairs (sorted by expert: sorted_experts[r], source token
+ * token_indices[r]), is copied - e4m3 row of q (n_tokens, d) and its n_scales fp32 scales - into the receive
+ * buffers of the rank that owns its expert, at row base_send[e] + (r - my_start[e]).  peer_q / peer_scales:
+ * DEVICE arrays of n_ranks base addresses (as int64) of the ranks' receive buffers, which must be mapped into
+ * this process (symmetric memory / CUDA IPC); capacity_rows: rows each of them holds.  base_send, my_start:
+ * (experts_per_rank * n_ranks) int64 device arrays (cinnamon_b200/p2p.py builds them from the all-gathered
+ * counts).  Table entries that point outside the buffers skip the row and set the device status word.
+ * The caller orders the exchange: a barrier over the ranks before (the buffers are free) and after (all rows
+ * have landed). */
+int cinn_p2p_dispatch(const void* q, const float* scales, const int64_t* token_indices, const int64_t* sorted_experts,
+                      const int64_t* base_send, const int64_t* my_start, const int64_t* peer_q, const int64_t* peer_scales,
+                      int64_t n_pairs, int64_t n_tokens, int64_t d, int64_t n_scales, int experts_per_rank, int n_ranks,
+                      int64_t capacity_rows, void* stream);
+
+/* The way home by peer stores: row r < n_rows of this rank's expert-grouped outputs (row_bytes each, a multiple of
+ * 16) belongs to segment i = (local expert, source rank) with seg_start[i] <= r < seg_start[i + 1] and is copied
+ * to rank i % n_ranks at row home_base[i] + (r - seg_start[i]) of its buffer peer_home[rank] (capacity_rows
+ * rows): the position of the pair in that rank's sorted order, which is what cinn_moe_combine reads.
+ * seg_start: (n_segments + 1), home_base: (n_segments) int64 device arrays. */
+int cinn_p2p_return(const void* rows, const int64_t* seg_start, const int64_t* home_base, const int64_t* peer_home,
+                    int64_t n_rows, int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity_rows, void* stream);
+
+/* Stream-ordered barrier over the ranks of one node for the peer-store exchange (no reference counterpart).
+ * peer_flags: DEVICE array of n_ranks base addresses of the ranks' flag arrays (n_ranks uint32 each, zeroed once,
+ * in symmetric memory); epoch: 1, 2, 3, ... the same sequence on every rank.  Work enqueued before the barrier on
+ * every rank's stream is complete (and its peer stores visible) before work enqueued after it starts.  The wait is
+ * bounded (about 2 s): a rank that never arrives leaves a code in the device status word instead of a hung GPU.
+ * Every rank must run on a GPU of its own. */
+int cinn_p2p_barrier(const int64_t* peer_flags, int rank, int n_ranks, unsigned epoch, void* stream);
+
 /* Routing of MoE.forward (src/layers.py:122-148) on the device: scores = sigmoid(logits), the top_k experts of
  * scores + bias per token (ties: the lower expert id), gates = score / (sum of the k scores + 1e-9), and the
  * (token, expert) pairs sorted by expert in the order of a stable sort.

@@ -116,6 +116,24 @@ def test_scatter_rows(K):
     assert torch.equal(K.scatter_rows(odd, perm), torch.empty_like(odd).index_copy_(0, perm, odd))
 
 
+def test_route_ties_and_saturation(K):
+    """Equal scores go to the lower expert id; saturated sigmoids (score exactly 1) and a NaN logit do not break
+    the invariants (k distinct experts per token, counts add up, rows sorted by expert)."""
+    T, E, k = 64, 40, 4
+    logits = torch.zeros(T, E, device="cuda")
+    logits[1] = 50.0                                  # every score saturates to 1.0: pure ties
+    logits[2, 7] = float("nan")
+    logits[3, :5] = torch.tensor([3.0, 3.0, 2.0, 3.0, 1.0], device="cuda")
+    got = K.moe_route(logits, torch.zeros(E, device="cuda"), k)
+    top = got["top_experts"].long()
+    assert top[0].tolist() == [0, 1, 2, 3] and top[1].tolist() == [0, 1, 2, 3]
+    assert 7 not in top[2].tolist() and top[3].tolist() == [0, 1, 3, 2]
+    assert all(len(set(row)) == k for row in top.tolist())
+    assert int(got["counts"].sum()) == T * k
+    assert torch.equal(got["sorted_experts"], got["sorted_experts"].sort().values)
+    assert torch.equal(torch.bincount(top.reshape(-1), minlength=E), got["counts"])
+
+
 def test_route_empty(K):
     got = K.moe_route(torch.empty(0, 32, device="cuda"), torch.zeros(32, device="cuda"), 4)
     assert got["counts"].tolist() == [0] * 32 and got["token_indices"].numel() == 0
@@ -216,8 +234,12 @@ y_layer = [layer(x) for _ in range(3)][-1]
 # and with the tokens in two chunks whose exchanges run under the other chunk's experts
 layer2 = moe.ExpertParallelMoE(router, bias, w12[lo:hi], w3[lo:hi], k, shared=moe.FP8SwiGLU(s1, s2, s3), n_chunks=2)
 y_chunked = [layer2(x) for _ in range(3)][-1]
+# and with the exchange done by peer stores into symmetric memory (three calls: the buffers are reused)
+layer3 = moe.ExpertParallelMoE(router, bias, w12[lo:hi], w3[lo:hi], k, shared=moe.FP8SwiGLU(s1, s2, s3), exchange="p2p")
+y_p2p = [layer3(x) for _ in range(3)][-1]
 torch.cuda.synchronize()
-torch.save({"y_ep": y_ep.cpu(), "y_layer": y_layer.cpu(), "y_chunked": y_chunked.cpu(), "x": x.cpu(), "status": K.device_status()},
+torch.save({"y_ep": y_ep.cpu(), "y_layer": y_layer.cpu(), "y_chunked": y_chunked.cpu(), "y_p2p": y_p2p.cpu(), "x": x.cpu(),
+            "status": K.device_status()},
            os.path.join(sys.argv[2], f"ep_{rank}.pt"))
 dist.barrier(); dist.destroy_process_group()
 '''
@@ -252,6 +274,7 @@ def test_expert_parallel_two_gpus_match_one(K, tmp_path):
         y_one = moe.moe_forward(x, r, experts, K.quantize_fp8_rowwise)
         assert rel_fro(got["y_layer"], (shared(x).float() + y_one).cpu().double()) < 1e-6
         assert rel_fro(got["y_chunked"], (shared(x).float() + y_one).cpu().double()) < 1e-6
+        assert torch.equal(got["y_p2p"], got["y_layer"])                  # same rows in the same order: same bits
         # same e4m3 payloads and the same per-row arithmetic: only the fp32 summation order of a token's
         # experts could differ, and index_add_ keeps it
         assert rel_fro(got["y_ep"], y_one.cpu().double()) < 1e-6

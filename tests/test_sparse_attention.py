@@ -100,6 +100,25 @@ def test_kernels_match_oracle(dtype, shape):
 
 
 @pytest.mark.gpu
+def test_edge_shapes():
+    """No indices at all, indices outside the sequence, one query, a list much longer than the sequence."""
+    from cinnamon_b200 import kernels as K
+    g = torch.Generator().manual_seed(77)
+    q, k, v = (torch.randn(1, 2, 9, 16, generator=g).cuda() for _ in range(3))
+    out, attn = K.sparse_attention(q, k, v, torch.zeros(1, 9, 0, dtype=torch.int64, device="cuda"))
+    assert attn.shape == (1, 2, 9, 0) and torch.all(out == 0)
+    idx = torch.randint(-3, 14, (1, 9, 40), generator=g)                     # some below 0, some beyond L - 1
+    ref_out, ref_attn, _ = SO.forward(q.cpu(), k.cpu(), v.cpu(), idx, 0.25)
+    out, attn = K.sparse_attention(q, k, v, idx.cuda(), 0.25)
+    torch.testing.assert_close(out.cpu().double(), ref_out, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(attn.cpu().double(), ref_attn, rtol=2e-5, atol=1e-7)
+    q1, k1, v1 = (t[:, :, :1].contiguous() for t in (q, k, v))
+    out, attn = K.sparse_attention(q1, k1, v1, torch.zeros(1, 1, 3, dtype=torch.int64, device="cuda"))
+    torch.testing.assert_close(out, v1.expand_as(out))                       # the only key, listed three times
+    torch.testing.assert_close(attn, torch.full_like(attn, 1.0 / 3.0))
+
+
+@pytest.mark.gpu
 def test_argument_checks():
     from cinnamon_b200 import kernels as K
     q = torch.randn(1, 1, 4, 8)
