@@ -368,6 +368,7 @@ def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label, chunks=1
         dist.all_reduce(load, op=dist.ReduceOp.MAX)
         dist.all_reduce(total, op=dist.ReduceOp.SUM)
     active = int((r.counts > 0).sum())
+    module_exchange = module.exchange              # "nccl" if symmetric memory was not available
     del experts, module
     torch.cuda.empty_cache()
     flop = float(total.item()) * 2.0 * c["d"] * 3 * c["I"]
@@ -375,7 +376,7 @@ def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label, chunks=1
             "ms_per_layer": ms.item(), "grouped_gemm_ms": gms.item(), "grouped_gemm_tflops": flop / (gms.item() * 1e-3) / 1e12,
             "expert_weight_quant_ms": wq_ms, "max_rank_rows": int(load.item()), "mean_rank_rows": total.item() / world,
             "active_experts_rank0_view": active, "scaling": "strong", "n_gpus": world,
-            "token_chunks": chunks if world > 1 else 1, "exchange": exchange if world > 1 else "none"}
+            "token_chunks": chunks if world > 1 else 1, "exchange": module_exchange if world > 1 else "none"}
 
 
 # ---------------------------------------------------------------------------------------
@@ -411,7 +412,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-moe", action="store_true", help="skip the MoE layer measurements")
-    ap.add_argument("--moe-exchange", default="nccl", choices=["nccl", "p2p"],
+    ap.add_argument("--moe-exchange", default="p2p", choices=["nccl", "p2p"],
                     help="expert-parallel exchange (N > 1): all-to-all collectives, or peer stores into symmetric memory")
     ap.add_argument("--moe-chunks", type=int, default=1,
                     help="token chunks of the expert-parallel layer (N > 1): exchanges of one chunk run under the experts of another")

@@ -502,7 +502,14 @@ class ExpertParallelMoE(torch.nn.Module):
             n_pairs, d = flat.shape[0] * self.top_k, flat.shape[1]
             if self._peer_buffers is None or not self._peer_buffers.fits(n_pairs * world, n_pairs, d, (d + 127) // 128):
                 # worst case: every pair of every rank routed to this rank's experts (all ranks bring equally many tokens)
-                self._peer_buffers = p2p.PeerBuffers(self.group, flat.device, n_pairs * world, n_pairs, d, (d + 127) // 128)
+                try:
+                    self._peer_buffers = p2p.PeerBuffers(self.group, flat.device, n_pairs * world, n_pairs, d, (d + 127) // 128)
+                except Exception as exc:                    # noqa: BLE001  (no symmetric memory here: the same on every rank)
+                    import warnings
+                    warnings.warn(f"symmetric memory is not available ({type(exc).__name__}: {exc}); "
+                                  "the expert-parallel exchange uses all-to-all collectives instead")
+                    self.exchange = "nccl"
+                    return self.forward(x)
             y = moe_forward_p2p(flat, r, self.experts, self.K.quantize_fp8_rowwise, self._peer_buffers, self.group, addend=sh,
                                 before_combine=join)
         elif world > 1 and self.n_chunks > 1 and flat.shape[0] >= self.n_chunks:
