@@ -44,7 +44,9 @@ int fp8_gemm(const void* A, const float* sA, int64_t ld_sa, const void* B, const
              void* C, int64_t M, int64_t N, int64_t K, int b_layout, int out_dtype, cudaStream_t st);
 int fp8_grouped_gemm(const void* A, const float* sA, const void* W, const float* sW, const int64_t* starts,
                      const int64_t* ends, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* C, int out_dtype,
-                     cudaStream_t st);
+                     cudaStream_t st, const long long* row_dst);
+int p2p_row_table(const int64_t* seg_start, const int64_t* home_base, const int64_t* peer_home, int64_t n_rows, int64_t row_bytes,
+                  int n_segments, int n_ranks, int64_t capacity, long long* row_dst, cudaStream_t st);
 
 int read_device_status(int* out, int reset);
 int fp8_grouped_gemm_dgrad(const void* dY, const float* sdY, const void* W, const float* sW, const int64_t* starts,
@@ -140,7 +142,7 @@ int cinn_fp8_gemm(const void* A, const float* sA, int64_t ld_sa, const void* B, 
 int cinn_fp8_grouped_gemm(const void* A, const float* sA, const void* W, const float* sW, const int64_t* starts,
                           const int64_t* ends, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* C,
                           int out_dtype, void* stream) {
-    return cinn::fp8_grouped_gemm(A, sA, W, sW, starts, ends, E, T, d_in, d_out, C, out_dtype, (cudaStream_t)stream);
+    return cinn::fp8_grouped_gemm(A, sA, W, sW, starts, ends, E, T, d_in, d_out, C, out_dtype, (cudaStream_t)stream, nullptr);
 }
 
 int cinn_fp8_grouped_gemm_dgrad(const void* dY, const float* sdY, const void* W, const float* sW, const int64_t* starts,
@@ -204,6 +206,19 @@ int cinn_p2p_return(const void* rows, const int64_t* seg_start, const int64_t* h
                     int64_t n_rows, int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity_rows, void* stream) {
     return cinn::p2p_return(rows, seg_start, home_base, peer_home, n_rows, row_bytes, n_segments, n_ranks, capacity_rows,
                             (cudaStream_t)stream);
+}
+
+int cinn_fp8_grouped_gemm_scatter(const void* A, const float* sA, const void* W, const float* sW, const int64_t* starts,
+                                  const int64_t* ends, int64_t E, int64_t T, int64_t d_in, int64_t d_out,
+                                  const int64_t* row_dst, int out_dtype, void* stream) {
+    return cinn::fp8_grouped_gemm(A, sA, W, sW, starts, ends, E, T, d_in, d_out, nullptr, out_dtype, (cudaStream_t)stream,
+                                  reinterpret_cast<const long long*>(row_dst));
+}
+
+int cinn_p2p_row_table(const int64_t* seg_start, const int64_t* home_base, const int64_t* peer_home, int64_t n_rows,
+                       int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity_rows, int64_t* row_dst, void* stream) {
+    return cinn::p2p_row_table(seg_start, home_base, peer_home, n_rows, row_bytes, n_segments, n_ranks, capacity_rows,
+                               reinterpret_cast<long long*>(row_dst), (cudaStream_t)stream);
 }
 
 int cinn_p2p_barrier(const int64_t* peer_flags, int rank, int n_ranks, unsigned epoch, void* stream) {

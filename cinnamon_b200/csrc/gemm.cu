@@ -48,6 +48,8 @@ struct GemmParams {
     int M, N, K;                   // dense: A is (M, K); grouped: M = total rows T
     const int64_t* starts; const int64_t* ends; int E; int b_rows_per_expert;
     int tma_out;                   // 1: finished tiles leave through TMA stores (2-byte outputs, N % 8 == 0)
+    const long long* row_dst;      // optional: byte address of every output row (0 = drop the row) instead of C + row * ldc;
+                                   // rows may live in another GPU's memory (expert-parallel way home)
 };
 
 // ---------------------------------------------------------------------------
@@ -255,7 +257,7 @@ __device__ __forceinline__ uint4 pack16(const float* a) {
 
 template <int OUT, int NCOLS>
 __device__ __forceinline__ void store_rows_staged(const float* acc, uint8_t* stage, void* C, int64_t ldc, int row0, int m_end,
-                                                  int col0, int N, int lane) {
+                                                  int col0, int N, int lane, const long long* row_dst = nullptr) {
     using T = typename OutT<OUT>::type;
     constexpr int PER16 = 16 / (int)sizeof(T);      // elements per 16-byte slot
     constexpr int PER64 = 4 * PER16;                // elements per staged row piece
@@ -270,7 +272,10 @@ __device__ __forceinline__ void store_rows_staged(const float* acc, uint8_t* sta
             const int r = i * 8 + (lane >> 2), c = lane & 3;
             const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 64 + ((c ^ ((r >> 1) & 3)) << 4));
             const int grow = row0 + r, gcol = col0 + ps * PER64 + c * PER16;
-            if (grow < m_end && gcol < N) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(C) + (int64_t)grow * ldc + gcol) = v;
+            if (grow < m_end && gcol < N) {
+                T* dst = row_dst ? reinterpret_cast<T*>(row_dst[grow]) : reinterpret_cast<T*>(C) + (int64_t)grow * ldc;
+                if (dst) *reinterpret_cast<uint4*>(dst + gcol) = v;
+            }
         }
         __syncwarp();
     }
@@ -522,7 +527,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 if (!alive) break;
             } else if (alive && vec_ok && !(TMA_OUT && p.tma_out)) {
                 // warp-uniform: every lane takes part in the staging even if its own row is past the end
-                if (cvalid) store_rows_staged<OUT, WCOLS>(acc, store_stage + warp * 2048, p.C, p.ldc, ti.m0 + q * 32, ti.m_end, col0, p.N, lane);
+                if (cvalid) store_rows_staged<OUT, WCOLS>(acc, store_stage + warp * 2048, p.C, p.ldc, ti.m0 + q * 32, ti.m_end, col0, p.N, lane,
+                                                          p.row_dst);
             } else if (alive && rvalid && cvalid) {
                 const int64_t base = (int64_t)row * p.ldc + col0;
 #pragma unroll
@@ -635,9 +641,13 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMa
 template <bool B_MN, bool GROUPED>
 static int launch_out(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, int out_dtype, int grid,
                       cudaStream_t st) {
-    CUtensorMap tc;
-    int rc = make_out_map(&tc, ta, p, out_dtype, p.M);
-    if (rc) return rc;
+    CUtensorMap tc = ta;
+    if (p.row_dst != nullptr) {
+        p.tma_out = 0;                               // rows go to scattered addresses: staged 16-byte stores
+    } else {
+        int rc = make_out_map(&tc, ta, p, out_dtype, p.M);
+        if (rc) return rc;
+    }
     switch (out_dtype) {
         case CINN_BF16: return launch<B_MN, GROUPED, CINN_BF16>(ta, tb, tc, p, grid, st);
         case CINN_F32: return launch<B_MN, GROUPED, CINN_F32>(ta, tb, tc, p, grid, st);
@@ -751,10 +761,12 @@ int fp8_gemm(const void* A, const float* sA, int64_t ld_sa, const void* B, const
 
 int fp8_grouped_gemm(const void* A, const float* sA, const void* W, const float* sW, const int64_t* starts,
                      const int64_t* ends, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* C, int out_dtype,
-                     cudaStream_t st) {
+                     cudaStream_t st, const long long* row_dst) {
     CINN_CHECK_ARG(E >= 0 && T >= 0 && d_in >= 0 && d_out >= 0, "grouped_gemm: negative shape");
     if (E == 0 || T == 0 || d_out == 0) return CINN_OK;
-    CINN_CHECK_ARG(A && sA && W && sW && starts && ends && C, "grouped_gemm: null pointer");
+    CINN_CHECK_ARG(A && sA && W && sW && starts && ends && (C || row_dst), "grouped_gemm: null pointer");
+    CINN_CHECK_ARG(row_dst == nullptr || (d_out % 8 == 0 && (out_dtype == CINN_BF16 || out_dtype == CINN_F16)),
+                   "grouped_gemm: scattered output rows need a 2-byte output type and d_out %% 8 == 0");
     CINN_CHECK_ARG(E <= MAX_EXPERTS, "grouped_gemm: at most %d experts are supported (got %lld)", MAX_EXPERTS, (long long)E);
     CINN_CHECK_ARG(d_in > 0 && d_in % 16 == 0, "grouped_gemm: d_in (%lld) must be a positive multiple of 16", (long long)d_in);
     CINN_CHECK_ARG(T < (1LL << 31) && d_out < (1LL << 31) && d_in < (1LL << 31) && E * d_out < (1LL << 31),
@@ -771,6 +783,7 @@ int fp8_grouped_gemm(const void* A, const float* sA, const void* W, const float*
     p.sB = sW; p.sb_stride_k = 1; p.sb_stride_n = nkb; p.sb_stride_e = nnb * nkb;
     p.C = C; p.ldc = d_out; p.M = (int)T; p.N = (int)d_out; p.K = (int)d_in;
     p.starts = starts; p.ends = ends; p.E = (int)E; p.b_rows_per_expert = (int)d_out;
+    p.row_dst = row_dst;
     return launch_out<false, true>(ta, tb, p, out_dtype, gemm_sms(), st);
 }
 

@@ -285,6 +285,43 @@ int p2p_barrier(const int64_t* peer_flags, int me, int n_ranks, unsigned epoch, 
     return CINN_OK;
 }
 
+// The same addresses as p2p_return_kernel computes, written out as a table (one byte address per row of the
+// expert-grouped order, 0 = no destination): the grouped GEMM takes it and stores every finished output row
+// straight to its home, so the way home runs under the GEMM instead of after it.
+__global__ void __launch_bounds__(256)
+p2p_row_table_kernel(const int64_t* __restrict__ seg_start, const int64_t* __restrict__ home_base,
+                     const int64_t* __restrict__ peer_home, int64_t n_rows, int n_segments, int n_ranks, int64_t row_bytes,
+                     int64_t capacity, long long* __restrict__ row_dst) {
+    for (int64_t r = (int64_t)blockIdx.x * 256 + threadIdx.x; r < n_rows; r += (int64_t)gridDim.x * 256) {
+        int lo = 0, hi = n_segments;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (seg_start[mid + 1] > r) hi = mid; else lo = mid + 1;
+        }
+        long long addr = 0;
+        if (lo < n_segments && seg_start[lo] <= r) {
+            const int64_t dst = home_base[lo] + (r - seg_start[lo]);
+            if (dst >= 0 && dst < capacity) addr = peer_home[lo % n_ranks] + dst * row_bytes;
+        }
+        if (addr == 0) atomicCAS(&g_moe_status, 0, (5 << 8) | 4);
+        row_dst[r] = addr;
+    }
+}
+
+int p2p_row_table(const int64_t* seg_start, const int64_t* home_base, const int64_t* peer_home, int64_t n_rows, int64_t row_bytes,
+                  int n_segments, int n_ranks, int64_t capacity, long long* row_dst, cudaStream_t st) {
+    CINN_CHECK_ARG(n_rows >= 0 && row_bytes >= 0 && n_segments >= 1 && n_ranks >= 1 && capacity >= 0, "p2p_row_table: bad shape");
+    if (n_rows == 0) return CINN_OK;
+    CINN_CHECK_ARG(seg_start && home_base && peer_home && row_dst, "p2p_row_table: null pointer");
+    CINN_CHECK_ARG(row_bytes % 16 == 0, "p2p_row_table: the row size (%lld bytes) must be a multiple of 16", (long long)row_bytes);
+    int64_t blocks = (n_rows + 255) / 256;
+    if (blocks > 4096) blocks = 4096;
+    p2p_row_table_kernel<<<(unsigned)blocks, 256, 0, st>>>(seg_start, home_base, peer_home, n_rows, n_segments, n_ranks, row_bytes,
+                                                          capacity, row_dst);
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
 int p2p_dispatch(const void* q, const float* s, const int64_t* token_indices, const int64_t* sorted_experts,
                  const int64_t* base_send, const int64_t* my_start, const int64_t* peer_q, const int64_t* peer_s,
                  int64_t n_pairs, int64_t n_tokens, int64_t d, int64_t ns, int e_local, int n_ranks, int64_t capacity,

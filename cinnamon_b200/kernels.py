@@ -434,6 +434,34 @@ def fp8_grouped_gemm(x_fp8, x_scale, w_fp8, w_scale, expert_starts, expert_ends,
     return out
 
 
+def fp8_grouped_gemm_scatter(x_fp8, x_scale, w_fp8, w_scale, expert_starts, expert_ends, row_dst: torch.Tensor,
+                             out_dtype=torch.bfloat16) -> None:
+    """The grouped GEMM with every finished output row stored at the byte address ``row_dst[r]`` (int64 device
+    tensor, one entry per row, 0 = drop), which may lie in a peer GPU's memory (``cinn_fp8_grouped_gemm_scatter``)."""
+    T, d_in = x_fp8.shape
+    E, d_out, _ = w_fp8.shape
+    assert row_dst.dtype == torch.int64 and row_dst.numel() == T, "row_dst: one int64 byte address per row"
+    starts = expert_starts.to(torch.int64).contiguous()
+    ends = expert_ends.to(torch.int64).contiguous()
+    with torch.cuda.device(x_fp8.device):
+        _lib.check(_L.cinn_fp8_grouped_gemm_scatter(_ptr(x_fp8), _ptr(x_scale), _ptr(w_fp8), _ptr(w_scale), _ptr(starts),
+                                                    _ptr(ends), E, T, d_in, d_out, _ptr(row_dst), _DTYPE_TAG[out_dtype],
+                                                    _stream(x_fp8)), "cinn_fp8_grouped_gemm_scatter")
+    _count()
+
+
+def p2p_row_table(seg_start, home_base, peer_home, n_rows: int, row_bytes: int, n_ranks: int, capacity_rows: int) -> torch.Tensor:
+    """Byte address, on the rank it goes home to, of every row of this rank's expert-grouped outputs
+    (``cinn_p2p_row_table``): the ``row_dst`` of ``fp8_grouped_gemm_scatter``."""
+    with torch.cuda.device(seg_start.device):
+        table = torch.empty(max(n_rows, 1), dtype=torch.int64, device=seg_start.device)[:n_rows]
+        _lib.check(_L.cinn_p2p_row_table(_ptr(seg_start), _ptr(home_base), _ptr(peer_home), n_rows, row_bytes,
+                                         home_base.numel(), n_ranks, capacity_rows, _ptr(table), _stream(seg_start)),
+                   "cinn_p2p_row_table")
+    _count()
+    return table
+
+
 def swiglu_quantize_rowwise(h12: torch.Tensor):
     """``h = (silu(h1) * h2).to(h12.dtype)`` with ``h1, h2 = h12.float().chunk(2, -1)`` (reference
     src/layers.py:72-74), quantised row-wise in 1x128 tiles, in one pass.

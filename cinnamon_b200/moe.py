@@ -106,12 +106,16 @@ class FP8Experts:
         self.w3_q, self.w3_s = self.K.quantize_expert_weights(w3)
 
     def __call__(self, x_q: torch.Tensor, x_s: torch.Tensor, starts: torch.Tensor, ends: torch.Tensor,
-                 out_dtype=torch.bfloat16) -> torch.Tensor:
+                 out_dtype=torch.bfloat16, row_dst: torch.Tensor = None) -> torch.Tensor:
         """x_q (R, d) e4m3 rows grouped by expert, x_s (R, d/128) -> (R, d) ``out_dtype``.
-        Rows outside [starts[0], ends[-1]) are not written."""
+        Rows outside [starts[0], ends[-1]) are not written.  With ``row_dst`` (one byte address per row) the
+        down-projection stores every output row there instead (possibly on a peer GPU) and nothing is returned."""
         K = self.K
         h12 = K.fp8_grouped_gemm(x_q, x_s, self.w12_q, self.w12_s, starts, ends, out_dtype=torch.bfloat16)
         h_q, h_s = K.swiglu_quantize_rowwise(h12)
+        if row_dst is not None:
+            K.fp8_grouped_gemm_scatter(h_q, h_s, self.w3_q, self.w3_s, starts, ends, row_dst, out_dtype=out_dtype)
+            return None
         return K.fp8_grouped_gemm(h_q, h_s, self.w3_q, self.w3_s, starts, ends, out_dtype=out_dtype)
 
 
@@ -289,14 +293,17 @@ def moe_forward(x: torch.Tensor, routing: Routing, experts: Callable, quantize: 
 
 
 def moe_forward_p2p(x: torch.Tensor, routing: Routing, experts: Callable, quantize: Callable, buffers, group=None,
-                    addend: Optional[torch.Tensor] = None, before_combine: Optional[Callable] = None) -> torch.Tensor:
+                    addend: Optional[torch.Tensor] = None, before_combine: Optional[Callable] = None,
+                    fused_return: bool = False) -> torch.Tensor:
     """``moe_forward`` with the exchange done by peer stores over NVLink (``cinnamon_b200/p2p.py``) instead of
     all-to-all collectives: one small all-gather of the routing counts, then every quantised row is written
     straight to its place in the expert-grouped buffer of the rank that owns its expert, and every expert output
     straight to its pair's place on the rank its token lives on.  No gather, regrouping or inverse permutation
     passes, no send/receive kernels; three stream-ordered barriers order the phases.  One host read-back (the
-    number of rows this rank received).  ``buffers``: a ``p2p.PeerBuffers``.  Same arithmetic per row as
-    ``moe_forward``; returns fp32 (T, d)."""
+    number of rows this rank received).  ``buffers``: a ``p2p.PeerBuffers``.  ``fused_return``: the expert
+    down-projection stores its output rows straight to their home ranks from its epilogue (``experts`` must accept
+    ``row_dst``), instead of a separate pass after the GEMM.  Same arithmetic per row as ``moe_forward``; returns
+    fp32 (T, d)."""
     from . import kernels as K
     from . import p2p
     world, me = dist.get_world_size(group), dist.get_rank(group)
@@ -315,8 +322,13 @@ def moe_forward_p2p(x: torch.Tensor, routing: Routing, experts: Callable, quanti
     assert rows <= buffers.capacity_rows and n_pairs <= buffers.home_rows, "peer buffers too small"
     recv_q = buffers.q.view(buffers.capacity_rows, buffers.d)[:rows].view(x_q.dtype)
     recv_s = buffers.s.view(buffers.capacity_rows, buffers.n_scales)[:rows]
-    out_rows = experts(recv_q, recv_s, t.starts, t.ends)
-    K.p2p_return(out_rows, t.seg_start, t.home_base, buffers.peer_home, world, buffers.home_rows)
+    if fused_return:
+        # the down-projection's epilogue stores every finished row straight to its home: the way home runs under the GEMM
+        table = K.p2p_row_table(t.seg_start, t.home_base, buffers.peer_home, rows, buffers.d * 2, world, buffers.home_rows)
+        experts(recv_q, recv_s, t.starts, t.ends, row_dst=table)
+    else:
+        out_rows = experts(recv_q, recv_s, t.starts, t.ends)
+        K.p2p_return(out_rows, t.seg_start, t.home_base, buffers.peer_home, world, buffers.home_rows)
     buffers.barrier()                                   # every expert output is home
     home = buffers.home.view(buffers.home_rows, buffers.d)[:n_pairs]
     if before_combine is not None:
@@ -453,7 +465,8 @@ class ExpertParallelMoE(torch.nn.Module):
                  w3_local: torch.Tensor, top_k: int, group=None, shared: Optional[FP8SwiGLU] = None, n_chunks: int = 1,
                  exchange: str = "nccl"):
         super().__init__()
-        assert exchange in ("nccl", "p2p"), "exchange must be 'nccl' (all-to-all collectives) or 'p2p' (peer stores)"
+        assert exchange in ("nccl", "p2p", "p2p-fused"), \
+            "exchange: 'nccl' (all-to-all collectives), 'p2p' (peer stores) or 'p2p-fused' (way home from the GEMM epilogue)"
         self.exchange = exchange
         self._peer_buffers = None
         from . import kernels as K
@@ -496,7 +509,7 @@ class ExpertParallelMoE(torch.nn.Module):
             join = lambda: cur.wait_stream(self._side)                    # noqa: E731
         elif self.shared is not None:
             sh = self.shared(flat)
-        if world > 1 and self.exchange == "p2p" and flat.is_cuda:
+        if world > 1 and self.exchange in ("p2p", "p2p-fused") and flat.is_cuda:
             from . import p2p
             r = route(flat, router, self.expert_bias, self.top_k)
             n_pairs, d = flat.shape[0] * self.top_k, flat.shape[1]
@@ -511,7 +524,7 @@ class ExpertParallelMoE(torch.nn.Module):
                     self.exchange = "nccl"
                     return self.forward(x)
             y = moe_forward_p2p(flat, r, self.experts, self.K.quantize_fp8_rowwise, self._peer_buffers, self.group, addend=sh,
-                                before_combine=join)
+                                before_combine=join, fused_return=self.exchange == "p2p-fused")
         elif world > 1 and self.n_chunks > 1 and flat.shape[0] >= self.n_chunks:
             routings = [route(c, router, self.expert_bias, self.top_k) for c in torch.tensor_split(flat, self.n_chunks)]
             y = moe_forward_pipelined(flat, routings, self.experts, self.K.quantize_fp8_rowwise, self.group, addend=sh,

@@ -208,6 +208,21 @@ int cinn_p2p_dispatch(const void* q, const float* scales, const int64_t* token_i
 int cinn_p2p_return(const void* rows, const int64_t* seg_start, const int64_t* home_base, const int64_t* peer_home,
                     int64_t n_rows, int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity_rows, void* stream);
 
+/* cinn_fp8_grouped_gemm whose finished output rows go to arbitrary addresses: row r of the result is stored at
+ * the BYTE address row_dst[r] (device array, T entries; 0 = drop the row) instead of C + r * d_out.  The addresses
+ * may lie in another GPU's memory that is mapped into this process: with the table of cinn_p2p_row_table the
+ * down-projection of an expert-parallel rank writes every expert output straight to the rank its token lives on,
+ * under the GEMM rather than after it.  out_dtype CINN_BF16 or CINN_F16, d_out a multiple of 8, every address
+ * 16-byte aligned.  No reference counterpart. */
+int cinn_fp8_grouped_gemm_scatter(const void* A, const float* sA, const void* W, const float* sW, const int64_t* starts,
+                                  const int64_t* ends, int64_t E, int64_t T, int64_t d_in, int64_t d_out,
+                                  const int64_t* row_dst, int out_dtype, void* stream);
+
+/* The destinations of cinn_p2p_return as a table: row_dst[r] = peer_home[rank] + row * row_bytes for r < n_rows
+ * (0 and a status code where the tables point outside the buffers). */
+int cinn_p2p_row_table(const int64_t* seg_start, const int64_t* home_base, const int64_t* peer_home, int64_t n_rows,
+                       int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity_rows, int64_t* row_dst, void* stream);
+
 /* Stream-ordered barrier over the ranks of one node for the peer-store exchange (no reference counterpart).
  * peer_flags: DEVICE array of n_ranks base addresses of the ranks' flag arrays (n_ranks uint32 each, zeroed once,
  * in symmetric memory); epoch: 1, 2, 3, ... the same sequence on every rank.  Work enqueued before the barrier on

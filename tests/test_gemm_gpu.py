@@ -140,6 +140,33 @@ def test_autograd_function_matches_oracle(K, M, Kd, N, rs):
         assert err < 4e-3, name          # bf16 rounding alone costs ~1.7e-3
 
 
+def test_grouped_gemm_scattered_rows(K):
+    """Output rows stored at per-row addresses (the expert-parallel way home): here a permutation inside a local
+    buffer, with a dropped row (address 0) and ragged expert sizes; same bits as the plain grouped GEMM."""
+    g = torch.Generator().manual_seed(41)
+    E, d_in, d_out = 4, 256, 384
+    counts = [130, 0, 77, 200]
+    T = sum(counts)
+    x = torch.randn(T, d_in, generator=g).bfloat16().cuda()
+    w = (torch.randn(E, d_out, d_in, generator=g) * 0.05).bfloat16().cuda()
+    ends = torch.tensor(counts).cumsum(0).cuda()
+    starts = ends - torch.tensor(counts).cuda()
+    xq, xs = K.quantize_fp8_rowwise(x)
+    wq, ws = K.quantize_expert_weights(w)
+    ref = K.fp8_grouped_gemm(xq, xs, wq, ws, starts, ends, out_dtype=torch.bfloat16)
+    perm = torch.randperm(T, generator=g).cuda()
+    out = torch.full((T + 3, d_out), 7.0, dtype=torch.bfloat16, device="cuda")
+    table = out.data_ptr() + perm * (d_out * 2)
+    table[5] = 0                                                            # this row has no destination
+    K.fp8_grouped_gemm_scatter(xq, xs, wq, ws, starts, ends, table.contiguous(), out_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    assert K.device_status() == 0
+    keep = torch.ones(T, dtype=torch.bool, device="cuda")
+    keep[5] = False
+    assert torch.equal(out[perm[keep]], ref[keep])
+    assert torch.all(out[perm[5]] == 7.0) and torch.all(out[T:] == 7.0)     # untouched
+
+
 def test_fp8_linear_module(K):
     g = torch.Generator().manual_seed(3)
     lin = K.FP8Linear(256, 384, bias=True, round_scale=True).cuda()

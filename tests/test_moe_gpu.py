@@ -237,8 +237,11 @@ y_chunked = [layer2(x) for _ in range(3)][-1]
 # and with the exchange done by peer stores into symmetric memory (three calls: the buffers are reused)
 layer3 = moe.ExpertParallelMoE(router, bias, w12[lo:hi], w3[lo:hi], k, shared=moe.FP8SwiGLU(s1, s2, s3), exchange="p2p")
 y_p2p = [layer3(x) for _ in range(3)][-1]
+# ... and with the way home written by the down-projection's epilogue
+layer4 = moe.ExpertParallelMoE(router, bias, w12[lo:hi], w3[lo:hi], k, shared=moe.FP8SwiGLU(s1, s2, s3), exchange="p2p-fused")
+y_fused = [layer4(x) for _ in range(3)][-1]
 torch.cuda.synchronize()
-torch.save({"y_ep": y_ep.cpu(), "y_layer": y_layer.cpu(), "y_chunked": y_chunked.cpu(), "y_p2p": y_p2p.cpu(), "x": x.cpu(),
+torch.save({"y_ep": y_ep.cpu(), "y_layer": y_layer.cpu(), "y_chunked": y_chunked.cpu(), "y_p2p": y_p2p.cpu(), "y_fused": y_fused.cpu(), "x": x.cpu(),
             "status": K.device_status()},
            os.path.join(sys.argv[2], f"ep_{rank}.pt"))
 dist.barrier(); dist.destroy_process_group()
@@ -275,6 +278,7 @@ def test_expert_parallel_two_gpus_match_one(K, tmp_path):
         assert rel_fro(got["y_layer"], (shared(x).float() + y_one).cpu().double()) < 1e-6
         assert rel_fro(got["y_chunked"], (shared(x).float() + y_one).cpu().double()) < 1e-6
         assert torch.equal(got["y_p2p"], got["y_layer"])                  # same rows in the same order: same bits
+        assert torch.equal(got["y_fused"], got["y_layer"])
         # same e4m3 payloads and the same per-row arithmetic: only the fp32 summation order of a token's
         # experts could differ, and index_add_ keeps it
         assert rel_fro(got["y_ep"], y_one.cpu().double()) < 1e-6
