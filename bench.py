@@ -412,7 +412,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-moe", action="store_true", help="skip the MoE layer measurements")
-    ap.add_argument("--moe-exchange", default="p2p", choices=["nccl", "p2p", "p2p-fused"],
+    ap.add_argument("--moe-exchange", default="p2p-fused", choices=["nccl", "p2p", "p2p-fused"],
                     help="expert-parallel exchange (N > 1): all-to-all collectives, or peer stores into symmetric memory")
     ap.add_argument("--moe-chunks", type=int, default=1,
                     help="token chunks of the expert-parallel layer (N > 1): exchanges of one chunk run under the experts of another")
