@@ -44,12 +44,10 @@ __device__ int g_device_status = 0;
 struct GemmParams {
     const float* sA; int64_t sa_stride_m, sa_stride_k;
     const float* sB; int64_t sb_stride_k, sb_stride_n, sb_stride_e;
-    void* C; int64_t ldc;
+    void* C; int64_t ldc;          // scatter variant: C is a table of byte addresses, one per output row (0 = drop the row)
     int M, N, K;                   // dense: A is (M, K); grouped: M = total rows T
     const int64_t* starts; const int64_t* ends; int E; int b_rows_per_expert;
     int tma_out;                   // 1: finished tiles leave through TMA stores (2-byte outputs, N % 8 == 0)
-    const long long* row_dst;      // optional: byte address of every output row (0 = drop the row) instead of C + row * ldc;
-                                   // rows may live in another GPU's memory (expert-parallel way home)
 };
 
 // ---------------------------------------------------------------------------
@@ -255,9 +253,9 @@ __device__ __forceinline__ uint4 pack16(const float* a) {
     return v;
 }
 
-template <int OUT, int NCOLS>
+template <int OUT, int NCOLS, bool SCATTER = false>
 __device__ __forceinline__ void store_rows_staged(const float* acc, uint8_t* stage, void* C, int64_t ldc, int row0, int m_end,
-                                                  int col0, int N, int lane, const long long* row_dst = nullptr) {
+                                                  int col0, int N, int lane) {
     using T = typename OutT<OUT>::type;
     constexpr int PER16 = 16 / (int)sizeof(T);      // elements per 16-byte slot
     constexpr int PER64 = 4 * PER16;                // elements per staged row piece
@@ -272,9 +270,14 @@ __device__ __forceinline__ void store_rows_staged(const float* acc, uint8_t* sta
             const int r = i * 8 + (lane >> 2), c = lane & 3;
             const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 64 + ((c ^ ((r >> 1) & 3)) << 4));
             const int grow = row0 + r, gcol = col0 + ps * PER64 + c * PER16;
-            if (grow < m_end && gcol < N) {
-                T* dst = row_dst ? reinterpret_cast<T*>(row_dst[grow]) : reinterpret_cast<T*>(C) + (int64_t)grow * ldc;
-                if (dst) *reinterpret_cast<uint4*>(dst + gcol) = v;
+            if constexpr (SCATTER) {
+                // C is a table of byte addresses, one per row; the rows may live in another GPU's memory
+                if (grow < m_end && gcol < N) {
+                    T* dst = reinterpret_cast<T*>(reinterpret_cast<const long long*>(C)[grow]);
+                    if (dst) *reinterpret_cast<uint4*>(dst + gcol) = v;
+                }
+            } else {
+                if (grow < m_end && gcol < N) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(C) + (int64_t)grow * ldc + gcol) = v;
             }
         }
         __syncwarp();
@@ -284,7 +287,7 @@ __device__ __forceinline__ void store_rows_staged(const float* acc, uint8_t* sta
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
-template <bool B_MN, bool GROUPED, int OUT>
+template <bool B_MN, bool GROUPED, int OUT, bool SCATTER = false>
 __global__ void __launch_bounds__(THREADS, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
@@ -527,8 +530,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 if (!alive) break;
             } else if (alive && vec_ok && !(TMA_OUT && p.tma_out)) {
                 // warp-uniform: every lane takes part in the staging even if its own row is past the end
-                if (cvalid) store_rows_staged<OUT, WCOLS>(acc, store_stage + warp * 2048, p.C, p.ldc, ti.m0 + q * 32, ti.m_end, col0, p.N, lane,
-                                                          p.row_dst);
+                if (cvalid) store_rows_staged<OUT, WCOLS, SCATTER>(acc, store_stage + warp * 2048, p.C, p.ldc, ti.m0 + q * 32, ti.m_end, col0, p.N, lane);
             } else if (alive && rvalid && cvalid) {
                 const int64_t base = (int64_t)row * p.ldc + col0;
 #pragma unroll
@@ -621,10 +623,10 @@ static int make_out_map(CUtensorMap* tc, const CUtensorMap& fallback, GemmParams
     return CINN_OK;
 }
 
-template <bool B_MN, bool GROUPED, int OUT>
+template <bool B_MN, bool GROUPED, int OUT, bool SCATTER = false>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid,
                   cudaStream_t st) {
-    auto kern = fp8_gemm_kernel<B_MN, GROUPED, OUT>;
+    auto kern = fp8_gemm_kernel<B_MN, GROUPED, OUT, SCATTER>;
     const size_t smem = smem_bytes(GROUPED ? p.E : 0);
     static thread_local size_t configured[64] = {};   // per instantiation, per thread, per device
     int dev = 0;
@@ -641,13 +643,9 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMa
 template <bool B_MN, bool GROUPED>
 static int launch_out(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, int out_dtype, int grid,
                       cudaStream_t st) {
-    CUtensorMap tc = ta;
-    if (p.row_dst != nullptr) {
-        p.tma_out = 0;                               // rows go to scattered addresses: staged 16-byte stores
-    } else {
-        int rc = make_out_map(&tc, ta, p, out_dtype, p.M);
-        if (rc) return rc;
-    }
+    CUtensorMap tc;
+    int rc = make_out_map(&tc, ta, p, out_dtype, p.M);
+    if (rc) return rc;
     switch (out_dtype) {
         case CINN_BF16: return launch<B_MN, GROUPED, CINN_BF16>(ta, tb, tc, p, grid, st);
         case CINN_F32: return launch<B_MN, GROUPED, CINN_F32>(ta, tb, tc, p, grid, st);
@@ -783,7 +781,13 @@ int fp8_grouped_gemm(const void* A, const float* sA, const void* W, const float*
     p.sB = sW; p.sb_stride_k = 1; p.sb_stride_n = nkb; p.sb_stride_e = nnb * nkb;
     p.C = C; p.ldc = d_out; p.M = (int)T; p.N = (int)d_out; p.K = (int)d_in;
     p.starts = starts; p.ends = ends; p.E = (int)E; p.b_rows_per_expert = (int)d_out;
-    p.row_dst = row_dst;
+    if (row_dst != nullptr) {
+        // scattered rows: the table travels in the C slot of the parameters, tiles leave through staged 16-byte stores
+        p.C = const_cast<long long*>(row_dst);
+        p.tma_out = 0;
+        return out_dtype == CINN_BF16 ? launch<false, true, CINN_BF16, true>(ta, tb, ta, p, gemm_sms(), st)
+                                      : launch<false, true, CINN_F16, true>(ta, tb, ta, p, gemm_sms(), st);
+    }
     return launch_out<false, true>(ta, tb, p, out_dtype, gemm_sms(), st);
 }
 
