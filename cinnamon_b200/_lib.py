@@ -28,6 +28,7 @@ SIGNATURES = {
     "cinn_requant_row_to_block": [_vp, _vp, _i64, _i64, _vp, _vp, _i32, _i32, _vp],
     "cinn_dequant": [_vp, _vp, _vp, _i32, _i64, _i64, _i32, _i32, _vp],
     "cinn_swiglu_quant_rowwise": [_vp, _i32, _i64, _i64, _vp, _vp, _i32, _vp],
+    "cinn_swiglu_quant_rowwise_n": [_vp, _i32, _i64, _i64, _vp, _vp, _vp, _i32, _vp],
     "cinn_transpose_bytes": [_vp, _i64, _vp, _i64, _i64, _vp],
     "cinn_fp8_gemm": [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _i32, _i32, _vp],
     "cinn_fp8_grouped_gemm_dgrad": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32, _vp],

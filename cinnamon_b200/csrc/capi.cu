@@ -39,14 +39,14 @@ int dequantize(const void* q, const float* scales, void* out, int out_dtype, int
                cudaStream_t st);
 int transpose_bytes(const void* in, int64_t ld_in, void* out, int64_t R, int64_t C, cudaStream_t st);
 int swiglu_quant_rowwise(const void* h12, int dtype, int64_t T_rows, int64_t I, void* q, float* scales, int div_mode,
-                         cudaStream_t st);
+                         cudaStream_t st, const int64_t* n_rows_dev);
 int fp8_gemm(const void* A, const float* sA, int64_t ld_sa, const void* B, const float* sB, int64_t sbk, int64_t sbn,
              void* C, int64_t M, int64_t N, int64_t K, int b_layout, int out_dtype, cudaStream_t st);
 int fp8_grouped_gemm(const void* A, const float* sA, const void* W, const float* sW, const int64_t* starts,
                      const int64_t* ends, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* C, int out_dtype,
                      cudaStream_t st, const long long* row_dst);
 int p2p_row_table(const int64_t* seg_start, const int64_t* home_base, const int64_t* peer_home, int64_t n_rows, int64_t row_bytes,
-                  int n_segments, int n_ranks, int64_t capacity, long long* row_dst, cudaStream_t st);
+                  int n_segments, int n_ranks, int64_t capacity, long long* row_dst, cudaStream_t st);   // rows past seg_start[n_segments] get 0
 
 int read_device_status(int* out, int reset);
 int fp8_grouped_gemm_dgrad(const void* dY, const float* sdY, const void* W, const float* sW, const int64_t* starts,
@@ -125,7 +125,12 @@ int cinn_dequant(const void* q, const float* scales, void* out, int out_dtype, i
 
 int cinn_swiglu_quant_rowwise(const void* h12, int dtype, int64_t T, int64_t I, void* q, float* scales, int div_mode,
                               void* stream) {
-    return cinn::swiglu_quant_rowwise(h12, dtype, T, I, q, scales, div_mode, (cudaStream_t)stream);
+    return cinn::swiglu_quant_rowwise(h12, dtype, T, I, q, scales, div_mode, (cudaStream_t)stream, nullptr);
+}
+
+int cinn_swiglu_quant_rowwise_n(const void* h12, int dtype, int64_t T, int64_t I, const int64_t* n_rows_dev, void* q,
+                                float* scales, int div_mode, void* stream) {
+    return cinn::swiglu_quant_rowwise(h12, dtype, T, I, q, scales, div_mode, (cudaStream_t)stream, n_rows_dev);
 }
 
 int cinn_transpose_bytes(const void* in, int64_t ld_in, void* out, int64_t R, int64_t C, void* stream) {

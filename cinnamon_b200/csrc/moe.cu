@@ -299,11 +299,13 @@ p2p_row_table_kernel(const int64_t* __restrict__ seg_start, const int64_t* __res
             if (seg_start[mid + 1] > r) hi = mid; else lo = mid + 1;
         }
         long long addr = 0;
-        if (lo < n_segments && seg_start[lo] <= r) {
-            const int64_t dst = home_base[lo] + (r - seg_start[lo]);
-            if (dst >= 0 && dst < capacity) addr = peer_home[lo % n_ranks] + dst * row_bytes;
+        if (r < seg_start[n_segments]) {                      // rows past the last segment hold no data: no destination
+            if (lo < n_segments && seg_start[lo] <= r) {
+                const int64_t dst = home_base[lo] + (r - seg_start[lo]);
+                if (dst >= 0 && dst < capacity) addr = peer_home[lo % n_ranks] + dst * row_bytes;
+            }
+            if (addr == 0) atomicCAS(&g_moe_status, 0, (5 << 8) | 4);
         }
-        if (addr == 0) atomicCAS(&g_moe_status, 0, (5 << 8) | 4);
         row_dst[r] = addr;
     }
 }

@@ -676,7 +676,10 @@ requant_row_to_block_kernel(const uint8_t* __restrict__ xq, const float* __restr
 template <typename T, int DIV>
 __global__ void __launch_bounds__(256)
 swiglu_quant_row_kernel(const T* __restrict__ h12, uint8_t* __restrict__ q, float* __restrict__ scales,
-                        int I, int nb, int64_t total_tiles, int step_rows, int step_cols) {
+                        int I, int nb, int64_t total_tiles, int step_rows, int step_cols,
+                        const int64_t* __restrict__ n_rows_dev) {
+    // optional row count that only the device knows (an expert-parallel rank's received rows): rows past it are skipped
+    if (n_rows_dev != nullptr) total_tiles = min(total_tiles, max(n_rows_dev[0], (int64_t)0) * nb);
     // the n-th tile of this half-warp is hw + n * n_hw; (step_rows, step_cols) = divmod(n_hw, nb): tile
     // coordinates advance without a division in the loop
     const int sub = threadIdx.x & 15;
@@ -1034,7 +1037,8 @@ int dequantize(const void* q, const float* scales, void* out, int out_dtype, int
 }
 
 template <typename T>
-static int launch_swiglu(const T* h12, int64_t T_rows, int64_t I, uint8_t* q, float* scales, int div_mode, cudaStream_t st) {
+static int launch_swiglu(const T* h12, int64_t T_rows, int64_t I, uint8_t* q, float* scales, int div_mode, cudaStream_t st,
+                         const int64_t* n_rows_dev) {
     const int nb = (int)((I + 127) / 128);
     const int64_t tiles = T_rows * nb;
     int64_t blocks = (tiles + 15) / 16;
@@ -1042,14 +1046,14 @@ static int launch_swiglu(const T* h12, int64_t T_rows, int64_t I, uint8_t* q, fl
     if (blocks > cap) blocks = cap;
     const int64_t n_hw = blocks * 16;
     const int sr = (int)(n_hw / nb), sc = (int)(n_hw % nb);
-    if (div_mode == CINN_DIV_FULL) swiglu_quant_row_kernel<T, CINN_DIV_FULL><<<(unsigned)blocks, 256, 0, st>>>(h12, q, scales, (int)I, nb, tiles, sr, sc);
-    else swiglu_quant_row_kernel<T, CINN_DIV_RN><<<(unsigned)blocks, 256, 0, st>>>(h12, q, scales, (int)I, nb, tiles, sr, sc);
+    if (div_mode == CINN_DIV_FULL) swiglu_quant_row_kernel<T, CINN_DIV_FULL><<<(unsigned)blocks, 256, 0, st>>>(h12, q, scales, (int)I, nb, tiles, sr, sc, n_rows_dev);
+    else swiglu_quant_row_kernel<T, CINN_DIV_RN><<<(unsigned)blocks, 256, 0, st>>>(h12, q, scales, (int)I, nb, tiles, sr, sc, n_rows_dev);
     CINN_CHECK_LAUNCH();
     return CINN_OK;
 }
 
 int swiglu_quant_rowwise(const void* h12, int dtype, int64_t T_rows, int64_t I, void* q, float* scales, int div_mode,
-                         cudaStream_t st) {
+                         cudaStream_t st, const int64_t* n_rows_dev) {
     CINN_CHECK_ARG(T_rows >= 0 && I >= 0, "swiglu_quant: negative shape");
     if (T_rows == 0 || I == 0) return CINN_OK;
     CINN_CHECK_ARG(h12 && q && scales, "swiglu_quant: null pointer");
@@ -1057,9 +1061,9 @@ int swiglu_quant_rowwise(const void* h12, int dtype, int64_t T_rows, int64_t I, 
     CINN_CHECK_ARG(aligned16(h12) && (reinterpret_cast<uintptr_t>(q) & 7) == 0, "swiglu_quant: buffers must be 16-byte aligned");
     CINN_CHECK_ARG(div_mode == CINN_DIV_FULL || div_mode == CINN_DIV_RN, "swiglu_quant: unknown div_mode %d", div_mode);
     switch (dtype) {
-        case CINN_BF16: return launch_swiglu((const __nv_bfloat16*)h12, T_rows, I, (uint8_t*)q, scales, div_mode, st);
-        case CINN_F16: return launch_swiglu((const __half*)h12, T_rows, I, (uint8_t*)q, scales, div_mode, st);
-        case CINN_F32: return launch_swiglu((const float*)h12, T_rows, I, (uint8_t*)q, scales, div_mode, st);
+        case CINN_BF16: return launch_swiglu((const __nv_bfloat16*)h12, T_rows, I, (uint8_t*)q, scales, div_mode, st, n_rows_dev);
+        case CINN_F16: return launch_swiglu((const __half*)h12, T_rows, I, (uint8_t*)q, scales, div_mode, st, n_rows_dev);
+        case CINN_F32: return launch_swiglu((const float*)h12, T_rows, I, (uint8_t*)q, scales, div_mode, st, n_rows_dev);
         default: set_error("swiglu_quant: unknown dtype tag %d", dtype); return CINN_ERR_INVALID;
     }
 }

@@ -462,10 +462,11 @@ def p2p_row_table(seg_start, home_base, peer_home, n_rows: int, row_bytes: int, 
     return table
 
 
-def swiglu_quantize_rowwise(h12: torch.Tensor):
+def swiglu_quantize_rowwise(h12: torch.Tensor, n_rows_dev: torch.Tensor = None):
     """``h = (silu(h1) * h2).to(h12.dtype)`` with ``h1, h2 = h12.float().chunk(2, -1)`` (reference
     src/layers.py:72-74), quantised row-wise in 1x128 tiles, in one pass.
-    Returns ``(h_fp8 [T, I], scales [T, ceil(I/128)])``."""
+    Returns ``(h_fp8 [T, I], scales [T, ceil(I/128)])``.  ``n_rows_dev`` (int64 device scalar, optional): only
+    that many leading rows hold data; the others are neither read nor written."""
     assert h12.is_cuda and h12.ndim == 2 and h12.shape[1] % 2 == 0
     h12 = h12.contiguous()
     T, I2 = h12.shape
@@ -473,8 +474,13 @@ def swiglu_quantize_rowwise(h12: torch.Tensor):
     with torch.cuda.device(h12.device):
         q = torch.empty((T, I), dtype=torch.float8_e4m3fn, device=h12.device)
         s = torch.empty((T, (I + 127) // 128), dtype=torch.float32, device=h12.device)
-        _lib.check(_L.cinn_swiglu_quant_rowwise(_ptr(h12), _DTYPE_TAG[h12.dtype], T, I, _ptr(q), _ptr(s), _DIV_MODE,
-                                                _stream(h12)), "cinn_swiglu_quant_rowwise")
+        if n_rows_dev is None:
+            _lib.check(_L.cinn_swiglu_quant_rowwise(_ptr(h12), _DTYPE_TAG[h12.dtype], T, I, _ptr(q), _ptr(s), _DIV_MODE,
+                                                    _stream(h12)), "cinn_swiglu_quant_rowwise")
+        else:
+            assert n_rows_dev.dtype == torch.int64 and n_rows_dev.is_cuda
+            _lib.check(_L.cinn_swiglu_quant_rowwise_n(_ptr(h12), _DTYPE_TAG[h12.dtype], T, I, _ptr(n_rows_dev), _ptr(q),
+                                                      _ptr(s), _DIV_MODE, _stream(h12)), "cinn_swiglu_quant_rowwise_n")
     _count()
     return q, s
 

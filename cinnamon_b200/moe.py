@@ -106,13 +106,15 @@ class FP8Experts:
         self.w3_q, self.w3_s = self.K.quantize_expert_weights(w3)
 
     def __call__(self, x_q: torch.Tensor, x_s: torch.Tensor, starts: torch.Tensor, ends: torch.Tensor,
-                 out_dtype=torch.bfloat16, row_dst: torch.Tensor = None) -> torch.Tensor:
+                 out_dtype=torch.bfloat16, row_dst: torch.Tensor = None, n_rows_dev: torch.Tensor = None) -> torch.Tensor:
         """x_q (R, d) e4m3 rows grouped by expert, x_s (R, d/128) -> (R, d) ``out_dtype``.
         Rows outside [starts[0], ends[-1]) are not written.  With ``row_dst`` (one byte address per row) the
-        down-projection stores every output row there instead (possibly on a peer GPU) and nothing is returned."""
+        down-projection stores every output row there instead (possibly on a peer GPU) and nothing is returned.
+        ``n_rows_dev``: device-side count of the leading rows of ``x_q`` that hold data (the rest of the buffer is
+        capacity that no expert range covers)."""
         K = self.K
         h12 = K.fp8_grouped_gemm(x_q, x_s, self.w12_q, self.w12_s, starts, ends, out_dtype=torch.bfloat16)
-        h_q, h_s = K.swiglu_quantize_rowwise(h12)
+        h_q, h_s = K.swiglu_quantize_rowwise(h12, n_rows_dev)
         if row_dst is not None:
             K.fp8_grouped_gemm_scatter(h_q, h_s, self.w3_q, self.w3_s, starts, ends, row_dst, out_dtype=out_dtype)
             return None
@@ -300,7 +302,7 @@ def moe_forward_p2p(x: torch.Tensor, routing: Routing, experts: Callable, quanti
     straight to its place in the expert-grouped buffer of the rank that owns its expert, and every expert output
     straight to its pair's place on the rank its token lives on.  No gather, regrouping or inverse permutation
     passes, no send/receive kernels; three stream-ordered barriers order the phases.  One host read-back (the
-    number of rows this rank received).  ``buffers``: a ``p2p.PeerBuffers``.  ``fused_return``: the expert
+    number of rows this rank received), none at all with ``fused_return``.  ``buffers``: a ``p2p.PeerBuffers``.  ``fused_return``: the expert
     down-projection stores its output rows straight to their home ranks from its epilogue (``experts`` must accept
     ``row_dst``), instead of a separate pass after the GEMM.  Same arithmetic per row as ``moe_forward``; returns
     fp32 (T, d)."""
@@ -318,15 +320,21 @@ def moe_forward_p2p(x: torch.Tensor, routing: Routing, experts: Callable, quanti
     K.p2p_dispatch(x_q, x_s, routing.token_indices, routing.sorted_experts, t.base_send, t.my_start, buffers.peer_q,
                    buffers.peer_s, e_local, world, buffers.capacity_rows)
     buffers.barrier()                                   # every row has landed
-    rows = int(t.total_rows)                            # the one host read-back: sizes the expert GEMMs' outputs
-    assert rows <= buffers.capacity_rows and n_pairs <= buffers.home_rows, "peer buffers too small"
-    recv_q = buffers.q.view(buffers.capacity_rows, buffers.d)[:rows].view(x_q.dtype)
-    recv_s = buffers.s.view(buffers.capacity_rows, buffers.n_scales)[:rows]
+    assert n_pairs <= buffers.home_rows, "peer buffers too small"
     if fused_return:
-        # the down-projection's epilogue stores every finished row straight to its home: the way home runs under the GEMM
-        table = K.p2p_row_table(t.seg_start, t.home_base, buffers.peer_home, rows, buffers.d * 2, world, buffers.home_rows)
-        experts(recv_q, recv_s, t.starts, t.ends, row_dst=table)
+        # The down-projection's epilogue stores every finished row straight to its home: the way home runs under
+        # the GEMM.  Nothing here needs the number of received rows on the host: the GEMMs walk the device-side
+        # expert ranges over the whole buffer, the SwiGLU pass and the address table take the count from the device.
+        cap = buffers.capacity_rows
+        recv_q = buffers.q.view(cap, buffers.d).view(x_q.dtype)
+        recv_s = buffers.s.view(cap, buffers.n_scales)
+        table = K.p2p_row_table(t.seg_start, t.home_base, buffers.peer_home, cap, buffers.d * 2, world, buffers.home_rows)
+        experts(recv_q, recv_s, t.starts, t.ends, row_dst=table, n_rows_dev=t.total_rows.reshape(1))
     else:
+        rows = int(t.total_rows)                        # host read-back: sizes the expert GEMMs' outputs
+        assert rows <= buffers.capacity_rows, "peer buffers too small"
+        recv_q = buffers.q.view(buffers.capacity_rows, buffers.d)[:rows].view(x_q.dtype)
+        recv_s = buffers.s.view(buffers.capacity_rows, buffers.n_scales)[:rows]
         out_rows = experts(recv_q, recv_s, t.starts, t.ends)
         K.p2p_return(out_rows, t.seg_start, t.home_base, buffers.peer_home, world, buffers.home_rows)
     buffers.barrier()                                   # every expert output is home

@@ -95,6 +95,12 @@ int cinn_dequant(const void* q, const float* scales, void* out, int out_dtype, i
 int cinn_swiglu_quant_rowwise(const void* h12, int dtype, int64_t T, int64_t I, void* q, float* scales, int div_mode,
                               void* stream);
 
+/* The same for a buffer of which only the first n_rows_dev[0] rows (a count in DEVICE memory, at most T) hold data:
+ * the rows an expert-parallel rank received in this step, known on the device only.  Rows past the count are
+ * neither read nor written. */
+int cinn_swiglu_quant_rowwise_n(const void* h12, int dtype, int64_t T, int64_t I, const int64_t* n_rows_dev, void* q,
+                                float* scales, int div_mode, void* stream);
+
 /* out (C, R) = in (R, C; row pitch ld_in) transposed, bytes.  Replaces the `.t().contiguous()` copies of
  * e4m3 operands (src/kernels.py:748). */
 int cinn_transpose_bytes(const void* in, int64_t ld_in, void* out, int64_t R, int64_t C, void* stream);
@@ -218,8 +224,9 @@ int cinn_fp8_grouped_gemm_scatter(const void* A, const float* sA, const void* W,
                                   const int64_t* ends, int64_t E, int64_t T, int64_t d_in, int64_t d_out,
                                   const int64_t* row_dst, int out_dtype, void* stream);
 
-/* The destinations of cinn_p2p_return as a table: row_dst[r] = peer_home[rank] + row * row_bytes for r < n_rows
- * (0 and a status code where the tables point outside the buffers). */
+/* The destinations of cinn_p2p_return as a table: row_dst[r] = peer_home[rank] + row * row_bytes for r < n_rows;
+ * 0 for rows at or past seg_start[n_segments] (n_rows may be the buffer's capacity when the true row count is
+ * known on the device only), 0 and a status code where the tables point outside the buffers. */
 int cinn_p2p_row_table(const int64_t* seg_start, const int64_t* home_base, const int64_t* peer_home, int64_t n_rows,
                        int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity_rows, int64_t* row_dst, void* stream);
 

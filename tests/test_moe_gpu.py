@@ -50,6 +50,26 @@ def test_swiglu_quantiser(K, dtype, T, I):
     assert torch.all((deq - h_cpu.float()).abs() <= tol)
 
 
+def test_swiglu_quantiser_device_row_count(K):
+    """Only the first n rows (a count that lives on the device) are converted; the rest of the buffer is left alone."""
+    g = torch.Generator().manual_seed(19)
+    h12 = (torch.randn(200, 512, generator=g) * 2).bfloat16().cuda()
+    n = torch.tensor([77], dtype=torch.int64, device="cuda")
+    q_all, s_all = K.swiglu_quantize_rowwise(h12)
+    from cinnamon_b200 import _lib
+    import ctypes
+    q = torch.full((200, 256), 0x55, dtype=torch.uint8, device="cuda")
+    s = torch.full((200, 2), -1.0, device="cuda")
+    tag = {torch.bfloat16: _lib.BF16}[h12.dtype]
+    mode = _lib.DIV_RN if K.get_div_mode() == "rn" else _lib.DIV_FULL
+    rc = _lib.lib.cinn_swiglu_quant_rowwise_n(ctypes.c_void_p(h12.data_ptr()), tag, 200, 256, ctypes.c_void_p(n.data_ptr()),
+                                              ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(s.data_ptr()), mode,
+                                              ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0, _lib.last_error()
+    assert torch.equal(q[:77], q_all.view(torch.uint8)[:77]) and torch.equal(s[:77], s_all[:77])
+    assert torch.all(q[77:] == 0x55) and torch.all(s[77:] == -1.0)
+
+
 def test_combine_kernel_matches_scatter_add(K):
     g = torch.Generator().manual_seed(8)
     T, k, d = 77, 4, 264
