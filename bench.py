@@ -200,11 +200,17 @@ def bench_kernels(Kmod, dev, x, w, dy, peaks):
         gbs = nbytes / (ms * 1e-3) / 1e9
         out.append({"kernel": name, "ms": ms, "bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm})
 
-    def gemm_line(name, fn, flop):
+    def gemm_line(name, fn, flop, nbytes=None):
+        """``nbytes``: algorithmic HBM bytes (e4m3 operands + scales + output), so that shapes near the ridge show
+        both bounds."""
         ms = _time_kernel(fn)
         tf = flop / (ms * 1e-3) / 1e12
-        out.append({"kernel": name, "ms": ms, "bound": "tensor", "achieved": tf, "peak": fp8_peak, "unit": "TFLOP/s",
-                    "frac": tf / fp8_peak})
+        line = {"kernel": name, "ms": ms, "bound": "tensor", "achieved": tf, "peak": fp8_peak, "unit": "TFLOP/s",
+                "frac": tf / fp8_peak}
+        if nbytes is not None:
+            gbs = nbytes / (ms * 1e-3) / 1e9
+            line.update({"hbm_achieved_gbs": gbs, "hbm_frac": gbs / hbm, "flop_per_byte": flop / nbytes})
+        out.append(line)
 
     xd, wd = x.detach(), w.detach()
     nkb, nnb = (K + 127) // 128, (N + 127) // 128
@@ -223,7 +229,8 @@ def bench_kernels(Kmod, dev, x, w, dy, peaks):
     dtq, dts = Kmod.quantize_fp8_rowwise(dy.t())
     xbq, xbs = Kmod.requantize_rowwise_to_blockwise(xq, xs)
     flop = 2.0 * M * N * K
-    gemm_line("gemm forward  16384x18432x7168 (B K-major, two-SM)", lambda: Kmod.fp8_matmul_dsv3(xq, wq.t(), xs, ws.t()), flop)
+    gemm_line("gemm forward  16384x18432x7168 (B K-major, two-SM)", lambda: Kmod.fp8_matmul_dsv3(xq, wq.t(), xs, ws.t()), flop,
+              M * K + N * K + 4 * (M * nkb + nnb * nkb) + 2 * M * N)
     gemm_line("gemm dgrad    16384x7168x18432 (B MN-major)", lambda: Kmod.fp8_matmul_dsv3(dq, wq, ds, ws), flop)
     gemm_line("gemm wgrad    18432x7168x16384 (B MN-major)", lambda: Kmod.fp8_matmul_dsv3(dtq, xbq, dts, xbs), flop)
     del dq, ds, dtq, dts, xbq, xbs, wq, ws
@@ -236,7 +243,8 @@ def bench_kernels(Kmod, dev, x, w, dy, peaks):
         b = (torch.randn(n, k, generator=g, device=dev) * 0.02).to(torch.bfloat16)
         aq, as_ = Kmod.quantize_fp8_rowwise(a)
         bq, bs = Kmod.quantize_fp8_blockwise(b)
-        gemm_line(f"gemm {name} ({m} tokens)", lambda: Kmod.fp8_matmul_dsv3(aq, bq.t(), as_, bs.t()), 2.0 * m * n * k)
+        gemm_line(f"gemm {name} ({m} tokens)", lambda: Kmod.fp8_matmul_dsv3(aq, bq.t(), as_, bs.t()), 2.0 * m * n * k,
+                  m * k + n * k + 4 * (m * ((k + 127) // 128) + ((n + 127) // 128) * ((k + 127) // 128)) + 2 * m * n)
     del a, b, aq, as_, bq, bs
     # MoE plumbing at the C4 sizes (32768 tokens, top-8, d = 7168, I = 2048): HBM-bound passes
     T, E, k8, d, I = MOE["tokens"], MOE["E"], MOE["top_k"], MOE["d"], MOE["I"]
