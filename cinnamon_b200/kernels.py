@@ -206,11 +206,14 @@ def requantize_rowwise_to_blockwise(x_fp8: torch.Tensor, x_scale: torch.Tensor, 
 # -----------------------------------------------------------------------------
 # GEMM (reference: src/kernels.py:667-702)
 # -----------------------------------------------------------------------------
-def _gemm(a, a_scales, b, b_layout, sb, sb_stride_k, sb_stride_n, M, N, K, out_dtype, bf16_rounded=False):
+def _gemm(a, a_scales, b, b_layout, sb, sb_stride_k, sb_stride_n, M, N, K, out_dtype, bf16_rounded=False, out=None):
     """``bf16_rounded`` (fp32 output only): store the result rounded to bf16, i.e. exactly what a
-    bf16 result cast to fp32 would hold."""
+    bf16 result cast to fp32 would hold.  ``out``: a contiguous (M, N) tensor of ``out_dtype`` to write into."""
     with torch.cuda.device(a.device):
-        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        if out is None:
+            out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        else:
+            assert out.shape == (M, N) and out.dtype == out_dtype and out.is_contiguous()
         tag = _lib.F32_BF16 if (bf16_rounded and out_dtype == torch.float32) else _DTYPE_TAG[out_dtype]
         ev = None
         if gemm_events is not None:
@@ -680,11 +683,12 @@ class MoEGroupedGemmFunction(torch.autograd.Function):
         dx_dtype = ctx.x_dtype if ctx.x_dtype in _DTYPE_TAG else torch.float32
         grad_x = fp8_grouped_gemm_dgrad(g_fp8, g_scale, w_fp8, w_scale, starts, ends, out_dtype=dx_dtype)
         w_dtype = ctx.w_dtype if ctx.w_dtype in (torch.float32, torch.bfloat16) else torch.float32
-        grad_w = torch.zeros((E, d_out, d_in), dtype=w_dtype, device=g.device)
+        grad_w = torch.empty((E, d_out, d_in), dtype=w_dtype, device=g.device)
         bounds = torch.stack([starts, ends]).tolist()              # one host read-back per backward
         for e, (s, t) in enumerate(zip(*bounds)):
             n = t - s
             if n <= 0:
+                grad_w[e].zero_()                                  # an expert without tokens gets no gradient
                 continue
             ge, xq, xs = g[s:t], x_fp8[s:t], x_scale[s:t]
             npad = (n + 15) // 16 * 16                             # the reduction axis in multiples of 16 (zero rows)
@@ -694,9 +698,9 @@ class MoEGroupedGemmFunction(torch.autograd.Function):
                 xs = torch.nn.functional.pad(xs, (0, 0, 0, npad - n), value=1.0)
             gt_fp8, gt_scale = quantize_fp8_rowwise(ge.t(), block_size=128)
             xb_fp8, xb_scale = requantize_rowwise_to_blockwise(xq.contiguous(), xs.contiguous())
-            grad_w[e] = _gemm(gt_fp8, gt_scale, xb_fp8, _lib.B_KN, xb_scale, xb_scale.stride(0), xb_scale.stride(1),
-                              d_out, d_in, npad, torch.float32 if w_dtype == torch.float32 else torch.bfloat16,
-                              bf16_rounded=True)
+            _gemm(gt_fp8, gt_scale, xb_fp8, _lib.B_KN, xb_scale, xb_scale.stride(0), xb_scale.stride(1),
+                  d_out, d_in, npad, torch.float32 if w_dtype == torch.float32 else torch.bfloat16,
+                  bf16_rounded=True, out=grad_w[e])              # straight into this expert's slice, no copy
         return grad_x.to(ctx.x_dtype), grad_w.to(ctx.w_dtype), None, None, None
 
 
