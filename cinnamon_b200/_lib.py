@@ -49,6 +49,8 @@ SIGNATURES = {
     "cinn_p2p_barrier": [_vp, _i32, _i32, ctypes.c_uint, _vp],
     "cinn_fp8_grouped_gemm_scatter": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32, _vp],
     "cinn_p2p_row_table": [_vp, _vp, _vp, _i64, _i64, _i32, _i32, _i64, _vp, _vp],
+    "cinn_fp8_grouped_wgrad_scratch_bytes": [_i64, _i64, _i64],
+    "cinn_fp8_grouped_wgrad": [_vp, _i32, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _i32, _i32, _vp],
     "cinn_moe_combine_add": [_vp, _i32, _vp, _vp, _vp, _i32, _vp, _i64, _i64, _i32, _i64, _vp],
     "cinn_device_status": [ctypes.POINTER(ctypes.c_int), _i32],
     "cinn_fp8_grouped_gemm": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32, _vp],
@@ -70,7 +72,8 @@ def _load() -> ctypes.CDLL:
         fn = getattr(lib, name)            # AttributeError if the symbol is not exported
         fn.argtypes = argtypes
         fn.restype = (ctypes.c_char_p if name == "cinn_last_error"
-                      else ctypes.c_int64 if name in ("cinn_moe_route_workspace_ints", "cinn_moe_route_static_max_ints")
+                      else ctypes.c_int64 if name in ("cinn_moe_route_workspace_ints", "cinn_moe_route_static_max_ints",
+                                                 "cinn_fp8_grouped_wgrad_scratch_bytes")
                       else ctypes.c_int)
     return lib
 

@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libcinnamon_b200.so")
-SOURCES = ["quant.cu", "gemm.cu", "moe.cu", "route.cu", "sparse_attn.cu", "indexer.cu", "capi.cu"]
+SOURCES = ["quant.cu", "gemm.cu", "moe.cu", "route.cu", "sparse_attn.cu", "indexer.cu", "wgrad.cu", "capi.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

@@ -73,6 +73,10 @@ int p2p_dispatch(const void* q, const float* s, const int64_t* token_indices, co
 int p2p_return(const void* rows, const int64_t* seg_start, const int64_t* home_base, const int64_t* peer_home, int64_t n_rows,
                int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity, cudaStream_t st);
 int p2p_barrier(const int64_t* peer_flags, int me, int n_ranks, unsigned epoch, cudaStream_t st);
+int64_t grouped_wgrad_scratch_bytes(int64_t max_rows, int64_t d_in, int64_t d_out);
+int fp8_grouped_wgrad(const void* dY, int dy_dtype, const void* x_q, const float* x_s, const int64_t* starts_host,
+                      const int64_t* ends_host, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* scratch,
+                      int64_t scratch_bytes, void* dW, int out_dtype, int div_mode, cudaStream_t st);
 int64_t moe_route_workspace_ints(int64_t T, int E);
 int moe_route(const float* logits, const float* bias, int64_t T, int E, int top_k, int* workspace, int* top_experts,
               float* top_gates, int64_t* token_indices, float* sorted_scores, int64_t* sorted_experts, int64_t* counts,
@@ -224,6 +228,17 @@ int cinn_p2p_row_table(const int64_t* seg_start, const int64_t* home_base, const
                        int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity_rows, int64_t* row_dst, void* stream) {
     return cinn::p2p_row_table(seg_start, home_base, peer_home, n_rows, row_bytes, n_segments, n_ranks, capacity_rows,
                                reinterpret_cast<long long*>(row_dst), (cudaStream_t)stream);
+}
+
+int64_t cinn_fp8_grouped_wgrad_scratch_bytes(int64_t max_rows, int64_t d_in, int64_t d_out) {
+    return cinn::grouped_wgrad_scratch_bytes(max_rows, d_in, d_out);
+}
+
+int cinn_fp8_grouped_wgrad(const void* dY, int dy_dtype, const void* x_q, const float* x_scales, const int64_t* starts_host,
+                           const int64_t* ends_host, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* scratch,
+                           int64_t scratch_bytes, void* dW, int out_dtype, int div_mode, void* stream) {
+    return cinn::fp8_grouped_wgrad(dY, dy_dtype, x_q, x_scales, starts_host, ends_host, E, T, d_in, d_out, scratch,
+                                   scratch_bytes, dW, out_dtype, div_mode, (cudaStream_t)stream);
 }
 
 int cinn_p2p_barrier(const int64_t* peer_flags, int rank, int n_ranks, unsigned epoch, void* stream) {

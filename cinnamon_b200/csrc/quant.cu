@@ -208,7 +208,9 @@ quant_row_generic_kernel(const T* __restrict__ x, int64_t ld_m, int64_t ld_n, ui
 template <typename T, int DIV, bool ROUND>
 __global__ void __launch_bounds__(256)
 quant_row_transposed_kernel(const T* __restrict__ x, int64_t L, uint8_t* __restrict__ q,
-                            float* __restrict__ scales, int M, int N, int nb, int tiles_per_cta) {
+                            float* __restrict__ scales, int M, int N, int nb, int tiles_per_cta, int N_in) {
+    // N_in <= N: only the first N_in positions along the tile axis are read, the rest count as zeros (a ragged
+    // expert range padded to a multiple of 16 without a padded copy of the input)
     constexpr int TM = 64;            // logical rows per CTA
     __shared__ float s_amax[2][8][TM];
     // staged output: 64 logical rows x 128 bytes; the 16-byte chunk index of a row is XOR-ed
@@ -231,7 +233,7 @@ quant_row_transposed_kernel(const T* __restrict__ x, int64_t L, uint8_t* __restr
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
             const int n = cb * 128 + nr * 4 + p;
-            nxt[p] = (cb < cb_last && n < N && m < M) ? load_raw8<T>(x + (int64_t)n * L + m) : zero_raw8<T>();
+            nxt[p] = (cb < cb_last && n < N_in && m < M) ? load_raw8<T>(x + (int64_t)n * L + m) : zero_raw8<T>();
         }
     };
     fetch(cb_first);
@@ -594,7 +596,8 @@ quant_block_generic_kernel(const T* __restrict__ x, int64_t ld_m, int64_t ld_n, 
 template <int DIV, bool TRANSPOSE_OUT>
 __global__ void __launch_bounds__(256)
 requant_row_to_block_kernel(const uint8_t* __restrict__ xq, const float* __restrict__ xs, int nkb_in,
-                            uint8_t* __restrict__ out, float* __restrict__ scales, int M, int K, int nb) {
+                            uint8_t* __restrict__ out, float* __restrict__ scales, int M, int K, int nb, int M_in) {
+    // M_in <= M: rows at or past M_in are not read and count as zeros (and are written as zeros)
     __shared__ float s_red[8];
     __shared__ __align__(16) uint8_t s_t[TRANSPOSE_OUT ? 128 * (128 + 16) : 16];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -604,7 +607,7 @@ requant_row_to_block_kernel(const uint8_t* __restrict__ xq, const float* __restr
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
         const int r = r0 + p * 32 + warp * 4 + (lane >> 3);
-        if (r < M && c < K) {
+        if (r < M_in && c < K) {
             const uint4 raw = *reinterpret_cast<const uint4*>(xq + (int64_t)r * K + c);
             const float rs = xs[(int64_t)r * nkb_in + blockIdx.x];
             const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -821,7 +824,7 @@ static int launch_rowwise(const T* x, int64_t M, int64_t N, int64_t ld_m, int64_
         while (per > 1 && slabs * ((nb + per - 1) / per) < (int64_t)sms * 8) per >>= 1;
         CINN_CHECK_ARG((nb + per - 1) / per <= 65535, "row-wise quantiser: too many tiles along the strided axis");
         dim3 grid((unsigned)slabs, (unsigned)((nb + per - 1) / per));
-        quant_row_transposed_kernel<T, DIV, ROUND><<<grid, 256, 0, st>>>(x, ld_n, q, scales, (int)M, (int)N, nb, per);
+        quant_row_transposed_kernel<T, DIV, ROUND><<<grid, 256, 0, st>>>(x, ld_n, q, scales, (int)M, (int)N, nb, per, (int)N);
     } else {
         int64_t blocks = (tiles + 7) / 8;
         const int64_t cap = (int64_t)sms * 16;
@@ -965,6 +968,62 @@ int selfcheck_division(unsigned long long* mismatches, cudaStream_t st) {
     return CINN_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Padded variants for ragged expert ranges (per-expert weight gradient): the logical tile axis has N_in (resp.
+// M_in) real positions and is padded with zeros to N (resp. M), a multiple of 16, without a padded copy of the input.
+// ---------------------------------------------------------------------------
+template <typename T>
+static int transposed_padded_typed(const T* x, int64_t M, int64_t N_in, int64_t N, int64_t L, uint8_t* q, float* scales,
+                                   int div_mode, cudaStream_t st) {
+    const int nb = (int)((N + 127) / 128);
+    const int64_t slabs = (M + 63) / 64;
+    int per = 4;
+    while (per > 1 && slabs * ((nb + per - 1) / per) < (int64_t)sm_count() * 8) per >>= 1;
+    CINN_CHECK_ARG((nb + per - 1) / per <= 65535, "transposed quantiser: too many tiles along the strided axis");
+    dim3 grid((unsigned)slabs, (unsigned)((nb + per - 1) / per));
+    if (div_mode == CINN_DIV_FULL)
+        quant_row_transposed_kernel<T, CINN_DIV_FULL, false><<<grid, 256, 0, st>>>(x, L, q, scales, (int)M, (int)N, nb, per, (int)N_in);
+    else
+        quant_row_transposed_kernel<T, CINN_DIV_RN, false><<<grid, 256, 0, st>>>(x, L, q, scales, (int)M, (int)N, nb, per, (int)N_in);
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+// x: element (m, n) at x[m + n * L] for m < M, n < N_in; q: (M, N) e4m3, scales (M, ceil(N / 128)); 1 x 128 tiles along n
+int quantize_transposed_padded(const void* x, int dtype, int64_t M, int64_t N_in, int64_t N, int64_t L, void* q,
+                               float* scales, int div_mode, cudaStream_t st) {
+    CINN_CHECK_ARG(M > 1 && N_in >= 0 && N >= N_in && N % 16 == 0 && M % 8 == 0 && L % 8 == 0 && L >= M,
+                   "padded transposed quantiser: needs M %% 8 == 0, a pitch that is a multiple of 8 and N %% 16 == 0");
+    if (N == 0) return CINN_OK;
+    CINN_CHECK_ARG(x && q && scales && aligned16(x) && aligned16(q), "padded transposed quantiser: null or unaligned pointer");
+    CINN_CHECK_ARG(M < (1LL << 31) && N < (1LL << 31), "padded transposed quantiser: dimension too large");
+    switch (dtype) {
+        case CINN_BF16: return transposed_padded_typed((const __nv_bfloat16*)x, M, N_in, N, L, (uint8_t*)q, scales, div_mode, st);
+        case CINN_F16: return transposed_padded_typed((const __half*)x, M, N_in, N, L, (uint8_t*)q, scales, div_mode, st);
+        case CINN_F32: return transposed_padded_typed((const float*)x, M, N_in, N, L, (uint8_t*)q, scales, div_mode, st);
+        default: set_error("padded transposed quantiser: unknown dtype tag %d", dtype); return CINN_ERR_INVALID;
+    }
+}
+
+// xq (M_in, K) e4m3 with row scales xs (M_in, ceil(K / 128)) -> out (M, K) block-scaled, scales (ceil(M/128), ceil(K/128))
+int requant_row_to_block_padded(const void* xq, const float* xs, int64_t M_in, int64_t M, int64_t K, void* out, float* scales,
+                                int div_mode, cudaStream_t st) {
+    CINN_CHECK_ARG(M_in >= 0 && M >= M_in && K >= 0, "padded requant: bad shape");
+    if (M == 0 || K == 0) return CINN_OK;
+    CINN_CHECK_ARG(xq && xs && out && scales, "padded requant: null pointer");
+    CINN_CHECK_ARG(K % 16 == 0 && aligned16(xq) && aligned16(out), "padded requant: K must be a multiple of 16 and buffers 16-byte aligned");
+    CINN_CHECK_ARG(M < (1LL << 31) && K < (1LL << 31), "padded requant: dimension too large");
+    const int nb = (int)((K + 127) / 128), mb = (int)((M + 127) / 128);
+    CINN_CHECK_ARG(mb <= 65535, "padded requant: too many row blocks");
+    dim3 grid((unsigned)nb, (unsigned)mb);
+    if (div_mode == CINN_DIV_FULL)
+        requant_row_to_block_kernel<CINN_DIV_FULL, false><<<grid, 256, 0, st>>>((const uint8_t*)xq, xs, nb, (uint8_t*)out, scales, (int)M, (int)K, nb, (int)M_in);
+    else
+        requant_row_to_block_kernel<CINN_DIV_RN, false><<<grid, 256, 0, st>>>((const uint8_t*)xq, xs, nb, (uint8_t*)out, scales, (int)M, (int)K, nb, (int)M_in);
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
 int read_quant_status(int* out, int reset) {
     int v = 0;
     CINN_CHECK_CUDA(cudaMemcpyFromSymbol(&v, g_quant_status, sizeof(int)));
@@ -1006,11 +1065,11 @@ int requant_row_to_block(const void* xq, const float* xs, int64_t M, int64_t K, 
     const uint8_t* in = (const uint8_t*)xq;
     uint8_t* o = (uint8_t*)out;
     if (div_mode == CINN_DIV_FULL) {
-        if (transpose_out) requant_row_to_block_kernel<CINN_DIV_FULL, true><<<grid, 256, 0, st>>>(in, xs, nb, o, scales, (int)M, (int)K, nb);
-        else requant_row_to_block_kernel<CINN_DIV_FULL, false><<<grid, 256, 0, st>>>(in, xs, nb, o, scales, (int)M, (int)K, nb);
+        if (transpose_out) requant_row_to_block_kernel<CINN_DIV_FULL, true><<<grid, 256, 0, st>>>(in, xs, nb, o, scales, (int)M, (int)K, nb, (int)M);
+        else requant_row_to_block_kernel<CINN_DIV_FULL, false><<<grid, 256, 0, st>>>(in, xs, nb, o, scales, (int)M, (int)K, nb, (int)M);
     } else {
-        if (transpose_out) requant_row_to_block_kernel<CINN_DIV_RN, true><<<grid, 256, 0, st>>>(in, xs, nb, o, scales, (int)M, (int)K, nb);
-        else requant_row_to_block_kernel<CINN_DIV_RN, false><<<grid, 256, 0, st>>>(in, xs, nb, o, scales, (int)M, (int)K, nb);
+        if (transpose_out) requant_row_to_block_kernel<CINN_DIV_RN, true><<<grid, 256, 0, st>>>(in, xs, nb, o, scales, (int)M, (int)K, nb, (int)M);
+        else requant_row_to_block_kernel<CINN_DIV_RN, false><<<grid, 256, 0, st>>>(in, xs, nb, o, scales, (int)M, (int)K, nb, (int)M);
     }
     CINN_CHECK_LAUNCH();
     return CINN_OK;

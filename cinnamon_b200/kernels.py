@@ -654,6 +654,34 @@ def fp8_grouped_gemm_dgrad(dy_fp8, dy_scale, w_fp8, w_scale, expert_starts, expe
     return dx
 
 
+def fp8_grouped_wgrad(grad_out: torch.Tensor, x_fp8: torch.Tensor, x_scale: torch.Tensor, expert_starts, expert_ends,
+                      n_experts: int, d_in: int, d_out: int, w_dtype=torch.float32) -> torch.Tensor:
+    """``dW[e] = rowwise(dY[e rows]^T) @ blockwise(dequant_rowwise(x_q[e rows]))`` for every expert: the weight
+    gradient of ``FP8MatmulFunction.backward`` (reference src/kernels.py:780-788) expert by expert.  The row
+    ranges are read back once; the per-expert launches (transposing quantiser, re-quantiser, GEMM straight into
+    ``dW[e]``) are enqueued by one library call.  Returns (E, d_out, d_in) of ``w_dtype`` (fp32 holds bf16-rounded
+    values, as a bf16 result cast to the master weight's type would)."""
+    g = grad_out if grad_out.is_contiguous() else grad_out.contiguous()
+    if g.dtype not in _DTYPE_TAG:
+        g = g.float()
+    x_fp8, x_scale = x_fp8.contiguous(), x_scale.float().contiguous()
+    T = g.shape[0]
+    bounds = torch.stack([expert_starts.to(torch.int64), expert_ends.to(torch.int64)]).cpu()     # one host read-back
+    starts_h, ends_h = bounds[0].contiguous(), bounds[1].contiguous()
+    max_rows = int((ends_h.clamp(max=T) - starts_h.clamp(min=0)).clamp(min=0).max()) if n_experts > 0 else 0
+    need = int(_L.cinn_fp8_grouped_wgrad_scratch_bytes(max_rows, d_in, d_out))
+    out_tag = _lib.F32_BF16 if w_dtype == torch.float32 else _lib.BF16
+    with torch.cuda.device(g.device):
+        scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=g.device)
+        grad_w = torch.empty((n_experts, d_out, d_in), dtype=w_dtype, device=g.device)
+        _lib.check(_L.cinn_fp8_grouped_wgrad(_ptr(g), _DTYPE_TAG[g.dtype], _ptr(x_fp8), _ptr(x_scale),
+                                             ctypes.c_void_p(starts_h.data_ptr()), ctypes.c_void_p(ends_h.data_ptr()), n_experts,
+                                             T, d_in, d_out, _ptr(scratch), scratch.numel(), _ptr(grad_w), out_tag, _DIV_MODE,
+                                             _stream(g)), "cinn_fp8_grouped_wgrad")
+    _count(3 * n_experts)
+    return grad_w
+
+
 class MoEGroupedGemmFunction(torch.autograd.Function):
     """Differentiable grouped GEMM.  The reference's ``moe_grouped_gemm`` is a plain function (src/kernels.py:526-581),
     so on CUDA no gradient reaches the routed experts there; this function gives the grouped GEMM the backward of
@@ -683,24 +711,7 @@ class MoEGroupedGemmFunction(torch.autograd.Function):
         dx_dtype = ctx.x_dtype if ctx.x_dtype in _DTYPE_TAG else torch.float32
         grad_x = fp8_grouped_gemm_dgrad(g_fp8, g_scale, w_fp8, w_scale, starts, ends, out_dtype=dx_dtype)
         w_dtype = ctx.w_dtype if ctx.w_dtype in (torch.float32, torch.bfloat16) else torch.float32
-        grad_w = torch.empty((E, d_out, d_in), dtype=w_dtype, device=g.device)
-        bounds = torch.stack([starts, ends]).tolist()              # one host read-back per backward
-        for e, (s, t) in enumerate(zip(*bounds)):
-            n = t - s
-            if n <= 0:
-                grad_w[e].zero_()                                  # an expert without tokens gets no gradient
-                continue
-            ge, xq, xs = g[s:t], x_fp8[s:t], x_scale[s:t]
-            npad = (n + 15) // 16 * 16                             # the reduction axis in multiples of 16 (zero rows)
-            if npad != n:
-                ge = torch.nn.functional.pad(ge, (0, 0, 0, npad - n))
-                xq = torch.nn.functional.pad(xq.view(torch.uint8), (0, 0, 0, npad - n)).view(torch.float8_e4m3fn)
-                xs = torch.nn.functional.pad(xs, (0, 0, 0, npad - n), value=1.0)
-            gt_fp8, gt_scale = quantize_fp8_rowwise(ge.t(), block_size=128)
-            xb_fp8, xb_scale = requantize_rowwise_to_blockwise(xq.contiguous(), xs.contiguous())
-            _gemm(gt_fp8, gt_scale, xb_fp8, _lib.B_KN, xb_scale, xb_scale.stride(0), xb_scale.stride(1),
-                  d_out, d_in, npad, torch.float32 if w_dtype == torch.float32 else torch.bfloat16,
-                  bf16_rounded=True, out=grad_w[e])              # straight into this expert's slice, no copy
+        grad_w = fp8_grouped_wgrad(g, x_fp8, x_scale, starts, ends, E, d_in, d_out, w_dtype)
         return grad_x.to(ctx.x_dtype), grad_w.to(ctx.w_dtype), None, None, None
 
 

@@ -135,6 +135,22 @@ int cinn_fp8_grouped_gemm_dgrad(const void* dY, const float* sdY, const void* W,
                                 const int64_t* ends, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* dX,
                                 int out_dtype, void* stream);
 
+/* Weight gradient of the grouped GEMM: dW[e] = dY[starts[e]:ends[e]]^T @ X[starts[e]:ends[e]] for every expert,
+ * with the operands quantised expert by expert as FP8MatmulFunction.backward does for one Linear
+ * (src/kernels.py:780-788: dY^T in 1 x 128 tiles along the tokens, the saved row-quantised x re-quantised in
+ * 128 x 128 blocks; token counts padded with zero rows to a multiple of 16).  The reference's grouped GEMM has no
+ * backward (src/kernels.py:526-581).
+ * dY: (T, d_out) of dy_dtype; x_q (T, d_in) e4m3 with x_scales (T, ceil(d_in/128)) as the forward saved them;
+ * starts_host / ends_host: the E row ranges in HOST memory (the caller has read them back; every expert is a
+ * GEMM problem of its own); dW: (E, d_out, d_in) of out_dtype (CINN_F32, CINN_F32_BF16 or CINN_BF16), experts
+ * without rows are zeroed; scratch: device memory of at least
+ * cinn_fp8_grouped_wgrad_scratch_bytes(largest expert's rows, d_in, d_out) bytes, reused expert after expert.
+ * d_in and d_out multiples of 16. */
+int64_t cinn_fp8_grouped_wgrad_scratch_bytes(int64_t max_rows, int64_t d_in, int64_t d_out);
+int cinn_fp8_grouped_wgrad(const void* dY, int dy_dtype, const void* x_q, const float* x_scales, const int64_t* starts_host,
+                           const int64_t* ends_host, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* scratch,
+                           int64_t scratch_bytes, void* dW, int out_dtype, int div_mode, void* stream);
+
 /* y[t, :] = sum_j gates[t, j] * rows[pos[t, j], :]  for t < n_tokens, j < top_k; fp32 result, no atomics.
  * Replaces the gate multiply, torch.zeros and scatter_add_ at the end of MoE.forward (src/layers.py:157-160).
  * rows: (n_rows, d) bf16 / fp16 / fp32.  pos: (n_tokens, top_k) int64 row indices (negative = skip), ascending per
