@@ -294,6 +294,44 @@ def bench_kernels(Kmod, dev, x, w, dy, peaks):
     return out
 
 
+def extras_small(Kmod, dev):
+    """The MoE plumbing passes and sparse attention on a reduced case (8192 tokens, top-8, d = 7168; attention
+    B 8 x H 8 x L 1024 x K 128): inputs larger than L2 but well under a GB each, for profiler captures.
+    Runs every kernel three times and prints one line of CUDA-event timings; not a headline number."""
+    g = torch.Generator(device=dev).manual_seed(77)
+    T, E, k8, d, I = 8192, 256, 8, 7168, 2048
+    logits = torch.randn(T, E, generator=g, device=dev)
+    bias = torch.randn(E, generator=g, device=dev)
+    tok = torch.randn(T, d, generator=g, device=dev).to(torch.bfloat16)
+    h12 = torch.randn(T * k8 // 2, 2 * I, generator=g, device=dev).to(torch.bfloat16)
+    rows = torch.randn(T * k8, d, generator=g, device=dev).to(torch.bfloat16)
+    shared = torch.randn(T, d, generator=g, device=dev).to(torch.bfloat16)
+    Bs, Hs, Ls, Ks, Dq, Dvv = 8, 8, 1024, 128, 192, 64
+    qa = torch.randn(Bs, Hs, Ls, Dq, generator=g, device=dev).to(torch.bfloat16).requires_grad_(True)
+    ka = torch.randn(Bs, Hs, Ls, Dq, generator=g, device=dev).to(torch.bfloat16).requires_grad_(True)
+    va = torch.randn(Bs, Hs, Ls, Dvv, generator=g, device=dev).to(torch.bfloat16).requires_grad_(True)
+    pos = torch.arange(Ls, device=dev).view(1, Ls, 1)
+    idx = (torch.rand(Bs, Ls, Ks, generator=g, device=dev) * (pos + 1)).long().clamp(max=Ls - 1)
+    go = torch.randn(Bs, Hs, Ls, Dvv, generator=g, device=dev).to(torch.bfloat16)
+    tq, ts = Kmod.quantize_fp8_rowwise(tok)
+    r = Kmod.moe_route(logits, bias, k8)
+
+    def attn():
+        o, _ = Kmod.sparse_attention(qa, ka, va, idx)
+        o.backward(go)
+        qa.grad = ka.grad = va.grad = None
+
+    passes = {"moe_route": lambda: Kmod.moe_route(logits, bias, k8),
+              "gather_rows": lambda: Kmod.gather_quantized_rows(tq, ts, r["token_indices"]),
+              "swiglu_quant": lambda: Kmod.swiglu_quantize_rowwise(h12),
+              "moe_combine_add": lambda: Kmod.moe_combine(rows, r["pair_pos"], r["pair_gate"], shared),
+              "sparse_attention_fwd_bwd": attn}
+    out = {}
+    for name, fn in passes.items():
+        out[name + "_ms"] = round(_time_kernel(fn, iters=2, warm=1), 4)
+    print(json.dumps({"extras_small": out}))
+
+
 # ---------------------------------------------------------------------------------------
 # MoE layer (expert parallel where N > 1): reported beside the dense line
 # ---------------------------------------------------------------------------------------
@@ -425,6 +463,8 @@ def main():
     ap.add_argument("--moe-chunks", type=int, default=1,
                     help="token chunks of the expert-parallel layer (N > 1): exchanges of one chunk run under the experts of another")
     ap.add_argument("--shape", default=None, help="M,K,N of a smaller case (profiling captures); default is the FFN workload")
+    ap.add_argument("--extras-small", action="store_true",
+                    help="run only the MoE plumbing passes and sparse attention on a reduced case (profiling captures) and exit")
     args = ap.parse_args()
     if args.shape:
         global M, K, N, FLOP_PER_STEP, WORKLOAD
@@ -449,6 +489,9 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     from cinnamon_b200 import kernels as Kmod      # raises if the CUDA library is missing
+    if args.extras_small:
+        extras_small(Kmod, dev)
+        return
 
     x_h, w_h, dy_h = make_inputs(1002 + rank, pinned=True)
     x = x_h.to(dev).requires_grad_(True)
