@@ -66,7 +66,12 @@ class PeerBuffers:
     group, plus the device arrays of peer base addresses that the kernels take.  Creating it is a collective."""
 
     def __init__(self, group, device, capacity_rows: int, home_rows: int, d: int, n_scales: int):
+        import os
         import torch.distributed as dist
+        # The exchange uses plain peer stores only.  PyTorch would otherwise also bind the buffers to an NVLink
+        # multicast object where the switch supports it; a rank that dies while bound to one can raise NVLink
+        # faults on its peers' GPUs, so the binding is switched off (PyTorch's documented environment switch).
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
         self.group = group if group is not None else dist.group.WORLD
         self.capacity_rows, self.home_rows, self.d, self.n_scales = int(capacity_rows), int(home_rows), int(d), int(n_scales)
