@@ -5,12 +5,13 @@
 // (src/kernels.py:618-664); the grouped variant follows grouped_gemm_kernel
 // (src/kernels.py:466-523) with the same e4m3 operands and scales.
 //
-// One persistent CTA per SM, 10 warps:
-//   warps 0-7  epilogue: tcgen05.ld a K block's partial tile, scale, accumulate, store the
-//              finished tile with row/column predicates (ragged expert tails need no padding)
-//   warp  8    TMA producer (one lane): A 128x128 B and B 256x128 B tiles, 128-byte swizzle
-//   warp  9    TMEM allocation + MMA issue (one lane): four 128x256x32 MMAs per K block into
-//              one of two 256-column TMEM buffers, so block i+1 runs while block i is promoted
+// One persistent CTA per SM, 11 warps:
+//   warps 0-7   promotion + epilogue: tcgen05.ld a K block's partial tile, scale, accumulate; a finished tile leaves
+//               through TMA stores (2-byte outputs, whole tiles) or staged 16-byte stores with row/column predicates
+//               (fp32 outputs, ragged expert tails, rows scattered to per-row addresses)
+//   warp  8     TMA producer (one lane): A 128x128 B and B 256x128 B tiles, 128-byte swizzle, 4-stage ring
+//   warps 9-10  MMA issuers (one lane each) on alternate K blocks: four 128x256x32 MMAs per block into one of two
+//               256-column TMEM buffers, so block i+1 runs while block i is promoted; warp 9 owns the TMEM allocation
 // Every wait is bounded: when one runs out the kernel records a code in a device status
 // word, every role leaves its loop, TMEM is freed and the kernel returns.
 #include "common.cuh"
