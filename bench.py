@@ -215,6 +215,8 @@ def bench_kernels(Kmod, dev, x, w, dy, peaks):
     xd, wd = x.detach(), w.detach()
     nkb, nnb = (K + 127) // 128, (N + 127) // 128
     quant_line("quant_row_vec x[16384,7168] bf16", lambda: Kmod.quantize_fp8_rowwise(xd), M * K * 3 + 4 * M * nkb)
+    quant_line("quant_row + block re-quantisation x[16384,7168] bf16, one pass (forward of a trained Linear)",
+               lambda: Kmod.quantize_fp8_rowwise_with_block(xd), M * K * 4 + 4 * M * nkb + 4 * (M // 128) * nkb)
     quant_line("quant_row_vec dy[16384,18432] bf16", lambda: Kmod.quantize_fp8_rowwise(dy), M * N * 3 + 4 * M * nnb)
     quant_line("quant_row_transposed dy^T (tiles along tokens)", lambda: Kmod.quantize_fp8_rowwise(dy.t()),
                M * N * 3 + 4 * N * (M // 128))

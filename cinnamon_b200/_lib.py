@@ -24,6 +24,7 @@ SIGNATURES = {
     "cinn_quant_rowwise": [_vp, _i32, _i64, _i64, _i64, _i64, _vp, _vp, _i32, _i32, _i32, _vp],
     "cinn_quant_rowwise_dual": [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _i32, _i32, _vp],
     "cinn_selfcheck_division": [_vp, _vp],
+    "cinn_quant_rowwise_with_block": [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _i32, _i32, _vp],
     "cinn_quant_blockwise": [_vp, _i32, _i64, _i64, _i64, _i64, _vp, _vp, _i32, _i32, _i32, _i32, _vp],
     "cinn_requant_row_to_block": [_vp, _vp, _i64, _i64, _vp, _vp, _i32, _i32, _vp],
     "cinn_dequant": [_vp, _vp, _vp, _i32, _i64, _i64, _i32, _i32, _vp],

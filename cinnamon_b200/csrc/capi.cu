@@ -77,6 +77,8 @@ int64_t grouped_wgrad_scratch_bytes(int64_t max_rows, int64_t d_in, int64_t d_ou
 int fp8_grouped_wgrad(const void* dY, int dy_dtype, const void* x_q, const float* x_s, const int64_t* starts_host,
                       const int64_t* ends_host, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* scratch,
                       int64_t scratch_bytes, void* dW, int out_dtype, int div_mode, cudaStream_t st);
+int quantize_row_block(const void* x, int dtype, int64_t M, int64_t N, int64_t ld, void* q_row, float* s_row, void* q_blk,
+                       float* s_blk, int round_scale, int div_mode, cudaStream_t st);
 int64_t moe_route_workspace_ints(int64_t T, int E);
 int moe_route(const float* logits, const float* bias, int64_t T, int E, int top_k, int* workspace, int* top_experts,
               float* top_gates, int64_t* token_indices, float* sorted_scores, int64_t* sorted_experts, int64_t* counts,
@@ -115,6 +117,12 @@ int cinn_quant_rowwise_dual(const void* x, int x_dtype, int64_t M, int64_t N, in
 
 int cinn_selfcheck_division(unsigned long long* mismatches, void* stream) {
     return cinn::selfcheck_division(mismatches, (cudaStream_t)stream);
+}
+
+int cinn_quant_rowwise_with_block(const void* x, int x_dtype, int64_t M, int64_t N, int64_t ld, void* q_row, float* s_row,
+                                  void* q_block, float* s_block, int round_scale, int div_mode, void* stream) {
+    return cinn::quantize_row_block(x, x_dtype, M, N, ld, q_row, s_row, q_block, s_block, round_scale, div_mode,
+                                    (cudaStream_t)stream);
 }
 
 int cinn_requant_row_to_block(const void* xq, const float* xs, int64_t M, int64_t K, void* out, float* scales,

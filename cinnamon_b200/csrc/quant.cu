@@ -398,8 +398,82 @@ __device__ __forceinline__ bool dual_tile(float (&v)[8][8], float (*s_amax)[128]
     return true;
 }
 
+// The forward of a trained Linear needs x quantised in 1x128 row tiles (its own GEMM) and, for the weight
+// gradient later, those quantised values de-quantised and quantised again in 128x128 blocks
+// (src/kernels.py:746 and :784-787).  Same piece layout as above: row tiles are reduced inside half-warps and
+// written; the thread then decodes its own bytes, multiplies by the row scale (exactly what
+// dequantize_fp8_rowwise yields), and the block's amax is one shuffle tree + shared memory.  Bit-identical to
+// quantize_fp8_rowwise followed by the row-to-block re-quantiser, with x read once and its e4m3 copy never re-read.
+template <int DIV, bool ROUND, typename AfterSync>
+__device__ __forceinline__ bool row_block_tile(float (&v)[8][8], float* s_red, bool ok, uint8_t* __restrict__ q_row,
+                                               float* __restrict__ s_row, uint8_t* __restrict__ q_blk,
+                                               float* __restrict__ s_blk, int M, int N, int nb_n, int bm, int bn,
+                                               AfterSync&& after_sync) {
+    const int sub = threadIdx.x & 15, hw = threadIdx.x >> 4, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = bn * 128 + sub * 8;
+    const int mt = bm * 128 + hw * 8;
+    float bmax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float a = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a = fmaxf(a, fabsf(v[i][j]));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+        const float s = scale_from_amax<DIV, ROUND>(a);
+        const float d = divisor_of<DIV>(s);
+        uint2 o2;
+        o2.x = cvt_e4m3x4(scaled_clamped<DIV>(v[i][0], d), scaled_clamped<DIV>(v[i][1], d),
+                          scaled_clamped<DIV>(v[i][2], d), scaled_clamped<DIV>(v[i][3], d));
+        o2.y = cvt_e4m3x4(scaled_clamped<DIV>(v[i][4], d), scaled_clamped<DIV>(v[i][5], d),
+                          scaled_clamped<DIV>(v[i][6], d), scaled_clamped<DIV>(v[i][7], d));
+        const bool inb = mt + i < M && n < N;
+        if (inb) {
+            __stcs(reinterpret_cast<uint2*>(q_row + (int64_t)(mt + i) * N + n), o2);
+            if (sub == 0) s_row[(int64_t)(mt + i) * nb_n + bn] = s;
+        }
+        // what the backward would read back: e4m3 value times the row scale (zero outside the matrix)
+        const uint32_t w[2] = {o2.x, o2.y};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float2 lo = e4m3x2_to_float2((uint16_t)(w[h] & 0xffff));
+            const float2 hi = e4m3x2_to_float2((uint16_t)(w[h] >> 16));
+            v[i][4 * h + 0] = inb ? __fmul_rn(lo.x, s) : 0.0f;
+            v[i][4 * h + 1] = inb ? __fmul_rn(lo.y, s) : 0.0f;
+            v[i][4 * h + 2] = inb ? __fmul_rn(hi.x, s) : 0.0f;
+            v[i][4 * h + 3] = inb ? __fmul_rn(hi.y, s) : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) bmax = fmaxf(bmax, fabsf(v[i][j]));
+    }
+    bmax = warp_max(bmax);
+    if (lane == 0) s_red[warp] = bmax;
+    if (!__syncthreads_and(ok)) return false;
+    after_sync();
+    bmax = s_red[0];
+#pragma unroll
+    for (int w8 = 1; w8 < 8; ++w8) bmax = fmaxf(bmax, s_red[w8]);
+    const float sb = scale_from_amax<DIV, false>(bmax);
+    const float db = divisor_of<DIV>(sb);
+    if (threadIdx.x == 0) s_blk[(int64_t)bm * nb_n + bn] = sb;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        if (mt + i < M && n < N) {
+            uint2 o2;
+            o2.x = cvt_e4m3x4(scaled_clamped<DIV>(v[i][0], db), scaled_clamped<DIV>(v[i][1], db),
+                              scaled_clamped<DIV>(v[i][2], db), scaled_clamped<DIV>(v[i][3], db));
+            o2.y = cvt_e4m3x4(scaled_clamped<DIV>(v[i][4], db), scaled_clamped<DIV>(v[i][5], db),
+                              scaled_clamped<DIV>(v[i][6], db), scaled_clamped<DIV>(v[i][7], db));
+            __stcs(reinterpret_cast<uint2*>(q_blk + (int64_t)(mt + i) * N + n), o2);
+        }
+    }
+    __syncthreads();                      // s_red is free for the next piece
+    return true;
+}
+
 // One CTA per piece, loads straight into registers (4-byte inputs, and rows whose pitch a tensor map cannot take).
-template <typename T, int DIV, bool ROUND>
+// MODE 0: q_col / s_col are the quantisation along the rows of the transpose; MODE 1: the 128x128 block re-quantisation.
+template <typename T, int DIV, bool ROUND, int MODE = 0>
 __global__ void __launch_bounds__(256, 2)
 quant_row_dual_kernel(const T* __restrict__ x, int64_t ld, uint8_t* __restrict__ q_row, float* __restrict__ s_row,
                       uint8_t* __restrict__ q_col, float* __restrict__ s_col, int M, int N, int nb_n, int nb_m) {
@@ -415,8 +489,12 @@ quant_row_dual_kernel(const T* __restrict__ x, int64_t ld, uint8_t* __restrict__
     float v[8][8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) unpack_raw8<T>(raw[i], v[i]);
-    dual_tile<DIV, ROUND>(v, s_amax, s_out, true, q_row, s_row, q_col, s_col, M, N, nb_n, nb_m, (int)blockIdx.y,
-                          (int)blockIdx.x, [] {});
+    if constexpr (MODE == 0)
+        dual_tile<DIV, ROUND>(v, s_amax, s_out, true, q_row, s_row, q_col, s_col, M, N, nb_n, nb_m, (int)blockIdx.y,
+                              (int)blockIdx.x, [] {});
+    else
+        row_block_tile<DIV, ROUND>(v, &s_amax[0][0], true, q_row, s_row, q_col, s_col, M, N, nb_n, (int)blockIdx.y,
+                                   (int)blockIdx.x, [] {});
 }
 
 // Persistent CTAs fed by TMA (2-byte inputs): the 128 x 128 pieces arrive in a ring of shared-memory stages
@@ -440,7 +518,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
     }
 }
 
-template <typename T, int DIV, bool ROUND>
+template <typename T, int DIV, bool ROUND, int MODE = 0>
 __global__ void __launch_bounds__(256, 2)
 quant_row_dual_tma_kernel(const __grid_constant__ CUtensorMap tmX, uint8_t* __restrict__ q_row, float* __restrict__ s_row,
                           uint8_t* __restrict__ q_col, float* __restrict__ s_col, int M, int N, int nb_n, int nb_m,
@@ -497,8 +575,12 @@ quant_row_dual_tma_kernel(const __grid_constant__ CUtensorMap tmX, uint8_t* __re
         const int tn = t + DUAL_STAGES * stride;
         int bm, bn;
         coords(t, bm, bn);
-        alive = dual_tile<DIV, ROUND>(v, s_amax, s_out, ok, q_row, s_row, q_col, s_col, M, N, nb_n, nb_m, bm, bn,
-                                      [&] { if (threadIdx.x == 0 && tn < total) issue(tn, s); });
+        if constexpr (MODE == 0)
+            alive = dual_tile<DIV, ROUND>(v, s_amax, s_out, ok, q_row, s_row, q_col, s_col, M, N, nb_n, nb_m, bm, bn,
+                                          [&] { if (threadIdx.x == 0 && tn < total) issue(tn, s); });
+        else
+            alive = row_block_tile<DIV, ROUND>(v, &s_amax[0][0], ok, q_row, s_row, q_col, s_col, M, N, nb_n, bm, bn,
+                                               [&] { if (threadIdx.x == 0 && tn < total) issue(tn, s); });
         if (!alive) break;
     }
     if (!alive && threadIdx.x == 0) {
@@ -924,6 +1006,70 @@ static int dispatch_dual(const T* x, int64_t M, int64_t N, int64_t ld, uint8_t* 
     }
     CINN_CHECK_LAUNCH();
     return CINN_OK;
+}
+
+int requant_row_to_block(const void* xq, const float* xs, int64_t M, int64_t K, void* out, float* scales,
+                         int transpose_out, int div_mode, cudaStream_t st);
+
+// Row-wise 1x128 quantisation plus the 128x128 re-quantisation of its result, one pass over x.
+template <typename T>
+static int dispatch_row_block(const T* x, int64_t M, int64_t N, int64_t ld, uint8_t* q_row, float* s_row, uint8_t* q_blk,
+                              float* s_blk, int round_scale, int div_mode, cudaStream_t st) {
+    const int nb_n = (int)((N + 127) / 128), nb_m = (int)((M + 127) / 128);
+    const bool fused = N % 16 == 0 && ld % 8 == 0 && nb_m <= 65535 && aligned16(x) && aligned16(q_row) && aligned16(q_blk);
+    if (!fused) {
+        int rc = dispatch_quant(false, x, M, N, ld, (int64_t)1, q_row, s_row, 1, 128, round_scale, div_mode, st);
+        if (rc) return rc;
+        return requant_row_to_block(q_row, s_row, M, N, q_blk, s_blk, 0, div_mode, st);
+    }
+    if constexpr (sizeof(T) == 2) {
+        CUtensorMap tm;
+        int rc = encode_map_2d(&tm, x, (uint64_t)N, (uint64_t)M, (uint64_t)ld * 2, 128, 128, CU_TENSOR_MAP_DATA_TYPE_UINT16,
+                               CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc) return rc;
+        const int64_t total = (int64_t)nb_n * nb_m;
+        CINN_CHECK_ARG(total < (1LL << 31), "row + block quantiser: too many tiles");
+        const int grid = (int)(total < 2 * (int64_t)sm_count() ? total : 2 * (int64_t)sm_count());
+#define CINN_D(DIV, RND)                                                                                              \
+    do {                                                                                                              \
+        auto kern = quant_row_dual_tma_kernel<T, DIV, RND, 1>;                                                        \
+        static std::once_flag once;                                                                                   \
+        static cudaError_t attr_err = cudaSuccess;                                                                    \
+        std::call_once(once, [&] {                                                                                    \
+            attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);      \
+        });                                                                                                           \
+        CINN_CHECK_CUDA(attr_err);                                                                                    \
+        kern<<<grid, 256, DUAL_SMEM_BYTES, st>>>(tm, q_row, s_row, q_blk, s_blk, (int)M, (int)N, nb_n, nb_m, (int)total); \
+    } while (0)
+        if (div_mode == CINN_DIV_FULL) { if (round_scale) CINN_D(CINN_DIV_FULL, true); else CINN_D(CINN_DIV_FULL, false); }
+        else                           { if (round_scale) CINN_D(CINN_DIV_RN, true);   else CINN_D(CINN_DIV_RN, false); }
+#undef CINN_D
+    } else {
+        dim3 grid((unsigned)nb_n, (unsigned)nb_m);
+#define CINN_D(DIV, RND) quant_row_dual_kernel<T, DIV, RND, 1><<<grid, 256, 0, st>>>(x, ld, q_row, s_row, q_blk, s_blk, (int)M, (int)N, nb_n, nb_m)
+        if (div_mode == CINN_DIV_FULL) { if (round_scale) CINN_D(CINN_DIV_FULL, true); else CINN_D(CINN_DIV_FULL, false); }
+        else                           { if (round_scale) CINN_D(CINN_DIV_RN, true);   else CINN_D(CINN_DIV_RN, false); }
+#undef CINN_D
+    }
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+int quantize_row_block(const void* x, int dtype, int64_t M, int64_t N, int64_t ld, void* q_row, float* s_row, void* q_blk,
+                       float* s_blk, int round_scale, int div_mode, cudaStream_t st) {
+    CINN_CHECK_ARG(M >= 0 && N >= 0, "row + block quantiser: negative shape (%lld, %lld)", (long long)M, (long long)N);
+    if (M == 0 || N == 0) return CINN_OK;
+    CINN_CHECK_ARG(x && q_row && s_row && q_blk && s_blk, "row + block quantiser: null pointer");
+    CINN_CHECK_ARG(N < (1LL << 31) && M < (1LL << 31), "row + block quantiser: dimension too large");
+    CINN_CHECK_ARG(ld >= N, "row + block quantiser: row pitch %lld below the row length %lld", (long long)ld, (long long)N);
+    CINN_CHECK_ARG(N % 16 == 0, "row + block quantiser: the row length (%lld) must be a multiple of 16", (long long)N);
+    CINN_CHECK_ARG(div_mode == CINN_DIV_FULL || div_mode == CINN_DIV_RN, "row + block quantiser: unknown div_mode %d", div_mode);
+    switch (dtype) {
+        case CINN_BF16: return dispatch_row_block((const __nv_bfloat16*)x, M, N, ld, (uint8_t*)q_row, s_row, (uint8_t*)q_blk, s_blk, round_scale, div_mode, st);
+        case CINN_F16:  return dispatch_row_block((const __half*)x, M, N, ld, (uint8_t*)q_row, s_row, (uint8_t*)q_blk, s_blk, round_scale, div_mode, st);
+        case CINN_F32:  return dispatch_row_block((const float*)x, M, N, ld, (uint8_t*)q_row, s_row, (uint8_t*)q_blk, s_blk, round_scale, div_mode, st);
+        default: set_error("row + block quantiser: unknown dtype tag %d", dtype); return CINN_ERR_INVALID;
+    }
 }
 
 // ---------------------------------------------------------------------------

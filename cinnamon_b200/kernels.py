@@ -140,6 +140,30 @@ def quantize_fp8_rowwise_dual(x: torch.Tensor, round_scale: bool = False):
     return q_row, s_row, q_col, s_col
 
 
+def quantize_fp8_rowwise_with_block(x: torch.Tensor, round_scale: bool = False):
+    """``quantize_fp8_rowwise(x)`` together with ``quantize_fp8_blockwise(dequantize_fp8_rowwise(q, s))`` of its result
+    (what ``FP8MatmulFunction`` computes in its forward, reference src/kernels.py:746, and on the saved activations in
+    its backward, :784-787) from one pass over ``x``.  Returns ``(q_row, s_row, q_block, s_block)``; bit-identical to
+    the separate calls.  The row length must be a multiple of 16."""
+    assert x.is_cuda, "Input must be on CUDA"
+    assert x.ndim == 2, "Input must be 2D for now"
+    x = _as_quant_input(x)
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    M, N = x.shape
+    nb = (N + 127) // 128
+    with torch.cuda.device(x.device):
+        q_row = torch.empty((M, N), dtype=torch.float8_e4m3fn, device=x.device)
+        s_row = torch.empty((M, nb), dtype=torch.float32, device=x.device)
+        q_blk = torch.empty((M, N), dtype=torch.float8_e4m3fn, device=x.device)
+        s_blk = torch.empty(((M + 127) // 128, nb), dtype=torch.float32, device=x.device)
+        _lib.check(_L.cinn_quant_rowwise_with_block(_ptr(x), _DTYPE_TAG[x.dtype], M, N, x.stride(0), _ptr(q_row), _ptr(s_row),
+                                                    _ptr(q_blk), _ptr(s_blk), int(bool(round_scale)), _DIV_MODE, _stream(x)),
+                   "cinn_quant_rowwise_with_block")
+    _count()
+    return q_row, s_row, q_blk, s_blk
+
+
 def quantize_fp8_blockwise(x: torch.Tensor, block_m: int = 128, block_n: int = 128, round_scale: bool = False):
     """Block-wise block_m x block_n quantisation (reference src/kernels.py:219-259).
 
@@ -289,13 +313,23 @@ class FP8MatmulFunction(torch.autograd.Function):
         x_flat = x.reshape(-1, x_shape[-1])
         M, K = x_flat.shape
         N = weight.shape[0]
-        x_fp8, x_scale = quantize_fp8_rowwise(x_flat, block_size=128, round_scale=round_scale)     # :746
+        # :746; when the weight will want a gradient, the block re-quantisation of the saved activations that the
+        # backward needs (:784-787) comes out of the same pass over x and is what gets saved
+        want_wgrad = ctx.needs_input_grad[1] and K % 16 == 0
+        if want_wgrad:
+            x_fp8, x_scale, x_blk, x_blk_scale = quantize_fp8_rowwise_with_block(x_flat, round_scale=round_scale)
+        else:
+            x_fp8, x_scale = quantize_fp8_rowwise(x_flat, block_size=128, round_scale=round_scale)
         w_fp8, w_scale = quantize_fp8_blockwise(weight.float() if weight.dtype not in _DTYPE_TAG else weight,
                                                 block_m=128, block_n=128)                            # :747
         # :748-752 without the transposed copies: B stays (N, K); sB[kb, nb] = w_scale[nb, kb]
         out = _gemm(x_fp8, x_scale, w_fp8, _lib.B_NK, w_scale, w_scale.stride(1), w_scale.stride(0), M, N, K,
                     torch.bfloat16)
-        ctx.save_for_backward(x_fp8, x_scale, w_fp8, w_scale)
+        if want_wgrad:
+            ctx.save_for_backward(x_blk, x_blk_scale, w_fp8, w_scale)
+        else:
+            ctx.save_for_backward(x_fp8, x_scale, w_fp8, w_scale)
+        ctx.x_is_block = want_wgrad
         ctx.x_shape = x_shape
         ctx.round_scale = round_scale
         ctx.weight_dtype = weight.dtype
@@ -317,14 +351,18 @@ class FP8MatmulFunction(torch.autograd.Function):
         if Mp != M:
             grad_flat = torch.nn.functional.pad(grad_flat, (0, 0, 0, Mp - M))
             x_fp8 = torch.nn.functional.pad(x_fp8.view(torch.uint8), (0, 0, 0, Mp - M)).view(torch.float8_e4m3fn)
-            x_scale = torch.nn.functional.pad(x_scale, (0, 0, 0, Mp - M), value=1.0)
+            if not ctx.x_is_block:                         # block scales: zero rows stay inside the last row block
+                x_scale = torch.nn.functional.pad(x_scale, (0, 0, 0, Mp - M), value=1.0)
         # dy quantised along features for dgrad (:771) and along tokens for wgrad (:781-783), one pass over dy
         grad_fp8, grad_scale, grad_fp8_t, grad_scale_t = quantize_fp8_rowwise_dual(grad_flat, round_scale=round_scale)
         # dgrad (:771-774): dy (M, N) @ W (N, K); W is the B operand stored (reduction, output)
         grad_x = _gemm(grad_fp8, grad_scale, w_fp8, _lib.B_KN, w_scale, w_scale.stride(0), w_scale.stride(1), M, K, N,
                        torch.bfloat16)
         # wgrad (:781-788): x re-quantised in 128x128 blocks
-        x_fp8_block, x_scale_block = requantize_rowwise_to_blockwise(x_fp8, x_scale)
+        if ctx.x_is_block:
+            x_fp8_block, x_scale_block = x_fp8, x_scale            # made by the forward's pass over x
+        else:
+            x_fp8_block, x_scale_block = requantize_rowwise_to_blockwise(x_fp8, x_scale)
         # the reference returns a bf16 grad_weight which autograd then casts to the fp32 master
         # weight's dtype (:788, :794); the GEMM writes those same values as fp32 directly
         ctx_w_fp32 = ctx.weight_dtype == torch.float32

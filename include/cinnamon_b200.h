@@ -68,6 +68,16 @@ int cinn_quant_rowwise_dual(const void* x, int x_dtype, int64_t M, int64_t N, in
  * Synchronises the stream. */
 int cinn_selfcheck_division(unsigned long long* mismatches, void* stream);
 
+/* Row-wise 1 x 128 quantisation of x (M, N; contiguous rows of pitch ld; N a multiple of 16) together with the
+ * 128 x 128 block re-quantisation of that result, in one pass over x:
+ *   q_row (M, N), s_row (M, ceil(N/128)):                  as cinn_quant_rowwise(x);
+ *   q_block (M, N), s_block (ceil(M/128), ceil(N/128)):    as cinn_requant_row_to_block(q_row, s_row).
+ * Replaces the quantize_fp8_rowwise of FP8MatmulFunction.forward (src/kernels.py:746) plus the
+ * dequantize_fp8_rowwise -> quantize_fp8_blockwise pair its backward runs on the saved activations (:784-787);
+ * bit-identical to those calls.  round_scale applies to the row-wise scales only, as in the reference. */
+int cinn_quant_rowwise_with_block(const void* x, int x_dtype, int64_t M, int64_t N, int64_t ld, void* q_row, float* s_row,
+                                  void* q_block, float* s_block, int round_scale, int div_mode, void* stream);
+
 /* Block-wise block_m x block_n quantisation.
  * Replaces quantize_fp8_blockwise_kernel + quantize_fp8_blockwise (src/kernels.py:74-132, 219-259).
  * scales: (ceil(M/block_m), ceil(N/block_n)). */

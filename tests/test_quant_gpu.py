@@ -98,6 +98,28 @@ def test_dual_rowwise_shapes(K, dtype, shape):
         assert torch.equal(q2.view(torch.uint8), q_col.view(torch.uint8)) and torch.equal(s2, s_col)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("shape", [(256, 384), (130, 272), (77, 208), (1000, 512), (16, 16)])
+@pytest.mark.parametrize("rs", [False, True])
+def test_rowwise_with_block_equals_separate_calls(K, dtype, shape, rs):
+    """One pass over x: its 1x128 quantisation and the 128x128 re-quantisation of that, bit for bit what the row-wise
+    quantiser followed by the row-to-block re-quantiser give, and what the oracle gives."""
+    M, N = shape
+    g = torch.Generator().manual_seed(M * 7 + N)
+    base = (torch.randn(M, N + 16, generator=g) * torch.logspace(-3, 2, N + 16)[None, :]).to(dtype)
+    base[M // 3, :] = 0
+    xc = base.cuda()
+    for view, ref in ((xc[:, :N].contiguous(), base[:, :N]), (xc[:, 16:N + 16], base[:, 16:N + 16])):
+        q_row, s_row, q_blk, s_blk = K.quantize_fp8_rowwise_with_block(view, rs)
+        q1, s1 = K.quantize_fp8_rowwise(view, 128, rs)
+        q2, s2 = K.requantize_rowwise_to_blockwise(q1, s1)
+        assert torch.equal(q_row.view(torch.uint8), q1.view(torch.uint8)) and torch.equal(s_row, s1)
+        assert torch.equal(q_blk.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(s_blk, s2)
+        oq, os_ = O.quantize_rowwise(ref.contiguous(), 128, rs)
+        assert_quant_equal(q_row, s_row, oq, os_, what="rows")
+        assert_quant_equal(q_blk, s_blk, *O.requantize_row_to_block(oq, os_), what="blocks")
+
+
 @pytest.mark.parametrize("rs", [False, True])
 def test_every_bf16_amax(K, rs):
     """For bf16 input the scale is a function of the tile's amax alone: sweep every
