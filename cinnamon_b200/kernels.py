@@ -307,7 +307,10 @@ class FP8MatmulFunction(torch.autograd.Function):
     activations / gradients 1x128, weights 128x128, e4m3 everywhere."""
 
     @staticmethod
-    def forward(ctx, x, weight, round_scale):
+    def forward(ctx, x, weight, round_scale, weight_fp8=None):
+        """``weight_fp8``: optional ``(w_fp8, w_scale)`` of this very weight (``quantize_fp8_blockwise``), for callers
+        that quantise a weight once per optimiser step instead of once per call; the reference's three-argument
+        call re-quantises every time (:747)."""
         assert x.is_cuda, "Input must be on CUDA"
         x_shape = x.shape
         x_flat = x.reshape(-1, x_shape[-1])
@@ -320,8 +323,12 @@ class FP8MatmulFunction(torch.autograd.Function):
             x_fp8, x_scale, x_blk, x_blk_scale = quantize_fp8_rowwise_with_block(x_flat, round_scale=round_scale)
         else:
             x_fp8, x_scale = quantize_fp8_rowwise(x_flat, block_size=128, round_scale=round_scale)
-        w_fp8, w_scale = quantize_fp8_blockwise(weight.float() if weight.dtype not in _DTYPE_TAG else weight,
-                                                block_m=128, block_n=128)                            # :747
+        if weight_fp8 is not None:
+            w_fp8, w_scale = weight_fp8
+        else:
+            w_fp8, w_scale = quantize_fp8_blockwise(weight.float() if weight.dtype not in _DTYPE_TAG else weight,
+                                                    block_m=128, block_n=128)                        # :747
+        ctx.n_inputs = 3 if weight_fp8 is None else 4
         # :748-752 without the transposed copies: B stays (N, K); sB[kb, nb] = w_scale[nb, kb]
         out = _gemm(x_fp8, x_scale, w_fp8, _lib.B_NK, w_scale, w_scale.stride(1), w_scale.stride(0), M, N, K,
                     torch.bfloat16)
@@ -369,18 +376,24 @@ class FP8MatmulFunction(torch.autograd.Function):
         grad_weight = _gemm(grad_fp8_t, grad_scale_t, x_fp8_block, _lib.B_KN, x_scale_block, x_scale_block.stride(0),
                             x_scale_block.stride(1), N, K, Mp, torch.float32 if ctx_w_fp32 else torch.bfloat16,
                             bf16_rounded=True)
-        return grad_x.reshape(x_shape), grad_weight, None
+        return (grad_x.reshape(x_shape), grad_weight, None) + (None,) * (ctx.n_inputs - 3)
 
 
 class FP8Linear(torch.nn.Module):
     """FP8 Linear layer (reference src/kernels.py:797-840): fp32 master weight,
     bias added after the matmul, ``round_scale`` applied to activations and gradients."""
 
-    def __init__(self, in_features: int, out_features: int, bias: bool = False, round_scale: bool = False):
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, round_scale: bool = False,
+                 cache_quantized_weight: bool = False):
+        """``cache_quantized_weight`` (not in the reference, off by default): keep the e4m3 copy of the weight until
+        the weight changes (an in-place optimiser update bumps its version), so the micro-steps of a gradient
+        accumulation quantise it once instead of once each."""
         super().__init__()
         self.in_features = in_features
         self.out_features = out_features
         self.round_scale = round_scale
+        self.cache_quantized_weight = cache_quantized_weight
+        self._w_cache = (None, None)
         self.weight = torch.nn.Parameter(torch.empty(out_features, in_features))
         torch.nn.init.normal_(self.weight, mean=0.0, std=0.02)
         if bias:
@@ -389,7 +402,14 @@ class FP8Linear(torch.nn.Module):
             self.register_parameter("bias", None)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if x.is_cuda:
+        if x.is_cuda and self.cache_quantized_weight:
+            w = self.weight
+            key = (w._version, w.data_ptr(), w.dtype)
+            if self._w_cache[0] != key:
+                with torch.no_grad():
+                    self._w_cache = (key, quantize_fp8_blockwise(w.float() if w.dtype not in _DTYPE_TAG else w, 128, 128))
+            out = FP8MatmulFunction.apply(x, w, self.round_scale, self._w_cache[1])
+        elif x.is_cuda:
             out = FP8MatmulFunction.apply(x, self.weight, self.round_scale)
         else:
             # the reference does the same: an unquantised linear on CPU tensors (:823-824)

@@ -140,6 +140,33 @@ def test_autograd_function_matches_oracle(K, M, Kd, N, rs):
         assert err < 4e-3, name          # bf16 rounding alone costs ~1.7e-3
 
 
+def test_fp8_linear_weight_cache(K):
+    """The optional e4m3 weight cache: same outputs and gradients, one quantiser launch fewer per call while the
+    weight is unchanged, refreshed after an in-place update."""
+    torch.manual_seed(5)
+    a = K.FP8Linear(256, 384).cuda()
+    b = K.FP8Linear(256, 384, cache_quantized_weight=True).cuda()
+    b.load_state_dict(a.state_dict())
+    x = torch.randn(64, 256, device="cuda")
+    for step in range(3):
+        ya, yb = a(x), b(x)
+        assert torch.equal(ya, yb)
+        ya.sum().backward()
+        yb.sum().backward()
+        assert torch.equal(a.weight.grad, b.weight.grad)
+        if step == 1:                                              # an optimiser step: the cache must notice
+            with torch.no_grad():
+                a.weight.add_(0.01)
+                b.weight.add_(0.01)
+        a.weight.grad = b.weight.grad = None
+    n0 = K.launch_count
+    b(x)
+    cached = K.launch_count - n0
+    n0 = K.launch_count
+    a(x)
+    assert K.launch_count - n0 == cached + 1
+
+
 def test_grouped_gemm_scattered_rows(K):
     """Output rows stored at per-row addresses (the expert-parallel way home): here a permutation inside a local
     buffer, with a dropped row (address 0) and ragged expert sizes; same bits as the plain grouped GEMM."""
