@@ -79,6 +79,7 @@ int fp8_grouped_wgrad(const void* dY, int dy_dtype, const void* x_q, const float
                       int64_t scratch_bytes, void* dW, int out_dtype, int div_mode, cudaStream_t st);
 int quantize_row_block(const void* x, int dtype, int64_t M, int64_t N, int64_t ld, void* q_row, float* s_row, void* q_blk,
                        float* s_blk, int round_scale, int div_mode, cudaStream_t st);
+int swiglu(const void* h12, const void* dh, void* out, int dtype, int64_t T_rows, int64_t I, int backward, cudaStream_t st);
 int64_t moe_route_workspace_ints(int64_t T, int E);
 int moe_route(const float* logits, const float* bias, int64_t T, int E, int top_k, int* workspace, int* top_experts,
               float* top_gates, int64_t* token_indices, float* sorted_scores, int64_t* sorted_experts, int64_t* counts,
@@ -247,6 +248,14 @@ int cinn_fp8_grouped_wgrad(const void* dY, int dy_dtype, const void* x_q, const 
                            int64_t scratch_bytes, void* dW, int out_dtype, int div_mode, void* stream) {
     return cinn::fp8_grouped_wgrad(dY, dy_dtype, x_q, x_scales, starts_host, ends_host, E, T, d_in, d_out, scratch,
                                    scratch_bytes, dW, out_dtype, div_mode, (cudaStream_t)stream);
+}
+
+int cinn_swiglu(const void* h12, void* h, int dtype, int64_t T, int64_t I, void* stream) {
+    return cinn::swiglu(h12, nullptr, h, dtype, T, I, 0, (cudaStream_t)stream);
+}
+
+int cinn_swiglu_backward(const void* h12, const void* grad_h, void* grad_h12, int dtype, int64_t T, int64_t I, void* stream) {
+    return cinn::swiglu(h12, grad_h, grad_h12, dtype, T, I, 1, (cudaStream_t)stream);
 }
 
 int cinn_p2p_barrier(const int64_t* peer_flags, int rank, int n_ranks, unsigned epoch, void* stream) {

@@ -97,6 +97,88 @@ int moe_combine(const void* rows, int dtype, const int64_t* pos, const float* ga
 }
 
 // ---------------------------------------------------------------------------
+// SwiGLU between the two grouped GEMMs, for training (src/layers.py:71-74: h1, h2 = h12.float().chunk(2);
+// h = (silu(h1) * h2).to(dtype)) and its backward:
+//   dh1 = dh * h2 * sig(h1) * (1 + h1 * (1 - sig(h1))),   dh2 = dh * silu(h1),   fp32 arithmetic, results rounded
+// to the activation type.  One pass each, 16-byte vectors, a thread owns eight consecutive columns of one row.
+// ---------------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
+
+template <typename T>
+__device__ __forceinline__ void store8f(T* p, const float (&v)[8]) {
+    if constexpr (sizeof(T) == 4) {
+        reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+        reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+        T t[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t[i] = from_float<T>(v[i]);
+        *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(t);
+    }
+}
+
+template <typename T, bool BACKWARD>
+__global__ void __launch_bounds__(256)
+swiglu_kernel(const T* __restrict__ h12, const T* __restrict__ dh, T* __restrict__ out, int64_t T_rows, int I) {
+    const int per_row = I >> 3;
+    const int64_t total = T_rows * per_row;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
+        const int64_t row = i / per_row;
+        const int col = (int)(i - row * per_row) << 3;
+        float a[8], b[8];
+        load8f<T>(h12 + row * 2 * (int64_t)I + col, a);
+        load8f<T>(h12 + row * 2 * (int64_t)I + I + col, b);
+        if constexpr (!BACKWARD) {
+            float h[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) h[j] = (a[j] / (1.0f + expf(-a[j]))) * b[j];
+            store8f<T>(out + row * (int64_t)I + col, h);
+        } else {
+            float g[8], d1[8], d2[8];
+            load8f<T>(dh + row * (int64_t)I + col, g);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float sig = 1.0f / (1.0f + expf(-a[j]));
+                d1[j] = g[j] * b[j] * sig * (1.0f + a[j] * (1.0f - sig));
+                d2[j] = g[j] * a[j] * sig;
+            }
+            store8f<T>(out + row * 2 * (int64_t)I + col, d1);
+            store8f<T>(out + row * 2 * (int64_t)I + I + col, d2);
+        }
+    }
+}
+
+template <typename T>
+static int swiglu_typed(const T* h12, const T* dh, T* out, int64_t T_rows, int64_t I, bool backward, cudaStream_t st) {
+    int64_t blocks = (T_rows * (I / 8) + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    if (backward) swiglu_kernel<T, true><<<(unsigned)blocks, 256, 0, st>>>(h12, dh, out, T_rows, (int)I);
+    else swiglu_kernel<T, false><<<(unsigned)blocks, 256, 0, st>>>(h12, dh, out, T_rows, (int)I);
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+// forward: out (T, I) = silu(h12[:, :I]) * h12[:, I:];  backward: out (T, 2I) = d h12 given dh (T, I)
+int swiglu(const void* h12, const void* dh, void* out, int dtype, int64_t T_rows, int64_t I, int backward, cudaStream_t st) {
+    CINN_CHECK_ARG(T_rows >= 0 && I >= 0, "swiglu: negative shape");
+    if (T_rows == 0 || I == 0) return CINN_OK;
+    CINN_CHECK_ARG(h12 && out && (!backward || dh), "swiglu: null pointer");
+    CINN_CHECK_ARG(I % 8 == 0 && I < (1LL << 30), "swiglu: the hidden width (%lld) must be a multiple of 8", (long long)I);
+    CINN_CHECK_ARG((reinterpret_cast<uintptr_t>(h12) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(dh) & 15) == 0, "swiglu: buffers must be 16-byte aligned");
+    switch (dtype) {
+        case CINN_BF16: return swiglu_typed((const __nv_bfloat16*)h12, (const __nv_bfloat16*)dh, (__nv_bfloat16*)out, T_rows, I, backward != 0, st);
+        case CINN_F16: return swiglu_typed((const __half*)h12, (const __half*)dh, (__half*)out, T_rows, I, backward != 0, st);
+        case CINN_F32: return swiglu_typed((const float*)h12, (const float*)dh, (float*)out, T_rows, I, backward != 0, st);
+        default: set_error("swiglu: unknown dtype tag %d", dtype); return CINN_ERR_INVALID;
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Dispatch gather: out_q[r, :] = q[idx[r], :] (e4m3 bytes) and out_s[r, :] = s[idx[r], :] (their 1x128 scales)
 // in one pass: the `flat_x[token_indices]` of MoE.forward (src/layers.py:140) applied to tokens that were
 // quantised once, before the gather.  One warp per output row, 16-byte vectors.

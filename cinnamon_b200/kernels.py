@@ -546,6 +546,44 @@ def swiglu_quantize_rowwise(h12: torch.Tensor, n_rows_dev: torch.Tensor = None):
     return q, s
 
 
+class SwiGLUFunction(torch.autograd.Function):
+    """``h = (silu(h1) * h2).to(h12.dtype)`` with ``h1, h2 = h12.float().chunk(2, -1)`` (the step between the two
+    expert GEMMs, reference src/layers.py:71-74) with its backward, one kernel each: the training-path sibling of
+    ``swiglu_quantize_rowwise``."""
+
+    @staticmethod
+    def forward(ctx, h12):
+        assert h12.is_cuda and h12.shape[-1] % 2 == 0, "Input must be on CUDA with an even last dimension"
+        shape = h12.shape
+        flat = h12.reshape(-1, shape[-1])
+        flat = flat.contiguous() if flat.dtype in _DTYPE_TAG else flat.float().contiguous()
+        T, I = flat.shape[0], flat.shape[1] // 2
+        with torch.cuda.device(flat.device):
+            h = torch.empty((T, I), dtype=flat.dtype, device=flat.device)
+            _lib.check(_L.cinn_swiglu(_ptr(flat), _ptr(h), _DTYPE_TAG[flat.dtype], T, I, _stream(flat)), "cinn_swiglu")
+        _count()
+        ctx.save_for_backward(flat)
+        ctx.shape, ctx.in_dtype = shape, h12.dtype
+        return h.reshape(*shape[:-1], I).to(h12.dtype)
+
+    @staticmethod
+    def backward(ctx, grad_h):
+        (flat,) = ctx.saved_tensors
+        T, I = flat.shape[0], flat.shape[1] // 2
+        g = grad_h.reshape(T, I).to(flat.dtype).contiguous()
+        with torch.cuda.device(flat.device):
+            grad = torch.empty_like(flat)
+            _lib.check(_L.cinn_swiglu_backward(_ptr(flat), _ptr(g), _ptr(grad), _DTYPE_TAG[flat.dtype], T, I, _stream(flat)),
+                       "cinn_swiglu_backward")
+        _count()
+        return grad.reshape(ctx.shape).to(ctx.in_dtype)
+
+
+def swiglu(h12: torch.Tensor) -> torch.Tensor:
+    """Differentiable ``silu(h12[..., :I]) * h12[..., I:]`` (reference src/layers.py:71-74) on the CUDA kernels."""
+    return SwiGLUFunction.apply(h12)
+
+
 def moe_combine(rows: torch.Tensor, pos: torch.Tensor, gates: torch.Tensor, addend: torch.Tensor = None) -> torch.Tensor:
     """``y[t] = sum_j gates[t, j] * rows[pos[t, j]]`` in fp32: the gate multiply + scatter-add of
     ``MoE.forward`` (reference src/layers.py:157-160) as one gather pass without atomics.

@@ -203,6 +203,12 @@ int cinn_lightning_indexer(const void* q, const void* k, const void* w, int dtyp
                            int64_t Lk, int64_t H, int64_t d, const int64_t* q_strides, const int64_t* k_strides,
                            const int64_t* w_strides, void* stream);
 
+/* SwiGLU between the two expert GEMMs, unquantised (the training path; cinn_swiglu_quant_rowwise is the
+ * inference path): h (T, I) = silu(h12[:, :I]) * h12[:, I:], fp32 arithmetic, rounded to `dtype`
+ * (src/layers.py:71-74), and its backward grad_h12 (T, 2I) from grad_h (T, I).  I a multiple of 8. */
+int cinn_swiglu(const void* h12, void* h, int dtype, int64_t T, int64_t I, void* stream);
+int cinn_swiglu_backward(const void* h12, const void* grad_h, void* grad_h12, int dtype, int64_t T, int64_t I, void* stream);
+
 /* Dispatch gather of quantised tokens: out_q[r, :] = q[idx[r], :], out_scales[r, :] = scales[idx[r], :] for
  * r < n_out, in one pass (the `flat_x[token_indices]` of MoE.forward, src/layers.py:140, on tokens that were
  * quantised once before the gather).  q: (n_src, d) e4m3 bytes, d a multiple of 16; scales: (n_src, n_scales)

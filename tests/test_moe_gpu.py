@@ -70,6 +70,24 @@ def test_swiglu_quantiser_device_row_count(K):
     assert torch.all(q[77:] == 0x55) and torch.all(s[77:] == -1.0)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_swiglu_forward_backward(K, dtype):
+    """The training-path SwiGLU kernels against torch's fp32 arithmetic (src/layers.py:71-74) and its autograd."""
+    g = torch.Generator().manual_seed(31)
+    h12 = (torch.randn(3, 50, 2 * 136, generator=g) * 2).to(dtype).cuda().requires_grad_(True)
+    go = torch.randn(3, 50, 136, generator=g).to(dtype).cuda()
+    h = K.swiglu(h12)
+    h.backward(go)
+    ref_in = h12.detach().float().requires_grad_(True)
+    h1, h2 = ref_in.chunk(2, dim=-1)
+    ref = torch.nn.functional.silu(h1) * h2
+    ref.backward(go.float())
+    tol = 1e-5 if dtype == torch.float32 else 8e-3
+    assert h.dtype == dtype and h12.grad.dtype == dtype
+    torch.testing.assert_close(h.float(), ref, rtol=tol, atol=tol)
+    torch.testing.assert_close(h12.grad.float(), ref_in.grad, rtol=tol, atol=tol)
+
+
 def test_combine_kernel_matches_scatter_add(K):
     g = torch.Generator().manual_seed(8)
     T, k, d = 77, 4, 264
