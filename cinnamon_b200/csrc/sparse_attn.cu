@@ -228,6 +228,23 @@ sparse_attn_bwd_kernel(const TG* __restrict__ d_out, const float* __restrict__ o
         __syncwarp();
         // dq[d] = scale * sum_j dp_j k_j[d];  dk[idx_j][d] += scale * dp_j q[d]
         const bool pair_qk = (Dqk & 1) == 0, pair_v = (Dv & 1) == 0;     // even widths: 8-byte aligned float2 atomics
+        const bool quad_qk = (Dqk & 3) == 0, quad_v = (Dv & 3) == 0;     // multiples of 4: one 16-byte atomic per lane and key
+        if (quad_qk) {
+            for (int d0 = lane * 4; d0 < Dqk; d0 += 128) {
+                float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                const float4 qv = *reinterpret_cast<const float4*>(s_q + d0);
+                for (int j = 0; j < K; ++j) {
+                    const int i = s_idx[j];
+                    if (i < 0) continue;
+                    const float dp = s_p[j] * scale;
+                    const T* kr = kb + (int64_t)i * Dqk + d0;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) a[c] = fmaf(dp, to_float<T>(kr[c]), a[c]);
+                    atomicAdd(reinterpret_cast<float4*>(dkb + (int64_t)i * Dqk + d0), make_float4(dp * qv.x, dp * qv.y, dp * qv.z, dp * qv.w));
+                }
+                *reinterpret_cast<float4*>(dq + w * Dqk + d0) = make_float4(a[0], a[1], a[2], a[3]);
+            }
+        } else
         for (int d0 = lane * 2; d0 < Dqk; d0 += 64) {
             float a0 = 0.0f, a1 = 0.0f;
             const bool two = d0 + 1 < Dqk;
@@ -251,6 +268,17 @@ sparse_attn_bwd_kernel(const TG* __restrict__ d_out, const float* __restrict__ o
             if (two) dq[w * Dqk + d0 + 1] = a1;
         }
         // dv[idx_j][d] += p_j dO[d]
+        if (quad_v) {
+            for (int d0 = lane * 4; d0 < Dv; d0 += 128) {
+                const float4 gv = *reinterpret_cast<const float4*>(s_do + d0);
+                for (int j = 0; j < K; ++j) {
+                    const int i = s_idx[j];
+                    if (i < 0) continue;
+                    const float p = s_pp[j];
+                    atomicAdd(reinterpret_cast<float4*>(dvb + (int64_t)i * Dv + d0), make_float4(p * gv.x, p * gv.y, p * gv.z, p * gv.w));
+                }
+            }
+        } else
         for (int d0 = lane * 2; d0 < Dv; d0 += 64) {
             const bool two = d0 + 1 < Dv;
             const float g0 = s_do[d0], g1 = two ? s_do[d0 + 1] : 0.0f;
