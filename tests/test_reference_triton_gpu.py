@@ -1,0 +1,200 @@
+"""The reference's own Triton kernels, run on the GPU next to this library on identical inputs.
+
+The unmodified reference sources are staged by ``baseline/stage_reference.py`` under ``baseline/_ref`` (ignored by
+git).  The library is left in its DEFAULT division flavour (``full`` = the ``div.full.f32`` Triton emits for the
+reference's two fp32 divisions): e4m3 bytes and the bits of every fp32 scale must be identical to what
+``quantize_fp8_rowwise`` / ``quantize_fp8_blockwise`` of src/kernels.py:178-259 return.  The GEMMs are compared
+against the reference's ``fp8_matmul_dsv3`` (:667-702, TF32 tensor-core products there) and ``FP8MatmulFunction``
+(:731-794) through the float64 product of the same quantised operands.  The reference's own
+``tests/test_kernels.py`` is then run, unchanged, with the drop-in module bound to the name ``kernels``.
+
+Skips, with the reason, when the staged copy or Triton is missing on the machine."""
+import importlib.util
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from _util import bits_of, bytes_of
+from cases import CASES, gen_input
+from oracle import fp8_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+
+
+@pytest.fixture(scope="module")
+def R():
+    path = os.path.join(REF_DIR, "src", "kernels.py")
+    if not os.path.isfile(path):
+        pytest.skip("reference not staged (python baseline/stage_reference.py needs the reference tree)")
+    try:
+        import triton  # noqa: F401
+    except Exception as e:                                     # pragma: no cover
+        pytest.skip(f"triton is not importable here: {e}")
+    spec = importlib.util.spec_from_file_location("ref_kernels", path)
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["ref_kernels"] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+@pytest.fixture(scope="module")
+def K():
+    from cinnamon_b200 import kernels
+    assert kernels.get_div_mode() == "full", "this file tests the library's default flavour"
+    yield kernels
+    assert kernels.device_status() == 0
+
+
+def assert_same_quantisation(ours, ref, what):
+    (q, s), (qr, sr) = ours, ref
+    assert q.shape == qr.shape and s.shape == sr.shape and q.dtype == qr.dtype == torch.float8_e4m3fn, what
+    ns = int((bits_of(s) != bits_of(sr)).sum())
+    nq = int((bytes_of(q) != bytes_of(qr)).sum())
+    assert ns == 0 and nq == 0, f"{what}: {ns} of {s.numel()} scales and {nq} of {q.numel()} bytes differ from the Triton output"
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
+@pytest.mark.parametrize("rs", [False, True])
+def test_rowwise_equals_triton(K, R, case, rs):
+    name, seed, M, N, dtype, std, special = case
+    x = gen_input(seed, M, N, dtype, std, special).cuda()
+    assert_same_quantisation(K.quantize_fp8_rowwise(x, 128, rs), R.quantize_fp8_rowwise(x, 128, rs), name)
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
+@pytest.mark.parametrize("rs", [False, True])
+def test_blockwise_equals_triton(K, R, case, rs):
+    name, seed, M, N, dtype, std, special = case
+    x = gen_input(seed, M, N, dtype, std, special).cuda()
+    assert_same_quantisation(K.quantize_fp8_blockwise(x, 128, 128, rs), R.quantize_fp8_blockwise(x, 128, 128, rs), name)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_transposed_and_strided_views_equal_triton(K, R, dtype):
+    g = torch.Generator().manual_seed(77)
+    base = torch.randn(384, 512, generator=g).to(dtype).cuda()
+    for what, v in (("transposed", base.t()), ("pitched", base[:, :256]), ("offset", base[3:50, 5:300]),
+                    ("strided", base[:, ::2])):
+        assert_same_quantisation(K.quantize_fp8_rowwise(v, 128, True), R.quantize_fp8_rowwise(v, 128, True), what)
+        assert_same_quantisation(K.quantize_fp8_blockwise(v), R.quantize_fp8_blockwise(v), what)
+
+
+def test_every_bf16_amax_equals_triton(K, R):
+    """One tile per positive finite bf16 value as its amax: the scale is a pure function of it."""
+    bits = torch.arange(1, 0x7F80, dtype=torch.int32)
+    amax = bits.to(torch.int16).view(torch.bfloat16)
+    x = torch.zeros(amax.numel(), 128, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(5)
+    x[:] = (torch.rand(amax.numel(), 128, generator=g) * 2 - 1).bfloat16() * amax[:, None]
+    x[:, 7] = amax
+    x = x.cuda()
+    for rs in (False, True):
+        assert_same_quantisation(K.quantize_fp8_rowwise(x, 128, rs), R.quantize_fp8_rowwise(x, 128, rs), f"amax sweep rs={rs}")
+
+
+def test_ffn_activation_and_weight_equal_triton(K, R):
+    """x [16384, 7168] bf16 row-wise and W [18432, 7168] fp32 block-wise, the FFN-width operands, in full."""
+    g = torch.Generator(device="cuda").manual_seed(1002)
+    x = torch.randn(16384, 7168, generator=g, device="cuda").bfloat16()
+    for rs in (False, True):
+        assert_same_quantisation(K.quantize_fp8_rowwise(x, 128, rs), R.quantize_fp8_rowwise(x, 128, rs), f"x rs={rs}")
+    del x
+    w = torch.randn(18432, 7168, generator=g, device="cuda") * 0.02
+    assert_same_quantisation(K.quantize_fp8_blockwise(w), R.quantize_fp8_blockwise(w), "W")
+
+
+def test_fused_passes_equal_triton_sequences(K, R):
+    """The fused passes against the call sequences of FP8MatmulFunction they replace: dy row-wise + dy^T row-wise
+    (:771, :781-783) and the block re-quantisation of the saved activations (:784-787)."""
+    g = torch.Generator().manual_seed(41)
+    dy = torch.randn(640, 896, generator=g).bfloat16().cuda()
+    for rs in (False, True):
+        q_row, s_row, q_col, s_col = K.quantize_fp8_rowwise_dual(dy, rs)
+        assert_same_quantisation((q_row, s_row), R.quantize_fp8_rowwise(dy, 128, rs), "dual rows")
+        assert_same_quantisation((q_col, s_col), R.quantize_fp8_rowwise(dy.t().contiguous(), 128, rs), "dual columns")
+        xq, xs, xbq, xbs = K.quantize_fp8_rowwise_with_block(dy, rs)
+        rq, rs_ = R.quantize_fp8_rowwise(dy, 128, rs)
+        assert_same_quantisation((xq, xs), (rq, rs_), "row part")
+        ref_block = R.quantize_fp8_blockwise(R.dequantize_fp8_rowwise(rq, rs_, 128), 128, 128, False)
+        assert_same_quantisation((xbq, xbs), ref_block, "block part")
+        assert_same_quantisation(K.requantize_rowwise_to_blockwise(rq, rs_), ref_block, "re-quantiser")
+
+
+def test_gemm_against_triton_gemm(K, R):
+    """Same quantised operands into both GEMMs.  The reference multiplies de-quantised fp32 operands on the TF32
+    tensor path, this library multiplies the e4m3 values exactly and scales in fp32: against the float64 product
+    this library must be inside the 1e-3 bound and at least as close as the reference."""
+    x, w, _ = O.make_linear_case(512, 1024, 768, seed=9)
+    xq, xs = K.quantize_fp8_rowwise(x.cuda())
+    wq, ws = K.quantize_fp8_blockwise(w.float().cuda())
+    ref64 = O.fp8_matmul_f64(xq.view(torch.uint8).cpu(), wq.view(torch.uint8).cpu().t(), xs.cpu(), ws.cpu().t())
+    theirs = R.fp8_matmul_dsv3(xq, wq.t().contiguous(), xs, ws.t().contiguous())
+    ours = K.fp8_matmul_dsv3(xq, wq.t(), xs, ws.t())
+    ours32 = K.fp8_matmul_dsv3(xq, wq.t(), xs, ws.t(), out_dtype=torch.float32)
+    e_theirs, e_ours, e_ours32 = (O.rel_fro(t.float().cpu(), ref64) for t in (theirs, ours, ours32))
+    assert e_ours32 < 1e-3 and e_ours <= e_theirs * 1.05 + 1e-5, (e_ours32, e_ours, e_theirs)
+    assert O.rel_fro(ours.float().cpu(), theirs.float().cpu().double()) < 5e-3
+
+
+def test_autograd_function_against_triton(K, R):
+    """FP8MatmulFunction forward + backward, reference and drop-in, on the same inputs: outputs and both
+    gradients agree to the reference's own precision (TF32 products, bf16 results)."""
+    x, w, dy = O.make_linear_case(384, 512, 640, seed=123)
+    res = []
+    for mod in (R, K):
+        xg = x.cuda().requires_grad_(True)
+        wg = w.float().cuda().requires_grad_(True)
+        out = mod.FP8MatmulFunction.apply(xg, wg, True)
+        out.backward(dy.cuda())
+        res.append((out.detach().float().cpu(), xg.grad.float().cpu(), wg.grad.float().cpu()))
+    for name, a, b in zip(("out", "grad_x", "grad_w"), res[0], res[1]):
+        err = O.rel_fro(b, a.double())
+        assert err < 6e-3, (name, err)
+
+
+def test_grouped_gemm_against_triton(K, R):
+    """moe_grouped_gemm: the reference multiplies in fp16, the drop-in in e4m3 with block scales (documented
+    deviation); both against the float64 product of the unquantised operands."""
+    g = torch.Generator().manual_seed(12)
+    E, d, h = 8, 512, 256
+    counts = torch.tensor([40, 0, 77, 1, 130, 64, 9, 63])
+    T = int(counts.sum())
+    w = (torch.randn(E, h, d, generator=g) * 0.02).bfloat16()
+    x = torch.randn(T, d, generator=g).bfloat16()
+    ends = counts.cumsum(0)
+    starts = ends - counts
+    ref64 = torch.zeros(T, h, dtype=torch.float64)
+    for e in range(E):
+        s, t = int(starts[e]), int(ends[e])
+        ref64[s:t] = x[s:t].double() @ w[e].double().t()
+    theirs = R.moe_grouped_gemm(x.cuda(), w.cuda(), starts.cuda(), ends.cuda(), int(counts.max()))
+    ours = K.moe_grouped_gemm(x.cuda(), w.cuda(), starts.cuda(), ends.cuda(), int(counts.max()))
+    assert ours.shape == theirs.shape and ours.dtype == theirs.dtype == torch.float16
+    assert O.rel_fro(theirs.float().cpu(), ref64) < 2e-3
+    assert O.rel_fro(ours.float().cpu(), ref64) < 5e-2            # e4m3 rounding of both operands
+
+
+def test_reference_test_suite_runs_against_the_drop_in():
+    """tests/test_kernels.py of the reference (quantiser, indexer and grouped-GEMM classes, :29-155), unchanged,
+    with ``kernels`` bound to this library's drop-in module."""
+    test_file = os.path.join(REF_DIR, "tests", "test_kernels.py")
+    if not os.path.isfile(test_file):
+        pytest.skip("reference not staged")
+    code = (
+        "import sys; sys.path.insert(0, %r)\n"
+        "import cinnamon_b200.kernels as k\n"
+        "sys.modules['kernels'] = k\n"
+        "import pytest\n"
+        "sys.exit(pytest.main(['-q', '-x', '-p', 'no:cacheprovider', '--rootdir', %r, %r, "
+        "'-k', 'TestFP8Quantization or TestLightningIndexer or TestMoEGroupedGEMM and test_output_shape']))\n"
+    ) % (ROOT, REF_DIR, test_file)
+    p = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600, cwd=REF_DIR)
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-2000:]
+    assert " passed" in p.stdout and "skipped" not in p.stdout.splitlines()[-1], p.stdout[-500:]
