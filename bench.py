@@ -233,8 +233,19 @@ def bench_kernels(Kmod, dev, x, w, dy, peaks):
     flop = 2.0 * M * N * K
     gemm_line("gemm forward  16384x18432x7168 (B K-major, two-SM)", lambda: Kmod.fp8_matmul_dsv3(xq, wq.t(), xs, ws.t()), flop,
               M * K + N * K + 4 * (M * nkb + nnb * nkb) + 2 * M * N)
-    gemm_line("gemm dgrad    16384x7168x18432 (B MN-major)", lambda: Kmod.fp8_matmul_dsv3(dq, wq, ds, ws), flop)
-    gemm_line("gemm wgrad    18432x7168x16384 (B MN-major)", lambda: Kmod.fp8_matmul_dsv3(dtq, xbq, dts, xbs), flop)
+    wq_t = Kmod.transpose_fp8(wq)
+    _, _, xbq_t, _ = Kmod.quantize_fp8_rowwise_with_block(xd, transpose_block=True)
+    gemm_line("gemm dgrad    16384x7168x18432 (W^T copy, B K-major, two-SM)", lambda: Kmod.fp8_matmul_dsv3(dq, wq_t.t(), ds, ws), flop)
+    gemm_line("gemm wgrad    18432x7168x16384 (x block copy transposed, B K-major, two-SM, fp32 out)",
+              lambda: Kmod.fp8_matmul_dsv3(dtq, xbq_t.t(), dts, xbs, out_dtype=torch.float32), flop)
+    gemm_line("gemm dgrad    16384x7168x18432 (B MN-major, one-SM)", lambda: Kmod.fp8_matmul_dsv3(dq, wq, ds, ws), flop)
+    gemm_line("gemm wgrad    18432x7168x16384 (B MN-major, one-SM)", lambda: Kmod.fp8_matmul_dsv3(dtq, xbq, dts, xbs), flop)
+    quant_line("quant_block_vec W[18432,7168] fp32 + transposed copy, one pass", lambda: Kmod.quantize_fp8_blockwise_t(wd),
+               N * K * 6 + 4 * nnb * nkb)
+    quant_line("quant_row + transposed block re-quantisation x[16384,7168] bf16, one pass",
+               lambda: Kmod.quantize_fp8_rowwise_with_block(xd, transpose_block=True), M * K * 4 + 4 * M * nkb + 4 * (M // 128) * nkb)
+    quant_line("transpose_fp8 W e4m3 [18432,7168]", lambda: Kmod.transpose_fp8(wq), 2 * N * K)
+    del wq_t, xbq_t
     del dq, ds, dtq, dts, xbq, xbs, wq, ws
     # other configurations: (tokens, in, out)
     g = torch.Generator(device=dev).manual_seed(1003)

@@ -25,6 +25,9 @@ SIGNATURES = {
     "cinn_quant_rowwise_dual": [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _i32, _i32, _vp],
     "cinn_selfcheck_division": [_vp, _vp],
     "cinn_quant_rowwise_with_block": [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _i32, _i32, _vp],
+    "cinn_quant_rowwise_with_block_t": [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _i32, _i32, _vp],
+    "cinn_set_wait_limit_cycles": [ctypes.c_longlong],
+    "cinn_quant_blockwise_t": [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _i32, _i32, _vp],
     "cinn_quant_blockwise": [_vp, _i32, _i64, _i64, _i64, _i64, _vp, _vp, _i32, _i32, _i32, _i32, _vp],
     "cinn_requant_row_to_block": [_vp, _vp, _i64, _i64, _vp, _vp, _i32, _i32, _vp],
     "cinn_dequant": [_vp, _vp, _vp, _i32, _i64, _i64, _i32, _i32, _vp],
@@ -75,6 +78,7 @@ def _load() -> ctypes.CDLL:
         fn = getattr(lib, name)            # AttributeError if the symbol is not exported
         fn.argtypes = argtypes
         fn.restype = (ctypes.c_char_p if name == "cinn_last_error"
+                      else ctypes.c_longlong if name == "cinn_set_wait_limit_cycles"
                       else ctypes.c_int64 if name in ("cinn_moe_route_workspace_ints", "cinn_moe_route_static_max_ints",
                                                  "cinn_fp8_grouped_wgrad_scratch_bytes")
                       else ctypes.c_int)

@@ -73,12 +73,15 @@ int p2p_dispatch(const void* q, const float* s, const int64_t* token_indices, co
 int p2p_return(const void* rows, const int64_t* seg_start, const int64_t* home_base, const int64_t* peer_home, int64_t n_rows,
                int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity, cudaStream_t st);
 int p2p_barrier(const int64_t* peer_flags, int me, int n_ranks, unsigned epoch, cudaStream_t st);
+long long set_p2p_wait_limit(long long cycles);
 int64_t grouped_wgrad_scratch_bytes(int64_t max_rows, int64_t d_in, int64_t d_out);
 int fp8_grouped_wgrad(const void* dY, int dy_dtype, const void* x_q, const float* x_s, const int64_t* starts_host,
                       const int64_t* ends_host, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* scratch,
                       int64_t scratch_bytes, void* dW, int out_dtype, int div_mode, cudaStream_t st);
 int quantize_row_block(const void* x, int dtype, int64_t M, int64_t N, int64_t ld, void* q_row, float* s_row, void* q_blk,
-                       float* s_blk, int round_scale, int div_mode, cudaStream_t st);
+                       float* s_blk, int round_scale, int div_mode, cudaStream_t st, int transpose_block);
+int quantize_block_t(const void* x, int dtype, int64_t M, int64_t N, int64_t ld, void* q, void* q_t, float* scales,
+                     int round_scale, int div_mode, cudaStream_t st);
 int swiglu(const void* h12, const void* dh, void* out, int dtype, int64_t T_rows, int64_t I, int backward, cudaStream_t st);
 int64_t moe_route_workspace_ints(int64_t T, int E);
 int moe_route(const float* logits, const float* bias, int64_t T, int E, int top_k, int* workspace, int* top_experts,
@@ -111,6 +114,11 @@ int cinn_quant_blockwise(const void* x, int x_dtype, int64_t M, int64_t N, int64
                           (cudaStream_t)stream);
 }
 
+int cinn_quant_blockwise_t(const void* x, int x_dtype, int64_t M, int64_t N, int64_t ld, void* q, void* q_t, float* scales,
+                           int round_scale, int div_mode, void* stream) {
+    return cinn::quantize_block_t(x, x_dtype, M, N, ld, q, q_t, scales, round_scale, div_mode, (cudaStream_t)stream);
+}
+
 int cinn_quant_rowwise_dual(const void* x, int x_dtype, int64_t M, int64_t N, int64_t ld, void* q_row, float* s_row,
                             void* q_col, float* s_col, int round_scale, int div_mode, void* stream) {
     return cinn::quantize_dual(x, x_dtype, M, N, ld, q_row, s_row, q_col, s_col, round_scale, div_mode, (cudaStream_t)stream);
@@ -123,7 +131,13 @@ int cinn_selfcheck_division(unsigned long long* mismatches, void* stream) {
 int cinn_quant_rowwise_with_block(const void* x, int x_dtype, int64_t M, int64_t N, int64_t ld, void* q_row, float* s_row,
                                   void* q_block, float* s_block, int round_scale, int div_mode, void* stream) {
     return cinn::quantize_row_block(x, x_dtype, M, N, ld, q_row, s_row, q_block, s_block, round_scale, div_mode,
-                                    (cudaStream_t)stream);
+                                    (cudaStream_t)stream, 0);
+}
+
+int cinn_quant_rowwise_with_block_t(const void* x, int x_dtype, int64_t M, int64_t N, int64_t ld, void* q_row, float* s_row,
+                                    void* q_block_t, float* s_block, int round_scale, int div_mode, void* stream) {
+    return cinn::quantize_row_block(x, x_dtype, M, N, ld, q_row, s_row, q_block_t, s_block, round_scale, div_mode,
+                                    (cudaStream_t)stream, 1);
 }
 
 int cinn_requant_row_to_block(const void* xq, const float* xs, int64_t M, int64_t K, void* out, float* scales,
@@ -261,6 +275,8 @@ int cinn_swiglu_backward(const void* h12, const void* grad_h, void* grad_h12, in
 int cinn_p2p_barrier(const int64_t* peer_flags, int rank, int n_ranks, unsigned epoch, void* stream) {
     return cinn::p2p_barrier(peer_flags, rank, n_ranks, epoch, (cudaStream_t)stream);
 }
+
+long long cinn_set_wait_limit_cycles(long long cycles) { return cinn::set_p2p_wait_limit(cycles); }
 
 int64_t cinn_moe_route_workspace_ints(int64_t n_tokens, int n_experts) {
     return cinn::moe_route_workspace_ints(n_tokens, n_experts);

@@ -81,7 +81,7 @@ __device__ __forceinline__ int pair_total(const GemmParams& p) {
 }
 __device__ __forceinline__ PairTile pair_tile(const GemmParams& p, int t) {
     const int m_tiles = (p.M + PM - 1) / PM, n_tiles = (p.N + PN - 1) / PN;
-    constexpr int GROUP = 8;                       // 8 x 256 rows per L2 group
+    constexpr int GROUP = 16;                      // 16 x 256 rows per L2 group
     const int per_group = GROUP * n_tiles;
     const int g = t / per_group;
     const int first_m = g * GROUP;

@@ -6,6 +6,7 @@
 // positions of a token given in ascending order the fp32 sum has the order of the reference's
 // scatter-add over the sorted pairs.
 #include "common.cuh"
+#include <atomic>
 
 namespace cinn {
 
@@ -337,10 +338,12 @@ p2p_return_kernel(const uint4* __restrict__ rows, const int64_t* __restrict__ se
 // have completed, so their peer stores are ordered before the flag.  The wait is bounded (about two seconds):
 // when it runs out the kernel records a code in the status word and returns.  Each rank must own its GPU: ranks
 // that share one could wait for a kernel that cannot run beside them.
-constexpr long long P2P_WAIT_LIMIT_CYCLES = 4000000000LL;
+// The limit is a launch argument (cinn_set_wait_limit_cycles), so a test can make the wait run out in a millisecond.
+static std::atomic<long long> g_p2p_wait_limit{4000000000LL};
+long long set_p2p_wait_limit(long long cycles) { return g_p2p_wait_limit.exchange(cycles > 0 ? cycles : 4000000000LL); }
 
 __global__ void __launch_bounds__(64)
-p2p_barrier_kernel(const int64_t* __restrict__ peer_flags, int me, int n_ranks, unsigned epoch) {
+p2p_barrier_kernel(const int64_t* __restrict__ peer_flags, int me, int n_ranks, unsigned epoch, long long wait_limit) {
     const int g = threadIdx.x;
     if (g >= n_ranks) return;
     __threadfence_system();
@@ -352,7 +355,7 @@ p2p_barrier_kernel(const int64_t* __restrict__ peer_flags, int me, int n_ranks, 
         unsigned seen;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
         if ((int)(seen - epoch) >= 0) break;
-        if ((spin & 63u) == 0 && clock64() - t0 > P2P_WAIT_LIMIT_CYCLES) {
+        if ((spin & 63u) == 0 && clock64() - t0 > wait_limit) {
             atomicCAS(&g_moe_status, 0, (5 << 8) | 3);
             break;
         }
@@ -362,7 +365,7 @@ p2p_barrier_kernel(const int64_t* __restrict__ peer_flags, int me, int n_ranks, 
 int p2p_barrier(const int64_t* peer_flags, int me, int n_ranks, unsigned epoch, cudaStream_t st) {
     CINN_CHECK_ARG(peer_flags != nullptr && n_ranks >= 1 && n_ranks <= 64 && me >= 0 && me < n_ranks,
                    "p2p_barrier: 1 <= ranks <= 64 and 0 <= rank < ranks (got %d, %d)", n_ranks, me);
-    p2p_barrier_kernel<<<1, 64, 0, st>>>(peer_flags, me, n_ranks, epoch);
+    p2p_barrier_kernel<<<1, 64, 0, st>>>(peer_flags, me, n_ranks, epoch, g_p2p_wait_limit.load(std::memory_order_relaxed));
     CINN_CHECK_LAUNCH();
     return CINN_OK;
 }

@@ -404,8 +404,11 @@ __device__ __forceinline__ bool dual_tile(float (&v)[8][8], float (*s_amax)[128]
 // written; the thread then decodes its own bytes, multiplies by the row scale (exactly what
 // dequantize_fp8_rowwise yields), and the block's amax is one shuffle tree + shared memory.  Bit-identical to
 // quantize_fp8_rowwise followed by the row-to-block re-quantiser, with x read once and its e4m3 copy never re-read.
-template <int DIV, bool ROUND, typename AfterSync>
-__device__ __forceinline__ bool row_block_tile(float (&v)[8][8], float* s_red, bool ok, uint8_t* __restrict__ q_row,
+// TRANS: the block-scaled bytes are written transposed, (N, M) with M contiguous (M a multiple of 16): the layout in
+// which the weight-gradient GEMM reads them K-major.  They leave through the staging tile of dual_tile.
+template <int DIV, bool ROUND, bool TRANS, typename AfterSync>
+__device__ __forceinline__ bool row_block_tile(float (&v)[8][8], float* s_red, uint8_t* s_out, bool ok,
+                                               uint8_t* __restrict__ q_row,
                                                float* __restrict__ s_row, uint8_t* __restrict__ q_blk,
                                                float* __restrict__ s_blk, int M, int N, int nb_n, int bm, int bn,
                                                AfterSync&& after_sync) {
@@ -456,23 +459,51 @@ __device__ __forceinline__ bool row_block_tile(float (&v)[8][8], float* s_red, b
     const float sb = scale_from_amax<DIV, false>(bmax);
     const float db = divisor_of<DIV>(sb);
     if (threadIdx.x == 0) s_blk[(int64_t)bm * nb_n + bn] = sb;
+    if constexpr (!TRANS) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        if (mt + i < M && n < N) {
-            uint2 o2;
-            o2.x = cvt_e4m3x4(scaled_clamped<DIV>(v[i][0], db), scaled_clamped<DIV>(v[i][1], db),
-                              scaled_clamped<DIV>(v[i][2], db), scaled_clamped<DIV>(v[i][3], db));
-            o2.y = cvt_e4m3x4(scaled_clamped<DIV>(v[i][4], db), scaled_clamped<DIV>(v[i][5], db),
-                              scaled_clamped<DIV>(v[i][6], db), scaled_clamped<DIV>(v[i][7], db));
-            __stcs(reinterpret_cast<uint2*>(q_blk + (int64_t)(mt + i) * N + n), o2);
+        for (int i = 0; i < 8; ++i) {
+            if (mt + i < M && n < N) {
+                uint2 o2;
+                o2.x = cvt_e4m3x4(scaled_clamped<DIV>(v[i][0], db), scaled_clamped<DIV>(v[i][1], db),
+                                  scaled_clamped<DIV>(v[i][2], db), scaled_clamped<DIV>(v[i][3], db));
+                o2.y = cvt_e4m3x4(scaled_clamped<DIV>(v[i][4], db), scaled_clamped<DIV>(v[i][5], db),
+                                  scaled_clamped<DIV>(v[i][6], db), scaled_clamped<DIV>(v[i][7], db));
+                __stcs(reinterpret_cast<uint2*>(q_blk + (int64_t)(mt + i) * N + n), o2);
+            }
         }
+        __syncthreads();                      // s_red is free for the next piece
+    } else {
+        // eight rows of one column per 8-byte store into the staging tile (elements outside the matrix are zeros)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            uint2 o2;
+            o2.x = cvt_e4m3x4(scaled_clamped<DIV>(v[0][j], db), scaled_clamped<DIV>(v[1][j], db),
+                              scaled_clamped<DIV>(v[2][j], db), scaled_clamped<DIV>(v[3][j], db));
+            o2.y = cvt_e4m3x4(scaled_clamped<DIV>(v[4][j], db), scaled_clamped<DIV>(v[5][j], db),
+                              scaled_clamped<DIV>(v[6][j], db), scaled_clamped<DIV>(v[7][j], db));
+            const int nl = sub * 8 + j;
+            *reinterpret_cast<uint2*>(&s_out[nl * 128 + ((((hw >> 1) ^ sub) & 7) << 4) + ((hw & 1) << 3)]) = o2;
+        }
+        __syncthreads();
+        const int m0 = bm * 128, n0 = bn * 128;
+#pragma unroll
+        for (int rep = 0; rep < 4; ++rep) {
+            const int idx = threadIdx.x + rep * 256;
+            const int nl = idx >> 3, ch = idx & 7;
+            const int nn = n0 + nl, mm = m0 + ch * 16;
+            if (nn < N && mm < M) {
+                const uint4 val = *reinterpret_cast<const uint4*>(&s_out[nl * 128 + (((ch ^ (nl >> 3)) & 7) << 4)]);
+                __stcs(reinterpret_cast<uint4*>(q_blk + (int64_t)nn * M + mm), val);
+            }
+        }
+        // the staging tile and s_red are next written after the next piece's block-wide barrier
     }
-    __syncthreads();                      // s_red is free for the next piece
     return true;
 }
 
 // One CTA per piece, loads straight into registers (4-byte inputs, and rows whose pitch a tensor map cannot take).
-// MODE 0: q_col / s_col are the quantisation along the rows of the transpose; MODE 1: the 128x128 block re-quantisation.
+// MODE 0: q_col / s_col are the quantisation along the rows of the transpose; MODE 1: the 128x128 block re-quantisation;
+// MODE 2: the same with its bytes written transposed.
 template <typename T, int DIV, bool ROUND, int MODE = 0>
 __global__ void __launch_bounds__(256, 2)
 quant_row_dual_kernel(const T* __restrict__ x, int64_t ld, uint8_t* __restrict__ q_row, float* __restrict__ s_row,
@@ -493,8 +524,8 @@ quant_row_dual_kernel(const T* __restrict__ x, int64_t ld, uint8_t* __restrict__
         dual_tile<DIV, ROUND>(v, s_amax, s_out, true, q_row, s_row, q_col, s_col, M, N, nb_n, nb_m, (int)blockIdx.y,
                               (int)blockIdx.x, [] {});
     else
-        row_block_tile<DIV, ROUND>(v, &s_amax[0][0], true, q_row, s_row, q_col, s_col, M, N, nb_n, (int)blockIdx.y,
-                                   (int)blockIdx.x, [] {});
+        row_block_tile<DIV, ROUND, MODE == 2>(v, &s_amax[0][0], s_out, true, q_row, s_row, q_col, s_col, M, N, nb_n,
+                                              (int)blockIdx.y, (int)blockIdx.x, [] {});
 }
 
 // Persistent CTAs fed by TMA (2-byte inputs): the 128 x 128 pieces arrive in a ring of shared-memory stages
@@ -579,8 +610,8 @@ quant_row_dual_tma_kernel(const __grid_constant__ CUtensorMap tmX, uint8_t* __re
             alive = dual_tile<DIV, ROUND>(v, s_amax, s_out, ok, q_row, s_row, q_col, s_col, M, N, nb_n, nb_m, bm, bn,
                                           [&] { if (threadIdx.x == 0 && tn < total) issue(tn, s); });
         else
-            alive = row_block_tile<DIV, ROUND>(v, &s_amax[0][0], ok, q_row, s_row, q_col, s_col, M, N, nb_n, bm, bn,
-                                               [&] { if (threadIdx.x == 0 && tn < total) issue(tn, s); });
+            alive = row_block_tile<DIV, ROUND, MODE == 2>(v, &s_amax[0][0], s_out, ok, q_row, s_row, q_col, s_col, M, N, nb_n,
+                                                          bm, bn, [&] { if (threadIdx.x == 0 && tn < total) issue(tn, s); });
         if (!alive) break;
     }
     if (!alive && threadIdx.x == 0) {
@@ -636,6 +667,89 @@ quant_block_vec_kernel(const T* __restrict__ x, int64_t ld, uint8_t* __restrict_
             *reinterpret_cast<uint32_t*>(q + (int64_t)r * N + c) = o;
         }
     }
+}
+
+// 4 x 4 byte transpose in registers: r[i] holds bytes (row i, columns 0..3); c[j] receives (rows 0..3, column j).
+__device__ __forceinline__ void transpose4x4_bytes(const uint32_t (&r)[4], uint32_t (&c)[4]) {
+    const uint32_t t0 = __byte_perm(r[0], r[1], 0x5140), t1 = __byte_perm(r[2], r[3], 0x5140);
+    const uint32_t t2 = __byte_perm(r[0], r[1], 0x7362), t3 = __byte_perm(r[2], r[3], 0x7362);
+    c[0] = __byte_perm(t0, t1, 0x5410);
+    c[1] = __byte_perm(t0, t1, 0x7632);
+    c[2] = __byte_perm(t2, t3, 0x5410);
+    c[3] = __byte_perm(t2, t3, 0x7632);
+}
+
+// A 128 x 128 byte tile written transposed.  `blk[a]` (a < 4) holds this thread's 4 x 4 block of rows
+// 16 * warp + 4 * a .. + 3 and columns 4 * lane .. + 3, already transposed (word j = four rows of column 4 * lane + j).
+// Staging: 128 transposed rows of 32 words; word position XOR-ed with (transposed row / 4) so that both the stores
+// (lanes = columns) and the loads (lanes = words of one row) touch 32 different banks.  Output rows of pitch
+// `pitch` bytes (a multiple of 4), 4 bytes per lane, 128 contiguous bytes per warp store.
+__device__ __forceinline__ void store_tile_transposed(const uint32_t (&blk)[4][4], uint32_t* s_t, uint8_t* __restrict__ out,
+                                                      int64_t pitch, int r0, int c0, int R, int C) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s_t[(lane * 4 + j) * 32 + ((warp * 4 + a) ^ lane)] = blk[a][j];
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+        const int n = warp * 16 + k;                       // transposed row = input column
+        const uint32_t w = s_t[n * 32 + (lane ^ (n >> 2))];
+        if (c0 + n < C && r0 + lane * 4 < R) *reinterpret_cast<uint32_t*>(out + (int64_t)(c0 + n) * pitch + r0 + lane * 4) = w;
+    }
+}
+
+// The block-wise quantiser with a second, byte-transposed copy of its output: q (M, N) and q_t (N, M), one set of
+// scales (a 128 x 128 block and its transpose share their scale).  The transposed copy is the weight as the input
+// gradient's GEMM wants it: reduction axis innermost.  Rows are dealt to warps in runs of 16 here, so that a thread
+// holds 4 x 4 byte blocks it can transpose in registers.  M must be a multiple of 4.
+template <typename T, int DIV, bool ROUND>
+__global__ void __launch_bounds__(256)
+quant_block_vec_t_kernel(const T* __restrict__ x, int64_t ld, uint8_t* __restrict__ q, uint8_t* __restrict__ q_t,
+                         float* __restrict__ scales, int M, int N, int nb) {
+    __shared__ float s_red[8];
+    __shared__ uint32_t s_t[128 * 32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r0 = blockIdx.y * 128, c = blockIdx.x * 128 + lane * 4;
+    float v[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int r = r0 + warp * 16 + i;
+        if (r < M && c < N) {
+            Elem<T>::load4(x + (int64_t)r * ld + c, v[i]);
+        } else {
+            v[i][0] = v[i][1] = v[i][2] = v[i][3] = 0.0f;
+        }
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) amax = fmaxf(amax, fabsf(v[i][j]));
+    amax = warp_max(amax);
+    if (lane == 0) s_red[warp] = amax;
+    __syncthreads();
+    amax = s_red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) amax = fmaxf(amax, s_red[w]);
+    const float s = scale_from_amax<DIV, ROUND>(amax);
+    const float d = divisor_of<DIV>(s);
+    if (threadIdx.x == 0) scales[(int64_t)blockIdx.y * nb + blockIdx.x] = s;
+    uint32_t blk[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        uint32_t rows[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = r0 + warp * 16 + a * 4 + i;
+            rows[i] = cvt_e4m3x4(scaled_clamped<DIV>(v[a * 4 + i][0], d), scaled_clamped<DIV>(v[a * 4 + i][1], d),
+                                 scaled_clamped<DIV>(v[a * 4 + i][2], d), scaled_clamped<DIV>(v[a * 4 + i][3], d));
+            if (r < M && c < N) *reinterpret_cast<uint32_t*>(q + (int64_t)r * N + c) = rows[i];
+        }
+        transpose4x4_bytes(rows, blk[a]);
+    }
+    store_tile_transposed(blk, s_t, q_t, M, r0, blockIdx.x * 128, M, N);
 }
 
 // Block-wise, arbitrary strides / block sizes: one CTA per block, two passes.
@@ -864,7 +978,7 @@ dequant_kernel(const uint8_t* __restrict__ q, const float* __restrict__ scales, 
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 transpose_bytes_kernel(const uint8_t* __restrict__ in, int64_t ld_in, uint8_t* __restrict__ out, int R, int C) {
-    // in: R x C (row pitch ld_in) -> out: C x R contiguous; 64 x 64 tiles
+    // in: R x C (row pitch ld_in) -> out: C x R contiguous; 64 x 64 tiles, byte by byte (any alignment)
     __shared__ uint8_t t[64][64 + 4];
     const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
     for (int i = threadIdx.x; i < 64 * 64; i += 256) {
@@ -876,6 +990,27 @@ transpose_bytes_kernel(const uint8_t* __restrict__ in, int64_t ld_in, uint8_t* _
         const int c = i >> 6, r = i & 63;
         if (r0 + r < R && c0 + c < C) out[(int64_t)(c0 + c) * R + r0 + r] = t[r][c];
     }
+}
+
+// The same for 4-byte aligned shapes (R, C, ld_in multiples of 4, 4-byte aligned pointers): 128 x 128 tiles,
+// 4-byte loads (128 contiguous bytes per warp), 4 x 4 blocks transposed in registers, 4-byte stores.
+__global__ void __launch_bounds__(256)
+transpose_bytes_vec_kernel(const uint8_t* __restrict__ in, int64_t ld_in, uint8_t* __restrict__ out, int R, int C) {
+    __shared__ uint32_t s_t[128 * 32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r0 = blockIdx.y * 128, c0 = blockIdx.x * 128;
+    uint32_t blk[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        uint32_t rows[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = r0 + warp * 16 + a * 4 + i;
+            rows[i] = (r < R && c0 + lane * 4 < C) ? __ldg(reinterpret_cast<const uint32_t*>(in + (int64_t)r * ld_in + c0 + lane * 4)) : 0u;
+        }
+        transpose4x4_bytes(rows, blk[a]);
+    }
+    store_tile_transposed(blk, s_t, out, R, r0, c0, R, C);
 }
 
 // ---------------------------------------------------------------------------
@@ -932,6 +1067,39 @@ static int launch_blockwise(const T* x, int64_t M, int64_t N, int64_t ld_m, int6
     }
     CINN_CHECK_LAUNCH();
     return CINN_OK;
+}
+
+template <typename T>
+static int dispatch_block_t(const T* x, int64_t M, int64_t N, int64_t ld, uint8_t* q, uint8_t* q_t, float* scales,
+                            int round_scale, int div_mode, cudaStream_t st) {
+    const int mb = (int)((M + 127) / 128), nb = (int)((N + 127) / 128);
+    CINN_CHECK_ARG(mb <= 65535, "block-wise quantiser: more than 65535 row blocks (%d)", mb);
+    dim3 grid((unsigned)nb, (unsigned)mb);
+#define CINN_B(DIV, RND) quant_block_vec_t_kernel<T, DIV, RND><<<grid, 256, 0, st>>>(x, ld, q, q_t, scales, (int)M, (int)N, nb)
+    if (div_mode == CINN_DIV_FULL) { if (round_scale) CINN_B(CINN_DIV_FULL, true); else CINN_B(CINN_DIV_FULL, false); }
+    else                           { if (round_scale) CINN_B(CINN_DIV_RN, true);   else CINN_B(CINN_DIV_RN, false); }
+#undef CINN_B
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+int quantize_block_t(const void* x, int dtype, int64_t M, int64_t N, int64_t ld, void* q, void* q_t, float* scales,
+                     int round_scale, int div_mode, cudaStream_t st) {
+    CINN_CHECK_ARG(M >= 0 && N >= 0, "block quantiser (+ transposed copy): negative shape");
+    if (M == 0 || N == 0) return CINN_OK;
+    CINN_CHECK_ARG(x && q && q_t && scales, "block quantiser (+ transposed copy): null pointer");
+    CINN_CHECK_ARG(N < (1LL << 31) && M < (1LL << 31), "block quantiser (+ transposed copy): dimension too large");
+    CINN_CHECK_ARG(M % 4 == 0 && N % 4 == 0 && ld % 4 == 0 && ld >= N,
+                   "block quantiser (+ transposed copy): M (%lld), N (%lld) and the row pitch (%lld) must be multiples of 4",
+                   (long long)M, (long long)N, (long long)ld);
+    CINN_CHECK_ARG(aligned16(x) && aligned16(q) && aligned16(q_t), "block quantiser (+ transposed copy): pointers must be 16-byte aligned");
+    CINN_CHECK_ARG(div_mode == CINN_DIV_FULL || div_mode == CINN_DIV_RN, "block quantiser (+ transposed copy): unknown div_mode %d", div_mode);
+    switch (dtype) {
+        case CINN_BF16: return dispatch_block_t((const __nv_bfloat16*)x, M, N, ld, (uint8_t*)q, (uint8_t*)q_t, scales, round_scale, div_mode, st);
+        case CINN_F16:  return dispatch_block_t((const __half*)x, M, N, ld, (uint8_t*)q, (uint8_t*)q_t, scales, round_scale, div_mode, st);
+        case CINN_F32:  return dispatch_block_t((const float*)x, M, N, ld, (uint8_t*)q, (uint8_t*)q_t, scales, round_scale, div_mode, st);
+        default: set_error("block quantiser (+ transposed copy): unknown dtype tag %d", dtype); return CINN_ERR_INVALID;
+    }
 }
 
 template <typename T>
@@ -1014,13 +1182,13 @@ int requant_row_to_block(const void* xq, const float* xs, int64_t M, int64_t K, 
 // Row-wise 1x128 quantisation plus the 128x128 re-quantisation of its result, one pass over x.
 template <typename T>
 static int dispatch_row_block(const T* x, int64_t M, int64_t N, int64_t ld, uint8_t* q_row, float* s_row, uint8_t* q_blk,
-                              float* s_blk, int round_scale, int div_mode, cudaStream_t st) {
+                              float* s_blk, int round_scale, int div_mode, cudaStream_t st, int transpose_block = 0) {
     const int nb_n = (int)((N + 127) / 128), nb_m = (int)((M + 127) / 128);
     const bool fused = N % 16 == 0 && ld % 8 == 0 && nb_m <= 65535 && aligned16(x) && aligned16(q_row) && aligned16(q_blk);
     if (!fused) {
         int rc = dispatch_quant(false, x, M, N, ld, (int64_t)1, q_row, s_row, 1, 128, round_scale, div_mode, st);
         if (rc) return rc;
-        return requant_row_to_block(q_row, s_row, M, N, q_blk, s_blk, 0, div_mode, st);
+        return requant_row_to_block(q_row, s_row, M, N, q_blk, s_blk, transpose_block, div_mode, st);
     }
     if constexpr (sizeof(T) == 2) {
         CUtensorMap tm;
@@ -1032,11 +1200,13 @@ static int dispatch_row_block(const T* x, int64_t M, int64_t N, int64_t ld, uint
         const int grid = (int)(total < 2 * (int64_t)sm_count() ? total : 2 * (int64_t)sm_count());
 #define CINN_D(DIV, RND)                                                                                              \
     do {                                                                                                              \
-        auto kern = quant_row_dual_tma_kernel<T, DIV, RND, 1>;                                                        \
+        auto kern = transpose_block ? quant_row_dual_tma_kernel<T, DIV, RND, 2> : quant_row_dual_tma_kernel<T, DIV, RND, 1>; \
         static std::once_flag once;                                                                                   \
         static cudaError_t attr_err = cudaSuccess;                                                                    \
         std::call_once(once, [&] {                                                                                    \
-            attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);      \
+            attr_err = cudaFuncSetAttribute(quant_row_dual_tma_kernel<T, DIV, RND, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES); \
+            if (attr_err == cudaSuccess)                                                                              \
+                attr_err = cudaFuncSetAttribute(quant_row_dual_tma_kernel<T, DIV, RND, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES); \
         });                                                                                                           \
         CINN_CHECK_CUDA(attr_err);                                                                                    \
         kern<<<grid, 256, DUAL_SMEM_BYTES, st>>>(tm, q_row, s_row, q_blk, s_blk, (int)M, (int)N, nb_n, nb_m, (int)total); \
@@ -1046,7 +1216,11 @@ static int dispatch_row_block(const T* x, int64_t M, int64_t N, int64_t ld, uint
 #undef CINN_D
     } else {
         dim3 grid((unsigned)nb_n, (unsigned)nb_m);
-#define CINN_D(DIV, RND) quant_row_dual_kernel<T, DIV, RND, 1><<<grid, 256, 0, st>>>(x, ld, q_row, s_row, q_blk, s_blk, (int)M, (int)N, nb_n, nb_m)
+#define CINN_D(DIV, RND)                                                                                              \
+    do {                                                                                                              \
+        if (transpose_block) quant_row_dual_kernel<T, DIV, RND, 2><<<grid, 256, 0, st>>>(x, ld, q_row, s_row, q_blk, s_blk, (int)M, (int)N, nb_n, nb_m); \
+        else quant_row_dual_kernel<T, DIV, RND, 1><<<grid, 256, 0, st>>>(x, ld, q_row, s_row, q_blk, s_blk, (int)M, (int)N, nb_n, nb_m); \
+    } while (0)
         if (div_mode == CINN_DIV_FULL) { if (round_scale) CINN_D(CINN_DIV_FULL, true); else CINN_D(CINN_DIV_FULL, false); }
         else                           { if (round_scale) CINN_D(CINN_DIV_RN, true);   else CINN_D(CINN_DIV_RN, false); }
 #undef CINN_D
@@ -1056,7 +1230,9 @@ static int dispatch_row_block(const T* x, int64_t M, int64_t N, int64_t ld, uint
 }
 
 int quantize_row_block(const void* x, int dtype, int64_t M, int64_t N, int64_t ld, void* q_row, float* s_row, void* q_blk,
-                       float* s_blk, int round_scale, int div_mode, cudaStream_t st) {
+                       float* s_blk, int round_scale, int div_mode, cudaStream_t st, int transpose_block) {
+    CINN_CHECK_ARG(!transpose_block || M % 16 == 0,
+                   "row + block quantiser: a transposed block copy needs a row count (%lld) that is a multiple of 16", (long long)M);
     CINN_CHECK_ARG(M >= 0 && N >= 0, "row + block quantiser: negative shape (%lld, %lld)", (long long)M, (long long)N);
     if (M == 0 || N == 0) return CINN_OK;
     CINN_CHECK_ARG(x && q_row && s_row && q_blk && s_blk, "row + block quantiser: null pointer");
@@ -1065,9 +1241,9 @@ int quantize_row_block(const void* x, int dtype, int64_t M, int64_t N, int64_t l
     CINN_CHECK_ARG(N % 16 == 0, "row + block quantiser: the row length (%lld) must be a multiple of 16", (long long)N);
     CINN_CHECK_ARG(div_mode == CINN_DIV_FULL || div_mode == CINN_DIV_RN, "row + block quantiser: unknown div_mode %d", div_mode);
     switch (dtype) {
-        case CINN_BF16: return dispatch_row_block((const __nv_bfloat16*)x, M, N, ld, (uint8_t*)q_row, s_row, (uint8_t*)q_blk, s_blk, round_scale, div_mode, st);
-        case CINN_F16:  return dispatch_row_block((const __half*)x, M, N, ld, (uint8_t*)q_row, s_row, (uint8_t*)q_blk, s_blk, round_scale, div_mode, st);
-        case CINN_F32:  return dispatch_row_block((const float*)x, M, N, ld, (uint8_t*)q_row, s_row, (uint8_t*)q_blk, s_blk, round_scale, div_mode, st);
+        case CINN_BF16: return dispatch_row_block((const __nv_bfloat16*)x, M, N, ld, (uint8_t*)q_row, s_row, (uint8_t*)q_blk, s_blk, round_scale, div_mode, st, transpose_block);
+        case CINN_F16:  return dispatch_row_block((const __half*)x, M, N, ld, (uint8_t*)q_row, s_row, (uint8_t*)q_blk, s_blk, round_scale, div_mode, st, transpose_block);
+        case CINN_F32:  return dispatch_row_block((const float*)x, M, N, ld, (uint8_t*)q_row, s_row, (uint8_t*)q_blk, s_blk, round_scale, div_mode, st, transpose_block);
         default: set_error("row + block quantiser: unknown dtype tag %d", dtype); return CINN_ERR_INVALID;
     }
 }
@@ -1277,8 +1453,15 @@ int transpose_bytes(const void* in, int64_t ld_in, void* out, int64_t R, int64_t
     if (R == 0 || C == 0) return CINN_OK;
     CINN_CHECK_ARG(in && out, "transpose: null pointer");
     CINN_CHECK_ARG(R < (1LL << 31) && C < (1LL << 31) && (R + 63) / 64 <= 65535, "transpose: shape too large");
-    dim3 grid((unsigned)((C + 63) / 64), (unsigned)((R + 63) / 64));
-    transpose_bytes_kernel<<<grid, 256, 0, st>>>((const uint8_t*)in, ld_in, (uint8_t*)out, (int)R, (int)C);
+    const bool vec = R % 4 == 0 && C % 4 == 0 && ld_in % 4 == 0 && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 3) == 0 &&
+                     (R + 127) / 128 <= 65535;
+    if (vec) {
+        dim3 grid((unsigned)((C + 127) / 128), (unsigned)((R + 127) / 128));
+        transpose_bytes_vec_kernel<<<grid, 256, 0, st>>>((const uint8_t*)in, ld_in, (uint8_t*)out, (int)R, (int)C);
+    } else {
+        dim3 grid((unsigned)((C + 63) / 64), (unsigned)((R + 63) / 64));
+        transpose_bytes_kernel<<<grid, 256, 0, st>>>((const uint8_t*)in, ld_in, (uint8_t*)out, (int)R, (int)C);
+    }
     CINN_CHECK_LAUNCH();
     return CINN_OK;
 }

@@ -35,6 +35,11 @@ FP8_E4M3_MAX = 448.0
 _DTYPE_TAG = {torch.bfloat16: _lib.BF16, torch.float32: _lib.F32, torch.float16: _lib.F16}
 _DIV_MODE = {"full": _lib.DIV_FULL, "rn": _lib.DIV_RN}[os.environ.get("CINN_DIV_MODE", "full")]
 
+# FP8MatmulFunction hands the dgrad / wgrad GEMMs operands with the reduction axis innermost (a transposed copy of
+# the quantised weight and of the block-quantised activations, both written by the quantiser passes themselves).
+# CINN_KMAJOR_BACKWARD=0 keeps the stored layouts and lets the GEMM read them (reduction, output).
+_KMAJOR_BACKWARD = os.environ.get("CINN_KMAJOR_BACKWARD", "1") != "0"
+
 # number of kernels of this library launched since import (the benchmark reports it)
 launch_count = 0
 # when set to a list, every GEMM launch appends a (start, end) pair of CUDA events to it
@@ -140,11 +145,13 @@ def quantize_fp8_rowwise_dual(x: torch.Tensor, round_scale: bool = False):
     return q_row, s_row, q_col, s_col
 
 
-def quantize_fp8_rowwise_with_block(x: torch.Tensor, round_scale: bool = False):
+def quantize_fp8_rowwise_with_block(x: torch.Tensor, round_scale: bool = False, transpose_block: bool = False):
     """``quantize_fp8_rowwise(x)`` together with ``quantize_fp8_blockwise(dequantize_fp8_rowwise(q, s))`` of its result
     (what ``FP8MatmulFunction`` computes in its forward, reference src/kernels.py:746, and on the saved activations in
     its backward, :784-787) from one pass over ``x``.  Returns ``(q_row, s_row, q_block, s_block)``; bit-identical to
-    the separate calls.  The row length must be a multiple of 16."""
+    the separate calls.  The row length must be a multiple of 16.  ``transpose_block``: ``q_block`` comes out as
+    (N, M) - the bytes of the block copy transposed, tokens contiguous (M a multiple of 16) - which is how the
+    weight-gradient GEMM reads it K-major."""
     assert x.is_cuda, "Input must be on CUDA"
     assert x.ndim == 2, "Input must be 2D for now"
     x = _as_quant_input(x)
@@ -155,10 +162,11 @@ def quantize_fp8_rowwise_with_block(x: torch.Tensor, round_scale: bool = False):
     with torch.cuda.device(x.device):
         q_row = torch.empty((M, N), dtype=torch.float8_e4m3fn, device=x.device)
         s_row = torch.empty((M, nb), dtype=torch.float32, device=x.device)
-        q_blk = torch.empty((M, N), dtype=torch.float8_e4m3fn, device=x.device)
+        q_blk = torch.empty((N, M) if transpose_block else (M, N), dtype=torch.float8_e4m3fn, device=x.device)
         s_blk = torch.empty(((M + 127) // 128, nb), dtype=torch.float32, device=x.device)
-        _lib.check(_L.cinn_quant_rowwise_with_block(_ptr(x), _DTYPE_TAG[x.dtype], M, N, x.stride(0), _ptr(q_row), _ptr(s_row),
-                                                    _ptr(q_blk), _ptr(s_blk), int(bool(round_scale)), _DIV_MODE, _stream(x)),
+        fn = _L.cinn_quant_rowwise_with_block_t if transpose_block else _L.cinn_quant_rowwise_with_block
+        _lib.check(fn(_ptr(x), _DTYPE_TAG[x.dtype], M, N, x.stride(0), _ptr(q_row), _ptr(s_row),
+                      _ptr(q_blk), _ptr(s_blk), int(bool(round_scale)), _DIV_MODE, _stream(x)),
                    "cinn_quant_rowwise_with_block")
     _count()
     return q_row, s_row, q_blk, s_blk
@@ -181,6 +189,27 @@ def quantize_fp8_blockwise(x: torch.Tensor, block_m: int = 128, block_n: int = 1
                    "cinn_quant_blockwise")
     _count()
     return q, s
+
+
+def quantize_fp8_blockwise_t(x: torch.Tensor, round_scale: bool = False):
+    """``quantize_fp8_blockwise(x)`` (128 x 128 blocks) that also returns the byte-transposed copy of the quantised
+    matrix, from one pass over ``x``: ``(x_fp8 [M, N], scales, x_fp8_t [N, M])``.  The scales serve both copies
+    (``scales.t()`` indexes the transposed one).  Replaces the reference's quantise + ``.t().contiguous()``
+    (src/kernels.py:747-748).  M and N must be multiples of 4."""
+    assert x.is_cuda, "Input must be on CUDA"
+    assert x.ndim == 2, "Input must be 2D"
+    x = _as_quant_input(x)
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    M, N = x.shape
+    with torch.cuda.device(x.device):
+        q = torch.empty((M, N), dtype=torch.float8_e4m3fn, device=x.device)
+        q_t = torch.empty((N, M), dtype=torch.float8_e4m3fn, device=x.device)
+        s = torch.empty(((M + 127) // 128, (N + 127) // 128), dtype=torch.float32, device=x.device)
+        _lib.check(_L.cinn_quant_blockwise_t(_ptr(x), _DTYPE_TAG[x.dtype], M, N, x.stride(0), _ptr(q), _ptr(q_t), _ptr(s),
+                                             int(bool(round_scale)), _DIV_MODE, _stream(x)), "cinn_quant_blockwise_t")
+    _count()
+    return q, s, q_t
 
 
 def _dequant(x_fp8, scales, block_m, block_n, out_dtype):
@@ -225,6 +254,22 @@ def requantize_rowwise_to_blockwise(x_fp8: torch.Tensor, x_scale: torch.Tensor, 
                    "cinn_requant_row_to_block")
     _count()
     return out, s
+
+
+def transpose_fp8(x_fp8: torch.Tensor) -> torch.Tensor:
+    """``x_fp8.t().contiguous()`` of a 2-D e4m3 (or uint8) tensor as one byte-transposing pass (the reference makes
+    such copies with torch, src/kernels.py:748).  Block scales of a 128x128-quantised matrix are those of its
+    transpose with the two indices swapped, so a transposed weight needs no second quantisation."""
+    assert x_fp8.is_cuda and x_fp8.ndim == 2 and x_fp8.element_size() == 1
+    if x_fp8.stride(1) != 1:
+        x_fp8 = x_fp8.contiguous()
+    R, C = x_fp8.shape
+    with torch.cuda.device(x_fp8.device):
+        out = torch.empty((C, R), dtype=x_fp8.dtype, device=x_fp8.device)
+        _lib.check(_L.cinn_transpose_bytes(_ptr(x_fp8), x_fp8.stride(0), _ptr(out), R, C, _stream(x_fp8)),
+                   "cinn_transpose_bytes")
+    _count()
+    return out
 
 
 # -----------------------------------------------------------------------------
@@ -308,9 +353,9 @@ class FP8MatmulFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, weight, round_scale, weight_fp8=None):
-        """``weight_fp8``: optional ``(w_fp8, w_scale)`` of this very weight (``quantize_fp8_blockwise``), for callers
-        that quantise a weight once per optimiser step instead of once per call; the reference's three-argument
-        call re-quantises every time (:747)."""
+        """``weight_fp8``: optional ``(w_fp8, w_scale)`` or ``(w_fp8, w_scale, w_fp8_t)`` of this very weight
+        (``quantize_fp8_blockwise``, ``transpose_fp8``), for callers that quantise a weight once per optimiser step
+        instead of once per call; the reference's three-argument call re-quantises every time (:747)."""
         assert x.is_cuda, "Input must be on CUDA"
         x_shape = x.shape
         x_flat = x.reshape(-1, x_shape[-1])
@@ -319,15 +364,27 @@ class FP8MatmulFunction(torch.autograd.Function):
         # :746; when the weight will want a gradient, the block re-quantisation of the saved activations that the
         # backward needs (:784-787) comes out of the same pass over x and is what gets saved
         want_wgrad = ctx.needs_input_grad[1] and K % 16 == 0
+        # the block copy is written with the token axis contiguous: the weight gradient reduces over tokens, and both
+        # of its operands are then K-major like the forward's (tensor-core operand reads are fastest that way)
+        x_blk_t = want_wgrad and M % 16 == 0 and _KMAJOR_BACKWARD
         if want_wgrad:
-            x_fp8, x_scale, x_blk, x_blk_scale = quantize_fp8_rowwise_with_block(x_flat, round_scale=round_scale)
+            x_fp8, x_scale, x_blk, x_blk_scale = quantize_fp8_rowwise_with_block(x_flat, round_scale=round_scale,
+                                                                                 transpose_block=x_blk_t)
         else:
             x_fp8, x_scale = quantize_fp8_rowwise(x_flat, block_size=128, round_scale=round_scale)
+        ctx.w_fp8_t = None
         if weight_fp8 is not None:
-            w_fp8, w_scale = weight_fp8
+            w_fp8, w_scale = weight_fp8[0], weight_fp8[1]
+            ctx.w_fp8_t = weight_fp8[2] if len(weight_fp8) > 2 else None
         else:
-            w_fp8, w_scale = quantize_fp8_blockwise(weight.float() if weight.dtype not in _DTYPE_TAG else weight,
-                                                    block_m=128, block_n=128)                        # :747
+            w_in = weight.float() if weight.dtype not in _DTYPE_TAG else weight
+            if (_KMAJOR_BACKWARD and ctx.needs_input_grad[0] and N % 16 == 0 and K % 4 == 0 and w_in.stride(1) == 1
+                    and w_in.stride(0) % 4 == 0):
+                # the input gradient multiplies by the weight with N as the reduction axis: the byte-transposed
+                # copy it reads comes out of the same pass (:747-748)
+                w_fp8, w_scale, ctx.w_fp8_t = quantize_fp8_blockwise_t(w_in)
+            else:
+                w_fp8, w_scale = quantize_fp8_blockwise(w_in, block_m=128, block_n=128)              # :747
         ctx.n_inputs = 3 if weight_fp8 is None else 4
         # :748-752 without the transposed copies: B stays (N, K); sB[kb, nb] = w_scale[nb, kb]
         out = _gemm(x_fp8, x_scale, w_fp8, _lib.B_NK, w_scale, w_scale.stride(1), w_scale.stride(0), M, N, K,
@@ -337,6 +394,7 @@ class FP8MatmulFunction(torch.autograd.Function):
         else:
             ctx.save_for_backward(x_fp8, x_scale, w_fp8, w_scale)
         ctx.x_is_block = want_wgrad
+        ctx.x_is_block_t = x_blk_t
         ctx.x_shape = x_shape
         ctx.round_scale = round_scale
         ctx.weight_dtype = weight.dtype
@@ -355,16 +413,23 @@ class FP8MatmulFunction(torch.autograd.Function):
         # The token axis is the reduction axis of the weight gradient; the GEMM wants it in multiples
         # of 16, so a ragged token count is padded with zero rows (they change neither an amax nor a sum).
         Mp = (M + 15) // 16 * 16
-        if Mp != M:
+        if Mp != M:                                        # (never with a transposed block copy: that needs M % 16 == 0)
             grad_flat = torch.nn.functional.pad(grad_flat, (0, 0, 0, Mp - M))
             x_fp8 = torch.nn.functional.pad(x_fp8.view(torch.uint8), (0, 0, 0, Mp - M)).view(torch.float8_e4m3fn)
             if not ctx.x_is_block:                         # block scales: zero rows stay inside the last row block
                 x_scale = torch.nn.functional.pad(x_scale, (0, 0, 0, Mp - M), value=1.0)
         # dy quantised along features for dgrad (:771) and along tokens for wgrad (:781-783), one pass over dy
         grad_fp8, grad_scale, grad_fp8_t, grad_scale_t = quantize_fp8_rowwise_dual(grad_flat, round_scale=round_scale)
-        # dgrad (:771-774): dy (M, N) @ W (N, K); W is the B operand stored (reduction, output)
-        grad_x = _gemm(grad_fp8, grad_scale, w_fp8, _lib.B_KN, w_scale, w_scale.stride(0), w_scale.stride(1), M, K, N,
-                       torch.bfloat16)
+        # dgrad (:771-774): dy (M, N) @ W (N, K).  W is the B operand with the reduction axis N; a byte-transposed
+        # copy (K, N) puts that axis innermost (the block scales are shared, indices swapped), otherwise the stored
+        # bytes are read (reduction, output)
+        if N % 16 == 0 and (_KMAJOR_BACKWARD or ctx.w_fp8_t is not None):
+            w_t = ctx.w_fp8_t if ctx.w_fp8_t is not None else transpose_fp8(w_fp8)
+            grad_x = _gemm(grad_fp8, grad_scale, w_t, _lib.B_NK, w_scale, w_scale.stride(0), w_scale.stride(1), M, K, N,
+                           torch.bfloat16)
+        else:
+            grad_x = _gemm(grad_fp8, grad_scale, w_fp8, _lib.B_KN, w_scale, w_scale.stride(0), w_scale.stride(1), M, K, N,
+                           torch.bfloat16)
         # wgrad (:781-788): x re-quantised in 128x128 blocks
         if ctx.x_is_block:
             x_fp8_block, x_scale_block = x_fp8, x_scale            # made by the forward's pass over x
@@ -373,9 +438,9 @@ class FP8MatmulFunction(torch.autograd.Function):
         # the reference returns a bf16 grad_weight which autograd then casts to the fp32 master
         # weight's dtype (:788, :794); the GEMM writes those same values as fp32 directly
         ctx_w_fp32 = ctx.weight_dtype == torch.float32
-        grad_weight = _gemm(grad_fp8_t, grad_scale_t, x_fp8_block, _lib.B_KN, x_scale_block, x_scale_block.stride(0),
-                            x_scale_block.stride(1), N, K, Mp, torch.float32 if ctx_w_fp32 else torch.bfloat16,
-                            bf16_rounded=True)
+        grad_weight = _gemm(grad_fp8_t, grad_scale_t, x_fp8_block, _lib.B_NK if ctx.x_is_block_t else _lib.B_KN,
+                            x_scale_block, x_scale_block.stride(0), x_scale_block.stride(1), N, K, Mp,
+                            torch.float32 if ctx_w_fp32 else torch.bfloat16, bf16_rounded=True)
         return (grad_x.reshape(x_shape), grad_weight, None) + (None,) * (ctx.n_inputs - 3)
 
 
@@ -407,7 +472,13 @@ class FP8Linear(torch.nn.Module):
             key = (w._version, w.data_ptr(), w.dtype)
             if self._w_cache[0] != key:
                 with torch.no_grad():
-                    self._w_cache = (key, quantize_fp8_blockwise(w.float() if w.dtype not in _DTYPE_TAG else w, 128, 128))
+                    wf = w.float() if w.dtype not in _DTYPE_TAG else w
+                    # the input gradient reads the weight transposed; cached with it when that copy can be made
+                    if w.shape[0] % 16 == 0 and w.shape[1] % 4 == 0:
+                        q, s, q_t = quantize_fp8_blockwise_t(wf)
+                        self._w_cache = (key, (q, s, q_t))
+                    else:
+                        self._w_cache = (key, quantize_fp8_blockwise(wf, 128, 128))
             out = FP8MatmulFunction.apply(x, w, self.round_scale, self._w_cache[1])
         elif x.is_cuda:
             out = FP8MatmulFunction.apply(x, self.weight, self.round_scale)

@@ -78,12 +78,27 @@ int cinn_selfcheck_division(unsigned long long* mismatches, void* stream);
 int cinn_quant_rowwise_with_block(const void* x, int x_dtype, int64_t M, int64_t N, int64_t ld, void* q_row, float* s_row,
                                   void* q_block, float* s_block, int round_scale, int div_mode, void* stream);
 
+/* The same with the block-scaled bytes written transposed: q_block_t is (N, M) with M contiguous (M a multiple of
+ * 16), s_block unchanged.  That is the layout in which the weight-gradient GEMM of FP8MatmulFunction.backward
+ * (src/kernels.py:788: grad_weight = dy^T @ x_block) reads x_block with the token axis - its reduction axis -
+ * contiguous, i.e. K-major, like the forward reads a weight. */
+int cinn_quant_rowwise_with_block_t(const void* x, int x_dtype, int64_t M, int64_t N, int64_t ld, void* q_row, float* s_row,
+                                    void* q_block_t, float* s_block, int round_scale, int div_mode, void* stream);
+
 /* Block-wise block_m x block_n quantisation.
  * Replaces quantize_fp8_blockwise_kernel + quantize_fp8_blockwise (src/kernels.py:74-132, 219-259).
  * scales: (ceil(M/block_m), ceil(N/block_n)). */
 int cinn_quant_blockwise(const void* x, int x_dtype, int64_t M, int64_t N, int64_t ld_m, int64_t ld_n,
                          void* q, float* scales, int block_m, int block_n, int round_scale, int div_mode,
                          void* stream);
+
+/* 128 x 128 block-wise quantisation of x (M, N; contiguous rows of pitch ld; M, N, ld multiples of 4) that also
+ * writes the byte-transposed copy q_t (N, M) in the same pass; one set of scales serves both (a block and its
+ * transpose share their scale).  Replaces quantize_fp8_blockwise on the weight (src/kernels.py:747) plus the
+ * `w_fp8.t().contiguous()` copy (:748): the forward reads q, the input gradient (:774) reads q_t, both with their
+ * reduction axis innermost. */
+int cinn_quant_blockwise_t(const void* x, int x_dtype, int64_t M, int64_t N, int64_t ld, void* q, void* q_t, float* scales,
+                           int round_scale, int div_mode, void* stream);
 
 /* Row-scaled e4m3 (1x128 tiles) -> block-scaled e4m3 (128x128) in one pass.
  * Replaces dequantize_fp8_rowwise followed by quantize_fp8_blockwise in the weight-gradient path
@@ -269,6 +284,13 @@ int cinn_p2p_row_table(const int64_t* seg_start, const int64_t* home_base, const
  * bounded (about 2 s): a rank that never arrives leaves a code in the device status word instead of a hung GPU.
  * Every rank must run on a GPU of its own. */
 int cinn_p2p_barrier(const int64_t* peer_flags, int rank, int n_ranks, unsigned epoch, void* stream);
+
+/* Limit, in SM clock cycles, of the bounded wait in cinn_p2p_barrier (default 4e9, about two seconds; cycles <= 0
+ * restores the default).  Returns the previous limit.  Applies to barriers launched afterwards.  When a wait runs
+ * out the barrier kernel returns, cinn_device_status reports (5 << 8) | 3, and whatever the layer computed after
+ * that barrier is invalid (rows may not have arrived): the caller discards the step.  No reference counterpart
+ * (the reference has no device-side waits). */
+long long cinn_set_wait_limit_cycles(long long cycles);
 
 /* Routing of MoE.forward (src/layers.py:122-148) on the device: scores = sigmoid(logits), the top_k experts of
  * scores + bias per token (ties: the lower expert id), gates = score / (sum of the k scores + 1e-9), and the

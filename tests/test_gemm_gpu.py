@@ -318,3 +318,115 @@ def test_grouped_gemm_backward(K, name):
     for e, c in enumerate(counts):
         if c == 0:
             assert torch.all(wg.grad[e] == 0)
+
+
+def test_config2_backward_full_size_sampled(K):
+    """Forward + backward of FP8MatmulFunction at the FFN width (x [16384, 7168], W [18432, 7168], dy [16384, 18432]),
+    i.e. the step the benchmark times, with the fused quantiser passes in the loop.  dgrad is checked on sampled token
+    rows, wgrad on sampled weight rows (all 7168 columns each), both against the float64 product of operands the CPU
+    oracle quantised (src/kernels.py:763-794: dy row-wise, dy^T row-wise, x row-wise then re-quantised in blocks)."""
+    M, Kd, N = 16384, 7168, 18432
+    g = torch.Generator().manual_seed(1002)
+    x = torch.randn(M, Kd, generator=g).bfloat16()
+    w = torch.randn(N, Kd, generator=g) * 0.02
+    dy = torch.randn(M, N, generator=g).bfloat16()
+    xg = x.cuda().requires_grad_(True)
+    wg = w.cuda().requires_grad_(True)
+    out = K.FP8MatmulFunction.apply(xg, wg, False)
+    out.backward(dy.cuda())
+    torch.cuda.synchronize()
+    assert K.device_status() == 0
+    assert xg.grad.shape == (M, Kd) and wg.grad.shape == (N, Kd) and wg.grad.dtype == torch.float32
+    wq, ws = O.quantize_blockwise(w, 128, 128)
+    # dgrad: sampled token rows
+    rows = torch.tensor([0, 1, 127, 128, 4097, 8191, 12345, 16383])
+    dq, ds = O.quantize_rowwise(dy[rows], 128)
+    ref_dx = O.fp8_matmul_f64(dq, wq, ds, ws)
+    assert_bf16_close(xg.grad[rows.cuda()], ref_dx, "C2 dgrad")
+    err_dx = rel_fro(xg.grad[rows.cuda()].float(), ref_dx)
+    # wgrad: sampled weight rows; the reduction runs over all 16384 tokens
+    nrows = torch.tensor([0, 127, 128, 255, 9000, 18431])
+    dtq, dts = O.quantize_rowwise(dy[:, nrows].t().contiguous(), 128)
+    xq, xs = O.quantize_rowwise(x, 128)
+    xbq, xbs = O.requantize_row_to_block(xq, xs)
+    ref_dw = O.fp8_matmul_f64(dtq, xbq, dts, xbs)
+    assert_bf16_close(wg.grad[nrows.cuda()].to(torch.bfloat16), ref_dw, "C2 wgrad")
+    err_dw = rel_fro(wg.grad[nrows.cuda()], ref_dw)
+    # forward once more on sampled rows (bf16 result of the autograd path)
+    ref_out = O.fp8_matmul_f64(xq[rows], wq.t(), xs[rows], ws.t())
+    assert_bf16_close(out[rows.cuda()], ref_out, "C2 forward")
+    print(f"C2 backward sampled: dgrad rel-Fro {err_dx:.3e}, wgrad rel-Fro {err_dw:.3e} (bf16 results)")
+    assert err_dx < 4e-3 and err_dw < 4e-3          # bf16 rounding alone is 1.7e-3
+
+
+def test_config4_grouped_gemm_literal_routing_sampled(K):
+    """Grouped GEMMs of the MoE configuration at full size: 256 experts, 32768 tokens, top-8 (262144 rows), d = 7168,
+    up-projection 7168 -> 4096 and down-projection 2048 -> 7168, with the row ranges that the literal routing
+    specification produces (sigmoid scores + bias ~ N(0, 1): about 30 experts receive rows, several receive every
+    token).  Gaps of a few rows that belong to no expert are inserted between some experts and a canary is written
+    everywhere first.  Sampled rows - the first and last row of several experts among them - are checked against
+    the float64 product."""
+    from cinnamon_b200 import moe
+    E, d, I, T, k = 256, 7168, 2048, 32768, 8
+    g = torch.Generator(device="cuda").manual_seed(1004)
+    xt = torch.randn(T, d, generator=g, device="cuda").bfloat16()
+    router = torch.randn(E, d, generator=g, device="cuda") * 0.02
+    bias = torch.randn(E, generator=g, device="cuda")
+    r = moe.route(xt, router, bias, k)
+    counts = r.counts.cpu()
+    active = [e for e in range(E) if counts[e] > 0]
+    assert int(counts.sum()) == T * k and len(active) < 64 and int(counts.max()) > 0.9 * T, "the literal routing is heavily skewed"
+    # ranges with a 5-row gap in front of every third active expert
+    starts, ends, pos = torch.zeros(E, dtype=torch.int64), torch.zeros(E, dtype=torch.int64), 0
+    for e in range(E):
+        if counts[e] > 0 and active.index(e) % 3 == 1:
+            pos += 5
+        starts[e], ends[e] = pos, pos + int(counts[e])
+        pos = int(ends[e])
+    R = pos + 9
+    src = torch.zeros(R, dtype=torch.int64)
+    for e in active:
+        seg = r.token_indices[int(counts[:e].sum()):int(counts[:e + 1].sum())].cpu()
+        src[int(starts[e]):int(ends[e])] = seg
+    xq_t, xs_t = K.quantize_fp8_rowwise(xt)
+    xq, xs = K.gather_quantized_rows(xq_t, xs_t, src.cuda())
+    del xt, xq_t, xs_t
+    covered = torch.zeros(R, dtype=torch.bool)
+    for e in active:
+        covered[int(starts[e]):int(ends[e])] = True
+    sample = []
+    for e in active[:4] + active[-3:] + [int(counts.argmax())]:
+        s, t = int(starts[e]), int(ends[e])
+        sample += [(e, s), (e, t - 1), (e, s + (t - s) // 2)]
+        if t - s > 300:
+            sample += [(e, s + 127), (e, s + 128), (e, t - 129)]
+    rows = torch.tensor([p for _, p in sample])
+    for name, d_in, d_out in (("up", d, 2 * I), ("down", I, d)):
+        gw = torch.Generator(device="cuda").manual_seed(2004 + d_in)
+        wq = torch.empty(E, d_out, d_in, dtype=torch.float8_e4m3fn, device="cuda")
+        wsc = torch.empty(E, d_out // 128, d_in // 128, device="cuda")
+        for e0 in range(0, E, 32):                                   # 32 experts at a time: the bf16 masters are large
+            wpart = (torch.randn(32, d_out, d_in, generator=gw, device="cuda") * 0.02).bfloat16()
+            wq[e0:e0 + 32], wsc[e0:e0 + 32] = K.quantize_expert_weights(wpart)
+        del wpart
+        if name == "up":
+            aq, asc = xq, xs
+        else:
+            h = torch.randn(R, I, generator=gw, device="cuda").bfloat16()
+            aq, asc = K.quantize_fp8_rowwise(h)
+            del h
+        out = torch.full((R, d_out), 777.0, dtype=torch.bfloat16, device="cuda")
+        K.fp8_grouped_gemm(aq, asc, wq, wsc, starts.cuda(), ends.cuda(), out=out)
+        torch.cuda.synchronize()
+        assert K.device_status() == 0
+        untouched = (out[(~covered).cuda()] == 777.0).all()
+        assert bool(untouched), f"{name}: rows that belong to no expert were written"
+        got = out[rows.cuda()].float().cpu()
+        worst = 0.0
+        for i, (e, p) in enumerate(sample):
+            ref = O.fp8_matmul_f64(aq[p:p + 1].view(torch.uint8).cpu(), wq[e].view(torch.uint8).cpu().t(),
+                                   asc[p:p + 1].cpu(), wsc[e].cpu().t())
+            assert_bf16_close(got[i:i + 1].to(torch.bfloat16), ref, f"{name} row {p} of expert {e}")
+            worst = max(worst, rel_fro(got[i:i + 1], ref))
+        print(f"C4 {name}-projection, {len(active)} active experts, {len(sample)} sampled rows: worst rel-Fro {worst:.3e} (bf16)")
+        del wq, wsc, out

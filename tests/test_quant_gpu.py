@@ -256,3 +256,42 @@ def test_config2_activation_full_size(K):
     q2, s2 = K.quantize_fp8_rowwise(y, 128, False)
     assert torch.equal(s2, s)
     assert (q2.view(torch.uint8) != q.view(torch.uint8)).float().mean().item() < 1e-6
+
+
+@pytest.mark.parametrize("shape", [(256, 512), (384, 640), (132, 200), (16, 128), (2048, 1024)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_blockwise_with_transposed_copy(K, shape, dtype):
+    """One pass, two layouts: (M, N) and its byte transpose (N, M), one set of scales (src/kernels.py:747-748)."""
+    M, N = shape
+    g = torch.Generator().manual_seed(M + N)
+    x = (torch.randn(M, N, generator=g) * 0.02).to(dtype)
+    q, s, q_t = K.quantize_fp8_blockwise_t(x.cuda())
+    assert_quant_equal(q, s, *O.quantize_blockwise(x, 128, 128, False), what="block copy")
+    assert q_t.shape == (N, M) and torch.equal(q_t.view(torch.uint8), q.view(torch.uint8).t())
+
+
+@pytest.mark.parametrize("shape", [(256, 512), (144, 272), (1024, 896), (16, 16), (130, 72), (7, 13), (64, 4)])
+def test_byte_transposer(K, shape):
+    R, C = shape
+    g = torch.Generator().manual_seed(R * C)
+    x = torch.randint(0, 256, (R, C), generator=g, dtype=torch.uint8).cuda()
+    assert torch.equal(K.transpose_fp8(x), x.t().contiguous())
+    wide = torch.randint(0, 256, (R, C + 8), generator=g, dtype=torch.uint8).cuda()
+    assert torch.equal(K.transpose_fp8(wide[:, :C]), wide[:, :C].t().contiguous())        # pitched rows
+
+
+@pytest.mark.parametrize("shape", [(256, 512), (144, 272), (16, 128), (1040, 384)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rs", [False, True])
+def test_rowwise_with_transposed_block_copy(K, shape, dtype, rs):
+    """The row + block pass with the block copy written (N, M): same bytes as the untransposed variant, transposed."""
+    M, N = shape
+    g = torch.Generator().manual_seed(3 * M + N)
+    x = torch.randn(M, N, generator=g).to(dtype).cuda()
+    q_row, s_row, q_blk, s_blk = K.quantize_fp8_rowwise_with_block(x, rs)
+    q_row2, s_row2, q_blk_t, s_blk2 = K.quantize_fp8_rowwise_with_block(x, rs, transpose_block=True)
+    assert torch.equal(q_row.view(torch.uint8), q_row2.view(torch.uint8)) and torch.equal(s_row, s_row2)
+    assert torch.equal(s_blk, s_blk2)
+    assert q_blk_t.shape == (N, M) and torch.equal(q_blk_t.view(torch.uint8), q_blk.view(torch.uint8).t())
+    ref_q, ref_s = O.requantize_row_to_block(*O.quantize_rowwise(x.cpu(), 128, rs))
+    assert_quant_equal(q_blk, s_blk, ref_q, ref_s, what="block copy")
