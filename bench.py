@@ -30,7 +30,15 @@ sys.path.insert(0, ROOT)
 M, K, N = 16384, 7168, 18432
 FLOP_PER_STEP = 3 * 2.0 * M * N * K
 WORKLOAD = "fp8_linear_fwd_bwd_ffn M=16384 K=7168 N=18432"
-GEMM_TRAFFIC_BYTES = 4 * (462.2e6 + 448.7e6 + 622.4e6) / 3      # per launch, see profiles/fp8_gemm_kernel_8192x9216x7168.md
+# DRAM bytes per GEMM launch: reduced-case ncu capture (8192 x 9216 x 7168, three GEMMs averaged) scaled by the
+# algorithmic bytes of the full launch over those of the reduced one (operands + scales + output: x3.1, not x4)
+GEMM_TRAFFIC_BYTES = 3.1 * (462.2e6 + 448.7e6 + 622.4e6) / 3
+
+
+def bench_config(world: int) -> dict:
+    """The ``config`` object of the JSON line: identical in both arms."""
+    return {"workload": WORKLOAD, "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
+            "l2": f"inputs larger than L2 (x {M * K * 2 >> 20} MiB, W {N * K * 4 >> 20} MiB, dy {M * N * 2 >> 20} MiB)"}
 
 
 def measured_peaks():
@@ -39,6 +47,68 @@ def measured_peaks():
             return json.load(f), "measured"
     except Exception:
         return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+def measure_fp8_peak(dev, sustained=True):
+    """Dense FP8 peak of this GPU as the library GEMM delivers it: e4m3 x e4m3 -> bf16, 8192^3, per-tensor scales,
+    through ``torch._scaled_mm`` (cuBLASLt).  Best of 10 single launches after a pause (burst: the figure for a kernel
+    timed alone) and back to back for about two seconds (sustained: the figure for a kernel inside a long step, where
+    the part sits at its power cap).  None when the call is not available."""
+    n = 8192
+    try:
+        g = torch.Generator(device=dev).manual_seed(7)
+        a = torch.randn(n, n, generator=g, device=dev).to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, generator=g, device=dev).to(torch.float8_e4m3fn).t()          # column-major operand
+        one = torch.ones((), device=dev)
+
+        def f():
+            return torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+
+        for _ in range(3):
+            f()
+        torch.cuda.synchronize()
+    except Exception as exc:                                    # noqa: BLE001
+        return {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+    flop = 2.0 * n ** 3
+    time.sleep(1.0)
+    best = float("inf")
+    for _ in range(10):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        f()
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    if not sustained:
+        return {"fp8_tflops": flop / (best * 1e-3) / 1e12, "how": f"torch._scaled_mm e4m3 {n}^3 -> bf16, per-tensor scales: best of 10 launches"}
+    reps = max(50, int(2000.0 / best))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        f()
+    e1.record()
+    torch.cuda.synchronize()
+    sustained_ms = e0.elapsed_time(e1) / reps
+    return {"fp8_tflops": flop / (best * 1e-3) / 1e12, "fp8_tflops_sustained": flop / (sustained_ms * 1e-3) / 1e12,
+            "how": f"torch._scaled_mm e4m3 {n}^3 -> bf16, per-tensor scales: best of 10 launches; {reps} launches back to back"}
+
+
+def load_reference_kernels():
+    """The unmodified reference module (its Triton kernels) from the staged copy beside the repository, or
+    (None, reason).  Used only to time the kernels this library replaces, next to it, on the same GPU."""
+    path = os.path.join(ROOT, "baseline", "_ref", "src", "kernels.py")
+    if not os.path.isfile(path):
+        return None, "reference not staged (baseline/stage_reference.py)"
+    try:
+        import importlib.util
+        import triton  # noqa: F401
+        spec = importlib.util.spec_from_file_location("ref_kernels", path)
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules["ref_kernels"] = mod
+        spec.loader.exec_module(mod)
+        return mod, None
+    except Exception as exc:                                    # noqa: BLE001
+        return None, f"{type(exc).__name__}: {exc}"[:200]
 
 
 class ClockSampler:
@@ -120,23 +190,29 @@ def make_inputs(seed: int, pinned: bool):
 # wrappers assert CUDA), on the host cores, on a bounded sample of the workload.
 # ---------------------------------------------------------------------------------------
 def cpu_step(sample_rows: int, w: torch.Tensor, x: torch.Tensor, dy: torch.Tensor):
+    """One step of the reference's CPU formulation on ``sample_rows`` token rows.  Returns (seconds spent on the
+    weight, which a full step pays once; seconds spent on the sampled rows, which grow with the row count)."""
     from oracle import fp8_oracle as O
     xs, dys = x[:sample_rows], dy[:sample_rows]
     t0 = time.perf_counter()
-    x_q, x_s = O.quantize_rowwise(xs, 128, False)
     w_q, w_s = O.quantize_blockwise(w, 128, 128)
-    x_deq = O.dequantize_rowwise(x_q, x_s)
     w_deq = O.dequantize_block(w_q, w_s, out_dtype=torch.float32)
+    t1 = time.perf_counter()
+    x_q, x_s = O.quantize_rowwise(xs, 128, False)
+    x_deq = O.dequantize_rowwise(x_q, x_s)
     out = x_deq @ w_deq.t()                                       # forward  (:754-756)
     g_q, g_s = O.quantize_rowwise(dys, 128, False)
     g_deq = O.dequantize_rowwise(g_q, g_s)
     grad_x = g_deq @ w_deq                                        # dgrad    (:776-778)
     grad_w = g_deq.t() @ x_deq                                    # wgrad    (:790-792)
-    dt = time.perf_counter() - t0
-    return dt, float(out[0, 0] + grad_x[0, 0] + grad_w[0, 0])
+    t2 = time.perf_counter()
+    assert torch.isfinite(out[0, 0] + grad_x[0, 0] + grad_w[0, 0])
+    return t1 - t0, t2 - t1
 
 
 def run_cpu_baseline(sample_rows: int, repeats: int, warmup: int = 0):
+    """The oracle port timed on all host threads.  A sample of the token rows is run; the time of a full step is
+    the weight's part (paid once per step) plus the rows' part scaled to all rows (it is linear in them)."""
     torch.set_num_threads(os.cpu_count() or 1)
     g = torch.Generator().manual_seed(1002)
     x = torch.randn(sample_rows, K, generator=g).to(torch.bfloat16)
@@ -144,12 +220,14 @@ def run_cpu_baseline(sample_rows: int, repeats: int, warmup: int = 0):
     dy = torch.randn(sample_rows, N, generator=g).to(torch.bfloat16)
     for _ in range(warmup):
         cpu_step(sample_rows, w, x, dy)
-    times = [cpu_step(sample_rows, w, x, dy)[0] for _ in range(repeats)]
-    flop = 3 * 2.0 * sample_rows * N * K
-    best = sum(times) / len(times)
-    return {"value": flop / best / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+    parts = [cpu_step(sample_rows, w, x, dy) for _ in range(repeats)]
+    t_w = sum(p[0] for p in parts) / len(parts)
+    t_rows = sum(p[1] for p in parts) / len(parts)
+    step_s = t_w + t_rows * (M / sample_rows)
+    return {"value": FLOP_PER_STEP / step_s / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
             "sample": f"{sample_rows} of {M} token rows, full K={K} N={N}, forward+dgrad+wgrad incl. quantisation, "
-                      f"{len(times)} run(s), {best:.2f} s each"}, best
+                      f"{len(parts)} run(s): weight quantise+dequantise {t_w:.2f} s (once per step), sampled rows "
+                      f"{t_rows:.2f} s; full step extrapolated to {step_s:.1f} s"}, step_s
 
 
 def reference_arm(args):
@@ -160,9 +238,10 @@ def reference_arm(args):
     base, sec = run_cpu_baseline(rows, repeats=max(1, args.steps), warmup=min(args.warmup, 1))
     line = {
         "impl": "reference", "metric": "fp8_linear_fwd_bwd_tflops", "value": base["value"], "unit": "TFLOP/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3 * (M / rows),
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "ms_per_step_extrapolated": True,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "l2": "inputs larger than L2"},
+        "config": bench_config(args.gpus),
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -186,13 +265,13 @@ def _time_kernel(fn, iters=10, warm=3):
     return a.elapsed_time(b) / iters
 
 
-def bench_kernels(Kmod, dev, x, w, dy, peaks):
+def bench_kernels(Kmod, dev, x, w, dy, peaks, fp8_peak_burst=None):
     """Each kernel of the step on the FFN shapes (inputs larger than L2, so every launch streams from HBM),
     against the roof that bounds it: measured copy bandwidth for the quantisers, 2 x measured bf16 burst for
     the GEMMs (kernels timed alone).  Then the GEMM shapes of the other configurations (single Linear
     4096x512 -> 2048; MLA projections at 16384 tokens)."""
     hbm = float(peaks["hbm_gbs"])
-    fp8_peak = 2.0 * float(peaks["bf16_tflops"])
+    fp8_peak = fp8_peak_burst if fp8_peak_burst else 2.0 * float(peaks["bf16_tflops"])
     out = []
 
     def quant_line(name, fn, nbytes):
@@ -206,7 +285,7 @@ def bench_kernels(Kmod, dev, x, w, dy, peaks):
         ms = _time_kernel(fn)
         tf = flop / (ms * 1e-3) / 1e12
         line = {"kernel": name, "ms": ms, "bound": "tensor", "achieved": tf, "peak": fp8_peak, "unit": "TFLOP/s",
-                "frac": tf / fp8_peak}
+                "frac": tf / fp8_peak, "frac_of_nominal_4500": tf / 4500.0}
         if nbytes is not None:
             gbs = nbytes / (ms * 1e-3) / 1e9
             line.update({"hbm_achieved_gbs": gbs, "hbm_frac": gbs / hbm, "flop_per_byte": flop / nbytes})
@@ -246,6 +325,59 @@ def bench_kernels(Kmod, dev, x, w, dy, peaks):
                lambda: Kmod.quantize_fp8_rowwise_with_block(xd, transpose_block=True), M * K * 4 + 4 * M * nkb + 4 * (M // 128) * nkb)
     quant_line("transpose_fp8 W e4m3 [18432,7168]", lambda: Kmod.transpose_fp8(wq), 2 * N * K)
     del wq_t, xbq_t
+    # the reference's own Triton kernels on the same GPU and the same operands: the kernels this library replaces
+    ref, why = load_reference_kernels()
+    if ref is None:
+        out.append({"kernel": "reference Triton kernels", "unavailable": why})
+    else:
+        def versus(name, ours_fn, ref_fn, iters_ref=3, **extra):
+            ours_ms = _time_kernel(ours_fn)
+            ref_ms = _time_kernel(ref_fn, iters=iters_ref, warm=2)
+            out.append(dict({"kernel": name, "ms": ours_ms, "reference_triton_ms": ref_ms,
+                             "speedup_vs_reference_triton": ref_ms / ours_ms}, **extra))
+
+        g1 = torch.Generator(device=dev).manual_seed(1001)
+        x1 = torch.randn(4096, 512, generator=g1, device=dev).to(torch.bfloat16)
+        w1 = (torch.randn(2048, 512, generator=g1, device=dev) * 0.02).to(torch.bfloat16)
+        x1q, x1s = Kmod.quantize_fp8_rowwise(x1)
+        w1q, w1s = Kmod.quantize_fp8_blockwise(w1)
+        w1q_t, w1s_t = w1q.t().contiguous(), w1s.t().contiguous()            # what the reference's forward feeds its GEMM
+        versus("fp8_matmul_dsv3 config 1 (4096x2048x512) vs reference fp8_gemm_kernel",
+               lambda: Kmod.fp8_matmul_dsv3(x1q, w1q.t(), x1s, w1s.t()),
+               lambda: ref.fp8_matmul_dsv3(x1q, w1q_t, x1s, w1s_t), iters_ref=10)
+        wq_t_ref, ws_t_ref = wq.t().contiguous(), ws.t().contiguous()
+        versus("fp8_matmul_dsv3 FFN forward (16384x18432x7168) vs reference fp8_gemm_kernel",
+               lambda: Kmod.fp8_matmul_dsv3(xq, wq.t(), xs, ws.t()),
+               lambda: ref.fp8_matmul_dsv3(xq, wq_t_ref, xs, ws_t_ref))
+        out[-1]["tflops"] = flop / (out[-1]["ms"] * 1e-3) / 1e12
+        out[-1]["reference_triton_tflops"] = flop / (out[-1]["reference_triton_ms"] * 1e-3) / 1e12
+        del wq_t_ref, ws_t_ref
+        versus("quantize_fp8_rowwise x[16384,7168] bf16 vs reference quantize_fp8_rowwise_kernel",
+               lambda: Kmod.quantize_fp8_rowwise(xd), lambda: ref.quantize_fp8_rowwise(xd), iters_ref=10)
+        versus("quantize_fp8_blockwise W[18432,7168] fp32 vs reference quantize_fp8_blockwise_kernel",
+               lambda: Kmod.quantize_fp8_blockwise(wd), lambda: ref.quantize_fp8_blockwise(wd), iters_ref=10)
+        # one 8-way expert-parallel rank's share of the MoE configuration: 32 experts x 1024 rows, 7168 -> 4096
+        Eg, rows_e = 32, 1024
+        xg_ = torch.randn(Eg * rows_e, MOE["d"], generator=g1, device=dev).to(torch.bfloat16)
+        wg_ = (torch.randn(Eg, 2 * MOE["I"], MOE["d"], generator=g1, device=dev) * 0.02).to(torch.bfloat16)
+        st_ = torch.arange(Eg, device=dev, dtype=torch.int64) * rows_e
+        en_ = st_ + rows_e
+        gflop = 2.0 * Eg * rows_e * MOE["d"] * 2 * MOE["I"]
+        prec = Kmod.set_moe_grouped_precision("fp8") if hasattr(Kmod, "set_moe_grouped_precision") else None
+        versus("moe_grouped_gemm 32 experts x 1024 rows, 7168->4096, bf16 in (e4m3 path, incl. quantising tokens + weights) "
+               "vs reference grouped_gemm_kernel", lambda: Kmod.moe_grouped_gemm(xg_, wg_, st_, en_, rows_e),
+               lambda: ref.moe_grouped_gemm(xg_, wg_, st_, en_, rows_e))
+        if prec is not None:
+            Kmod.set_moe_grouped_precision(prec)
+        out[-1]["tflops"] = gflop / (out[-1]["ms"] * 1e-3) / 1e12
+        out[-1]["reference_triton_tflops"] = gflop / (out[-1]["reference_triton_ms"] * 1e-3) / 1e12
+        xgq, xgs = Kmod.quantize_fp8_rowwise(xg_)
+        wgq, wgs = Kmod.quantize_expert_weights(wg_)
+        versus("fp8_grouped_gemm (operands quantised beforehand, weights cached), same shape vs reference grouped_gemm_kernel",
+               lambda: Kmod.fp8_grouped_gemm(xgq, xgs, wgq, wgs, st_, en_, out_dtype=torch.bfloat16),
+               lambda: ref.moe_grouped_gemm(xg_, wg_, st_, en_, rows_e))
+        out[-1]["tflops"] = gflop / (out[-1]["ms"] * 1e-3) / 1e12
+        del xg_, wg_, xgq, xgs, wgq, wgs, x1, w1
     del dq, ds, dtq, dts, xbq, xbs, wq, ws
     # other configurations: (tokens, in, out)
     g = torch.Generator(device=dev).manual_seed(1003)
@@ -354,7 +486,9 @@ MOE = dict(E=256, d=7168, I=2048, tokens=32768, top_k=8, shared_hidden=2048)
 def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label, chunks=1, exchange="nccl"):
     """256 routed experts (SwiGLU 7168 -> 2x2048 -> 7168) + 1 shared expert, 32768 tokens, top-8 with
     sigmoid scores + per-expert bias.  Strong scaling: tokens and experts are both split over the ranks.
-    Returns a dict (rank 0) with whole-layer tokens/s, the grouped-GEMM rate and the load imbalance."""
+    Returns a dict (rank 0) with whole-layer tokens/s, the per-phase times of the most loaded rank, the grouped-GEMM
+    rate on the rows that rank really received, the load imbalance, and a parity check of sampled tokens against the
+    same arithmetic done on one GPU with every expert's weights."""
     import torch.distributed as dist
     from cinnamon_b200 import moe
     c = MOE
@@ -376,7 +510,7 @@ def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label, chunks=1
     # the layer as a user builds it: router + this rank's routed experts + the shared expert (round_scale on the
     # shared expert's input, as the reference's converted model has it)
     module = moe.ExpertParallelMoE(router, bias, w12, w3, c["top_k"], shared=moe.FP8SwiGLU(*sw, round_scale=True),
-                                   n_chunks=chunks, exchange=exchange)
+                                   n_chunks=chunks, exchange=exchange, max_tokens_per_rank=T_local)
     t1.record()
     torch.cuda.synchronize()
     wq_ms = t0.elapsed_time(t1)
@@ -398,44 +532,175 @@ def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label, chunks=1
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
-        layer()
+        y = layer()
     e1.record()
     sync()
     ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
-    # grouped GEMMs alone, on the rows this rank received in the last step
+
+    # ---- phases of one more call (CUDA events on the layer's main stream; outside the timed region)
+    module.trace = []
+    y = layer()
+    sync()
+    trace, module.trace = module.trace, None
+    phases = [{"phase": name, "ms": round(trace[i - 1][1].elapsed_time(ev), 4)} for i, (name, ev) in enumerate(trace) if i > 0]
+
+    # ---- the grouped GEMMs alone, on the quantised rows this rank really received in that call
     with torch.no_grad():
-        r = moe.route(x, router, bias, c["top_k"])
-    plan = moe.make_plan(r.counts)
-    rows = int(plan.ends[-1])
-    xq = torch.empty(rows, c["d"], dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
-    xs = torch.ones(rows, c["d"] // 128, device=dev)
+        logits = moe.router_logits(x, module._router_as(x.dtype))
+        r = Kmod.moe_route(logits, bias, c["top_k"])
+    if world > 1 and module.exchange in ("p2p", "p2p-fused") and module._peer_buffers is not None and module._peer_buffers.n_experts:
+        pb = module._peer_buffers
+        rows = int(pb._tables.total_rows)
+        rq = pb.q.view(pb.capacity_rows, pb.d)[:rows].view(torch.float8_e4m3fn)
+        rs = pb.s.view(pb.capacity_rows, pb.n_scales)[:rows]
+        starts, ends = pb._tables.starts.clone(), pb._tables.ends.clone()
+    else:
+        plan = moe.make_plan(r["counts"]) if world == 1 else None
+        xq_, xs_ = Kmod.quantize_fp8_rowwise(x)
+        if world == 1:
+            rq, rs = Kmod.gather_quantized_rows(xq_, xs_, r["token_indices"])
+            starts, ends, rows = plan.starts, plan.ends, int(plan.ends[-1])
+        else:                                        # all-to-all path: time the GEMMs on this rank's own pairs of its experts
+            lo = rank * E_local
+            cnt = r["counts"][lo:lo + E_local]
+            ends = cnt.cumsum(0)
+            starts = ends - cnt
+            first = int(r["counts"][:lo].sum())
+            rows = int(ends[-1])
+            rq, rs = Kmod.gather_quantized_rows(xq_, xs_, r["token_indices"][first:first + rows])
+        del xq_, xs_
     for _ in range(2):
-        experts(xq, xs, plan.starts, plan.ends)
+        experts(rq, rs, starts, ends)
     sync()
     g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     g0.record()
     for _ in range(steps):
-        experts(xq, xs, plan.starts, plan.ends)
+        experts(rq, rs, starts, ends)
     g1.record()
     sync()
-    gms = torch.tensor([g0.elapsed_time(g1) / steps], device=dev, dtype=torch.float64)
+    my_gms = g0.elapsed_time(g1) / steps
+    my_flop = float(rows) * 2.0 * c["d"] * 3 * c["I"]
+
+    # ---- parity: sampled tokens of this rank recomputed on this GPU alone with every expert's quantised weights
+    parity = None
+    n_s = 256
+    with torch.no_grad():
+        if world > 1:
+            def gathered(t):
+                out = torch.empty((world,) + tuple(t.shape), dtype=torch.uint8 if t.dtype == torch.float8_e4m3fn else t.dtype, device=dev)
+                dist.all_gather_into_tensor(out, (t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t).contiguous())
+                out = out.view((world * t.shape[0],) + tuple(t.shape[1:]))
+                return out.view(torch.float8_e4m3fn) if t.dtype == torch.float8_e4m3fn else out
+            full = moe.FP8Experts.__new__(moe.FP8Experts)
+            full.K, full.n_experts, full.d_model, full.hidden = Kmod, c["E"], c["d"], c["I"]
+            full.w12_q, full.w12_s = gathered(experts.w12_q), gathered(experts.w12_s)
+            full.w3_q, full.w3_s = gathered(experts.w3_q), gathered(experts.w3_s)
+        else:
+            full = experts
+        idx = torch.randperm(T_local, generator=torch.Generator().manual_seed(9 + rank))[:n_s].sort().values.to(dev)
+        x_s = x[idx].contiguous()
+        r_s = Kmod.moe_route(logits[idx].contiguous(), bias, c["top_k"])
+        cnt = r_s["counts"]
+        ends_s = cnt.cumsum(0)
+        starts_s = ends_s - cnt
+        q_s, s_s = Kmod.quantize_fp8_rowwise(x_s)
+        gq, gsc = Kmod.gather_quantized_rows(q_s, s_s, r_s["token_indices"])
+        rows_out = full(gq, gsc, starts_s, ends_s)
+        y_ref = Kmod.moe_combine(rows_out, r_s["pair_pos"], r_s["pair_gate"], module.shared(x_s))
+        y_got = y.reshape(T_local, c["d"])[idx]
+        err = float((y_got - y_ref).norm() / y_ref.norm())
+        bit_equal = bool(torch.equal(y_got, y_ref))
+        parity = {"sampled_tokens": n_s, "max_rel_err": err, "bit_equal_to_one_gpu_path": bit_equal}
+        assert err < 1e-5, f"expert-parallel layer differs from the one-GPU arithmetic on sampled tokens: rel err {err}"
+        del full, rows_out, gq, gsc
+
     load = torch.tensor([float(rows)], device=dev, dtype=torch.float64)
     total = load.clone()
+    info = {"rank": rank, "rows": rows, "phases": phases, "grouped_gemm_ms": my_gms,
+            "grouped_gemm_tflops": my_flop / (my_gms * 1e-3) / 1e12 if rows else 0.0, "parity": parity}
+    infos = [info]
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        dist.all_reduce(gms, op=dist.ReduceOp.MAX)
         dist.all_reduce(load, op=dist.ReduceOp.MAX)
         dist.all_reduce(total, op=dist.ReduceOp.SUM)
-    active = int((r.counts > 0).sum())
+        infos = [None] * world
+        dist.all_gather_object(infos, info)
+    busiest = max(infos, key=lambda i: i["rows"])
+    active = int((r["counts"] > 0).sum())
     module_exchange = module.exchange              # "nccl" if symmetric memory was not available
-    del experts, module
+    del experts, module, rq, rs
     torch.cuda.empty_cache()
-    flop = float(total.item()) * 2.0 * c["d"] * 3 * c["I"]
+    mean_rows = total.item() / world
     return {"workload": f"moe_layer E=256 d=7168 I=2048 tokens=32768 top8 {label}", "tokens_per_s": c["tokens"] / (ms.item() * 1e-3),
-            "ms_per_layer": ms.item(), "grouped_gemm_ms": gms.item(), "grouped_gemm_tflops": flop / (gms.item() * 1e-3) / 1e12,
-            "expert_weight_quant_ms": wq_ms, "max_rank_rows": int(load.item()), "mean_rank_rows": total.item() / world,
+            "ms_per_layer": ms.item(), "expert_weight_quant_ms": wq_ms, "max_rank_rows": int(load.item()),
+            "mean_rank_rows": mean_rows, "imbalance_bound_mean_over_max": mean_rows / max(1.0, load.item()),
+            "most_loaded_rank": {"rank": busiest["rank"], "rows": busiest["rows"], "phases_ms": busiest["phases"],
+                                 "grouped_gemm_ms": busiest["grouped_gemm_ms"], "grouped_gemm_tflops": busiest["grouped_gemm_tflops"],
+                                 "grouped_gemm_note": "up-projection + SwiGLU/quantise + down-projection alone, on the e4m3 rows "
+                                                      "this rank received in the traced call"},
+            "parity": {"sampled_tokens_per_rank": n_s, "max_rel_err": max(i["parity"]["max_rel_err"] for i in infos),
+                       "bit_equal_to_one_gpu_path": all(i["parity"]["bit_equal_to_one_gpu_path"] for i in infos),
+                       "ranks_checked": len(infos)},
             "active_experts_rank0_view": active, "scaling": "strong", "n_gpus": world,
             "token_chunks": chunks if world > 1 else 1, "exchange": module_exchange if world > 1 else "none"}
+
+
+# ---------------------------------------------------------------------------------------
+# End-to-end training step of the reference's model on the drop-in (data parallel where N > 1)
+# ---------------------------------------------------------------------------------------
+def bench_c5(dev, rank, world, steps=5, warmup=2, batch_size=32, seq_len=1024):
+    """The reference's ``Cinnamon`` model (d_model 512, 8 layers, MLA, 16 routed experts top-2 + 1 shared expert,
+    MTP depth 1, vocabulary 32000) with ``convert_to_fp8`` applied, on this library's ``kernels`` module: one
+    training step = host batch -> device, forward + backward under bf16 autocast (src/train.py:338-376), gradient
+    all-reduce (DistributedDataParallel over NCCL, as src/train.py:702), clip, AdamW.  Uniform random token ids,
+    ``batch_size`` x ``seq_len`` per GPU; tokens/s is the whole job's.  ``torch.compile`` is off."""
+    import torch.distributed as dist
+    sys.path.insert(0, ROOT)
+    from baseline import reference_model as RM
+    if not RM.available():
+        return {"workload": "config 5 end-to-end training step", "unavailable": "reference not staged (baseline/stage_reference.py)"}
+    torch.manual_seed(1005)
+    model, cfg, Kmod = RM.build_model(dev)
+    n_fp8 = sum(1 for m in model.modules() if isinstance(m, Kmod.FP8Linear))
+    model.train()
+    net = model
+    if world > 1:
+        from torch.nn.parallel import DistributedDataParallel as DDP
+        net = DDP(model, device_ids=[dev.index], find_unused_parameters=True)
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, weight_decay=0.1)
+    g = torch.Generator().manual_seed(1005 + rank)
+    host = torch.randint(0, cfg.vocab_size, (batch_size, seq_len + 1), generator=g).pin_memory()
+
+    def step():
+        return RM.train_step(net, host.to(dev, non_blocking=True), optimizer=opt)
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        loss = step()
+    sync()
+    launches0 = Kmod.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        loss = step()
+    e1.record()
+    sync()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    out = {"workload": "config 5: reference Cinnamon model + convert_to_fp8 on the drop-in kernels module, "
+                       f"{batch_size} x {seq_len} tokens per GPU, forward + backward + AdamW",
+           "tokens_per_s": world * batch_size * seq_len / (ms.item() * 1e-3), "ms_per_step": ms.item(), "n_gpus": world,
+           "parallelism": f"DistributedDataParallel x{world} (NCCL all-reduce of the gradients)" if world > 1 else "single GPU",
+           "scaling": "weak", "fp8_linear_layers": n_fp8, "library_launches_per_step": (Kmod.launch_count - launches0) / steps,
+           "loss": float(loss), "torch_compile": False, "device_status": Kmod.device_status()}
+    del net, model, opt
+    torch.cuda.empty_cache()
+    return out
 
 
 # ---------------------------------------------------------------------------------------
@@ -471,6 +736,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-moe", action="store_true", help="skip the MoE layer measurements")
+    ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel list (N = 1)")
+    ap.add_argument("--no-c5", action="store_true", help="skip the end-to-end training step of the reference's model")
     ap.add_argument("--moe-exchange", default="p2p-fused", choices=["nccl", "p2p", "p2p-fused"],
                     help="expert-parallel exchange (N > 1): all-to-all collectives, or peer stores into symmetric memory")
     ap.add_argument("--moe-chunks", type=int, default=1,
@@ -614,9 +881,17 @@ def main():
     h2d = x_h.numel() * 2 + dy_h.numel() * 2
     d2h = out_h.numel() * 2 + gx_h.numel() * 2 + gw_h.numel() * 4
 
+    # dense FP8 peak of this GPU (library GEMM), measured here: the denominator of the roofline fractions
+    # (the burst figure first and the per-kernel list right after it, while the part is cool; the two-second
+    # sustained loop afterwards, followed by a pause before anything else is timed)
     kernel_lines = []
-    if rank == 0 and world == 1 and not args.shape and not args.no_moe:
-        kernel_lines = bench_kernels(Kmod, dev, x, w, dy, measured_peaks()[0])
+    if rank == 0 and world == 1 and not args.shape and not args.no_kernels:
+        time.sleep(2.0)
+        burst = measure_fp8_peak(dev, sustained=False)
+        kernel_lines = bench_kernels(Kmod, dev, x, w, dy, measured_peaks()[0], (burst or {}).get("fp8_tflops"))
+    fp8 = measure_fp8_peak(dev) if rank == 0 else None
+    time.sleep(2.0)
+    barrier()
     moe_lines = []
     if not args.no_moe and not args.shape:
         del x, w, dy, out_h, gx_h, gw_h
@@ -626,6 +901,10 @@ def main():
                                        chunks=args.moe_chunks, exchange=args.moe_exchange))
         assert Kmod.device_status() == 0, "a kernel reported a device-side failure in the MoE layer"
 
+    c5_line = None
+    if not args.no_c5 and not args.shape:
+        c5_line = bench_c5(dev, rank, world)
+
     if rank == 0:
         peaks, peak_kind = measured_peaks()
         ms_per_step = ms_max / args.steps
@@ -633,22 +912,28 @@ def main():
         gemm_avg_ms = sum(gemm_ms) / max(1, len(gemm_ms))
         gemm_flop = 2.0 * M * N * K
         achieved = gemm_flop / (gemm_avg_ms * 1e-3) / 1e12 if gemm_ms else None
-        fp8_peak = 2.0 * float(peaks["bf16_tflops_sustained"])
+        if fp8 and "fp8_tflops_sustained" in fp8:
+            fp8_peak = float(fp8["fp8_tflops_sustained"])
+            peak_source = ("dense FP8 GEMM measured in this run, sustained (" + fp8["how"] + "); the GEMM launches are "
+                           "timed inside a long step, where the part sits at its power cap")
+        else:
+            fp8_peak = 2.0 * float(peaks["bf16_tflops_sustained"])
+            peak_source = (f"2 x bf16_tflops_sustained of {peak_kind} MEASURED_PEAKS (the FP8 library GEMM was not "
+                           f"available: {(fp8 or {}).get('unavailable')})")
         line = {
             "metric": "fp8_linear_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
-                       "l2": f"inputs larger than L2 (x {M * K * 2 >> 20} MiB, W {N * K * 4 >> 20} MiB, dy {M * N * 2 >> 20} MiB)"},
+            "config": bench_config(world),
             "roofline": {"kernel": "fp8_gemm_kernel / fp8_gemm_pair_kernel (forward, dgrad, wgrad launches averaged)", "bound": "tensor", "achieved": achieved, "peak": fp8_peak,
                          "unit": "TFLOP/s", "frac": (achieved / fp8_peak) if achieved else None,
-                         "peak_source": f"2 x bf16_tflops_sustained of {peak_kind} MEASURED_PEAKS (dense FP8 runs at twice "
-                                        "the bf16 rate; no FP8 figure is measured)",
+                         "peak_source": peak_source, "fp8_peak_measured": fp8,
+                         "frac_of_2x_bf16_sustained": (achieved / (2.0 * float(peaks["bf16_tflops_sustained"]))) if achieved else None,
                          "frac_of_nominal_4500": (achieved / 4500.0) if achieved else None,
                          "launches_timed": len(gemm_ms), "avg_launch_ms": gemm_avg_ms,
                          "traffic": GEMM_TRAFFIC_BYTES if not args.shape else None,
-                         "traffic_source": "ncu dram__bytes_read+write of the three GEMMs on the 8192x7168x9216 case, averaged, "
-                                           "x4 for the FFN launch (operands and output scale with M*N); profiles/"},
+                         "traffic_source": "ncu dram__bytes_read+write of the three GEMMs on a reduced case (8192x9216x7168), "
+                                           "averaged, scaled by the algorithmic bytes of the full launch (x3.1)"},
             "e2e": {"value": world * FLOP_PER_STEP / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
             "gpu_launches": launches,
@@ -658,6 +943,8 @@ def main():
             line["kernels"] = kernel_lines
         if moe_lines:
             line["moe"] = moe_lines
+        if c5_line:
+            line["c5"] = c5_line
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"], _ = run_cpu_baseline(256, repeats=1)
         emit(line)

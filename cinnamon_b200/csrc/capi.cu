@@ -74,6 +74,16 @@ int p2p_return(const void* rows, const int64_t* seg_start, const int64_t* home_b
                int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity, cudaStream_t st);
 int p2p_barrier(const int64_t* peer_flags, int me, int n_ranks, unsigned epoch, cudaStream_t st);
 long long set_p2p_wait_limit(long long cycles);
+int p2p_plan(const int64_t* my_counts, const int64_t* peer_counts, const int64_t* peer_flags, int me, int G, int E,
+             int flag_slot, unsigned epoch, int64_t* base_send, int64_t* my_start, int64_t* starts, int64_t* ends,
+             int64_t* seg_start, int64_t* home_base, int64_t* total_rows, cudaStream_t st);
+int p2p_dispatch_signal(const void* q, const float* s, const int64_t* token_indices, const int64_t* sorted_experts,
+                        const int64_t* base_send, const int64_t* my_start, const int64_t* peer_q, const int64_t* peer_s,
+                        int64_t n_pairs, int64_t n_tokens, int64_t d, int64_t ns, int e_local, int n_ranks, int64_t capacity,
+                        const int64_t* peer_flags, int me, int flag_slot, unsigned epoch, unsigned* done, cudaStream_t st);
+int p2p_row_table_wait(const int64_t* seg_start, const int64_t* home_base, const int64_t* peer_home, int64_t n_rows,
+                       int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity, long long* row_dst,
+                       const int64_t* peer_flags, int me, int flag_slot, unsigned epoch, cudaStream_t st);
 int64_t grouped_wgrad_scratch_bytes(int64_t max_rows, int64_t d_in, int64_t d_out);
 int fp8_grouped_wgrad(const void* dY, int dy_dtype, const void* x_q, const float* x_s, const int64_t* starts_host,
                       const int64_t* ends_host, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* scratch,
@@ -277,6 +287,30 @@ int cinn_p2p_barrier(const int64_t* peer_flags, int rank, int n_ranks, unsigned 
 }
 
 long long cinn_set_wait_limit_cycles(long long cycles) { return cinn::set_p2p_wait_limit(cycles); }
+
+int cinn_p2p_plan(const int64_t* my_counts, const int64_t* peer_counts, const int64_t* peer_flags, int rank, int n_ranks,
+                  int n_experts, int flag_slot, unsigned epoch, int64_t* base_send, int64_t* my_start, int64_t* starts,
+                  int64_t* ends, int64_t* seg_start, int64_t* home_base, int64_t* total_rows, void* stream) {
+    return cinn::p2p_plan(my_counts, peer_counts, peer_flags, rank, n_ranks, n_experts, flag_slot, epoch, base_send, my_start,
+                          starts, ends, seg_start, home_base, total_rows, (cudaStream_t)stream);
+}
+
+int cinn_p2p_dispatch_signal(const void* q, const float* s, const int64_t* token_indices, const int64_t* sorted_experts,
+                             const int64_t* base_send, const int64_t* my_start, const int64_t* peer_q, const int64_t* peer_s,
+                             int64_t n_pairs, int64_t n_tokens, int64_t d, int64_t n_scales, int experts_per_rank, int n_ranks,
+                             int64_t capacity_rows, const int64_t* peer_flags, int rank, int flag_slot, unsigned epoch,
+                             unsigned* done_counter, void* stream) {
+    return cinn::p2p_dispatch_signal(q, s, token_indices, sorted_experts, base_send, my_start, peer_q, peer_s, n_pairs, n_tokens,
+                                     d, n_scales, experts_per_rank, n_ranks, capacity_rows, peer_flags, rank, flag_slot, epoch,
+                                     done_counter, (cudaStream_t)stream);
+}
+
+int cinn_p2p_row_table_wait(const int64_t* seg_start, const int64_t* home_base, const int64_t* peer_home, int64_t n_rows,
+                            int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity_rows, int64_t* row_dst,
+                            const int64_t* peer_flags, int rank, int flag_slot, unsigned epoch, void* stream) {
+    return cinn::p2p_row_table_wait(seg_start, home_base, peer_home, n_rows, row_bytes, n_segments, n_ranks, capacity_rows,
+                                    (long long*)row_dst, peer_flags, rank, flag_slot, epoch, (cudaStream_t)stream);
+}
 
 int64_t cinn_moe_route_workspace_ints(int64_t n_tokens, int n_experts) {
     return cinn::moe_route_workspace_ints(n_tokens, n_experts);

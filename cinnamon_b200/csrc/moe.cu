@@ -267,12 +267,18 @@ __device__ int g_moe_status = 0;      // 0 = fine, otherwise (5 << 8) | reason
 
 // Dispatch: pair r of this rank (sorted by expert) -> the rank owning its expert, in that rank's expert-grouped
 // order.  Fuses `flat_x[token_indices]` (src/layers.py:140), the two dispatch all-to-alls and the regrouping.
+// SIGNAL: the CTA that finishes last tells every rank "all my rows have landed" (release store of `epoch` into
+// slot flag_slot + me of each rank's flag array), which replaces a separate barrier launch after the dispatch; the
+// consumer waits for the flags of all ranks (p2p_row_table with wait, or p2p_wait_flags).  `done` is a zeroed
+// device counter that the last CTA resets.
+template <bool SIGNAL>
 __global__ void __launch_bounds__(256)
 p2p_dispatch_kernel(const uint8_t* __restrict__ q, const float* __restrict__ s, const int64_t* __restrict__ token_indices,
                     const int64_t* __restrict__ sorted_experts, const int64_t* __restrict__ base_send,
                     const int64_t* __restrict__ my_start, const int64_t* __restrict__ peer_q,
                     const int64_t* __restrict__ peer_s, int64_t n_pairs, int64_t n_tokens, int d, int ns, int e_local,
-                    int n_ranks, int64_t capacity) {
+                    int n_ranks, int64_t capacity, const int64_t* __restrict__ peer_flags = nullptr, int me = 0,
+                    int flag_slot = 0, unsigned epoch = 0, unsigned* __restrict__ done = nullptr) {
     const int lane = threadIdx.x & 31;
     const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     const int64_t n_warps = (int64_t)gridDim.x * 8;
@@ -297,6 +303,21 @@ p2p_dispatch_kernel(const uint8_t* __restrict__ q, const float* __restrict__ s, 
         for (int v = lane; v < vecs; v += 32) out[v] = __ldg(in + v);
         float* so = reinterpret_cast<float*>(peer_s[rank]) + dst * ns;
         for (int c = lane; c < ns; c += 32) so[c] = s[tok * ns + c];
+    }
+    if constexpr (SIGNAL) {
+        __shared__ bool last;
+        __threadfence_system();                          // this thread's peer stores are visible system-wide
+        __syncthreads();
+        if (threadIdx.x == 0) last = atomicAdd(done, 1u) == gridDim.x - 1;
+        __syncthreads();
+        if (last) {
+            __threadfence_system();
+            if (threadIdx.x == 0) *done = 0;
+            if ((int)threadIdx.x < n_ranks) {
+                unsigned* remote = reinterpret_cast<unsigned*>(peer_flags[threadIdx.x]) + flag_slot + me;
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+            }
+        }
     }
 }
 
@@ -362,6 +383,165 @@ p2p_barrier_kernel(const int64_t* __restrict__ peer_flags, int me, int n_ranks, 
     }
 }
 
+// Bounded wait of thread g (< n_ranks) for slot flag_slot + g of this rank's own flag array to reach `epoch`.
+// Returns false (and records `code`) when the limit runs out.
+__device__ __forceinline__ bool p2p_wait_flag(const int64_t* peer_flags, int me, int g, int flag_slot, unsigned epoch,
+                                              long long wait_limit, int code) {
+    const unsigned* mine = reinterpret_cast<const unsigned*>(peer_flags[me]) + flag_slot + g;
+    const long long t0 = clock64();
+    for (unsigned spin = 1;; ++spin) {
+        unsigned seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+        if ((int)(seen - epoch) >= 0) return true;
+        if ((spin & 63u) == 0 && clock64() - t0 > wait_limit) {
+            atomicCAS(&g_moe_status, 0, code);
+            return false;
+        }
+    }
+}
+
+// The exchange plan in one launch (one CTA): this rank's routing counts (E) are written into slot `me` of every
+// rank's (G, E) count matrix in symmetric memory and flagged; once the counts of all ranks have arrived (bounded
+// wait) the address tables of the exchange are derived from the matrix - the arithmetic of p2p.exchange_tables:
+//   base_send[e]  destination row of my first pair of expert e, on the rank that owns e
+//   my_start[e]   first position of expert e among my sorted pairs
+//   starts/ends   row range of each of my local experts in my expert-grouped receive buffer
+//   seg_start     first row of segment (local expert, source rank), expert-major; last entry = total rows
+//   home_base     row on the source rank where that segment's outputs go
+// Replaces an all-gather of the counts plus about twenty small tensor operations per layer call.
+constexpr int PLAN_MAX_E = 1024, PLAN_MAX_G = 16;
+
+__global__ void __launch_bounds__(256)
+p2p_plan_kernel(const int64_t* __restrict__ my_counts, const int64_t* __restrict__ peer_counts,
+                const int64_t* __restrict__ peer_flags, int me, int G, int E, int flag_slot, unsigned epoch,
+                long long wait_limit, int64_t* __restrict__ base_send, int64_t* __restrict__ my_start,
+                int64_t* __restrict__ starts, int64_t* __restrict__ ends, int64_t* __restrict__ seg_start,
+                int64_t* __restrict__ home_base, int64_t* __restrict__ total_rows) {
+    __shared__ long long per_expert[PLAN_MAX_E];      // column sums
+    __shared__ long long starts_all[PLAN_MAX_E];      // first row of expert e on the rank that owns it
+    __shared__ long long row_total[PLAN_MAX_G];
+    __shared__ int ok_all;
+    const int tid = threadIdx.x;
+    const int e_local = E / G;
+    if (tid == 0) ok_all = 1;
+    // 1. my counts into every rank's matrix (my own included)
+    for (int i = tid; i < G * E; i += 256) {
+        const int g = i / E, e = i - g * E;
+        reinterpret_cast<long long*>(peer_counts[g])[(int64_t)me * E + e] = my_counts[e];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < G) {
+        unsigned* remote = reinterpret_cast<unsigned*>(peer_flags[tid]) + flag_slot + me;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+        if (!p2p_wait_flag(peer_flags, me, tid, flag_slot, epoch, wait_limit, (5 << 8) | 5)) ok_all = 0;
+    }
+    __syncthreads();
+    // 2. tables from the (G, E) matrix (read past L1: peers wrote it)
+    const long long* C = reinterpret_cast<const long long*>(peer_counts[me]);
+    for (int e = tid; e < E; e += 256) {
+        long long sum = 0;
+        for (int g = 0; g < G; ++g) sum += ok_all ? __ldcg(C + (int64_t)g * E + e) : 0;
+        per_expert[e] = sum;
+    }
+    __syncthreads();
+    if (tid < G) {                                   // thread r: running start of the experts owned by rank r
+        long long run = 0;
+        for (int el = 0; el < e_local; ++el) {
+            starts_all[tid * e_local + el] = run;
+            run += per_expert[tid * e_local + el];
+        }
+        row_total[tid] = run;
+    }
+    __syncthreads();
+    const int lo = me * e_local;
+    for (int e = tid; e < E; e += 256) {
+        long long below = 0;                          // rows of lower-ranked sources for expert e
+        for (int g = 0; g < me; ++g) below += ok_all ? __ldcg(C + (int64_t)g * E + e) : 0;
+        base_send[e] = starts_all[e] + below;
+    }
+    if (tid == 0) {                                  // my sorted pairs: exclusive running sum of my own counts
+        long long run = 0;
+        for (int e = 0; e < E; ++e) { my_start[e] = run; run += my_counts[e]; }
+        *total_rows = row_total[me];
+        seg_start[(int64_t)e_local * G] = row_total[me];
+    }
+    for (int el = tid; el < e_local; el += 256) {
+        starts[el] = starts_all[lo + el];
+        ends[el] = starts_all[lo + el] + per_expert[lo + el];
+        long long below = 0;
+        for (int g = 0; g < G; ++g) {
+            seg_start[(int64_t)el * G + g] = starts_all[lo + el] + below;
+            below += ok_all ? __ldcg(C + (int64_t)g * E + lo + el) : 0;
+        }
+    }
+    if (tid < G) {                                   // thread g: where rank g's pairs of my local experts sit in its sorted order
+        long long run = 0;
+        for (int e = 0; e < lo + e_local; ++e) {
+            if (e >= lo) home_base[(int64_t)(e - lo) * G + tid] = run;
+            run += ok_all ? __ldcg(C + (int64_t)tid * E + e) : 0;
+        }
+    }
+}
+
+int p2p_plan(const int64_t* my_counts, const int64_t* peer_counts, const int64_t* peer_flags, int me, int G, int E,
+             int flag_slot, unsigned epoch, int64_t* base_send, int64_t* my_start, int64_t* starts, int64_t* ends,
+             int64_t* seg_start, int64_t* home_base, int64_t* total_rows, cudaStream_t st) {
+    CINN_CHECK_ARG(G >= 1 && G <= PLAN_MAX_G && E >= G && E <= PLAN_MAX_E && E % G == 0 && me >= 0 && me < G && flag_slot >= 0,
+                   "p2p_plan: 1 <= ranks <= %d, experts <= %d and divisible by the ranks (got %d, %d)", PLAN_MAX_G, PLAN_MAX_E, G, E);
+    CINN_CHECK_ARG(my_counts && peer_counts && peer_flags && base_send && my_start && starts && ends && seg_start && home_base &&
+                   total_rows, "p2p_plan: null pointer");
+    p2p_plan_kernel<<<1, 256, 0, st>>>(my_counts, peer_counts, peer_flags, me, G, E, flag_slot, epoch,
+                                       g_p2p_wait_limit.load(std::memory_order_relaxed), base_send, my_start, starts, ends,
+                                       seg_start, home_base, total_rows);
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+// p2p_row_table that first waits (bounded) until every rank has flagged "all my rows have landed"
+// (p2p_dispatch_signal): the table is built - and the GEMMs that follow it on the stream start - only then.
+__global__ void __launch_bounds__(256)
+p2p_row_table_wait_kernel(const int64_t* __restrict__ seg_start, const int64_t* __restrict__ home_base,
+                          const int64_t* __restrict__ peer_home, int64_t n_rows, int n_segments, int n_ranks, int64_t row_bytes,
+                          int64_t capacity, long long* __restrict__ row_dst, const int64_t* __restrict__ peer_flags, int me,
+                          int flag_slot, unsigned epoch, long long wait_limit) {
+    if ((int)threadIdx.x < n_ranks) p2p_wait_flag(peer_flags, me, threadIdx.x, flag_slot, epoch, wait_limit, (5 << 8) | 6);
+    __syncthreads();
+    for (int64_t r = (int64_t)blockIdx.x * 256 + threadIdx.x; r < n_rows; r += (int64_t)gridDim.x * 256) {
+        int lo = 0, hi = n_segments;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (seg_start[mid + 1] > r) hi = mid; else lo = mid + 1;
+        }
+        long long addr = 0;
+        if (r < seg_start[n_segments]) {
+            if (lo < n_segments && seg_start[lo] <= r) {
+                const int64_t dst = home_base[lo] + (r - seg_start[lo]);
+                if (dst >= 0 && dst < capacity) addr = peer_home[lo % n_ranks] + dst * row_bytes;
+            }
+            if (addr == 0) atomicCAS(&g_moe_status, 0, (5 << 8) | 4);
+        }
+        row_dst[r] = addr;
+    }
+}
+
+int p2p_row_table_wait(const int64_t* seg_start, const int64_t* home_base, const int64_t* peer_home, int64_t n_rows,
+                       int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity, long long* row_dst,
+                       const int64_t* peer_flags, int me, int flag_slot, unsigned epoch, cudaStream_t st) {
+    CINN_CHECK_ARG(n_rows >= 0 && row_bytes >= 0 && n_segments >= 1 && n_ranks >= 1 && n_ranks <= 64 && capacity >= 0 &&
+                   me >= 0 && me < n_ranks && flag_slot >= 0, "p2p_row_table_wait: bad shape");
+    CINN_CHECK_ARG(seg_start && home_base && peer_home && peer_flags && (row_dst || n_rows == 0), "p2p_row_table_wait: null pointer");
+    CINN_CHECK_ARG(row_bytes % 16 == 0, "p2p_row_table_wait: the row size (%lld bytes) must be a multiple of 16", (long long)row_bytes);
+    int64_t blocks = (n_rows + 255) / 256;
+    if (blocks > 4096) blocks = 4096;
+    if (blocks < 1) blocks = 1;                                 // the wait happens even when there is no row
+    p2p_row_table_wait_kernel<<<(unsigned)blocks, 256, 0, st>>>(seg_start, home_base, peer_home, n_rows, n_segments, n_ranks,
+                                                               row_bytes, capacity, row_dst, peer_flags, me, flag_slot, epoch,
+                                                               g_p2p_wait_limit.load(std::memory_order_relaxed));
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
 int p2p_barrier(const int64_t* peer_flags, int me, int n_ranks, unsigned epoch, cudaStream_t st) {
     CINN_CHECK_ARG(peer_flags != nullptr && n_ranks >= 1 && n_ranks <= 64 && me >= 0 && me < n_ranks,
                    "p2p_barrier: 1 <= ranks <= 64 and 0 <= rank < ranks (got %d, %d)", n_ranks, me);
@@ -424,8 +604,31 @@ int p2p_dispatch(const void* q, const float* s, const int64_t* token_indices, co
     int64_t blocks = (n_pairs + 7) / 8;
     const int64_t cap = (int64_t)sm_count() * 16;
     if (blocks > cap) blocks = cap;
-    p2p_dispatch_kernel<<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)q, s, token_indices, sorted_experts, base_send, my_start,
-                                                         peer_q, peer_s, n_pairs, n_tokens, (int)d, (int)ns, e_local, n_ranks, capacity);
+    p2p_dispatch_kernel<false><<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)q, s, token_indices, sorted_experts, base_send,
+                                                                my_start, peer_q, peer_s, n_pairs, n_tokens, (int)d, (int)ns,
+                                                                e_local, n_ranks, capacity);
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+int p2p_dispatch_signal(const void* q, const float* s, const int64_t* token_indices, const int64_t* sorted_experts,
+                        const int64_t* base_send, const int64_t* my_start, const int64_t* peer_q, const int64_t* peer_s,
+                        int64_t n_pairs, int64_t n_tokens, int64_t d, int64_t ns, int e_local, int n_ranks, int64_t capacity,
+                        const int64_t* peer_flags, int me, int flag_slot, unsigned epoch, unsigned* done, cudaStream_t st) {
+    CINN_CHECK_ARG(n_pairs >= 0 && n_tokens >= 0 && d > 0 && ns >= 0 && e_local >= 1 && n_ranks >= 1 && n_ranks <= 64 &&
+                   capacity >= 0 && me >= 0 && me < n_ranks && flag_slot >= 0, "p2p_dispatch_signal: bad shape");
+    CINN_CHECK_ARG(q && s && token_indices && sorted_experts && base_send && my_start && peer_q && peer_s && peer_flags && done,
+                   "p2p_dispatch_signal: null pointer");
+    CINN_CHECK_ARG(d % 16 == 0 && d < (1LL << 31) && ns < (1LL << 31),
+                   "p2p_dispatch_signal: the row width (%lld) must be a multiple of 16", (long long)d);
+    CINN_CHECK_ARG((reinterpret_cast<uintptr_t>(q) & 15) == 0, "p2p_dispatch_signal: q must be 16-byte aligned");
+    int64_t blocks = (n_pairs + 7) / 8;                     // with no rows one CTA still signals
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    p2p_dispatch_kernel<true><<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)q, s, token_indices, sorted_experts, base_send,
+                                                               my_start, peer_q, peer_s, n_pairs, n_tokens, (int)d, (int)ns,
+                                                               e_local, n_ranks, capacity, peer_flags, me, flag_slot, epoch, done);
     CINN_CHECK_LAUNCH();
     return CINN_OK;
 }

@@ -480,6 +480,8 @@ class FP8Linear(torch.nn.Module):
                     else:
                         self._w_cache = (key, quantize_fp8_blockwise(wf, 128, 128))
             out = FP8MatmulFunction.apply(x, w, self.round_scale, self._w_cache[1])
+        elif x.is_cuda and _ops is not None and torch.compiler.is_compiling():
+            out = _ops.fp8_linear(x, self.weight, self.round_scale)       # one opaque graph node under torch.compile
         elif x.is_cuda:
             out = FP8MatmulFunction.apply(x, self.weight, self.round_scale)
         else:
@@ -762,6 +764,37 @@ def p2p_dispatch(x_fp8, x_scale, token_indices, sorted_experts, base_send, my_st
     _count()
 
 
+def p2p_dispatch_signal(x_fp8, x_scale, token_indices, sorted_experts, tables, buffers) -> None:
+    """``p2p_dispatch`` whose last CTA flags "all my rows have landed" to every rank (``cinn_p2p_dispatch_signal``);
+    ``tables``: what ``buffers.plan`` returned for this layer call, ``buffers``: a ``p2p.PeerBuffers``."""
+    assert x_fp8.is_cuda, "Inputs must be on CUDA"
+    n_tokens, d = x_fp8.shape
+    x_fp8, x_scale = x_fp8.contiguous(), x_scale.float().contiguous()
+    b = buffers
+    with torch.cuda.device(x_fp8.device):
+        _lib.check(_L.cinn_p2p_dispatch_signal(_ptr(x_fp8), _ptr(x_scale), _ptr(token_indices), _ptr(sorted_experts),
+                                               _ptr(tables.base_send), _ptr(tables.my_start), _ptr(b.peer_q), _ptr(b.peer_s),
+                                               token_indices.numel(), n_tokens, d, x_scale.shape[1], b.n_experts // b.world,
+                                               b.world, b.capacity_rows, _ptr(b.peer_flags), b.rank, b.LANDED_SLOT,
+                                               b._call & 0x7FFFFFFF, _ptr(b.done), _stream(x_fp8)), "cinn_p2p_dispatch_signal")
+    _count()
+
+
+def p2p_row_table_wait(tables, buffers, n_rows: int, row_bytes: int) -> torch.Tensor:
+    """``p2p_row_table`` that first waits for the "landed" flags of all ranks (``cinn_p2p_row_table_wait``)."""
+    b = buffers
+    dev = b.flags.device
+    with torch.cuda.device(dev):
+        table = torch.empty(max(n_rows, 1), dtype=torch.int64, device=dev)[:n_rows]
+        _lib.check(_L.cinn_p2p_row_table_wait(_ptr(tables.seg_start), _ptr(tables.home_base), _ptr(b.peer_home), n_rows,
+                                              row_bytes, tables.home_base.numel(), b.world, b.home_rows, _ptr(table),
+                                              _ptr(b.peer_flags), b.rank, b.LANDED_SLOT, b._call & 0x7FFFFFFF,
+                                              ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)),
+                   "cinn_p2p_row_table_wait")
+    _count()
+    return table
+
+
 def p2p_return(rows, seg_start, home_base, peer_home, n_ranks: int, capacity_rows: int) -> None:
     """Writes this rank's expert outputs straight into the home buffers of the ranks the tokens live on
     (``cinn_p2p_return``)."""
@@ -894,9 +927,34 @@ def moe_grouped_gemm(sorted_x: torch.Tensor, weights: torch.Tensor, expert_start
     to e4m3 on the fly; returns fp16 like the reference unless ``dtype`` says otherwise.
     Unlike the reference it is differentiable (``MoEGroupedGemmFunction``)."""
     assert sorted_x.is_cuda and weights.is_cuda, "Inputs must be on CUDA"
+    if _ops is not None and torch.compiler.is_compiling():
+        return _ops.grouped_gemm(sorted_x, weights, expert_starts, expert_ends, dtype)
     if torch.is_grad_enabled() and (sorted_x.requires_grad or weights.requires_grad):
         return MoEGroupedGemmFunction.apply(sorted_x, weights, expert_starts, expert_ends, dtype)
     x = sorted_x if sorted_x.stride(-1) == 1 else sorted_x.contiguous()
     x_fp8, x_scale = quantize_fp8_rowwise(x, block_size=128)
     w_fp8, w_scale = quantize_expert_weights(weights)
     return fp8_grouped_gemm(x_fp8, x_scale, w_fp8, w_scale, expert_starts, expert_ends, out_dtype=dtype)
+
+
+# -----------------------------------------------------------------------------
+# torch.compile: the differentiable entry points as torch.library operators (cinnamon_b200/ops.py)
+# -----------------------------------------------------------------------------
+try:
+    from . import ops as _ops
+except Exception as _exc:                                   # noqa: BLE001  (an older torch without torch.library.custom_op)
+    import warnings
+    warnings.warn(f"cinnamon_b200: torch.library operators were not registered ({type(_exc).__name__}: {_exc}); "
+                  "torch.compile will break the graph at every call into the library")
+    _ops = None
+
+_sparse_attention_eager = sparse_attention
+
+
+def sparse_attention(q, k, v, idx, scale=None):             # noqa: F811
+    """Attention over the K selected positions of every query (reference src/kernels.py:1292-1312).
+    q, k: [B, H, L, D_qk]; v: [B, H, L, D_v]; idx: [B, L, K] int64.  Returns ``(output, attn_weights)``.
+    Under ``torch.compile`` the call is one opaque graph node (``cinnamon_b200::sparse_attn_fwd``)."""
+    if _ops is not None and torch.compiler.is_compiling():
+        return _ops.sparse_attention(q, k, v, idx, q.shape[-1] ** -0.5 if scale is None else scale)
+    return _sparse_attention_eager(q, k, v, idx, scale)

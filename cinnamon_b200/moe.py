@@ -106,7 +106,8 @@ class FP8Experts:
         self.w3_q, self.w3_s = self.K.quantize_expert_weights(w3)
 
     def __call__(self, x_q: torch.Tensor, x_s: torch.Tensor, starts: torch.Tensor, ends: torch.Tensor,
-                 out_dtype=torch.bfloat16, row_dst: torch.Tensor = None, n_rows_dev: torch.Tensor = None) -> torch.Tensor:
+                 out_dtype=torch.bfloat16, row_dst: torch.Tensor = None, n_rows_dev: torch.Tensor = None,
+                 trace: Optional[list] = None) -> torch.Tensor:
         """x_q (R, d) e4m3 rows grouped by expert, x_s (R, d/128) -> (R, d) ``out_dtype``.
         Rows outside [starts[0], ends[-1]) are not written.  With ``row_dst`` (one byte address per row) the
         down-projection stores every output row there instead (possibly on a peer GPU) and nothing is returned.
@@ -114,11 +115,16 @@ class FP8Experts:
         capacity that no expert range covers)."""
         K = self.K
         h12 = K.fp8_grouped_gemm(x_q, x_s, self.w12_q, self.w12_s, starts, ends, out_dtype=torch.bfloat16)
+        _mark(trace, "grouped GEMM up-projection")
         h_q, h_s = K.swiglu_quantize_rowwise(h12, n_rows_dev)
+        _mark(trace, "SwiGLU + quantise")
         if row_dst is not None:
             K.fp8_grouped_gemm_scatter(h_q, h_s, self.w3_q, self.w3_s, starts, ends, row_dst, out_dtype=out_dtype)
+            _mark(trace, "grouped GEMM down-projection (+ rows stored at their home ranks)")
             return None
-        return K.fp8_grouped_gemm(h_q, h_s, self.w3_q, self.w3_s, starts, ends, out_dtype=out_dtype)
+        out = K.fp8_grouped_gemm(h_q, h_s, self.w3_q, self.w3_s, starts, ends, out_dtype=out_dtype)
+        _mark(trace, "grouped GEMM down-projection")
+        return out
 
 
 class FP8SwiGLU:
@@ -247,7 +253,8 @@ def all_to_all_rows(rows: torch.Tensor, send_splits, recv_splits, group=None) ->
 # the layer
 # ---------------------------------------------------------------------------------------
 def moe_forward(x: torch.Tensor, routing: Routing, experts: Callable, quantize: Optional[Callable],
-                group=None, addend: Optional[torch.Tensor] = None, before_combine: Optional[Callable] = None) -> torch.Tensor:
+                group=None, addend: Optional[torch.Tensor] = None, before_combine: Optional[Callable] = None,
+                trace: Optional[list] = None) -> torch.Tensor:
     """Routed part of ``MoE.forward`` for this rank's tokens ``x`` (T, d).
 
     ``experts(rows_q, rows_s, starts, ends)`` computes the expert SwiGLU for rows grouped by
@@ -255,6 +262,7 @@ def moe_forward(x: torch.Tensor, routing: Routing, experts: Callable, quantize: 
     unquantised and ``experts`` receives ``(rows, None, starts, ends)``: the CPU test path).
     ``addend`` (T, d), optional: the shared experts' output, folded into the combine pass
     (``shared_out + routed_out``, src/layers.py:179); ``before_combine`` is called right before that pass.
+    (``moe_forward_p2p`` also takes a callable that produces it, called once the dispatch has been enqueued.)
     Returns the gate-weighted sum over each token's experts (plus ``addend``), fp32 (T, d).
     """
     T, d = x.shape
@@ -267,7 +275,9 @@ def moe_forward(x: torch.Tensor, routing: Routing, experts: Callable, quantize: 
         recv_s = all_to_all_rows(send_s, plan.send_splits, plan.recv_splits, group)
         if len(plan.recv_splits) > 1:
             recv_q, recv_s = K.gather_quantized_rows(recv_q, recv_s, plan.perm)
-        out_rows = experts(recv_q, recv_s, plan.starts, plan.ends)
+        _mark(trace, "quantise + gather" + (" + all-to-all + regroup" if len(plan.recv_splits) > 1 else ""))
+        out_rows = experts(recv_q, recv_s, plan.starts, plan.ends, trace=trace) if trace is not None else \
+            experts(recv_q, recv_s, plan.starts, plan.ends)
     else:
         send = x.index_select(0, routing.token_indices)
         recv = all_to_all_rows(send, plan.send_splits, plan.recv_splits, group)
@@ -287,18 +297,31 @@ def moe_forward(x: torch.Tensor, routing: Routing, experts: Callable, quantize: 
         before_combine()                       # e.g. join the stream that produced ``addend``
     if out_rows.is_cuda:
         from . import kernels as K
-        return K.moe_combine(out_rows, routing.pair_pos, routing.pair_gate, addend)   # src/layers.py:157-160, fused
+        if len(plan.recv_splits) > 1:
+            _mark(trace, "inverse permutation + all-to-all home")
+        y = K.moe_combine(out_rows, routing.pair_pos, routing.pair_gate, addend)      # src/layers.py:157-160, fused
+        _mark(trace, "combine (+ shared expert output)")
+        return y
     weighted = out_rows.float() * routing.sorted_scores[:, None]                 # host-logic tests (CPU ranks)
     y = torch.zeros(T, d, dtype=torch.float32, device=x.device)
     y.index_add_(0, routing.token_indices, weighted)
     return y if addend is None else addend.float() + y
 
 
+def _mark(trace: Optional[list], name: str) -> None:
+    """Phase timing for the benchmark: appends (name, CUDA event recorded on the current stream) when tracing."""
+    if trace is not None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        trace.append((name, ev))
+
+
 def moe_forward_p2p(x: torch.Tensor, routing: Routing, experts: Callable, quantize: Callable, buffers, group=None,
                     addend: Optional[torch.Tensor] = None, before_combine: Optional[Callable] = None,
-                    fused_return: bool = False) -> torch.Tensor:
+                    fused_return: bool = False, trace: Optional[list] = None) -> torch.Tensor:
     """``moe_forward`` with the exchange done by peer stores over NVLink (``cinnamon_b200/p2p.py``) instead of
-    all-to-all collectives: one small all-gather of the routing counts, then every quantised row is written
+    all-to-all collectives: the routing counts of all ranks are exchanged (by the plan kernel itself with
+    ``fused_return``, else by one small all-gather), then every quantised row is written
     straight to its place in the expert-grouped buffer of the rank that owns its expert, and every expert output
     straight to its pair's place on the rank its token lives on.  No gather, regrouping or inverse permutation
     passes, no send/receive kernels; three stream-ordered barriers order the phases.  One host read-back (the
@@ -311,16 +334,47 @@ def moe_forward_p2p(x: torch.Tensor, routing: Routing, experts: Callable, quanti
     world, me = dist.get_world_size(group), dist.get_rank(group)
     n_experts = routing.counts.numel()
     e_local = n_experts // world
+    n_pairs = routing.token_indices.numel()
+    assert n_pairs <= buffers.home_rows, "peer buffers too small"
+    if fused_return and buffers.n_experts == n_experts:
+        # Thirteen launches per layer call, no collective, no host read-back:
+        #   plan        counts to every rank, wait for all, address tables (also: every rank is done with the buffers)
+        #   dispatch    rows straight into the owners' expert-grouped buffers; its last CTA flags "landed"
+        #   row table   waits for the flags of all ranks, then the home address of every output row
+        #   experts     up-projection, SwiGLU + quantise, down-projection storing every row at its home
+        #   barrier     every expert output is home
+        t = buffers.plan(routing.counts.to(torch.int64).contiguous())
+        _mark(trace, "plan (counts to all ranks + tables)")
+        x_q, x_s = quantize(x)
+        _mark(trace, "quantise tokens")
+        K.p2p_dispatch_signal(x_q, x_s, routing.token_indices, routing.sorted_experts, t, buffers)
+        _mark(trace, "dispatch (peer stores)")
+        if callable(addend):
+            addend = addend()                           # the shared expert, on its own stream, from here on
+        cap = buffers.capacity_rows
+        recv_q = buffers.q.view(cap, buffers.d).view(x_q.dtype)
+        recv_s = buffers.s.view(cap, buffers.n_scales)
+        table = K.p2p_row_table_wait(t, buffers, cap, buffers.d * 2)
+        _mark(trace, "wait for all rows + address table")
+        experts(recv_q, recv_s, t.starts, t.ends, row_dst=table, n_rows_dev=t.total_rows, trace=trace)
+        buffers.barrier()                               # every expert output is home
+        _mark(trace, "barrier (outputs home)")
+        home = buffers.home.view(buffers.home_rows, buffers.d)[:n_pairs]
+        if before_combine is not None:
+            before_combine()
+        y = K.moe_combine(home, routing.pair_pos, routing.pair_gate, addend)
+        _mark(trace, "combine (+ shared expert output)")
+        return y
+    if callable(addend):
+        addend = addend()
     counts_all = torch.empty((world, n_experts), dtype=torch.int64, device=x.device)
     dist.all_gather_into_tensor(counts_all, routing.counts.to(torch.int64).contiguous(), group=group)
     t = p2p.exchange_tables(counts_all, me)
     x_q, x_s = quantize(x)
-    n_pairs = routing.token_indices.numel()
     buffers.barrier()                                   # every rank is done with the buffers' previous contents
     K.p2p_dispatch(x_q, x_s, routing.token_indices, routing.sorted_experts, t.base_send, t.my_start, buffers.peer_q,
                    buffers.peer_s, e_local, world, buffers.capacity_rows)
     buffers.barrier()                                   # every row has landed
-    assert n_pairs <= buffers.home_rows, "peer buffers too small"
     if fused_return:
         # The down-projection's epilogue stores every finished row straight to its home: the way home runs under
         # the GEMM.  Nothing here needs the number of received rows on the host: the GEMMs walk the device-side
@@ -471,8 +525,19 @@ class ExpertParallelMoE(torch.nn.Module):
 
     def __init__(self, router_weight: torch.Tensor, expert_bias: torch.Tensor, w12_local: torch.Tensor,
                  w3_local: torch.Tensor, top_k: int, group=None, shared: Optional[FP8SwiGLU] = None, n_chunks: int = 1,
-                 exchange: str = "nccl"):
+                 exchange: str = "nccl", max_tokens_per_rank: Optional[int] = None, check_status_every: int = 0):
+        """``max_tokens_per_rank`` (peer-store exchanges): the largest number of tokens any rank will ever bring to a
+        call; it sizes the receive buffers, whose allocation is a collective, so it must be the same on every rank.
+        When omitted the first call agrees on it (one all-reduce of the ranks' token counts, on the first call
+        only); a later call with more tokens raises instead of re-allocating (a rank re-allocating on its own would
+        leave the others waiting).  ``check_status_every``: read the device status word every so many calls (a host
+        synchronisation) and raise when a bounded wait ran out or a row was dropped; 0 = never, the caller polls
+        ``kernels.device_status()`` itself.  The output of a call that left a non-zero status is invalid."""
         super().__init__()
+        self.max_tokens_per_rank = max_tokens_per_rank
+        self.check_status_every = int(check_status_every)
+        self._calls = 0
+        self.trace = None                            # set to a list to collect (phase, CUDA event) pairs of a call
         assert exchange in ("nccl", "p2p", "p2p-fused"), \
             "exchange: 'nccl' (all-to-all collectives), 'p2p' (peer stores) or 'p2p-fused' (way home from the GEMM epilogue)"
         self.exchange = exchange
@@ -504,40 +569,75 @@ class ExpertParallelMoE(torch.nn.Module):
         router = self._router_as(flat.dtype)
         world = dist.get_world_size(self.group) if dist.is_initialized() else 1
         sh, join = None, None
+        if self.trace is not None and flat.is_cuda:
+            _mark(self.trace, "start")
+        else:
+            self.trace = None
+        launch_shared = None
         if self.shared is not None and world > 1 and flat.is_cuda:
-            # the shared expert needs nothing from the exchange: it runs on a second stream, under the
-            # all-to-alls and the host read-back of the split sizes, and is joined before the combine pass
+            # The shared expert needs nothing from the exchange: it runs on a second stream and is joined before the
+            # combine pass.  It is enqueued once the routing (and, with peer stores, the dispatch) has been: its GEMMs
+            # take every SM, and launched first they would hold up the routing that every other rank waits for.
             cur = torch.cuda.current_stream(flat.device)
             if self._side is None:
                 self._side = torch.cuda.Stream(flat.device)
-            self._side.wait_stream(cur)
-            with torch.cuda.stream(self._side):
-                sh = self.shared(flat)
-            sh.record_stream(cur)
+
+            def launch_shared():
+                self._side.wait_stream(cur)
+                with torch.cuda.stream(self._side):
+                    out = self.shared(flat)
+                out.record_stream(cur)
+                return out
             join = lambda: cur.wait_stream(self._side)                    # noqa: E731
         elif self.shared is not None:
             sh = self.shared(flat)
+            _mark(self.trace, "shared expert (on the main stream: one rank)")
         if world > 1 and self.exchange in ("p2p", "p2p-fused") and flat.is_cuda:
             from . import p2p
             r = route(flat, router, self.expert_bias, self.top_k)
-            n_pairs, d = flat.shape[0] * self.top_k, flat.shape[1]
-            if self._peer_buffers is None or not self._peer_buffers.fits(n_pairs * world, n_pairs, d, (d + 127) // 128):
-                # worst case: every pair of every rank routed to this rank's experts (all ranks bring equally many tokens)
+            _mark(self.trace, "router GEMM + routing")
+            T, d = flat.shape
+            if self._peer_buffers is None:
+                if self.max_tokens_per_rank is None:
+                    # first call: the ranks agree on the largest token count among them (they all are in their first call)
+                    m = torch.tensor([T], dtype=torch.int64, device=flat.device)
+                    dist.all_reduce(m, op=dist.ReduceOp.MAX, group=self.group)
+                    self.max_tokens_per_rank = int(m.item())
+                home_rows = self.max_tokens_per_rank * self.top_k
                 try:
-                    self._peer_buffers = p2p.PeerBuffers(self.group, flat.device, n_pairs * world, n_pairs, d, (d + 127) // 128)
+                    # worst case: every pair of every rank routed to this rank's experts
+                    self._peer_buffers = p2p.PeerBuffers(self.group, flat.device, home_rows * world, home_rows, d,
+                                                         (d + 127) // 128, n_experts=self.router_weight.shape[0])
                 except Exception as exc:                    # noqa: BLE001  (no symmetric memory here: the same on every rank)
                     import warnings
                     warnings.warn(f"symmetric memory is not available ({type(exc).__name__}: {exc}); "
                                   "the expert-parallel exchange uses all-to-all collectives instead")
                     self.exchange = "nccl"
                     return self.forward(x)
-            y = moe_forward_p2p(flat, r, self.experts, self.K.quantize_fp8_rowwise, self._peer_buffers, self.group, addend=sh,
-                                before_combine=join, fused_return=self.exchange == "p2p-fused")
+            if T > self.max_tokens_per_rank or d != self._peer_buffers.d:
+                raise ValueError(f"{T} tokens of width {d} in this call, but the peer buffers were sized for at most "
+                                 f"{self.max_tokens_per_rank} tokens of width {self._peer_buffers.d} per rank: construct the "
+                                 "layer with max_tokens_per_rank set to the largest batch (the same value on every rank)")
+            y = moe_forward_p2p(flat, r, self.experts, self.K.quantize_fp8_rowwise, self._peer_buffers, self.group,
+                                addend=launch_shared if launch_shared is not None else sh,
+                                before_combine=join, fused_return=self.exchange == "p2p-fused", trace=self.trace)
+            self._calls += 1
+            if self.check_status_every and self._calls % self.check_status_every == 0:
+                status = self.K.device_status()
+                if status:
+                    raise RuntimeError(f"expert-parallel exchange: device status {status >> 8}/{status & 255} (a bounded wait "
+                                       "ran out or a row fell outside a buffer); the outputs since the last check are invalid")
         elif world > 1 and self.n_chunks > 1 and flat.shape[0] >= self.n_chunks:
             routings = [route(c, router, self.expert_bias, self.top_k) for c in torch.tensor_split(flat, self.n_chunks)]
+            if launch_shared is not None:
+                sh = launch_shared()
             y = moe_forward_pipelined(flat, routings, self.experts, self.K.quantize_fp8_rowwise, self.group, addend=sh,
                                       before_combine=join)
         else:
             r = route(flat, router, self.expert_bias, self.top_k)
-            y = moe_forward(flat, r, self.experts, self.K.quantize_fp8_rowwise, self.group, addend=sh, before_combine=join)
+            _mark(self.trace, "router GEMM + routing")
+            if launch_shared is not None:
+                sh = launch_shared()
+            y = moe_forward(flat, r, self.experts, self.K.quantize_fp8_rowwise, self.group, addend=sh, before_combine=join,
+                            trace=self.trace)
         return y.reshape(x.shape)

@@ -65,7 +65,10 @@ class PeerBuffers:
     """The three receive buffers of one rank, allocated in symmetric memory and mapped into every rank of the
     group, plus the device arrays of peer base addresses that the kernels take.  Creating it is a collective."""
 
-    def __init__(self, group, device, capacity_rows: int, home_rows: int, d: int, n_scales: int):
+    # flag slots: [0, 64) the barrier, [64, 128) "my routing counts are in your matrix", [128, 192) "my rows have landed"
+    PLAN_SLOT, LANDED_SLOT = 64, 128
+
+    def __init__(self, group, device, capacity_rows: int, home_rows: int, d: int, n_scales: int, n_experts: int = 0):
         import os
         import torch.distributed as dist
         # The exchange uses plain peer stores only.  PyTorch would otherwise also bind the buffers to an NVLink
@@ -78,13 +81,25 @@ class PeerBuffers:
         self.q = symm_mem.empty(self.capacity_rows * d, dtype=torch.uint8, device=device)
         self.s = symm_mem.empty(self.capacity_rows * n_scales, dtype=torch.float32, device=device)
         self.home = symm_mem.empty(self.home_rows * d, dtype=torch.bfloat16, device=device)
-        self.flags = symm_mem.empty(64, dtype=torch.int32, device=device)
+        self.flags = symm_mem.empty(256, dtype=torch.int32, device=device)
         self.flags.zero_()
-        self._handles = [symm_mem.rendezvous(t, self.group) for t in (self.q, self.s, self.home, self.flags)]
-        as_dev = lambda h: torch.tensor([int(p) for p in h.buffer_ptrs], dtype=torch.int64, device=device)   # noqa: E731
-        self.peer_q, self.peer_s, self.peer_home, self.peer_flags = (as_dev(h) for h in self._handles)
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.n_experts = int(n_experts)
+        # every rank's routing counts, one row per source rank (written by the ranks themselves, cinn_p2p_plan)
+        self.counts = symm_mem.empty(max(1, self.world * self.n_experts), dtype=torch.int64, device=device)
+        self.counts.zero_()
+        self._handles = [symm_mem.rendezvous(t, self.group) for t in (self.q, self.s, self.home, self.flags, self.counts)]
+        as_dev = lambda h: torch.tensor([int(p) for p in h.buffer_ptrs], dtype=torch.int64, device=device)   # noqa: E731
+        self.peer_q, self.peer_s, self.peer_home, self.peer_flags, self.peer_counts = (as_dev(h) for h in self._handles)
         self._epoch = 0
+        self._call = 0                                  # layer calls so far: the epoch of the plan / landed flags
+        self.done = torch.zeros(1, dtype=torch.int32, device=device)
+        if self.n_experts:
+            e_local = self.n_experts // self.world
+            i64 = lambda n: torch.empty(n, dtype=torch.int64, device=device)                                 # noqa: E731
+            self._tables = ExchangeTables(base_send=i64(self.n_experts), my_start=i64(self.n_experts), starts=i64(e_local),
+                                          ends=i64(e_local), seg_start=i64(e_local * self.world + 1),
+                                          home_base=i64(e_local * self.world), total_rows=i64(1))
         torch.cuda.synchronize(device)
         dist.barrier(self.group)                        # every rank's flags are zero before anyone signals
 
@@ -98,6 +113,25 @@ class PeerBuffers:
         with torch.cuda.device(self.flags.device):
             _lib.check(_lib.lib.cinn_p2p_barrier(ctypes.c_void_p(self.peer_flags.data_ptr()), self.rank, self.world,
                                                  self._epoch & 0x7FFFFFFF, stream), "cinn_p2p_barrier")
+
+    def plan(self, counts: torch.Tensor) -> "ExchangeTables":
+        """One launch (``cinn_p2p_plan``): this rank's routing counts go to every rank, the counts of all ranks are
+        awaited (bounded), and the address tables of ``exchange_tables`` come out.  Starts a new layer call: the
+        epoch it uses is the one ``dispatch_signal`` / ``row_table_wait`` of the same call use.  The tables are
+        buffers owned by this object, overwritten by the next call."""
+        import ctypes
+        from . import _lib
+        assert self.n_experts and counts.numel() == self.n_experts and counts.dtype == torch.int64 and counts.is_contiguous()
+        self._call += 1
+        t = self._tables
+        p = lambda x: ctypes.c_void_p(x.data_ptr())                                                          # noqa: E731
+        stream = ctypes.c_void_p(torch.cuda.current_stream(self.flags.device).cuda_stream)
+        with torch.cuda.device(self.flags.device):
+            _lib.check(_lib.lib.cinn_p2p_plan(p(counts), p(self.peer_counts), p(self.peer_flags), self.rank, self.world,
+                                              self.n_experts, self.PLAN_SLOT, self._call & 0x7FFFFFFF, p(t.base_send),
+                                              p(t.my_start), p(t.starts), p(t.ends), p(t.seg_start), p(t.home_base),
+                                              p(t.total_rows), stream), "cinn_p2p_plan")
+        return t
 
     def fits(self, capacity_rows: int, home_rows: int, d: int, n_scales: int) -> bool:
         return (capacity_rows <= self.capacity_rows and home_rows <= self.home_rows and d == self.d

@@ -292,6 +292,35 @@ int cinn_p2p_barrier(const int64_t* peer_flags, int rank, int n_ranks, unsigned 
  * (the reference has no device-side waits). */
 long long cinn_set_wait_limit_cycles(long long cycles);
 
+/* The exchange plan of an expert-parallel layer call in one launch (no reference counterpart: the reference keeps
+ * every expert on every rank, src/layers.py:89-179).  my_counts (n_experts int64, device): pairs this rank routed
+ * to every global expert.  peer_counts: DEVICE array of n_ranks base addresses of the ranks' (n_ranks, n_experts)
+ * int64 count matrices in symmetric memory; peer_flags as in cinn_p2p_barrier, flag slots
+ * [flag_slot, flag_slot + n_ranks) are used with `epoch` (1, 2, 3, ... the same on every rank).  The kernel writes
+ * this rank's counts into row `rank` of every matrix, flags it, waits (bounded, code (5 << 8) | 5 on expiry) for
+ * the rows of all ranks, and derives the address tables of the exchange:
+ *   base_send, my_start (n_experts); starts, ends (n_experts / n_ranks); seg_start (n_experts / n_ranks * n_ranks + 1);
+ *   home_base (n_experts / n_ranks * n_ranks); total_rows (1)   - all int64, device.
+ * Every rank must run on a GPU of its own.  Passing this kernel also means every rank has finished what it had
+ * enqueued before it, so the receive buffers of the previous layer call are free. */
+int cinn_p2p_plan(const int64_t* my_counts, const int64_t* peer_counts, const int64_t* peer_flags, int rank, int n_ranks,
+                  int n_experts, int flag_slot, unsigned epoch, int64_t* base_send, int64_t* my_start, int64_t* starts,
+                  int64_t* ends, int64_t* seg_start, int64_t* home_base, int64_t* total_rows, void* stream);
+
+/* cinn_p2p_dispatch whose last CTA flags "all my rows have landed" to every rank (slot flag_slot + rank, value
+ * epoch); done_counter: one zeroed uint32 in device memory, left zero.  Pairs with cinn_p2p_row_table_wait. */
+int cinn_p2p_dispatch_signal(const void* q, const float* s, const int64_t* token_indices, const int64_t* sorted_experts,
+                             const int64_t* base_send, const int64_t* my_start, const int64_t* peer_q, const int64_t* peer_s,
+                             int64_t n_pairs, int64_t n_tokens, int64_t d, int64_t n_scales, int experts_per_rank, int n_ranks,
+                             int64_t capacity_rows, const int64_t* peer_flags, int rank, int flag_slot, unsigned epoch,
+                             unsigned* done_counter, void* stream);
+
+/* cinn_p2p_row_table that first waits (bounded, code (5 << 8) | 6 on expiry) for the flags of cinn_p2p_dispatch_signal
+ * from all ranks: work enqueued after it sees every dispatched row. */
+int cinn_p2p_row_table_wait(const int64_t* seg_start, const int64_t* home_base, const int64_t* peer_home, int64_t n_rows,
+                            int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity_rows, int64_t* row_dst,
+                            const int64_t* peer_flags, int rank, int flag_slot, unsigned epoch, void* stream);
+
 /* Routing of MoE.forward (src/layers.py:122-148) on the device: scores = sigmoid(logits), the top_k experts of
  * scores + bias per token (ties: the lower expert id), gates = score / (sum of the k scores + 1e-9), and the
  * (token, expert) pairs sorted by expert in the order of a stable sort.

@@ -286,8 +286,12 @@ dist.barrier(); dist.destroy_process_group()
 '''
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_expert_parallel_two_gpus_match_one(K, tmp_path):
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_expert_parallel_matches_one_gpu(K, tmp_path, world):
+    """Every exchange (all-to-all, chunked, peer stores, peer stores from the GEMM epilogue) on 2, 4 or 8 GPUs, one
+    process each, against the one-GPU layer on the same tokens: bit-identical outputs."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs, this machine shows {torch.cuda.device_count()}")
     from cinnamon_b200 import moe
     script = tmp_path / "ep_worker.py"
     script.write_text(EP_WORKER)
@@ -295,7 +299,7 @@ def test_expert_parallel_two_gpus_match_one(K, tmp_path):
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", CINN_DIV_MODE="rn")
-    subprocess.check_call([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+    subprocess.check_call([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
                            "--master-addr", "127.0.0.1", "--master-port", str(port), str(script), ROOT, str(tmp_path)],
                           env=env, timeout=300)
     E, d, I, T, k = 16, 512, 256, 256, 2
@@ -307,7 +311,7 @@ def test_expert_parallel_two_gpus_match_one(K, tmp_path):
     experts = moe.FP8Experts(w12, w3)
     s1, s2, s3 = [(torch.randn(*shape, generator=g) * 0.02).cuda() for shape in ((384, d), (384, d), (d, 384))]
     shared = moe.FP8SwiGLU(s1, s2, s3)
-    for rank in range(2):
+    for rank in range(world):
         got = torch.load(tmp_path / f"ep_{rank}.pt")
         assert got["status"] == 0
         x = got["x"].cuda()
@@ -320,3 +324,80 @@ def test_expert_parallel_two_gpus_match_one(K, tmp_path):
         # same e4m3 payloads and the same per-row arithmetic: only the fp32 summation order of a token's
         # experts could differ, and index_add_ keeps it
         assert rel_fro(got["y_ep"], y_one.cpu().double()) < 1e-6
+
+
+def _fake_peers(t, n):
+    return torch.tensor([t.data_ptr()] * n, dtype=torch.int64, device="cuda")
+
+
+@pytest.mark.parametrize("G,me", [(1, 0), (2, 0), (2, 1), (4, 2), (8, 7)])
+def test_plan_kernel_matches_exchange_tables(K, G, me):
+    """cinn_p2p_plan for rank `me` of G, with the other ranks played by the host: their rows of the count matrix
+    and their flags are filled in beforehand, all "peer" pointers name local memory.  The tables must equal the
+    tensor-arithmetic statement (p2p.exchange_tables, itself checked against a sort-based exchange on the CPU)."""
+    import ctypes
+    from cinnamon_b200 import p2p
+    E = 32
+    g = torch.Generator().manual_seed(100 * G + me)
+    counts_all = torch.randint(0, 50, (G, E), generator=g, dtype=torch.int64)
+    counts_all[:, 3] = 0                                              # an expert nobody uses
+    counts_all[me, 5] = 0
+    ref = p2p.exchange_tables(counts_all, me)
+    matrix = counts_all.clone().cuda()
+    matrix[me] = -1                                                   # the kernel must write this row itself
+    flags = torch.zeros(256, dtype=torch.int32, device="cuda")
+    flags[64:64 + G] = 7                                              # every rank's counts "have arrived" (epoch 7)
+    flags[64 + me] = 0
+    e_local = E // G
+    i64 = lambda n: torch.full((n,), -5, dtype=torch.int64, device="cuda")          # noqa: E731
+    out = dict(base_send=i64(E), my_start=i64(E), starts=i64(e_local), ends=i64(e_local), seg_start=i64(e_local * G + 1),
+               home_base=i64(e_local * G), total_rows=i64(1))
+    p = lambda t: ctypes.c_void_p(t.data_ptr())                                       # noqa: E731
+    mine = counts_all[me].contiguous().cuda()
+    peer_matrix, peer_flags = _fake_peers(matrix, G), _fake_peers(flags, G)           # kept alive across the launch
+    K._lib.check(K._lib.lib.cinn_p2p_plan(p(mine), p(peer_matrix), p(peer_flags), me, G, E, 64, 7,
+                                          p(out["base_send"]), p(out["my_start"]), p(out["starts"]), p(out["ends"]),
+                                          p(out["seg_start"]), p(out["home_base"]), p(out["total_rows"]),
+                                          ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "cinn_p2p_plan")
+    torch.cuda.synchronize()
+    assert K.device_status() == 0
+    assert torch.equal(matrix.cpu(), counts_all) and int(flags[64 + me]) == 7
+    for name, got in out.items():
+        want = getattr(ref, name).reshape(-1)
+        assert torch.equal(got.cpu(), want), name
+
+
+def test_dispatch_signal_and_row_table_wait(K):
+    """One rank: the dispatch's last CTA sets the "landed" flag, the row-table kernel waits for it; rows and table
+    equal those of the plain kernels."""
+    import ctypes
+    T, d, E, k = 96, 256, 4, 2
+    g = torch.Generator().manual_seed(8)
+    xq, xs = K.quantize_fp8_rowwise(torch.randn(T, d, generator=g).bfloat16().cuda())
+    r = K.moe_route(torch.randn(T, E, generator=g).cuda(), torch.zeros(E).cuda(), k)
+    from cinnamon_b200 import p2p
+    t = p2p.exchange_tables(r["counts"].view(1, E).cpu(), 0)
+    t = p2p.ExchangeTables(**{f: getattr(t, f).cuda().reshape(-1) for f in t.__dataclass_fields__})
+    n = T * k
+    recv = [torch.zeros(n, d, dtype=torch.uint8, device="cuda") for _ in range(2)]
+    recs = [torch.zeros(n, d // 128, device="cuda") for _ in range(2)]
+    flags = torch.zeros(256, dtype=torch.int32, device="cuda")
+    done = torch.zeros(1, dtype=torch.int32, device="cuda")
+    p = lambda x: ctypes.c_void_p(x.data_ptr())                                       # noqa: E731
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    home = torch.zeros(n, d, dtype=torch.bfloat16, device="cuda")
+    table = torch.zeros(n, dtype=torch.int64, device="cuda")
+    # the pointer arrays stay referenced until the launches that read them have run
+    pq = [_fake_peers(recv[i], 1) for i in range(2)]
+    ps = [_fake_peers(recs[i], 1) for i in range(2)]
+    pf, ph = _fake_peers(flags, 1), _fake_peers(home, 1)
+    K.p2p_dispatch(xq, xs, r["token_indices"], r["sorted_experts"], t.base_send, t.my_start, pq[0], ps[0], E, 1, n)
+    K._lib.check(K._lib.lib.cinn_p2p_dispatch_signal(p(xq), p(xs), p(r["token_indices"]), p(r["sorted_experts"]), p(t.base_send),
+                                                     p(t.my_start), p(pq[1]), p(ps[1]), n, T, d, d // 128, E, 1, n, p(pf), 0, 128,
+                                                     3, p(done), st), "cinn_p2p_dispatch_signal")
+    K._lib.check(K._lib.lib.cinn_p2p_row_table_wait(p(t.seg_start), p(t.home_base), p(ph), n, d * 2, E, 1, n, p(table), p(pf), 0,
+                                                    128, 3, st), "cinn_p2p_row_table_wait")
+    torch.cuda.synchronize()
+    assert K.device_status() == 0 and int(flags[128]) == 3 and int(done) == 0
+    assert torch.equal(recv[0], recv[1]) and torch.equal(recs[0], recs[1])
+    assert torch.equal(table, K.p2p_row_table(t.seg_start, t.home_base, ph, n, d * 2, 1, n))
