@@ -74,6 +74,8 @@ int p2p_return(const void* rows, const int64_t* seg_start, const int64_t* home_b
                int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity, cudaStream_t st);
 int p2p_barrier(const int64_t* peer_flags, int me, int n_ranks, unsigned epoch, cudaStream_t st);
 long long set_p2p_wait_limit(long long cycles);
+int moe_combine_backward(const void* rows, int dtype, const int64_t* pos, const float* gates, const float* dy, void* d_rows,
+                         float* d_gates, int64_t n_tokens, int64_t n_rows, int top_k, int64_t d, cudaStream_t st);
 int p2p_plan(const int64_t* my_counts, const int64_t* peer_counts, const int64_t* peer_flags, int me, int G, int E,
              int flag_slot, unsigned epoch, int64_t* base_send, int64_t* my_start, int64_t* starts, int64_t* ends,
              int64_t* seg_start, int64_t* home_base, int64_t* total_rows, cudaStream_t st);
@@ -287,6 +289,12 @@ int cinn_p2p_barrier(const int64_t* peer_flags, int rank, int n_ranks, unsigned 
 }
 
 long long cinn_set_wait_limit_cycles(long long cycles) { return cinn::set_p2p_wait_limit(cycles); }
+
+int cinn_moe_combine_backward(const void* rows, int rows_dtype, const int64_t* pos, const float* gates, const float* dy,
+                              void* d_rows, float* d_gates, int64_t n_tokens, int64_t n_rows, int top_k, int64_t d, void* stream) {
+    return cinn::moe_combine_backward(rows, rows_dtype, pos, gates, dy, d_rows, d_gates, n_tokens, n_rows, top_k, d,
+                                      (cudaStream_t)stream);
+}
 
 int cinn_p2p_plan(const int64_t* my_counts, const int64_t* peer_counts, const int64_t* peer_flags, int rank, int n_ranks,
                   int n_experts, int flag_slot, unsigned epoch, int64_t* base_send, int64_t* my_start, int64_t* starts,

@@ -121,6 +121,41 @@ __device__ __forceinline__ void store8f(T* p, const float (&v)[8]) {
     }
 }
 
+// Backward of the combine pass, y[t] = sum_j gate[t, j] * rows[pos[t, j]] (+ addend[t]):
+//   d_rows[pos[t, j]] = gate[t, j] * dy[t]         (every row belongs to exactly one pair: no accumulation)
+//   d_gate[t, j]      = < rows[pos[t, j]], dy[t] >
+// One warp per (token, slot) pair, 16-byte vectors.  Rows that no pair names are left as the caller initialised them.
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_combine_backward_kernel(const T* __restrict__ rows, const int64_t* __restrict__ pos, const float* __restrict__ gates,
+                            const float* __restrict__ dy, T* __restrict__ d_rows, float* __restrict__ d_gates,
+                            int64_t n_pairs, int64_t n_rows, int top_k, int d) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int64_t n_warps = (int64_t)gridDim.x * 8;
+    for (int64_t pr = warp; pr < n_pairs; pr += n_warps) {
+        const int64_t p = pos[pr];
+        if (p < 0 || p >= n_rows) {
+            if (lane == 0) d_gates[pr] = 0.0f;
+            continue;
+        }
+        const int64_t t = pr / top_k;
+        const float g = gates[pr];
+        float dot = 0.0f;
+        for (int c = lane * 8; c < d; c += 32 * 8) {
+            float r[8], gy[8], o[8];
+            load8f<T>(rows + p * d + c, r);
+            load8f<float>(dy + t * d + c, gy);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { o[i] = g * gy[i]; dot = fmaf(r[i], gy[i], dot); }
+            store8f<T>(d_rows + p * d + c, o);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (lane == 0) d_gates[pr] = dot;
+    }
+}
+
 template <typename T, bool BACKWARD>
 __global__ void __launch_bounds__(256)
 swiglu_kernel(const T* __restrict__ h12, const T* __restrict__ dh, T* __restrict__ out, int64_t T_rows, int I) {
@@ -646,6 +681,29 @@ int p2p_return(const void* rows, const int64_t* seg_start, const int64_t* home_b
     if (blocks > cap) blocks = cap;
     p2p_return_kernel<<<(unsigned)blocks, 256, 0, st>>>((const uint4*)rows, seg_start, home_base, peer_home, n_rows, n_segments,
                                                        n_ranks, (int)(row_bytes / 16), capacity);
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+int moe_combine_backward(const void* rows, int dtype, const int64_t* pos, const float* gates, const float* dy, void* d_rows,
+                         float* d_gates, int64_t n_tokens, int64_t n_rows, int top_k, int64_t d, cudaStream_t st) {
+    CINN_CHECK_ARG(n_tokens >= 0 && n_rows >= 0 && d >= 0, "moe_combine_backward: negative shape");
+    if (n_tokens == 0 || d == 0) return CINN_OK;
+    CINN_CHECK_ARG(rows && pos && gates && dy && d_rows && d_gates, "moe_combine_backward: null pointer");
+    CINN_CHECK_ARG(top_k >= 1 && top_k <= kMaxTopK, "moe_combine_backward: top_k must be in [1, %d]", kMaxTopK);
+    CINN_CHECK_ARG(d % 8 == 0 && d < (1LL << 31), "moe_combine_backward: the row width (%lld) must be a multiple of 8", (long long)d);
+    CINN_CHECK_ARG(((reinterpret_cast<uintptr_t>(rows) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(d_rows)) & 15) == 0,
+                   "moe_combine_backward: rows, dy and d_rows must be 16-byte aligned");
+    const int64_t n_pairs = n_tokens * top_k;
+    int64_t blocks = (n_pairs + 7) / 8;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    switch (dtype) {
+        case CINN_BF16: moe_combine_backward_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>((const __nv_bfloat16*)rows, pos, gates, dy, (__nv_bfloat16*)d_rows, d_gates, n_pairs, n_rows, top_k, (int)d); break;
+        case CINN_F16: moe_combine_backward_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>((const __half*)rows, pos, gates, dy, (__half*)d_rows, d_gates, n_pairs, n_rows, top_k, (int)d); break;
+        case CINN_F32: moe_combine_backward_kernel<float><<<(unsigned)blocks, 256, 0, st>>>((const float*)rows, pos, gates, dy, (float*)d_rows, d_gates, n_pairs, n_rows, top_k, (int)d); break;
+        default: set_error("moe_combine_backward: unknown dtype tag %d", dtype); return CINN_ERR_INVALID;
+    }
     CINN_CHECK_LAUNCH();
     return CINN_OK;
 }

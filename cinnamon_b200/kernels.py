@@ -23,6 +23,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import weakref
 
 import torch
 
@@ -452,7 +453,8 @@ class FP8Linear(torch.nn.Module):
                  cache_quantized_weight: bool = False):
         """``cache_quantized_weight`` (not in the reference, off by default): keep the e4m3 copy of the weight until
         the weight changes (an in-place optimiser update bumps its version), so the micro-steps of a gradient
-        accumulation quantise it once instead of once each."""
+        accumulation quantise it once instead of once each.  An update made through ``weight.data`` leaves the
+        version counter untouched: call ``invalidate_weight_cache(model)`` after one."""
         super().__init__()
         self.in_features = in_features
         self.out_features = out_features
@@ -548,6 +550,40 @@ def quantize_expert_weights(weights: torch.Tensor):
         qe, se = quantize_fp8_blockwise(w[e])
         q[e], s[e] = qe, se
     return q, s
+
+
+# e4m3 copies of expert weight stacks, kept while the weight tensor lives and until it changes
+_EXPERT_WEIGHT_CACHE = {}           # id(weight tensor) -> (key, e4m3 bytes, scales); entries leave with their tensor
+
+
+def cached_expert_weights(weights: torch.Tensor):
+    """``quantize_expert_weights(weights)``, remembered per weight tensor until the tensor changes: the key is the
+    tensor's version counter (every in-place update through the tensor itself bumps it: optimiser steps,
+    ``load_state_dict``, DDP's parameter broadcast), its storage address and dtype.  At the MoE benchmark's size a
+    call would otherwise re-read and re-quantise 22.5 GB of expert weights.  An update made through ``weights.data``
+    does not bump the counter: call ``invalidate_weight_cache()`` after such an update."""
+    key = (weights._version, weights.data_ptr(), weights.dtype, tuple(weights.shape))
+    ident = id(weights)
+    hit = _EXPERT_WEIGHT_CACHE.get(ident)
+    if hit is not None and hit[0] == key:
+        return hit[1], hit[2]
+    with torch.no_grad():
+        q, s = quantize_expert_weights(weights.detach())
+    if hit is None:
+        weakref.finalize(weights, _EXPERT_WEIGHT_CACHE.pop, ident, None)
+    _EXPERT_WEIGHT_CACHE[ident] = (key, q, s)
+    return q, s
+
+
+def invalidate_weight_cache(module: torch.nn.Module = None) -> None:
+    """Drops every cached e4m3 weight copy (expert stacks of ``moe_grouped_gemm``; with ``module`` also the caches of
+    its ``FP8Linear(cache_quantized_weight=True)`` layers).  Needed only after weights were changed behind autograd's
+    back (``p.data.copy_(...)``, ``p.data.add_(...)``), which leaves the version counter untouched."""
+    _EXPERT_WEIGHT_CACHE.clear()
+    if module is not None:
+        for m in module.modules():
+            if isinstance(m, FP8Linear):
+                m._w_cache = (None, None)
 
 
 def fp8_grouped_gemm(x_fp8, x_scale, w_fp8, w_scale, expert_starts, expert_ends, out_dtype=torch.float16,
@@ -684,6 +720,41 @@ def moe_combine(rows: torch.Tensor, pos: torch.Tensor, gates: torch.Tensor, adde
                        "cinn_moe_combine_add")
     _count()
     return y
+
+
+class MoECombineFunction(torch.autograd.Function):
+    """``moe_combine`` with its backward (one kernel each): gradients for the expert outputs, the gates and the
+    addend.  The reference's gate multiply + ``scatter_add_`` (src/layers.py:157-160) is differentiated by autograd;
+    this is the same derivative for the fused gather pass."""
+
+    @staticmethod
+    def forward(ctx, rows, pos, gates, addend):
+        y = moe_combine(rows.detach(), pos, gates.detach(), None if addend is None else addend.detach())
+        ctx.save_for_backward(rows, pos, gates)
+        ctx.addend_dtype = None if addend is None else addend.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        rows, pos, gates = ctx.saved_tensors
+        T, k = pos.shape
+        dy = dy.float().contiguous()
+        rows_c = rows.contiguous()
+        pos_c, gates_c = pos.to(torch.int64).contiguous(), gates.float().contiguous()
+        with torch.cuda.device(rows.device):
+            d_rows = torch.zeros_like(rows_c)
+            d_gates = torch.empty((T, k), dtype=torch.float32, device=rows.device)
+            _lib.check(_L.cinn_moe_combine_backward(_ptr(rows_c), _DTYPE_TAG[rows_c.dtype], _ptr(pos_c), _ptr(gates_c), _ptr(dy),
+                                                    _ptr(d_rows), _ptr(d_gates), T, rows_c.shape[0], k, rows_c.shape[1],
+                                                    _stream(rows_c)), "cinn_moe_combine_backward")
+        _count()
+        d_add = None if ctx.addend_dtype is None else dy.to(ctx.addend_dtype)
+        return d_rows, None, d_gates.to(gates.dtype), d_add
+
+
+def moe_combine_autograd(rows, pos, gates, addend=None):
+    """Differentiable ``moe_combine`` (gradients reach ``rows``, ``gates`` and ``addend``)."""
+    return MoECombineFunction.apply(rows, pos, gates, addend)
 
 
 def lightning_indexer_fused(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
@@ -896,7 +967,7 @@ class MoEGroupedGemmFunction(torch.autograd.Function):
     def forward(ctx, sorted_x, weights, expert_starts, expert_ends, out_dtype):
         x = sorted_x if sorted_x.stride(-1) == 1 else sorted_x.contiguous()
         x_fp8, x_scale = quantize_fp8_rowwise(x, block_size=128)
-        w_fp8, w_scale = quantize_expert_weights(weights)
+        w_fp8, w_scale = cached_expert_weights(weights)
         out = fp8_grouped_gemm(x_fp8, x_scale, w_fp8, w_scale, expert_starts, expert_ends, out_dtype=out_dtype)
         ctx.save_for_backward(x_fp8, x_scale, w_fp8, w_scale, expert_starts, expert_ends)
         ctx.x_dtype, ctx.w_dtype = sorted_x.dtype, weights.dtype
@@ -933,7 +1004,7 @@ def moe_grouped_gemm(sorted_x: torch.Tensor, weights: torch.Tensor, expert_start
         return MoEGroupedGemmFunction.apply(sorted_x, weights, expert_starts, expert_ends, dtype)
     x = sorted_x if sorted_x.stride(-1) == 1 else sorted_x.contiguous()
     x_fp8, x_scale = quantize_fp8_rowwise(x, block_size=128)
-    w_fp8, w_scale = quantize_expert_weights(weights)
+    w_fp8, w_scale = cached_expert_weights(weights)
     return fp8_grouped_gemm(x_fp8, x_scale, w_fp8, w_scale, expert_starts, expert_ends, out_dtype=dtype)
 
 

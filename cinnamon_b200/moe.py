@@ -308,6 +308,65 @@ def moe_forward(x: torch.Tensor, routing: Routing, experts: Callable, quantize: 
     return y if addend is None else addend.float() + y
 
 
+# ---------------------------------------------------------------------------------------
+# the layer with gradients (training)
+# ---------------------------------------------------------------------------------------
+class _AllToAllRows(torch.autograd.Function):
+    """Variable-size all-to-all of rows whose backward is the same exchange run the other way: what went from rank a
+    to rank b as a row comes back from b to a as that row's gradient.  ``anchor`` is a scalar that requires grad on
+    every rank: the backward is a collective, so it has to run on every rank, also on one whose ``rows`` happen not
+    to require grad (a rank that received no row for its experts in this step)."""
+
+    @staticmethod
+    def forward(ctx, rows, send_splits, recv_splits, group, anchor):
+        ctx.splits, ctx.group = (list(send_splits), list(recv_splits)), group
+        return all_to_all_rows(rows, send_splits, recv_splits, group)
+
+    @staticmethod
+    def backward(ctx, grad):
+        send, recv = ctx.splits
+        return all_to_all_rows(grad.contiguous(), recv, send, ctx.group), None, None, None, None
+
+
+def moe_forward_train(x: torch.Tensor, routing: Routing, gates: torch.Tensor, experts: Callable, group=None,
+                      addend: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The routed part of ``MoE.forward`` (src/layers.py:137-160) built from differentiable pieces, with the experts
+    sharded over ``group``: gather -> all-to-all -> regroup by expert -> ``experts(rows, starts, ends)`` -> inverse
+    permutation -> all-to-all home -> gate-weighted sum (+ ``addend``).  In the backward the two exchanges run in
+    reverse: the gradients of the returned rows are dispatched to the experts' ranks, and the gradients of the
+    dispatched rows come home.  Rows travel in the activations' own type and are quantised where the experts run
+    (row-wise quantisation commutes with the permutation, so the expert arithmetic is that of ``moe_forward``).
+
+    ``gates`` (T, k): the normalised gates, differentiable, in the order of ``routing.pair_pos`` (ascending expert
+    id per token).  ``experts`` must be differentiable.  ``group=None`` means every expert is on this rank (also
+    inside a data-parallel job: nothing is exchanged).  Works on any backend (the CPU ranks of the tests pass a
+    torch expert function).  Returns (T, d) fp32."""
+    world = dist.get_world_size(group) if group is not None else 1
+    if world > 1:
+        plan = make_plan(routing.counts, group, n_pairs=routing.token_indices.numel())
+    else:
+        starts, ends = offsets_from_counts(routing.counts.to(torch.int64))
+        plan = DispatchPlan(None, None, None, None, starts.contiguous(), ends.contiguous())
+    rows = x.index_select(0, routing.token_indices)
+    if world > 1:
+        # Both exchanges are collectives in the backward too.  The anchor makes their outputs part of the graph on
+        # every rank, and the returned rows are tied to the received ones, so that a rank whose experts got no row
+        # (and whose expert outputs therefore carry no gradient) still takes part in both reverse exchanges.
+        anchor = torch.zeros((), dtype=rows.dtype, device=rows.device, requires_grad=torch.is_grad_enabled())
+        received = _AllToAllRows.apply(rows, plan.send_splits, plan.recv_splits, group, anchor)
+        rows = received.index_select(0, plan.perm)
+    out_rows = experts(rows, plan.starts, plan.ends)
+    if world > 1:
+        back = torch.zeros_like(out_rows).index_copy(0, plan.perm, out_rows)
+        back = back + (received.sum() * 0).to(back.dtype)
+        out_rows = _AllToAllRows.apply(back, plan.recv_splits, plan.send_splits, group, anchor)
+    if out_rows.is_cuda:
+        from . import kernels as K
+        return K.moe_combine_autograd(out_rows, routing.pair_pos, gates, addend)
+    y = (out_rows.float()[routing.pair_pos] * gates.float().unsqueeze(-1)).sum(dim=1)
+    return y if addend is None else addend.float() + y
+
+
 def _mark(trace: Optional[list], name: str) -> None:
     """Phase timing for the benchmark: appends (name, CUDA event recorded on the current stream) when tracing."""
     if trace is not None:

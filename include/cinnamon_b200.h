@@ -190,6 +190,12 @@ int cinn_moe_combine(const void* rows, int dtype, const int64_t* pos, const floa
 int cinn_moe_combine_add(const void* rows, int dtype, const int64_t* pos, const float* gates, const void* addend,
                          int addend_dtype, void* y, int64_t n_tokens, int64_t n_rows, int top_k, int64_t d, void* stream);
 
+/* Backward of cinn_moe_combine (the reference's gate multiply + scatter_add_, src/layers.py:157-160, is
+ * differentiated by autograd there): d_rows[pos[t, j]] = gates[t, j] * dy[t] (type of rows; rows that no pair names
+ * are left untouched) and d_gates[t, j] = < rows[pos[t, j]], dy[t] > (fp32; 0 for a skipped pair).  dy (T, d) fp32. */
+int cinn_moe_combine_backward(const void* rows, int rows_dtype, const int64_t* pos, const float* gates, const float* dy,
+                              void* d_rows, float* d_gates, int64_t n_tokens, int64_t n_rows, int top_k, int64_t d, void* stream);
+
 /* Sparse attention over per-query index lists, forward.
  * Replaces sparse_attention_fwd_kernel + SparseAttentionFunction.forward (src/kernels.py:913-1052, 1194-1245).
  * q, k: (B, H, L, d_qk), v: (B, H, L, d_v) of `dtype`, contiguous; idx: (B, L, K) int64, shared by the heads.

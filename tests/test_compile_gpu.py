@@ -47,11 +47,20 @@ def test_converted_swiglu_block_compiles_as_one_graph(K):
     launches = K.launch_count
     y1, gx1, gp1 = _grads(block, x, compiled)
     assert K.launch_count - launches >= 9 * 2 - 3, "the compiled block did not run the library's kernels"
-    assert torch.equal(y0, y1) and torch.equal(gx0, gx1)
+    # the element-wise part between the linears (silu, product) is fused by the compiler and keeps fp32 intermediates
+    # where eager rounds to bf16 twice, so the block agrees to bf16 precision, not to the bit
+    # (and every differently rounded intermediate is re-quantised to e4m3 by the next layer, forward and backward)
+    err = lambda a, b: float((a.float() - b.float()).norm() / b.float().norm())               # noqa: E731
+    assert err(y1, y0) < 2e-2 and err(gx1, gx0) < 1e-1
     for a, b in zip(gp0, gp1):
-        assert torch.equal(a, b)
+        assert err(b, a) < 1e-1
     y2, _, _ = _grads(block, x, compiled)                     # a second call reuses the graph
-    assert torch.equal(y0, y2)
+    assert torch.equal(y1, y2)
+    # one layer alone has nothing for the compiler to fuse: compiled and eager results are the same bits
+    lin = block.w1
+    z0, gz0, gw0 = _grads(lin, x, lin)
+    z1, gz1, gw1 = _grads(lin, x, torch.compile(lin, fullgraph=True))
+    assert torch.equal(z0, z1) and torch.equal(gz0, gz1) and torch.equal(gw0[0], gw1[0])
 
 
 def test_grouped_gemm_and_sparse_attention_compile(K):

@@ -207,6 +207,34 @@ def test_fp8_linear_module(K):
     assert lin.weight.grad is not None and lin.weight.grad.dtype == torch.float32
 
 
+def test_weight_caches_and_updates_through_data(K):
+    """The e4m3 copies follow every update that goes through the tensor (version counter); an update through
+    ``.data`` leaves them stale until ``invalidate_weight_cache`` is called - the documented behaviour."""
+    torch.manual_seed(6)
+    E, d, h, T = 3, 256, 128, 96
+    w = (torch.randn(E, h, d, device="cuda") * 0.02)
+    x = torch.randn(T, d, device="cuda").bfloat16()
+    starts = torch.tensor([0, 32, 64], device="cuda")
+    ends = torch.tensor([32, 64, 96], device="cuda")
+    y0 = K.moe_grouped_gemm(x, w, starts, ends)
+    n0 = K.launch_count
+    assert torch.equal(K.moe_grouped_gemm(x, w, starts, ends), y0)
+    assert K.launch_count - n0 == 2                                 # token quantiser + GEMM: the weights came from the cache
+    w.mul_(2.0)                                                     # in place through the tensor: noticed
+    y1 = K.moe_grouped_gemm(x, w, starts, ends)
+    torch.testing.assert_close(y1.float(), 2 * y0.float(), rtol=2e-2, atol=1e-3)
+    w.data.mul_(0.5)                                                # behind autograd's back: not noticed ...
+    assert torch.equal(K.moe_grouped_gemm(x, w, starts, ends), y1)
+    K.invalidate_weight_cache()                                     # ... until the caches are dropped
+    assert torch.equal(K.moe_grouped_gemm(x, w, starts, ends), y0)
+    lin = K.FP8Linear(256, 128, cache_quantized_weight=True).cuda()
+    z0 = lin(x)
+    lin.weight.data.mul_(2.0)
+    assert torch.equal(lin(x), z0)
+    K.invalidate_weight_cache(lin)
+    torch.testing.assert_close(lin(x).float(), 2 * z0.float(), rtol=2e-2, atol=1e-3)
+
+
 def _grouped_case(E, d_in, d_out, counts, seed, gap=0):
     g = torch.Generator().manual_seed(seed)
     T = sum(counts) + gap
