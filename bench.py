@@ -30,9 +30,10 @@ sys.path.insert(0, ROOT)
 M, K, N = 16384, 7168, 18432
 FLOP_PER_STEP = 3 * 2.0 * M * N * K
 WORKLOAD = "fp8_linear_fwd_bwd_ffn M=16384 K=7168 N=18432"
-# DRAM bytes per GEMM launch: reduced-case ncu capture (8192 x 9216 x 7168, three GEMMs averaged) scaled by the
-# algorithmic bytes of the full launch over those of the reduced one (operands + scales + output: x3.1, not x4)
-GEMM_TRAFFIC_BYTES = 3.1 * (462.2e6 + 448.7e6 + 622.4e6) / 3
+# DRAM bytes per GEMM launch: reduced-case ncu capture (8192 x 9216 x 7168: forward 363 MB, dgrad 389 MB, wgrad 600 MB
+# read + written, for 276 / 259 / 398 MB of operands, scales and output) scaled to the full launch by the algorithmic
+# bytes (854 / 669 / 947 MB), averaged over the three
+GEMM_TRAFFIC_BYTES = (363.0e6 * 854 / 276 + 389.0e6 * 669 / 259 + 600.5e6 * 947 / 398) / 3
 
 
 def bench_config(world: int) -> dict:
@@ -703,6 +704,71 @@ def bench_c5(dev, rank, world, steps=5, warmup=2, batch_size=32, seq_len=1024):
     return out
 
 
+def run_e2e(Kmod, dev, args, world, x_h, dy_h, w, barrier):
+    """The step measured end to end: inputs start in pinned host memory, results end there, every step.
+    Returns (ms per step, bytes host->device per step, bytes device->host per step)."""
+    import torch.distributed as dist
+    out_h = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+    gx_h = torch.empty(M, K, dtype=torch.bfloat16).pin_memory()
+    gw_h = torch.empty(N, K, dtype=torch.float32).pin_memory()
+
+    # Three streams, two sets of device buffers: while step i computes, step i+1's inputs come in over PCIe and
+    # step i-1's results go out.  Every step still copies all of its inputs in and all of its results out.
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    s_cmp = torch.cuda.current_stream(dev)
+    xd = [torch.empty(M, K, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    dyd = [torch.empty(M, N, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_free = [torch.cuda.Event() for _ in range(2)]
+    ev_out = torch.cuda.Event()
+    for e in ev_free:
+        e.record(s_cmp)
+    ev_out.record(s_out)
+
+    def e2e_step(i):
+        b = i & 1
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(ev_free[b])                      # the step that last used these buffers has consumed them
+            xd[b].copy_(x_h, non_blocking=True)
+            dyd[b].copy_(dy_h, non_blocking=True)
+            ev_in[b].record(s_in)
+        s_cmp.wait_event(ev_in[b])
+        xin = xd[b].detach().requires_grad_(True)
+        w.grad = None
+        out = Kmod.FP8MatmulFunction.apply(xin, w, False)
+        out.backward(dyd[b])
+        ev_free[b].record(s_cmp)
+        done = torch.cuda.Event()
+        done.record(s_cmp)
+        results = (out.detach(), xin.grad, w.grad)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(done)
+            for t, h in zip(results, (out_h, gx_h, gw_h)):
+                t.record_stream(s_out)
+                h.copy_(t, non_blocking=True)
+            ev_out.record(s_out)
+
+    e2e_steps = max(4, min(args.steps, 8))
+    e2e_step(0)
+    e2e_step(1)
+    s_cmp.wait_event(ev_out)
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    s_cmp.wait_event(ev_out)                                 # the last results have reached the host buffers
+    f1.record()
+    barrier()
+    t2 = torch.tensor([f0.elapsed_time(f1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t2.item()) / e2e_steps
+    h2d = x_h.numel() * 2 + dy_h.numel() * 2
+    d2h = out_h.numel() * 2 + gx_h.numel() * 2 + gw_h.numel() * 4
+    return e2e_ms, h2d, d2h
+
+
 # ---------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------
@@ -738,6 +804,8 @@ def main():
     ap.add_argument("--no-moe", action="store_true", help="skip the MoE layer measurements")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel list (N = 1)")
     ap.add_argument("--no-c5", action="store_true", help="skip the end-to-end training step of the reference's model")
+    ap.add_argument("--no-peak", action="store_true", help="skip the library FP8 GEMM peak measurement (roofline falls back to 2 x bf16)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-to-host leg (e2e is then null)")
     ap.add_argument("--moe-exchange", default="p2p-fused", choices=["nccl", "p2p", "p2p-fused"],
                     help="expert-parallel exchange (N > 1): all-to-all collectives, or peer stores into symmetric memory")
     ap.add_argument("--moe-chunks", type=int, default=1,
@@ -822,64 +890,10 @@ def main():
     assert Kmod.device_status() == 0, "a kernel reported a device-side failure in the timed region"
 
     # ---- end to end: pinned host inputs in, host results out, every step ----
-    out_h = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
-    gx_h = torch.empty(M, K, dtype=torch.bfloat16).pin_memory()
-    gw_h = torch.empty(N, K, dtype=torch.float32).pin_memory()
-
-    # Three streams, two sets of device buffers: while step i computes, step i+1's inputs come in over PCIe and
-    # step i-1's results go out.  Every step still copies all of its inputs in and all of its results out.
-    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    s_cmp = torch.cuda.current_stream(dev)
-    xd = [torch.empty(M, K, dtype=torch.bfloat16, device=dev) for _ in range(2)]
-    dyd = [torch.empty(M, N, dtype=torch.bfloat16, device=dev) for _ in range(2)]
-    ev_in = [torch.cuda.Event() for _ in range(2)]
-    ev_free = [torch.cuda.Event() for _ in range(2)]
-    ev_out = torch.cuda.Event()
-    for e in ev_free:
-        e.record(s_cmp)
-    ev_out.record(s_out)
-
-    def e2e_step(i):
-        b = i & 1
-        with torch.cuda.stream(s_in):
-            s_in.wait_event(ev_free[b])                      # the step that last used these buffers has consumed them
-            xd[b].copy_(x_h, non_blocking=True)
-            dyd[b].copy_(dy_h, non_blocking=True)
-            ev_in[b].record(s_in)
-        s_cmp.wait_event(ev_in[b])
-        xin = xd[b].detach().requires_grad_(True)
-        w.grad = None
-        out = Kmod.FP8MatmulFunction.apply(xin, w, False)
-        out.backward(dyd[b])
-        ev_free[b].record(s_cmp)
-        done = torch.cuda.Event()
-        done.record(s_cmp)
-        results = (out.detach(), xin.grad, w.grad)
-        with torch.cuda.stream(s_out):
-            s_out.wait_event(done)
-            for t, h in zip(results, (out_h, gx_h, gw_h)):
-                t.record_stream(s_out)
-                h.copy_(t, non_blocking=True)
-            ev_out.record(s_out)
-
-    e2e_steps = max(4, min(args.steps, 8))
-    e2e_step(0)
-    e2e_step(1)
-    s_cmp.wait_event(ev_out)
-    barrier()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    f0.record()
-    for i in range(e2e_steps):
-        e2e_step(i)
-    s_cmp.wait_event(ev_out)                                 # the last results have reached the host buffers
-    f1.record()
-    barrier()
-    t2 = torch.tensor([f0.elapsed_time(f1)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t2.item()) / e2e_steps
-    h2d = x_h.numel() * 2 + dy_h.numel() * 2
-    d2h = out_h.numel() * 2 + gx_h.numel() * 2 + gw_h.numel() * 4
+    e2e_ms, h2d, d2h = None, 0, 0
+    out_h = gx_h = gw_h = None
+    if not args.no_e2e:
+        e2e_ms, h2d, d2h = run_e2e(Kmod, dev, args, world, x_h, dy_h, w, barrier)
 
     # dense FP8 peak of this GPU (library GEMM), measured here: the denominator of the roofline fractions
     # (the burst figure first and the per-kernel list right after it, while the part is cool; the two-second
@@ -889,12 +903,12 @@ def main():
         time.sleep(2.0)
         burst = measure_fp8_peak(dev, sustained=False)
         kernel_lines = bench_kernels(Kmod, dev, x, w, dy, measured_peaks()[0], (burst or {}).get("fp8_tflops"))
-    fp8 = measure_fp8_peak(dev) if rank == 0 else None
+    fp8 = measure_fp8_peak(dev) if rank == 0 and not args.no_peak else None
     time.sleep(2.0)
     barrier()
     moe_lines = []
     if not args.no_moe and not args.shape:
-        del x, w, dy, out_h, gx_h, gw_h
+        del x, w, dy
         torch.cuda.empty_cache()
         for scale, label in ((1.0, "bias~N(0,1) as specified"), (0.1, "mild skew: bias~N(0,0.1)")):
             moe_lines.append(bench_moe(Kmod, dev, rank, world, steps=5, warmup=3, bias_scale=scale, label=label,
@@ -932,10 +946,10 @@ def main():
                          "frac_of_nominal_4500": (achieved / 4500.0) if achieved else None,
                          "launches_timed": len(gemm_ms), "avg_launch_ms": gemm_avg_ms,
                          "traffic": GEMM_TRAFFIC_BYTES if not args.shape else None,
-                         "traffic_source": "ncu dram__bytes_read+write of the three GEMMs on a reduced case (8192x9216x7168), "
-                                           "averaged, scaled by the algorithmic bytes of the full launch (x3.1)"},
-            "e2e": {"value": world * FLOP_PER_STEP / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+                         "traffic_source": "ncu dram__bytes_read+write of the three GEMMs on a reduced case (8192x9216x7168), each "
+                                           "scaled by the algorithmic bytes of its full launch, averaged"},
+            "e2e": ({"value": world * FLOP_PER_STEP / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms} if e2e_ms else None),
             "gpu_launches": launches,
             "clocks": clocks,
         }
