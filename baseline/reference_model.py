@@ -24,17 +24,24 @@ def available() -> bool:
     return os.path.isfile(os.path.join(REF_SRC, "model.py"))
 
 
-def import_reference():
-    """Imports the reference's ``config`` and ``model`` modules with ``kernels`` bound to the drop-in."""
+def import_reference(own_kernels: bool = False):
+    """Imports the reference's ``config`` and ``model`` modules with ``kernels`` bound to the drop-in - or, with
+    ``own_kernels``, to the reference's own Triton ``src/kernels.py`` (the unmodified reference end to end; a process
+    can hold only one of the two)."""
     if not available():
         raise RuntimeError("the reference is not staged: run baseline/stage_reference.py where the reference tree is present")
     root = os.path.dirname(HERE)
     if root not in sys.path:
         sys.path.insert(0, root)
-    import cinnamon_b200.dropin as dropin
-    K = dropin.install()
-    if REF_SRC not in sys.path:
-        sys.path.append(REF_SRC)            # appended: `kernels` is already bound, the rest resolves here
+    if own_kernels:
+        sys.path.insert(0, REF_SRC)
+        import kernels as K
+        assert os.path.dirname(os.path.abspath(K.__file__)) == REF_SRC
+    else:
+        import cinnamon_b200.dropin as dropin
+        K = dropin.install()
+        if REF_SRC not in sys.path:
+            sys.path.append(REF_SRC)        # appended: `kernels` is already bound, the rest resolves here
     import config as ref_config
     import model as ref_model
     import layers as ref_layers
@@ -42,8 +49,9 @@ def import_reference():
     return ref_config, ref_model, K
 
 
-def build_model(device, overrides: dict | None = None, fp8: bool = True, balance_alpha: float = 0.0):
-    ref_config, ref_model, K = import_reference()
+def build_model(device, overrides: dict | None = None, fp8: bool = True, balance_alpha: float = 0.0,
+                own_kernels: bool = False):
+    ref_config, ref_model, K = import_reference(own_kernels)
     c = ref_config.ModelConfig()
     for k, v in dict(CONFIG_5, **(overrides or {})).items():
         assert hasattr(c, k), k
@@ -84,3 +92,41 @@ def train_step(model, batch, optimizer=None, mtp_lambda: float = 0.3, dsa_kl_wei
         optimizer.step()
         optimizer.zero_grad(set_to_none=True)
     return loss.detach()
+
+
+def _main():
+    """``python baseline/reference_model.py [--own-kernels] [--steps N] [--batch B] [--seq L]``: times the training
+    step on cuda:0 and prints one JSON line.  With ``--own-kernels`` the model runs on the reference's own Triton
+    kernels: the unmodified reference, for a side-by-side figure on the same GPU."""
+    import argparse
+    import json
+    import torch
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--own-kernels", action="store_true")
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--seq", type=int, default=1024)
+    a = ap.parse_args()
+    torch.manual_seed(1005)
+    model, cfg, _ = build_model("cuda", own_kernels=a.own_kernels)
+    model.train()
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, weight_decay=0.1)
+    host = torch.randint(0, cfg.vocab_size, (a.batch, a.seq + 1), generator=torch.Generator().manual_seed(1005)).pin_memory()
+    for _ in range(a.warmup):
+        loss = train_step(model, host.to("cuda", non_blocking=True), optimizer=opt)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        loss = train_step(model, host.to("cuda", non_blocking=True), optimizer=opt)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / a.steps
+    print("RESULT " + json.dumps({"kernels": "reference (Triton)" if a.own_kernels else "cinnamon_b200", "ms_per_step": ms,
+                                  "tokens_per_s": a.batch * a.seq / (ms * 1e-3), "loss": float(loss),
+                                  "loss_is_finite": bool(torch.isfinite(loss))}))
+
+
+if __name__ == "__main__":
+    _main()

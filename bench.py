@@ -701,6 +701,20 @@ def bench_c5(dev, rank, world, steps=5, warmup=2, batch_size=32, seq_len=1024):
            "loss": float(loss), "torch_compile": False, "device_status": Kmod.device_status()}
     del net, model, opt
     torch.cuda.empty_cache()
+    if world == 1:
+        # the unmodified reference (its own Triton kernels) on the same GPU and batch, in a process of its own
+        try:
+            p = subprocess.run([sys.executable, os.path.join(ROOT, "baseline", "reference_model.py"), "--own-kernels", "--steps", "3",
+                                "--batch", str(batch_size), "--seq", str(seq_len)], capture_output=True, text=True, timeout=900)
+            lines = [ln for ln in p.stdout.splitlines() if ln.startswith("RESULT ")]
+            if p.returncode == 0 and lines:
+                ref = json.loads(lines[-1][len("RESULT "):])
+                out["reference_triton"] = ref
+                out["speedup_vs_reference_triton"] = ref["ms_per_step"] / out["ms_per_step"]
+            else:
+                out["reference_triton"] = {"unavailable": (p.stderr.strip().splitlines() or ["no output"])[-1][:300]}
+        except Exception as exc:                                # noqa: BLE001
+            out["reference_triton"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
     return out
 
 

@@ -35,6 +35,7 @@ SIGNATURES = {
     "cinn_swiglu_quant_rowwise_n": [_vp, _i32, _i64, _i64, _vp, _vp, _vp, _i32, _vp],
     "cinn_transpose_bytes": [_vp, _i64, _vp, _i64, _i64, _vp],
     "cinn_fp8_gemm": [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _i32, _i32, _vp],
+    "cinn_grouped_gemm_16bit": [_vp, _vp, _i32, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32, _vp],
     "cinn_fp8_grouped_gemm_dgrad": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32, _vp],
     "cinn_moe_combine": [_vp, _i32, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _vp],
     "cinn_moe_combine_backward": [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _vp],

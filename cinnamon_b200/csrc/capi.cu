@@ -74,6 +74,8 @@ int p2p_return(const void* rows, const int64_t* seg_start, const int64_t* home_b
                int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity, cudaStream_t st);
 int p2p_barrier(const int64_t* peer_flags, int me, int n_ranks, unsigned epoch, cudaStream_t st);
 long long set_p2p_wait_limit(long long cycles);
+int grouped_gemm_16bit(const void* A, const void* W, int in_dtype, const int64_t* starts, const int64_t* ends, int64_t E,
+                       int64_t T, int64_t d_in, int64_t d_out, void* C, int out_dtype, cudaStream_t st);
 int moe_combine_backward(const void* rows, int dtype, const int64_t* pos, const float* gates, const float* dy, void* d_rows,
                          float* d_gates, int64_t n_tokens, int64_t n_rows, int top_k, int64_t d, cudaStream_t st);
 int p2p_plan(const int64_t* my_counts, const int64_t* peer_counts, const int64_t* peer_flags, int me, int G, int E,
@@ -289,6 +291,13 @@ int cinn_p2p_barrier(const int64_t* peer_flags, int rank, int n_ranks, unsigned 
 }
 
 long long cinn_set_wait_limit_cycles(long long cycles) { return cinn::set_p2p_wait_limit(cycles); }
+
+int cinn_grouped_gemm_16bit(const void* A, const void* W, int in_dtype, const int64_t* expert_starts, const int64_t* expert_ends,
+                            int64_t n_experts, int64_t total_rows, int64_t d_in, int64_t d_out, void* C, int out_dtype,
+                            void* stream) {
+    return cinn::grouped_gemm_16bit(A, W, in_dtype, expert_starts, expert_ends, n_experts, total_rows, d_in, d_out, C, out_dtype,
+                                    (cudaStream_t)stream);
+}
 
 int cinn_moe_combine_backward(const void* rows, int rows_dtype, const int64_t* pos, const float* gates, const float* dy,
                               void* d_rows, float* d_gates, int64_t n_tokens, int64_t n_rows, int top_k, int64_t d, void* stream) {

@@ -553,6 +553,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 }
 
 #include "gemm_pair.cuh"
+#include "gemm16.cuh"
 
 // ---------------------------------------------------------------------------
 // host side
@@ -821,6 +822,69 @@ int fp8_grouped_gemm_dgrad(const void* dY, const float* sdY, const void* W, cons
     p.C = dX; p.ldc = d_in; p.M = (int)T; p.N = (int)d_in; p.K = (int)d_out;
     p.starts = starts; p.ends = ends; p.E = (int)E; p.b_rows_per_expert = (int)d_out;
     return launch_out<true, true>(ta, tb, p, out_dtype, gemm_sms(), st);
+}
+
+// Grouped GEMM on 16-bit operands: C[starts[e]:ends[e]] = A[starts[e]:ends[e]] @ W[e]^T with A (T, d_in) and
+// W (E, d_out, d_in) both bf16 or both fp16, fp32 accumulation (the reference's grouped_gemm_kernel arithmetic).
+template <bool BF16_IN, int OUT>
+static int launch16(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid,
+                    cudaStream_t st) {
+    auto kern = g16::grouped_gemm16_kernel<BF16_IN, OUT>;
+    const size_t smem = smem_bytes(p.E);
+    static thread_local size_t configured[64] = {};
+    int dev = 0;
+    CINN_CHECK_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || configured[dev] < smem) {
+        CINN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (dev >= 0 && dev < 64) configured[dev] = smem;
+    }
+    kern<<<grid, g16::GTHREADS, smem, st>>>(ta, tb, tc, p);
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+int grouped_gemm_16bit(const void* A, const void* W, int in_dtype, const int64_t* starts, const int64_t* ends, int64_t E,
+                       int64_t T, int64_t d_in, int64_t d_out, void* C, int out_dtype, cudaStream_t st) {
+    CINN_CHECK_ARG(E >= 0 && T >= 0 && d_in >= 0 && d_out >= 0, "grouped_gemm_16bit: negative shape");
+    if (E == 0 || T == 0 || d_out == 0) return CINN_OK;
+    CINN_CHECK_ARG(A && W && starts && ends && C, "grouped_gemm_16bit: null pointer");
+    CINN_CHECK_ARG(in_dtype == CINN_BF16 || in_dtype == CINN_F16, "grouped_gemm_16bit: operands must be bf16 or fp16 (tag %d)", in_dtype);
+    CINN_CHECK_ARG(E <= MAX_EXPERTS, "grouped_gemm_16bit: at most %d experts are supported (got %lld)", MAX_EXPERTS, (long long)E);
+    CINN_CHECK_ARG(d_in > 0 && d_in % 8 == 0, "grouped_gemm_16bit: d_in (%lld) must be a positive multiple of 8", (long long)d_in);
+    CINN_CHECK_ARG(T < (1LL << 31) && d_out < (1LL << 31) && d_in < (1LL << 30) && E * d_out < (1LL << 31),
+                   "grouped_gemm_16bit: dimension too large");
+    CINN_CHECK_ARG(al16(A) && al16(W) && al16(C), "grouped_gemm_16bit: A, W and C must be 16-byte aligned");
+    const CUtensorMapDataType dt = in_dtype == CINN_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUtensorMap ta, tb;
+    int rc = make_map(&ta, A, (uint64_t)d_in, (uint64_t)T, (uint64_t)d_in * 2, BK / 2, BM, dt);
+    if (rc) return rc;
+    rc = make_map(&tb, W, (uint64_t)d_in, (uint64_t)(E * d_out), (uint64_t)d_in * 2, BK / 2, BN, dt);
+    if (rc) return rc;
+    GemmParams p{};
+    p.sA = nullptr; p.sB = nullptr;
+    p.C = C; p.ldc = d_out; p.M = (int)T; p.N = (int)d_out; p.K = (int)d_in;
+    p.starts = starts; p.ends = ends; p.E = (int)E; p.b_rows_per_expert = (int)d_out;
+    CUtensorMap tc;
+    rc = make_out_map(&tc, ta, p, out_dtype, p.M);
+    if (rc) return rc;
+    const int grid = gemm_sms();
+#define CINN_G16(BF, O) return launch16<BF, O>(ta, tb, tc, p, grid, st)
+    if (in_dtype == CINN_BF16) {
+        switch (out_dtype) {
+            case CINN_BF16: CINN_G16(true, CINN_BF16);
+            case CINN_F16: CINN_G16(true, CINN_F16);
+            case CINN_F32: CINN_G16(true, CINN_F32);
+        }
+    } else {
+        switch (out_dtype) {
+            case CINN_BF16: CINN_G16(false, CINN_BF16);
+            case CINN_F16: CINN_G16(false, CINN_F16);
+            case CINN_F32: CINN_G16(false, CINN_F32);
+        }
+    }
+#undef CINN_G16
+    set_error("grouped_gemm_16bit: unknown output dtype tag %d", out_dtype);
+    return CINN_ERR_INVALID;
 }
 
 int read_quant_status(int* out, int reset);

@@ -41,6 +41,12 @@ _DIV_MODE = {"full": _lib.DIV_FULL, "rn": _lib.DIV_RN}[os.environ.get("CINN_DIV_
 # CINN_KMAJOR_BACKWARD=0 keeps the stored layouts and lets the GEMM read them (reduction, output).
 _KMAJOR_BACKWARD = os.environ.get("CINN_KMAJOR_BACKWARD", "1") != "0"
 
+# Arithmetic of the drop-in ``moe_grouped_gemm``: "fp8" = e4m3 operands with 1x128 / 128x128 scales (default: what this
+# library is for), "16bit" = fp16 operands and fp32 accumulation, the reference kernel's own arithmetic
+# (src/kernels.py:515-523).  CINN_MOE_GROUPED or ``set_moe_grouped_precision``.
+_MOE_GROUPED_PRECISION = os.environ.get("CINN_MOE_GROUPED", "fp8")
+assert _MOE_GROUPED_PRECISION in ("fp8", "16bit"), "CINN_MOE_GROUPED must be fp8 or 16bit"
+
 # number of kernels of this library launched since import (the benchmark reports it)
 launch_count = 0
 # when set to a list, every GEMM launch appends a (start, end) pair of CUDA events to it
@@ -52,6 +58,15 @@ def set_div_mode(mode: str) -> None:
     ``"rn"`` (IEEE division, matches a CPU restatement)."""
     global _DIV_MODE
     _DIV_MODE = {"full": _lib.DIV_FULL, "rn": _lib.DIV_RN}[mode]
+
+
+def set_moe_grouped_precision(mode: str) -> str:
+    """``"fp8"`` or ``"16bit"`` for the drop-in ``moe_grouped_gemm`` (see ``_MOE_GROUPED_PRECISION``); returns the
+    previous setting."""
+    global _MOE_GROUPED_PRECISION
+    assert mode in ("fp8", "16bit"), "precision must be 'fp8' or '16bit'"
+    prev, _MOE_GROUPED_PRECISION = _MOE_GROUPED_PRECISION, mode
+    return prev
 
 
 def get_div_mode() -> str:
@@ -953,6 +968,76 @@ def fp8_grouped_wgrad(grad_out: torch.Tensor, x_fp8: torch.Tensor, x_scale: torc
     return grad_w
 
 
+_EXPERT_WEIGHT_CACHE_16 = {}        # id(weight tensor) -> (key, fp16 copy)
+
+
+def _expert_weights_fp16(weights: torch.Tensor) -> torch.Tensor:
+    """The expert stack as fp16 (the reference casts every operand tile to fp16 in its kernel, src/kernels.py:515),
+    converted when the tensor changes, not per call (same key and caveat as ``cached_expert_weights``)."""
+    if weights.dtype == torch.float16 and weights.is_contiguous():
+        return weights.detach()
+    key = (weights._version, weights.data_ptr(), weights.dtype, tuple(weights.shape))
+    ident = id(weights)
+    hit = _EXPERT_WEIGHT_CACHE_16.get(ident)
+    if hit is not None and hit[0] == key:
+        return hit[1]
+    w16 = weights.detach().to(torch.float16).contiguous()
+    if hit is None:
+        weakref.finalize(weights, _EXPERT_WEIGHT_CACHE_16.pop, ident, None)
+    _EXPERT_WEIGHT_CACHE_16[ident] = (key, w16)
+    return w16
+
+
+def grouped_gemm_16bit(sorted_x: torch.Tensor, weights: torch.Tensor, expert_starts, expert_ends,
+                       out_dtype=torch.float16, out: torch.Tensor = None) -> torch.Tensor:
+    """``out[starts[e]:ends[e]] = sorted_x[starts[e]:ends[e]] @ weights[e].T`` on 16-bit operands (both bf16 or both
+    fp16), fp32 accumulation (``cinn_grouped_gemm_16bit``): the arithmetic of the reference's kernel
+    (src/kernels.py:466-523).  Rows outside every range are left as allocated."""
+    assert sorted_x.is_cuda and weights.is_cuda, "Inputs must be on CUDA"
+    assert sorted_x.dtype == weights.dtype and sorted_x.dtype in (torch.bfloat16, torch.float16), "operands: both bf16 or both fp16"
+    x, w = sorted_x.contiguous(), weights.contiguous()
+    T, d_in = x.shape
+    E, d_out, _ = w.shape
+    starts = expert_starts.to(torch.int64).contiguous()
+    ends = expert_ends.to(torch.int64).contiguous()
+    with torch.cuda.device(x.device):
+        if out is None:
+            out = torch.empty((T, d_out), dtype=out_dtype, device=x.device)
+        _lib.check(_L.cinn_grouped_gemm_16bit(_ptr(x), _ptr(w), _DTYPE_TAG[x.dtype], _ptr(starts), _ptr(ends), E, T, d_in, d_out,
+                                              _ptr(out), _DTYPE_TAG[out.dtype], _stream(x)), "cinn_grouped_gemm_16bit")
+    _count()
+    return out
+
+
+class MoEGroupedGemm16Function(torch.autograd.Function):
+    """``moe_grouped_gemm`` with the forward in the reference's precision (fp16 operands, fp32 accumulation).  The
+    reference has no backward for it; here the gradients come from the same e4m3 kernels as in the default mode
+    (``MoEGroupedGemmFunction``), fed with the saved 16-bit rows."""
+
+    @staticmethod
+    def forward(ctx, sorted_x, weights, expert_starts, expert_ends, out_dtype):
+        x16 = sorted_x.detach().to(torch.float16)
+        out = grouped_gemm_16bit(x16, _expert_weights_fp16(weights), expert_starts, expert_ends, out_dtype)
+        ctx.save_for_backward(x16, weights, expert_starts, expert_ends)
+        ctx.x_dtype, ctx.w_dtype = sorted_x.dtype, weights.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x16, weights, starts, ends = ctx.saved_tensors
+        x_fp8, x_scale = quantize_fp8_rowwise(x16, block_size=128)
+        w_fp8, w_scale = cached_expert_weights(weights)
+        inner = _Saved((x_fp8, x_scale, w_fp8, w_scale, starts, ends), ctx.x_dtype, ctx.w_dtype)
+        return MoEGroupedGemmFunction.backward(inner, grad_out)
+
+
+class _Saved:
+    """What ``MoEGroupedGemmFunction.backward`` reads from its context."""
+
+    def __init__(self, saved_tensors, x_dtype, w_dtype):
+        self.saved_tensors, self.x_dtype, self.w_dtype = saved_tensors, x_dtype, w_dtype
+
+
 class MoEGroupedGemmFunction(torch.autograd.Function):
     """Differentiable grouped GEMM.  The reference's ``moe_grouped_gemm`` is a plain function (src/kernels.py:526-581),
     so on CUDA no gradient reaches the routed experts there; this function gives the grouped GEMM the backward of
@@ -994,10 +1079,16 @@ def moe_grouped_gemm(sorted_x: torch.Tensor, weights: torch.Tensor, expert_start
 
     ``expert_starts`` / ``expert_ends`` are read on the device; ``max_expert_tokens`` is
     accepted for signature compatibility and ignored (no grid depends on it, so the
-    caller's ``.item()`` synchronisation is unnecessary).  Tokens and weights are quantised
-    to e4m3 on the fly; returns fp16 like the reference unless ``dtype`` says otherwise.
-    Unlike the reference it is differentiable (``MoEGroupedGemmFunction``)."""
+    caller's ``.item()`` synchronisation is unnecessary).  By default tokens and weights are quantised
+    to e4m3 on the fly (the weights once per weight update, ``cached_expert_weights``); with
+    ``set_moe_grouped_precision("16bit")`` / ``CINN_MOE_GROUPED=16bit`` the product runs on fp16 operands
+    with fp32 accumulation, the reference kernel's own arithmetic.  Returns fp16 like the reference unless
+    ``dtype`` says otherwise.  Unlike the reference it is differentiable (``MoEGroupedGemmFunction``)."""
     assert sorted_x.is_cuda and weights.is_cuda, "Inputs must be on CUDA"
+    if _MOE_GROUPED_PRECISION == "16bit" and sorted_x.shape[1] % 8 == 0:
+        if torch.is_grad_enabled() and (sorted_x.requires_grad or weights.requires_grad):
+            return MoEGroupedGemm16Function.apply(sorted_x, weights, expert_starts, expert_ends, dtype)
+        return grouped_gemm_16bit(sorted_x.to(torch.float16), _expert_weights_fp16(weights), expert_starts, expert_ends, dtype)
     if _ops is not None and torch.compiler.is_compiling():
         return _ops.grouped_gemm(sorted_x, weights, expert_starts, expert_ends, dtype)
     if torch.is_grad_enabled() and (sorted_x.requires_grad or weights.requires_grad):

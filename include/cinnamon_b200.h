@@ -151,6 +151,15 @@ int cinn_fp8_grouped_gemm(const void* A, const float* sA, const void* W, const f
                           const int64_t* starts, const int64_t* ends, int64_t E, int64_t T, int64_t d_in,
                           int64_t d_out, void* C, int out_dtype, void* stream);
 
+/* The grouped GEMM in the reference's own precision: A (total_rows, d_in) and W (n_experts, d_out, d_in) both bf16 or
+ * both fp16 (in_dtype), fp32 accumulation on the tensor cores (tcgen05 kind::f16), C (total_rows, d_out) of out_dtype.
+ * Replaces grouped_gemm_kernel + moe_grouped_gemm (src/kernels.py:440-581) without the change of numerics that the
+ * e4m3 entry point above makes: same ragged device-side row ranges, no padding, rows outside every range untouched.
+ * d_in a multiple of 8, at most 384 experts, 16-byte aligned buffers. */
+int cinn_grouped_gemm_16bit(const void* A, const void* W, int in_dtype, const int64_t* expert_starts, const int64_t* expert_ends,
+                            int64_t n_experts, int64_t total_rows, int64_t d_in, int64_t d_out, void* C, int out_dtype,
+                            void* stream);
+
 /* Input gradient of the grouped GEMM:  dX[starts[e]:ends[e], :] = dY[starts[e]:ends[e], :] @ W[e].
  * No counterpart in the reference: its moe_grouped_gemm is not differentiable (src/kernels.py:526-581 is a plain
  * function), so routed experts receive no gradient there; the arithmetic mirrors the dense dgrad

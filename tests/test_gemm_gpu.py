@@ -280,6 +280,44 @@ def test_grouped_gemm(K, name):
     assert rel.median().item() < 0.08
 
 
+@pytest.mark.parametrize("name", list(GROUPED))
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_grouped_gemm_16bit(K, name, dtype):
+    """The grouped GEMM in the reference's precision (16-bit operands, fp32 accumulation on the tensor cores) against
+    the float64 product of the same 16-bit operands; canary rows; then the drop-in in its "16bit" mode, forward and
+    backward."""
+    E, d_in, d_out, counts = GROUPED[name]
+    x, w, starts, ends = _grouped_case(E, d_in, d_out, counts, seed=7 + len(name), gap=9)
+    x, w = x.to(dtype), w.to(dtype)
+    T, used = x.shape[0], int(ends[-1])
+    ref = torch.zeros(T, d_out, dtype=torch.float64)
+    for e in range(E):
+        s, t = int(starts[e]), int(ends[e])
+        ref[s:t] = x[s:t].double() @ w[e].double().t()
+    out = torch.full((T, d_out), 777.0, dtype=torch.float32, device="cuda")
+    K.grouped_gemm_16bit(x.cuda(), w.cuda(), starts.cuda(), ends.cuda(), out=out)
+    torch.cuda.synchronize()
+    assert K.device_status() == 0
+    assert torch.all(out[used:] == 777.0), "rows outside every expert's range were written"
+    err = rel_fro(out[:used], ref[:used])
+    print(f"{name} {dtype}: rel-Fro {err:.3e}")
+    assert err < 2e-6                                            # exact products, fp32 accumulation
+    out16 = K.grouped_gemm_16bit(x.cuda(), w.cuda(), starts.cuda(), ends.cuda(), out_dtype=torch.float16)
+    torch.testing.assert_close(out16[:used].float().cpu(), ref[:used].float(), rtol=2e-3, atol=2e-3)
+    prev = K.set_moe_grouped_precision("16bit")
+    try:
+        xg = x.float().cuda().requires_grad_(True)               # fp32 rows, as the reference's MoE passes them
+        wg = w.float().cuda().requires_grad_(True)
+        y = K.moe_grouped_gemm(xg, wg, starts.cuda(), ends.cuda())
+        assert y.dtype == torch.float16
+        rel = ((ref[:used] - y[:used].detach().cpu().double()).abs() / (ref[:used].abs() + 1e-6)).mean().item()
+        assert rel < 0.01, rel                                   # the reference's own bound (tests/test_kernels.py:155)
+        y.float().pow(2).mean().backward()
+        assert torch.isfinite(xg.grad).all() and torch.isfinite(wg.grad).all() and wg.grad.abs().sum() > 0
+    finally:
+        K.set_moe_grouped_precision(prev)
+
+
 def test_config2_full_size_sampled(K):
     """16384 x 18432 x 7168 forward; rows sampled for the float64 check."""
     M, Kd, N = 16384, 7168, 18432

@@ -179,11 +179,22 @@ def test_grouped_gemm_against_triton(K, R):
     assert ours.shape == theirs.shape and ours.dtype == theirs.dtype == torch.float16
     assert O.rel_fro(theirs.float().cpu(), ref64) < 2e-3
     assert O.rel_fro(ours.float().cpu(), ref64) < 5e-2            # e4m3 rounding of both operands
+    prev = K.set_moe_grouped_precision("16bit")                   # the reference's own arithmetic: fp16 operands
+    try:
+        ours16 = K.moe_grouped_gemm(x.cuda(), w.cuda(), starts.cuda(), ends.cuda(), int(counts.max()))
+    finally:
+        K.set_moe_grouped_precision(prev)
+    used = int(ends[-1])
+    assert O.rel_fro(ours16[:used].float().cpu(), theirs[:used].float().cpu().double()) < 1e-3
+    assert O.rel_fro(ours16.float().cpu(), ref64) <= O.rel_fro(theirs.float().cpu(), ref64) * 1.05 + 1e-6
 
 
-def test_reference_test_suite_runs_against_the_drop_in():
+@pytest.mark.parametrize("grouped", ["fp8", "16bit"])
+def test_reference_test_suite_runs_against_the_drop_in(grouped):
     """tests/test_kernels.py of the reference (quantiser, indexer and grouped-GEMM classes, :29-155), unchanged,
-    with ``kernels`` bound to this library's drop-in module."""
+    with ``kernels`` bound to this library's drop-in module.  With the grouped GEMM in the reference's precision
+    (CINN_MOE_GROUPED=16bit) every test passes; in the default e4m3 mode the grouped-GEMM accuracy test is left out:
+    its bound (mean element-wise relative error below 1 %) is a bound on 16-bit arithmetic."""
     test_file = os.path.join(REF_DIR, "tests", "test_kernels.py")
     if not os.path.isfile(test_file):
         pytest.skip("reference not staged")
@@ -193,8 +204,11 @@ def test_reference_test_suite_runs_against_the_drop_in():
         "sys.modules['kernels'] = k\n"
         "import pytest\n"
         "sys.exit(pytest.main(['-q', '-x', '-p', 'no:cacheprovider', '--rootdir', %r, %r, "
-        "'-k', 'TestFP8Quantization or TestLightningIndexer or TestMoEGroupedGEMM and test_output_shape']))\n"
-    ) % (ROOT, REF_DIR, test_file)
-    p = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600, cwd=REF_DIR)
+        "'-k', %r]))\n"
+    ) % (ROOT, REF_DIR, test_file,
+         "TestFP8Quantization or TestLightningIndexer or TestMoEGroupedGEMM" if grouped == "16bit" else
+         "TestFP8Quantization or TestLightningIndexer or TestMoEGroupedGEMM and test_output_shape")
+    p = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600, cwd=REF_DIR,
+                       env=dict(os.environ, CINN_MOE_GROUPED=grouped))
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-2000:]
     assert " passed" in p.stdout and "skipped" not in p.stdout.splitlines()[-1], p.stdout[-500:]
