@@ -173,7 +173,8 @@ sparse_attn_bwd_kernel(const TG* __restrict__ d_out, const float* __restrict__ o
                        const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                        const int64_t* __restrict__ idx, float* __restrict__ dq, float* __restrict__ dk,
                        float* __restrict__ dv, int B, int H, int L, int K, int Dqk, int Dv, float scale,
-                       int warps_per_cta, bool vec_qk, bool vec_v) {
+                       int warps_per_cta, bool vec_qk, bool vec_v, int atom_qk, int atom_v) {
+    // atom_qk / atom_v: widest vector (4, 2 or 1 floats) the gradient buffers' widths AND addresses allow
     extern __shared__ __align__(16) float sm[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (warp >= warps_per_cta) return;
@@ -227,8 +228,8 @@ sparse_attn_bwd_kernel(const TG* __restrict__ d_out, const float* __restrict__ o
         }
         __syncwarp();
         // dq[d] = scale * sum_j dp_j k_j[d];  dk[idx_j][d] += scale * dp_j q[d]
-        const bool pair_qk = (Dqk & 1) == 0, pair_v = (Dv & 1) == 0;     // even widths: 8-byte aligned float2 atomics
-        const bool quad_qk = (Dqk & 3) == 0, quad_v = (Dv & 3) == 0;     // multiples of 4: one 16-byte atomic per lane and key
+        const bool pair_qk = atom_qk >= 2, pair_v = atom_v >= 2;         // 8-byte aligned float2 atomics
+        const bool quad_qk = atom_qk >= 4, quad_v = atom_v >= 4;         // one 16-byte atomic per lane and key
         if (quad_qk) {
             for (int d0 = lane * 4; d0 < Dqk; d0 += 128) {
                 float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -370,8 +371,15 @@ static int sparse_bwd_typed(const TG* d_out, const float* out, const float* lse,
     if (rc) return rc;
     const bool vec_qk = (Dqk * sizeof(T)) % 16 == 0 && (reinterpret_cast<uintptr_t>(k) & 15) == 0;
     const bool vec_v = (Dv * sizeof(T)) % 16 == 0 && (reinterpret_cast<uintptr_t>(v) & 15) == 0;
+    // 16- and 8-byte atomics and stores need rows that start on such boundaries: width and base address both
+    auto widest = [](int D, const void* a, const void* b) {
+        const uintptr_t bits = reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b);
+        if ((D & 3) == 0 && (bits & 15) == 0) return 4;
+        if ((D & 1) == 0 && (bits & 7) == 0) return 2;
+        return 1;
+    };
     sparse_attn_bwd_kernel<T, TG><<<grid, 256, smem, st>>>(d_out, out, lse, q, k, v, idx, dq, dk, dv, B, H, L, K, Dqk, Dv, scale,
-                                                         warps, vec_qk, vec_v);
+                                                         warps, vec_qk, vec_v, widest(Dqk, dk, dq), widest(Dv, dv, dv));
     CINN_CHECK_LAUNCH();
     return CINN_OK;
 }

@@ -64,6 +64,7 @@ xs = [torch.randn(2, 5 + 3 * r, d, generator=torch.Generator().manual_seed(40 + 
 # the unsharded layer sees all tokens of all ranks as one batch of sequences; pad-free: run it per rank's tokens
 res = {}
 full.train(); sharded.train()
+full.gamma = 0.0        # `full` is called once per rank's tokens: its bias must not move between the calls
 x_full = [t.clone().requires_grad_(True) for t in xs]
 outs = [full(t) for t in x_full]
 # the bias update of `full` ran once per call; undo and apply the update for the global counts instead (what the

