@@ -138,11 +138,11 @@ def fp8_linear(x: Tensor, weight: Tensor, round_scale: bool) -> Tensor:
 # ---------------------------------------------------------------------------------------------------------------
 @torch.library.custom_op("cinnamon_b200::grouped_gemm_fwd", mutates_args=(), device_types="cuda")
 def grouped_gemm_fwd(sorted_x: Tensor, weights: Tensor, expert_starts: Tensor, expert_ends: Tensor,
-                     out_dtype: int) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
+                     out_dtype: int) -> Tuple[Tensor, Tensor, Tensor]:
     ctx = _Ctx()
     out = K.MoEGroupedGemmFunction.forward(ctx, sorted_x, weights, expert_starts, expert_ends, _DTYPES[out_dtype])
-    x_fp8, x_scale, w_fp8, w_scale, _, _ = ctx.saved_tensors
-    return out, x_fp8, x_scale, w_fp8, w_scale
+    x_fp8, x_scale = ctx.saved_tensors[0], ctx.saved_tensors[1]
+    return out, x_fp8, x_scale          # the e4m3 weights live in the library's cache: the backward asks for them again
 
 
 @grouped_gemm_fwd.register_fake
@@ -150,36 +150,35 @@ def _(sorted_x, weights, expert_starts, expert_ends, out_dtype):
     T, d_in = sorted_x.shape
     E, d_out, _ = weights.shape
     e = lambda shape, dt: torch.empty(shape, dtype=dt, device=sorted_x.device)                  # noqa: E731
-    return (e((T, d_out), _DTYPES[out_dtype]), e((T, d_in), F8), e((T, _nb(d_in)), torch.float32), e((E, d_out, d_in), F8),
-            e((E, _nb(d_out), _nb(d_in)), torch.float32))
+    return e((T, d_out), _DTYPES[out_dtype]), e((T, d_in), F8), e((T, _nb(d_in)), torch.float32)
 
 
 @torch.library.custom_op("cinnamon_b200::grouped_gemm_bwd", mutates_args=(), device_types="cuda")
-def grouped_gemm_bwd(grad_out: Tensor, x_fp8: Tensor, x_scale: Tensor, w_fp8: Tensor, w_scale: Tensor, expert_starts: Tensor,
-                     expert_ends: Tensor, x_dtype: int, w_dtype: int) -> Tuple[Tensor, Tensor]:
+def grouped_gemm_bwd(grad_out: Tensor, x_fp8: Tensor, x_scale: Tensor, weights: Tensor, expert_starts: Tensor,
+                     expert_ends: Tensor, x_dtype: int) -> Tuple[Tensor, Tensor]:
     ctx = _Ctx()
+    w_fp8, w_scale = K.cached_expert_weights(weights)
     ctx.saved_tensors = (x_fp8, x_scale, w_fp8, w_scale, expert_starts, expert_ends)
-    ctx.x_dtype, ctx.w_dtype = _DTYPES[x_dtype], _DTYPES[w_dtype]
+    ctx.x_dtype, ctx.w_dtype = _DTYPES[x_dtype], weights.dtype
     gx, gw = K.MoEGroupedGemmFunction.backward(ctx, grad_out)[:2]
     return gx, gw
 
 
 @grouped_gemm_bwd.register_fake
-def _(grad_out, x_fp8, x_scale, w_fp8, w_scale, expert_starts, expert_ends, x_dtype, w_dtype):
-    return (torch.empty(x_fp8.shape, dtype=_DTYPES[x_dtype], device=grad_out.device),
-            torch.empty(w_fp8.shape, dtype=_DTYPES[w_dtype], device=grad_out.device))
+def _(grad_out, x_fp8, x_scale, weights, expert_starts, expert_ends, x_dtype):
+    return (torch.empty(x_fp8.shape, dtype=_DTYPES[x_dtype], device=grad_out.device), torch.empty_like(weights))
 
 
 def _grouped_setup(ctx, inputs, output):
     sorted_x, weights, starts, ends, _ = inputs
-    ctx.save_for_backward(*output[1:], starts, ends)
-    ctx.x_dtype, ctx.w_dtype = _tag(sorted_x.dtype), _tag(weights.dtype)
+    ctx.save_for_backward(output[1], output[2], weights, starts, ends)
+    ctx.x_dtype = _tag(sorted_x.dtype)
     ctx.set_materialize_grads(False)
 
 
 def _grouped_backward(ctx, g_out, *ignored):
-    x_fp8, x_scale, w_fp8, w_scale, starts, ends = ctx.saved_tensors
-    gx, gw = torch.ops.cinnamon_b200.grouped_gemm_bwd(g_out, x_fp8, x_scale, w_fp8, w_scale, starts, ends, ctx.x_dtype, ctx.w_dtype)
+    x_fp8, x_scale, weights, starts, ends = ctx.saved_tensors
+    gx, gw = torch.ops.cinnamon_b200.grouped_gemm_bwd(g_out, x_fp8, x_scale, weights, starts, ends, ctx.x_dtype)
     return gx, gw, None, None, None
 
 
@@ -197,7 +196,7 @@ def grouped_gemm(sorted_x: Tensor, weights: Tensor, expert_starts: Tensor, exper
 def sparse_attn_fwd(q: Tensor, k: Tensor, v: Tensor, idx: Tensor, scale: float) -> Tuple[Tensor, Tensor, Tensor, Tensor]:
     ctx = _Ctx()
     out, attn = SA.SparseAttentionFunction.forward(ctx, q, k, v, idx, scale)
-    _, _, _, _, out32, lse = ctx.saved_tensors
+    out32, lse = ctx.saved_tensors[4], ctx.saved_tensors[5]
     return out, attn, out32 if out32.data_ptr() != out.data_ptr() else out32.clone(), lse
 
 
@@ -210,34 +209,34 @@ def _(q, k, v, idx, scale):
 
 
 @torch.library.custom_op("cinnamon_b200::sparse_attn_bwd", mutates_args=(), device_types="cuda")
-def sparse_attn_bwd(grad_out: Tensor, q: Tensor, k: Tensor, v: Tensor, idx: Tensor, out32: Tensor, lse: Tensor,
+def sparse_attn_bwd(grad_out: Tensor, q: Tensor, k: Tensor, v: Tensor, idx: Tensor, out32: Tensor, lse: Tensor, attn: Tensor,
                     scale: float) -> Tuple[Tensor, Tensor, Tensor]:
     ctx = _Ctx()
     in_dtype = q.dtype
     work = in_dtype if in_dtype in SA._TAG else torch.float32
-    ctx.saved_tensors = tuple(t.to(work).contiguous() for t in (q, k, v)) + (idx.to(torch.int64).contiguous(), out32, lse)
+    ctx.saved_tensors = tuple(t.to(work).contiguous() for t in (q, k, v)) + (idx.to(torch.int64).contiguous(), out32, lse, attn)
     ctx.scale, ctx.in_dtype = float(scale), in_dtype
     gq, gk, gv = SA.SparseAttentionFunction.backward(ctx, grad_out, None)[:3]
     return gq, gk, gv
 
 
 @sparse_attn_bwd.register_fake
-def _(grad_out, q, k, v, idx, out32, lse, scale):
+def _(grad_out, q, k, v, idx, out32, lse, attn, scale):
     return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
 
 
 def _attn_setup(ctx, inputs, output):
     q, k, v, idx, scale = inputs
-    ctx.save_for_backward(q, k, v, idx, output[2], output[3])
+    ctx.save_for_backward(q, k, v, idx, output[2], output[3], output[1])
     ctx.scale = scale
     ctx.set_materialize_grads(False)
 
 
 def _attn_backward(ctx, g_out, *ignored):
-    q, k, v, idx, out32, lse = ctx.saved_tensors
+    q, k, v, idx, out32, lse, attn = ctx.saved_tensors
     if g_out is None:
         return None, None, None, None, None
-    gq, gk, gv = torch.ops.cinnamon_b200.sparse_attn_bwd(g_out, q, k, v, idx, out32, lse, ctx.scale)
+    gq, gk, gv = torch.ops.cinnamon_b200.sparse_attn_bwd(g_out, q, k, v, idx, out32, lse, attn, ctx.scale)
     return gq, gk, gv, None, None
 
 
