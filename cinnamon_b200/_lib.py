@@ -47,9 +47,6 @@ SIGNATURES = {
     "cinn_sparse_attn_fwd": [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, ctypes.c_float, _vp],
     "cinn_sparse_attn_bwd": [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
                              ctypes.c_float, _vp],
-    "cinn_sparse_attn_bwd_workspace_bytes": [_i64, _i64, _i64, _i64],
-    "cinn_sparse_attn_bwd_ws": [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
-                                _i64, ctypes.c_float, _vp],
     "cinn_lightning_indexer": [_vp, _vp, _vp, _i32, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp],
     "cinn_scatter_rows": [_vp, _vp, _vp, _i64, _i64, _i64, _vp],
     "cinn_set_gemm_sm_limit": [_i32],
@@ -89,7 +86,6 @@ def _load() -> ctypes.CDLL:
         fn.restype = (ctypes.c_char_p if name == "cinn_last_error"
                       else ctypes.c_longlong if name == "cinn_set_wait_limit_cycles"
                       else ctypes.c_int64 if name in ("cinn_moe_route_workspace_ints", "cinn_moe_route_static_max_ints",
-                                                 "cinn_sparse_attn_bwd_workspace_bytes",
                                                  "cinn_fp8_grouped_wgrad_scratch_bytes")
                       else ctypes.c_int)
     return lib

@@ -74,11 +74,6 @@ int p2p_return(const void* rows, const int64_t* seg_start, const int64_t* home_b
                int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity, cudaStream_t st);
 int p2p_barrier(const int64_t* peer_flags, int me, int n_ranks, unsigned epoch, cudaStream_t st);
 long long set_p2p_wait_limit(long long cycles);
-int64_t sparse_attn_bwd_workspace_bytes(int64_t B, int64_t H, int64_t L, int64_t K);
-int sparse_attn_bwd_ws(const void* d_out, int grad_dtype, const float* out, const float* attn_w, const void* q, const void* k,
-                       const void* v, int dtype, const int64_t* idx, float* dq, float* dk, float* dv, void* workspace,
-                       int64_t workspace_bytes, int64_t B, int64_t H, int64_t L, int64_t K, int64_t Dqk, int64_t Dv, float scale,
-                       cudaStream_t st);
 int grouped_gemm_16bit(const void* A, const void* W, int in_dtype, const int64_t* starts, const int64_t* ends, int64_t E,
                        int64_t T, int64_t d_in, int64_t d_out, void* C, int out_dtype, cudaStream_t st);
 int moe_combine_backward(const void* rows, int dtype, const int64_t* pos, const float* gates, const float* dy, void* d_rows,
@@ -296,18 +291,6 @@ int cinn_p2p_barrier(const int64_t* peer_flags, int rank, int n_ranks, unsigned 
 }
 
 long long cinn_set_wait_limit_cycles(long long cycles) { return cinn::set_p2p_wait_limit(cycles); }
-
-int64_t cinn_sparse_attn_bwd_workspace_bytes(int64_t B, int64_t H, int64_t L, int64_t K) {
-    return cinn::sparse_attn_bwd_workspace_bytes(B, H, L, K);
-}
-
-int cinn_sparse_attn_bwd_ws(const void* grad_out, int grad_dtype, const float* out, const float* attn_weights, const void* q,
-                            const void* k, const void* v, int dtype, const int64_t* idx, float* grad_q, float* grad_k,
-                            float* grad_v, void* workspace, int64_t workspace_bytes, int64_t B, int64_t H, int64_t L, int64_t K,
-                            int64_t d_qk, int64_t d_v, float scale, void* stream) {
-    return cinn::sparse_attn_bwd_ws(grad_out, grad_dtype, out, attn_weights, q, k, v, dtype, idx, grad_q, grad_k, grad_v, workspace,
-                                    workspace_bytes, B, H, L, K, d_qk, d_v, scale, (cudaStream_t)stream);
-}
 
 int cinn_grouped_gemm_16bit(const void* A, const void* W, int in_dtype, const int64_t* expert_starts, const int64_t* expert_ends,
                             int64_t n_experts, int64_t total_rows, int64_t d_in, int64_t d_out, void* C, int out_dtype,

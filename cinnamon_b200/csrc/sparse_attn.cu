@@ -301,219 +301,6 @@ sparse_attn_bwd_kernel(const TG* __restrict__ d_out, const float* __restrict__ o
 }
 
 // ---------------------------------------------------------------------------
-// Backward without atomics.  The reference adds every (query, key) pair's contribution to dk / dv with atomics
-// (src/kernels.py:1160-1170), and so does sparse_attn_bwd_kernel above: at model sizes that is hundreds of millions
-// of contended fp32 atomics per call.  With a workspace the work is split by owner instead:
-//   1. per query (one warp each): dS[t, j] = scale * p_j (dO.v_j - delta) is written out, dq = sum_j dS_j k_j;
-//   2. the index lists are inverted once per call (they are shared by all heads): for every (batch, key) the list of
-//      (query, slot) pairs that name it - a counting sort in three small kernels;
-//   3. per key (one warp each): dk[s] = sum over its pairs of dS[t, j] q_t, dv[s] = sum of p[t, j] dO_t, plain stores.
-// The probabilities p come from the forward pass (its attn_weights output).  The order of a key's pairs in the
-// inverted list depends on the order in which the counting sort's atomics land, so the fp32 sums can differ in the
-// last bits from run to run - as with the atomic version.
-// ---------------------------------------------------------------------------
-template <typename T, typename TG>
-__global__ void __launch_bounds__(256)
-sparse_attn_bwd_q_kernel(const TG* __restrict__ d_out, const float* __restrict__ out, const float* __restrict__ attn_w,
-                         const T* __restrict__ k, const T* __restrict__ v, const int64_t* __restrict__ idx,
-                         float* __restrict__ dq, float* __restrict__ dS, int B, int H, int L, int K, int Dqk, int Dv,
-                         float scale, int warps_per_cta, bool vec_v, int vec_dq) {
-    extern __shared__ __align__(16) float sm[];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (warp >= warps_per_cta) return;
-    float* base = sm + (size_t)warp * warp_smem_floats(K, Dqk, Dv, true);
-    int* s_idx = reinterpret_cast<int*>(base);
-    float* s_pp = base + pad4(K);                           // probability
-    float* s_ds = base + 2 * pad4(K);                       // dS
-    float* s_do = base + 3 * pad4(K) + pad4(Dqk);
-    const int64_t n_queries = (int64_t)B * H * L;
-    for (int64_t w = (int64_t)blockIdx.x * warps_per_cta + warp; w < n_queries; w += (int64_t)gridDim.x * warps_per_cta) {
-        const int t = (int)(w % L);
-        const int64_t bh = w / L;
-        const int b = (int)(bh / H);
-        const T* kb = k + bh * (int64_t)L * Dqk;
-        const T* vb = v + bh * (int64_t)L * Dv;
-        float delta = 0.0f;
-        for (int d = lane; d < Dv; d += 32) {
-            const float g = to_float<TG>(d_out[w * Dv + d]);
-            s_do[d] = g;
-            delta = fmaf(g, out[w * Dv + d], delta);
-        }
-        delta = warp_sum(delta);
-        const int64_t* irow = idx + ((int64_t)b * L + t) * K;
-        for (int j = lane; j < K; j += 32) {
-            const int64_t i = irow[j];
-            s_idx[j] = (i >= 0 && i <= t) ? (int)i : -1;
-            s_pp[j] = attn_w[w * K + j];
-        }
-        __syncwarp();
-        const int grp = lane >> 3, l8 = lane & 7;
-        for (int j0 = 0; j0 < K; j0 += 4) {
-            const int j = j0 + grp;
-            const int i = j < K ? s_idx[j] : -1;
-            float dov = 0.0f;
-            if (i >= 0) dov = dot_row_part<T>(s_do, vb + (int64_t)i * Dv, Dv, l8, vec_v);
-            dov = group8_sum(dov);
-            if (l8 == 0 && j < K) s_ds[j] = i >= 0 ? s_pp[j] * (dov - delta) * scale : 0.0f;
-        }
-        __syncwarp();
-        for (int j = lane; j < K; j += 32) dS[w * K + j] = s_ds[j];
-        if (vec_dq >= 4) {
-            for (int d0 = lane * 4; d0 < Dqk; d0 += 128) {
-                float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll 4
-                for (int j = 0; j < K; ++j) {
-                    const int i = s_idx[j];
-                    if (i < 0) continue;
-                    const float ds = s_ds[j];
-                    const T* kr = kb + (int64_t)i * Dqk + d0;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) a[c] = fmaf(ds, to_float<T>(kr[c]), a[c]);
-                }
-                *reinterpret_cast<float4*>(dq + w * Dqk + d0) = make_float4(a[0], a[1], a[2], a[3]);
-            }
-        } else {
-            for (int d0 = lane; d0 < Dqk; d0 += 32) {
-                float a0 = 0.0f;
-                for (int j = 0; j < K; ++j) {
-                    const int i = s_idx[j];
-                    if (i >= 0) a0 = fmaf(s_ds[j], to_float<T>(kb[(int64_t)i * Dqk + d0]), a0);
-                }
-                dq[w * Dqk + d0] = a0;
-            }
-        }
-        __syncwarp();
-    }
-}
-
-// inverted index lists, step 1: how many valid pairs name key s of batch b (counts[b * (L + 1) + s + 1])
-__global__ void __launch_bounds__(256)
-sparse_invert_count_kernel(const int64_t* __restrict__ idx, int* __restrict__ counts, int64_t n_pairs, int L, int K) {
-    for (int64_t p = (int64_t)blockIdx.x * 256 + threadIdx.x; p < n_pairs; p += (int64_t)gridDim.x * 256) {
-        const int64_t bt = p / K;
-        const int t = (int)(bt % L);
-        const int64_t b = bt / L;
-        const int64_t s = idx[p];
-        if (s >= 0 && s <= t) atomicAdd(&counts[b * (L + 1) + s + 1], 1);
-    }
-}
-
-// step 2: per batch, counts -> running offsets in place (offsets[b][0] = 0, offsets[b][s + 1] = pairs of keys <= s);
-// one CTA per batch, chunks of 1024 with a carry
-__global__ void __launch_bounds__(1024)
-sparse_invert_scan_kernel(int* __restrict__ offsets, int L) {
-    __shared__ int s_w[32];
-    __shared__ int s_carry;
-    int* row = offsets + (int64_t)blockIdx.x * (L + 1);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (threadIdx.x == 0) s_carry = 0;
-    __syncthreads();
-    for (int base = 1; base <= L; base += 1024) {
-        const int i = base + threadIdx.x;
-        int v = i <= L ? row[i] : 0;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int u = __shfl_up_sync(0xffffffffu, v, o);
-            if (lane >= o) v += u;
-        }
-        if (lane == 31) s_w[warp] = v;
-        __syncthreads();
-        if (warp == 0) {
-            int u = s_w[lane];
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int x = __shfl_up_sync(0xffffffffu, u, o);
-                if (lane >= o) u += x;
-            }
-            s_w[lane] = u;
-        }
-        __syncthreads();
-        const int total = s_w[31];
-        v += (warp > 0 ? s_w[warp - 1] : 0) + s_carry;
-        if (i <= L) row[i] = v;
-        __syncthreads();
-        if (threadIdx.x == 0) s_carry += total;
-        __syncthreads();
-    }
-}
-
-// step 3: every valid pair takes the next free place in its key's list
-__global__ void __launch_bounds__(256)
-sparse_invert_fill_kernel(const int64_t* __restrict__ idx, const int* __restrict__ offsets, int* __restrict__ cursor,
-                          int* __restrict__ list, int64_t n_pairs, int L, int K) {
-    for (int64_t p = (int64_t)blockIdx.x * 256 + threadIdx.x; p < n_pairs; p += (int64_t)gridDim.x * 256) {
-        const int64_t bt = p / K;
-        const int t = (int)(bt % L);
-        const int64_t b = bt / L;
-        const int64_t s = idx[p];
-        if (s >= 0 && s <= t) {
-            const int at = offsets[b * (L + 1) + s] + atomicAdd(&cursor[b * L + s], 1);
-            list[b * (int64_t)L * K + at] = (int)(p - b * (int64_t)L * K);         // t * K + j
-        }
-    }
-}
-
-// per key: lanes own feature columns (up to 256 per pass), four pairs in flight
-template <typename T, typename TG>
-__global__ void __launch_bounds__(256)
-sparse_attn_bwd_kv_kernel(const TG* __restrict__ d_out, const T* __restrict__ q, const float* __restrict__ attn_w,
-                          const float* __restrict__ dS, const int* __restrict__ offsets, const int* __restrict__ list,
-                          float* __restrict__ dk, float* __restrict__ dv, int B, int H, int L, int K, int Dqk, int Dv) {
-    const int lane = threadIdx.x & 31;
-    const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-    const int64_t n_warps = (int64_t)gridDim.x * 8;
-    const int64_t n_keys = (int64_t)B * H * L;
-    for (int64_t w = warp; w < n_keys; w += n_warps) {
-        const int s = (int)(w % L);
-        const int64_t bh = w / L;
-        const int64_t b = bh / H;
-        const int begin = offsets[b * (L + 1) + s], end = offsets[b * (L + 1) + s + 1];
-        const int* lst = list + b * (int64_t)L * K;
-        const int64_t row0 = bh * L;                       // first query row of this (batch, head)
-        for (int c0 = 0; c0 < Dqk; c0 += 256) {
-            float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-            for (int e = begin; e < end; ++e) {
-                const int ent = lst[e];
-                const int64_t qr = row0 + ent / K;
-                const float ds = dS[qr * K + ent % K];
-                const T* qrow = q + qr * Dqk + c0;
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int d = lane + 32 * u;
-                    if (c0 + d < Dqk) a[u] = fmaf(ds, to_float<T>(qrow[d]), a[u]);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int d = c0 + lane + 32 * u;
-                if (d < Dqk) dk[w * Dqk + d] = a[u];
-            }
-        }
-        for (int c0 = 0; c0 < Dv; c0 += 256) {
-            float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-            for (int e = begin; e < end; ++e) {
-                const int ent = lst[e];
-                const int64_t qr = row0 + ent / K;
-                const float p = attn_w[qr * K + ent % K];
-                const TG* grow = d_out + qr * Dv + c0;
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int d = lane + 32 * u;
-                    if (c0 + d < Dv) a[u] = fmaf(p, to_float<TG>(grow[d]), a[u]);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int d = c0 + lane + 32 * u;
-                if (d < Dv) dv[w * Dv + d] = a[u];
-            }
-        }
-    }
-}
-
-// ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
 constexpr size_t SPARSE_SMEM_LIMIT = 96 * 1024;
@@ -616,86 +403,6 @@ int sparse_attn_bwd(const void* d_out, int grad_dtype, const float* out, const f
         default: set_error("sparse_attention: unknown dtype tag %d", dtype); return CINN_ERR_INVALID;
     }
 #undef CINN_SB
-}
-
-// Workspace of the atomic-free backward: dS (B H L K floats) | offsets (B (L + 1) ints) | cursor (B L ints) |
-// list (B L K ints), each part rounded up to 16 bytes.
-static inline size_t up16(size_t n) { return (n + 15) & ~(size_t)15; }
-int64_t sparse_attn_bwd_workspace_bytes(int64_t B, int64_t H, int64_t L, int64_t K) {
-    if (B <= 0 || H <= 0 || L <= 0 || K <= 0) return 16;
-    return (int64_t)(up16((size_t)B * H * L * K * 4) + up16((size_t)B * (L + 1) * 4) + up16((size_t)B * L * 4) +
-                     up16((size_t)B * L * K * 4));
-}
-
-template <typename T, typename TG>
-static int sparse_bwd_ws_typed(const TG* d_out, const float* out, const float* attn_w, const T* q, const T* k, const T* v,
-                               const int64_t* idx, float* dq, float* dk, float* dv, void* ws, int B, int H, int L, int K, int Dqk,
-                               int Dv, float scale, cudaStream_t st) {
-    uint8_t* base = reinterpret_cast<uint8_t*>(ws);
-    float* dS = reinterpret_cast<float*>(base);
-    int* offsets = reinterpret_cast<int*>(base + up16((size_t)B * H * L * K * 4));
-    int* cursor = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(offsets) + up16((size_t)B * (L + 1) * 4));
-    int* list = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(cursor) + up16((size_t)B * L * 4));
-    // offsets and cursor are adjacent: one clear for both
-    CINN_CHECK_CUDA(cudaMemsetAsync(offsets, 0, up16((size_t)B * (L + 1) * 4) + up16((size_t)B * L * 4), st));
-    int warps; unsigned grid; size_t smem;
-    int rc = sparse_launch_shape(K, Dqk, Dv, true, (int64_t)B * H * L, &warps, &grid, &smem);
-    if (rc) return rc;
-    rc = allow_smem(sparse_attn_bwd_q_kernel<T, TG>);
-    if (rc) return rc;
-    const bool vec_v = (Dv * sizeof(T)) % 16 == 0 && (reinterpret_cast<uintptr_t>(v) & 15) == 0;
-    const int vec_dq = ((Dqk & 3) == 0 && (reinterpret_cast<uintptr_t>(dq) & 15) == 0) ? 4 : 1;
-    sparse_attn_bwd_q_kernel<T, TG><<<grid, 256, smem, st>>>(d_out, out, attn_w, k, v, idx, dq, dS, B, H, L, K, Dqk, Dv, scale,
-                                                           warps, vec_v, vec_dq);
-    CINN_CHECK_LAUNCH();
-    const int64_t n_pairs = (int64_t)B * L * K;
-    int64_t blocks = (n_pairs + 255) / 256;
-    const int64_t cap = (int64_t)sm_count() * 16;
-    if (blocks > cap) blocks = cap;
-    sparse_invert_count_kernel<<<(unsigned)blocks, 256, 0, st>>>(idx, offsets, n_pairs, L, K);
-    CINN_CHECK_LAUNCH();
-    sparse_invert_scan_kernel<<<(unsigned)B, 1024, 0, st>>>(offsets, L);
-    CINN_CHECK_LAUNCH();
-    sparse_invert_fill_kernel<<<(unsigned)blocks, 256, 0, st>>>(idx, offsets, cursor, list, n_pairs, L, K);
-    CINN_CHECK_LAUNCH();
-    int64_t kv_blocks = ((int64_t)B * H * L + 7) / 8;
-    if (kv_blocks > cap) kv_blocks = cap;
-    sparse_attn_bwd_kv_kernel<T, TG><<<(unsigned)kv_blocks, 256, 0, st>>>(d_out, q, attn_w, dS, offsets, list, dk, dv, B, H, L, K,
-                                                                        Dqk, Dv);
-    CINN_CHECK_LAUNCH();
-    return CINN_OK;
-}
-
-// dq, dk and dv are all WRITTEN (no accumulation, no zeroing needed).  attn_w: the forward's probabilities.
-int sparse_attn_bwd_ws(const void* d_out, int grad_dtype, const float* out, const float* attn_w, const void* q, const void* k,
-                       const void* v, int dtype, const int64_t* idx, float* dq, float* dk, float* dv, void* workspace,
-                       int64_t workspace_bytes, int64_t B, int64_t H, int64_t L, int64_t K, int64_t Dqk, int64_t Dv, float scale,
-                       cudaStream_t st) {
-    int rc = check_sparse_args(B, H, L, K, Dqk, Dv);
-    if (rc) return rc;
-    if (B * H * L == 0) return CINN_OK;
-    CINN_CHECK_ARG(d_out && out && q && k && v && dq && dk && dv, "sparse_attention: null pointer");
-    if (K == 0) {
-        CINN_CHECK_CUDA(cudaMemsetAsync(dq, 0, (size_t)B * H * L * Dqk * 4, st));
-        CINN_CHECK_CUDA(cudaMemsetAsync(dk, 0, (size_t)B * H * L * Dqk * 4, st));
-        CINN_CHECK_CUDA(cudaMemsetAsync(dv, 0, (size_t)B * H * L * Dv * 4, st));
-        return CINN_OK;
-    }
-    CINN_CHECK_ARG(idx && attn_w && workspace, "sparse_attention: null pointer");
-    CINN_CHECK_ARG(L * K < (1LL << 31), "sparse_attention: L * K (%lld) is too large for the inverted lists", (long long)(L * K));
-    CINN_CHECK_ARG(workspace_bytes >= sparse_attn_bwd_workspace_bytes(B, H, L, K) && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0,
-                   "sparse_attention: the workspace must hold %lld bytes and be 16-byte aligned",
-                   (long long)sparse_attn_bwd_workspace_bytes(B, H, L, K));
-    CINN_CHECK_ARG(grad_dtype == dtype || grad_dtype == CINN_F32, "sparse_attention: the output gradient must have the inputs' "
-                   "type or be fp32 (tags %d, %d)", grad_dtype, dtype);
-#define CINN_SW(T, TG) sparse_bwd_ws_typed((const TG*)d_out, out, attn_w, (const T*)q, (const T*)k, (const T*)v, idx, dq, dk, dv,                                            workspace, (int)B, (int)H, (int)L, (int)K, (int)Dqk, (int)Dv, scale, st)
-    switch (dtype) {
-        case CINN_BF16: return grad_dtype == CINN_F32 ? CINN_SW(__nv_bfloat16, float) : CINN_SW(__nv_bfloat16, __nv_bfloat16);
-        case CINN_F16: return grad_dtype == CINN_F32 ? CINN_SW(__half, float) : CINN_SW(__half, __half);
-        case CINN_F32: return CINN_SW(float, float);
-        default: set_error("sparse_attention: unknown dtype tag %d", dtype); return CINN_ERR_INVALID;
-    }
-#undef CINN_SW
 }
 
 }  // namespace cinn

@@ -196,7 +196,7 @@ def grouped_gemm(sorted_x: Tensor, weights: Tensor, expert_starts: Tensor, exper
 def sparse_attn_fwd(q: Tensor, k: Tensor, v: Tensor, idx: Tensor, scale: float) -> Tuple[Tensor, Tensor, Tensor, Tensor]:
     ctx = _Ctx()
     out, attn = SA.SparseAttentionFunction.forward(ctx, q, k, v, idx, scale)
-    out32, lse = ctx.saved_tensors[4], ctx.saved_tensors[5]
+    _, _, _, _, out32, lse = ctx.saved_tensors
     return out, attn, out32 if out32.data_ptr() != out.data_ptr() else out32.clone(), lse
 
 
@@ -209,34 +209,34 @@ def _(q, k, v, idx, scale):
 
 
 @torch.library.custom_op("cinnamon_b200::sparse_attn_bwd", mutates_args=(), device_types="cuda")
-def sparse_attn_bwd(grad_out: Tensor, q: Tensor, k: Tensor, v: Tensor, idx: Tensor, out32: Tensor, lse: Tensor, attn: Tensor,
+def sparse_attn_bwd(grad_out: Tensor, q: Tensor, k: Tensor, v: Tensor, idx: Tensor, out32: Tensor, lse: Tensor,
                     scale: float) -> Tuple[Tensor, Tensor, Tensor]:
     ctx = _Ctx()
     in_dtype = q.dtype
     work = in_dtype if in_dtype in SA._TAG else torch.float32
-    ctx.saved_tensors = tuple(t.to(work).contiguous() for t in (q, k, v)) + (idx.to(torch.int64).contiguous(), out32, lse, attn)
+    ctx.saved_tensors = tuple(t.to(work).contiguous() for t in (q, k, v)) + (idx.to(torch.int64).contiguous(), out32, lse)
     ctx.scale, ctx.in_dtype = float(scale), in_dtype
     gq, gk, gv = SA.SparseAttentionFunction.backward(ctx, grad_out, None)[:3]
     return gq, gk, gv
 
 
 @sparse_attn_bwd.register_fake
-def _(grad_out, q, k, v, idx, out32, lse, attn, scale):
+def _(grad_out, q, k, v, idx, out32, lse, scale):
     return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
 
 
 def _attn_setup(ctx, inputs, output):
     q, k, v, idx, scale = inputs
-    ctx.save_for_backward(q, k, v, idx, output[2], output[3], output[1])
+    ctx.save_for_backward(q, k, v, idx, output[2], output[3])
     ctx.scale = scale
     ctx.set_materialize_grads(False)
 
 
 def _attn_backward(ctx, g_out, *ignored):
-    q, k, v, idx, out32, lse, attn = ctx.saved_tensors
+    q, k, v, idx, out32, lse = ctx.saved_tensors
     if g_out is None:
         return None, None, None, None, None
-    gq, gk, gv = torch.ops.cinnamon_b200.sparse_attn_bwd(g_out, q, k, v, idx, out32, lse, attn, ctx.scale)
+    gq, gk, gv = torch.ops.cinnamon_b200.sparse_attn_bwd(g_out, q, k, v, idx, out32, lse, ctx.scale)
     return gq, gk, gv, None, None
 
 

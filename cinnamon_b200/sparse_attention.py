@@ -44,7 +44,7 @@ class SparseAttentionFunction(torch.autograd.Function):
             _lib.check(_L.cinn_sparse_attn_fwd(_ptr(q), _ptr(k), _ptr(v), _TAG[work], _ptr(idx), _ptr(out), _ptr(lse),
                                                _ptr(attn), B, H, L, K, d_qk, d_v, float(scale), _stream(q)),
                        "cinn_sparse_attn_fwd")
-        ctx.save_for_backward(q, k, v, idx, out, lse, attn)
+        ctx.save_for_backward(q, k, v, idx, out, lse)
         ctx.scale = float(scale)
         ctx.in_dtype = in_dtype
         ctx.mark_non_differentiable(attn)
@@ -52,27 +52,13 @@ class SparseAttentionFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_output, grad_attn_weights):
-        q, k, v, idx, out, lse = ctx.saved_tensors[:6]
-        attn = ctx.saved_tensors[6] if len(ctx.saved_tensors) > 6 else None
+        q, k, v, idx, out, lse = ctx.saved_tensors
         B, H, L, d_qk = q.shape
         d_v = v.shape[-1]
         K = idx.shape[-1]
         g = grad_output.contiguous()
         if g.dtype != q.dtype and g.dtype != torch.float32:
             g = g.float()
-        dt = ctx.in_dtype
-        if attn is not None and K > 0 and L * K < 2 ** 31:
-            # without atomics: per query dS and dq, the index lists inverted once for all heads, per key dk and dv
-            with torch.cuda.device(q.device):
-                need = int(_L.cinn_sparse_attn_bwd_workspace_bytes(B, H, L, K))
-                ws = torch.empty(need, dtype=torch.uint8, device=q.device)
-                gq = torch.empty((B, H, L, d_qk), dtype=torch.float32, device=q.device)
-                gk = torch.empty((B, H, L, d_qk), dtype=torch.float32, device=q.device)
-                gv = torch.empty((B, H, L, d_v), dtype=torch.float32, device=q.device)
-                _lib.check(_L.cinn_sparse_attn_bwd_ws(_ptr(g), _TAG[g.dtype], _ptr(out), _ptr(attn), _ptr(q), _ptr(k), _ptr(v),
-                                                      _TAG[q.dtype], _ptr(idx), _ptr(gq), _ptr(gk), _ptr(gv), _ptr(ws), need,
-                                                      B, H, L, K, d_qk, d_v, ctx.scale, _stream(q)), "cinn_sparse_attn_bwd_ws")
-            return gq.to(dt), gk.to(dt), gv.to(dt), None, None
         with torch.cuda.device(q.device):
             gq = torch.empty((B, H, L, d_qk), dtype=torch.float32, device=q.device)
             gk = torch.zeros((B, H, L, d_qk), dtype=torch.float32, device=q.device)     # accumulated into (:1257-1259)

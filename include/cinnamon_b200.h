@@ -224,16 +224,6 @@ int cinn_sparse_attn_bwd(const void* grad_out, int grad_dtype, const float* out,
                          float* grad_v, int64_t B, int64_t H, int64_t L, int64_t K, int64_t d_qk, int64_t d_v, float scale,
                          void* stream);
 
-/* The same gradients without atomics, for callers that can lend a workspace (cinn_sparse_attn_bwd_workspace_bytes
- * bytes, 16-byte aligned) and kept the forward's attn_weights: per query dS and grad_q; the index lists inverted
- * once for all heads (which queries name a key); per key grad_k and grad_v as plain sums.  Replaces
- * sparse_attention_bwd_kernel (src/kernels.py:1053-1173), whose per-element atomic adds (:1160-1170) are what the
- * entry point above mirrors.  grad_q, grad_k and grad_v are all written: no zeroing by the caller.  L * K < 2^31. */
-int64_t cinn_sparse_attn_bwd_workspace_bytes(int64_t B, int64_t H, int64_t L, int64_t K);
-int cinn_sparse_attn_bwd_ws(const void* grad_out, int grad_dtype, const float* out, const float* attn_weights, const void* q,
-                            const void* k, const void* v, int dtype, const int64_t* idx, float* grad_q, float* grad_k,
-                            float* grad_v, void* workspace, int64_t workspace_bytes, int64_t B, int64_t H, int64_t L, int64_t K,
-                            int64_t d_qk, int64_t d_v, float scale, void* stream);
 
 /* Lightning indexer logits: out[b, t, s] = sum_h relu(q[b, t, h, :] . k[b, s, :]) * w[b, t, h], fp16.
  * Replaces lightning_indexer_kernel + lightning_indexer_fused (src/kernels.py:321-433): dot-product operands

@@ -158,39 +158,3 @@ def test_backward_with_gradient_buffers_at_odd_addresses():
     for a, b in zip(*grads):
         torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
     assert K.device_status() == 0
-
-
-@pytest.mark.gpu
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_backward_without_atomics_equals_the_atomic_one(dtype):
-    """cinn_sparse_attn_bwd_ws (per-query pass + inverted index lists + per-key pass) against cinn_sparse_attn_bwd
-    (atomics, as the reference) through the C ABI: same gradients up to the order of the fp32 sums.  Lists with
-    duplicates, keys after the query and out-of-range entries included."""
-    import ctypes
-    from cinnamon_b200 import kernels as K
-    lib = K._lib.lib
-    tag = {torch.float32: 1, torch.bfloat16: 0}[dtype]
-    g = torch.Generator().manual_seed(57)
-    B, H, L, Kk, dqk, dv = 2, 3, 150, 20, 48, 24
-    q, k = (torch.randn(B, H, L, dqk, generator=g).to(dtype).cuda() for _ in range(2))
-    v = torch.randn(B, H, L, dv, generator=g).to(dtype).cuda()
-    idx = torch.randint(-2, L + 3, (B, L, Kk), generator=g).cuda()
-    go = torch.randn(B, H, L, dv, generator=g).cuda()
-    out = torch.empty(B, H, L, dv, device="cuda")
-    lse = torch.empty(B, H, L, device="cuda")
-    attn = torch.empty(B, H, L, Kk, device="cuda")
-    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    p = lambda t: ctypes.c_void_p(t.data_ptr())                                        # noqa: E731
-    K._lib.check(lib.cinn_sparse_attn_fwd(p(q), p(k), p(v), tag, p(idx), p(out), p(lse), p(attn), B, H, L, Kk, dqk, dv, 0.2, st), "fwd")
-    a = [torch.empty(B, H, L, dqk, device="cuda"), torch.zeros(B, H, L, dqk, device="cuda"), torch.zeros(B, H, L, dv, device="cuda")]
-    K._lib.check(lib.cinn_sparse_attn_bwd(p(go), 1, p(out), p(lse), p(q), p(k), p(v), tag, p(idx), p(a[0]), p(a[1]), p(a[2]), B, H, L,
-                                          Kk, dqk, dv, 0.2, st), "bwd")
-    need = int(lib.cinn_sparse_attn_bwd_workspace_bytes(B, H, L, Kk))
-    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
-    b = [torch.full((B, H, L, d), 9.0, device="cuda") for d in (dqk, dqk, dv)]          # every element must be overwritten
-    K._lib.check(lib.cinn_sparse_attn_bwd_ws(p(go), 1, p(out), p(attn), p(q), p(k), p(v), tag, p(idx), p(b[0]), p(b[1]), p(b[2]),
-                                             p(ws), need, B, H, L, Kk, dqk, dv, 0.2, st), "bwd_ws")
-    torch.cuda.synchronize()
-    for name, x, y in zip(("dq", "dk", "dv"), a, b):
-        torch.testing.assert_close(y, x, rtol=2e-4, atol=2e-5, msg=name)
-    assert K.device_status() == 0
