@@ -378,7 +378,24 @@ def bench_kernels(Kmod, dev, x, w, dy, peaks, fp8_peak_burst=None):
                lambda: Kmod.fp8_grouped_gemm(xgq, xgs, wgq, wgs, st_, en_, out_dtype=torch.bfloat16),
                lambda: ref.moe_grouped_gemm(xg_, wg_, st_, en_, rows_e))
         out[-1]["tflops"] = gflop / (out[-1]["ms"] * 1e-3) / 1e12
-        del xg_, wg_, xgq, xgs, wgq, wgs, x1, w1
+        del xgq, xgs, wgq, wgs, x1, w1
+        # forward + backward of that up-projection through the differentiable drop-in (the reference's has no backward):
+        # token quantiser, grouped GEMM; output-gradient quantiser, grouped dgrad, weight gradients of all experts
+        xg_t = xg_.clone().requires_grad_(True)
+        wg_t = wg_.float().requires_grad_(True)
+        go_ = torch.randn(Eg * rows_e, 2 * MOE["I"], generator=g1, device=dev).to(torch.bfloat16)
+
+        def fwd_bwd():
+            xg_t.grad = None
+            wg_t.grad = None
+            Kmod.moe_grouped_gemm(xg_t, wg_t, st_, en_, dtype=torch.bfloat16).backward(go_)
+
+        ms_fb = _time_kernel(fwd_bwd, iters=5, warm=2)
+        out.append({"kernel": "moe_grouped_gemm forward + backward, 32 experts x 1024 rows, 7168->4096 (e4m3; expert weights cached; "
+                              "weight gradients of all experts in one grouped-K GEMM)", "ms": ms_fb, "bound": "tensor",
+                    "achieved": 3 * gflop / (ms_fb * 1e-3) / 1e12, "peak": fp8_peak, "unit": "TFLOP/s",
+                    "frac": 3 * gflop / (ms_fb * 1e-3) / 1e12 / fp8_peak})
+        del xg_, wg_, xg_t, wg_t, go_
     del dq, ds, dtq, dts, xbq, xbs, wq, ws
     # other configurations: (tokens, in, out)
     g = torch.Generator(device=dev).manual_seed(1003)

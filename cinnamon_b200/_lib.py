@@ -60,6 +60,8 @@ SIGNATURES = {
     "cinn_fp8_grouped_gemm_scatter": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32, _vp],
     "cinn_p2p_row_table": [_vp, _vp, _vp, _i64, _i64, _i32, _i32, _i64, _vp, _vp],
     "cinn_fp8_grouped_wgrad_scratch_bytes": [_i64, _i64, _i64],
+    "cinn_fp8_grouped_wgrad_fused_scratch_bytes": [_i64, _i64, _i64, _i64],
+    "cinn_fp8_grouped_wgrad_fused": [_vp, _i32, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _i32, _i32, _vp],
     "cinn_fp8_grouped_wgrad": [_vp, _i32, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _i32, _i32, _vp],
     "cinn_swiglu": [_vp, _vp, _i32, _i64, _i64, _vp],
     "cinn_swiglu_backward": [_vp, _vp, _vp, _i32, _i64, _i64, _vp],
@@ -86,7 +88,7 @@ def _load() -> ctypes.CDLL:
         fn.restype = (ctypes.c_char_p if name == "cinn_last_error"
                       else ctypes.c_longlong if name == "cinn_set_wait_limit_cycles"
                       else ctypes.c_int64 if name in ("cinn_moe_route_workspace_ints", "cinn_moe_route_static_max_ints",
-                                                 "cinn_fp8_grouped_wgrad_scratch_bytes")
+                                                 "cinn_fp8_grouped_wgrad_scratch_bytes", "cinn_fp8_grouped_wgrad_fused_scratch_bytes")
                       else ctypes.c_int)
     return lib
 

@@ -74,6 +74,10 @@ int p2p_return(const void* rows, const int64_t* seg_start, const int64_t* home_b
                int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity, cudaStream_t st);
 int p2p_barrier(const int64_t* peer_flags, int me, int n_ranks, unsigned epoch, cudaStream_t st);
 long long set_p2p_wait_limit(long long cycles);
+int64_t grouped_wgrad_fused_scratch_bytes(int64_t T, int64_t E, int64_t d_in, int64_t d_out);
+int fp8_grouped_wgrad_fused(const void* dY, int dy_dtype, const void* x_q, const float* x_s, const int64_t* starts_dev,
+                            const int64_t* ends_dev, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* scratch,
+                            int64_t scratch_bytes, void* dW, int out_dtype, int div_mode, cudaStream_t st);
 int grouped_gemm_16bit(const void* A, const void* W, int in_dtype, const int64_t* starts, const int64_t* ends, int64_t E,
                        int64_t T, int64_t d_in, int64_t d_out, void* C, int out_dtype, cudaStream_t st);
 int moe_combine_backward(const void* rows, int dtype, const int64_t* pos, const float* gates, const float* dy, void* d_rows,
@@ -291,6 +295,17 @@ int cinn_p2p_barrier(const int64_t* peer_flags, int rank, int n_ranks, unsigned 
 }
 
 long long cinn_set_wait_limit_cycles(long long cycles) { return cinn::set_p2p_wait_limit(cycles); }
+
+int64_t cinn_fp8_grouped_wgrad_fused_scratch_bytes(int64_t total_rows, int64_t n_experts, int64_t d_in, int64_t d_out) {
+    return cinn::grouped_wgrad_fused_scratch_bytes(total_rows, n_experts, d_in, d_out);
+}
+
+int cinn_fp8_grouped_wgrad_fused(const void* dY, int dy_dtype, const void* x_q, const float* x_scales, const int64_t* expert_starts,
+                                 const int64_t* expert_ends, int64_t n_experts, int64_t total_rows, int64_t d_in, int64_t d_out,
+                                 void* scratch, int64_t scratch_bytes, void* dW, int out_dtype, int div_mode, void* stream) {
+    return cinn::fp8_grouped_wgrad_fused(dY, dy_dtype, x_q, x_scales, expert_starts, expert_ends, n_experts, total_rows, d_in, d_out,
+                                         scratch, scratch_bytes, dW, out_dtype, div_mode, (cudaStream_t)stream);
+}
 
 int cinn_grouped_gemm_16bit(const void* A, const void* W, int in_dtype, const int64_t* expert_starts, const int64_t* expert_ends,
                             int64_t n_experts, int64_t total_rows, int64_t d_in, int64_t d_out, void* C, int out_dtype,

@@ -824,6 +824,69 @@ int fp8_grouped_gemm_dgrad(const void* dY, const float* sdY, const void* W, cons
     return launch_out<true, true>(ta, tb, p, out_dtype, gemm_sms(), st);
 }
 
+// Weight gradients of all experts in one launch (the GK instantiation of the pair kernel): dW (E, d_out, d_in) with
+// A = dY^T quantised per expert segment, (d_out, max_tiles * 128), and B = x block-quantised per segment and
+// transposed, (d_in, max_tiles * 128); kb_start (E + 1 ints, device) gives every expert's K blocks.
+template <int OUT>
+static int launch_pair_gk(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int clusters,
+                          cudaStream_t st) {
+    auto kern = pair::fp8_gemm_pair_kernel<false, OUT, true>;
+    const size_t smem = pair::PSMEM_BYTES;
+    static thread_local bool configured[64] = {};
+    int dev = 0;
+    CINN_CHECK_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        CINN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * clusters, 1, 1);
+    cfg.blockDim = dim3(pair::PTHREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CINN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p));
+    return CINN_OK;
+}
+
+int fp8_gemm_grouped_k(const void* A, const float* sA, const void* B, const float* sB, const int* kb_start, int64_t E,
+                       int64_t M, int64_t N, int64_t max_tiles, void* C, int out_dtype, cudaStream_t st) {
+    CINN_CHECK_ARG(E >= 1 && M > 0 && N > 0 && max_tiles >= 1, "grouped-K GEMM: bad shape");
+    CINN_CHECK_ARG(M % pair::PM == 0 && N % pair::PN == 0, "grouped-K GEMM: M (%lld) and N (%lld) must be multiples of 256",
+                   (long long)M, (long long)N);
+    CINN_CHECK_ARG(A && sA && B && sB && kb_start && C && al16(A) && al16(B) && al16(C), "grouped-K GEMM: null or unaligned pointer");
+    CINN_CHECK_ARG(E * M < (1LL << 31) && N < (1LL << 31) && max_tiles * 128 < (1LL << 31), "grouped-K GEMM: dimension too large");
+    const int64_t Kp = max_tiles * 128;
+    CUtensorMap ta, tb;
+    int rc = make_map(&ta, A, (uint64_t)Kp, (uint64_t)M, (uint64_t)Kp, BK, BM);
+    if (rc) return rc;
+    rc = make_map(&tb, B, (uint64_t)Kp, (uint64_t)N, (uint64_t)Kp, BK, 128);
+    if (rc) return rc;
+    const int64_t nnb = (N + 127) / 128;
+    GemmParams p{};
+    p.sA = sA; p.sa_stride_m = max_tiles; p.sa_stride_k = 1;
+    p.sB = sB; p.sb_stride_k = nnb; p.sb_stride_n = 1; p.sb_stride_e = 0;
+    p.C = C; p.ldc = N; p.M = (int)M; p.N = (int)N; p.K = 0;
+    p.starts = reinterpret_cast<const int64_t*>(kb_start); p.ends = nullptr; p.E = (int)E; p.b_rows_per_expert = 0;
+    CUtensorMap tc;
+    rc = make_out_map(&tc, ta, p, out_dtype, E * M);
+    if (rc) return rc;
+    const int64_t tiles = E * (M / pair::PM) * (N / pair::PN);
+    const int clusters = (int)(tiles < gemm_sms() / 2 ? tiles : gemm_sms() / 2);
+    switch (out_dtype) {
+        case CINN_BF16: return launch_pair_gk<CINN_BF16>(ta, tb, tc, p, clusters, st);
+        case CINN_F32: return launch_pair_gk<CINN_F32>(ta, tb, tc, p, clusters, st);
+        case CINN_F32_BF16: return launch_pair_gk<CINN_F32_BF16>(ta, tb, tc, p, clusters, st);
+        default: set_error("grouped-K GEMM: the gradient is fp32 (optionally holding bf16-rounded values) or bf16"); return CINN_ERR_INVALID;
+    }
+}
+
 // Grouped GEMM on 16-bit operands: C[starts[e]:ends[e]] = A[starts[e]:ends[e]] @ W[e]^T with A (T, d_in) and
 // W (E, d_out, d_in) both bf16 or both fp16, fp32 accumulation (the reference's grouped_gemm_kernel arithmetic).
 template <bool BF16_IN, int OUT>

@@ -93,7 +93,12 @@ __device__ __forceinline__ PairTile pair_tile(const GemmParams& p, int t) {
     return ti;
 }
 
-template <bool B_MN, int OUT>
+// GK ("grouped K"): E independent problems of the same M x N whose reduction ranges differ - the weight gradients
+// of the experts, dW[e] = dY[rows of e]^T @ x[rows of e].  Both operands are K-major over one padded token axis on
+// which expert e owns the K blocks [kb_start[e], kb_start[e + 1]) (p.starts holds that int array, p.E = E); tile t
+// belongs to expert t / (tiles per expert) and is stored at rows e * M + ... of the (E * M, N) output.  An expert
+// without rows gets zeros.  M and N are multiples of 256 here, so every tile is whole.
+template <bool B_MN, int OUT, bool GK = false>
 __global__ void __launch_bounds__(PTHREADS, 1)
 fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
@@ -131,9 +136,23 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int KB = (p.K + BK - 1) / BK;
-    const int n_total = pair_total(p);
+    const int KB_dense = (p.K + BK - 1) / BK;
+    const int per_expert = pair_total(p);
+    const int n_total = GK ? per_expert * p.E : per_expert;
     const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+    const int* kb_start = reinterpret_cast<const int*>(p.starts);
+    // tile t -> its coordinates inside one problem, the expert it belongs to, its K blocks
+    auto locate = [&](int t, PairTile& ti, int& e, int& kb0, int& KB) {
+        if constexpr (GK) {
+            e = t / per_expert;
+            ti = pair_tile(p, t - e * per_expert);
+            kb0 = kb_start[e];
+            KB = kb_start[e + 1] - kb0;
+        } else {
+            e = 0; kb0 = 0; KB = KB_dense;
+            ti = pair_tile(p, t);
+        }
+    };
 
     if (warp == 8) {
         // ------------------------------ TMA producer (both CTAs) ------------------------------
@@ -142,16 +161,17 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             uint32_t it = 0;
             bool alive = true;
             for (int t = cluster_id; t < n_total && alive; t += n_clusters) {
-                const PairTile ti = pair_tile(p, t);
+                PairTile ti; int e, kb0, KB;
+                locate(t, ti, e, kb0, KB);
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % PSTAGES;
                     const uint32_t ph = (it / PSTAGES) & 1;
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, (1 << 8) | 1)) { alive = false; break; }
                     if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * (PA_BYTES + PB_BYTES));
                     const uint32_t fb = full_leader + 8 * s;
-                    tma_load_2d_pair(&tmA, fb, smem_u32(smem_a + s * PA_BYTES), kb * BK, ti.m0 + 128 * (int)rank);
-                    if constexpr (!B_MN) tma_load_2d_pair(&tmB, fb, smem_u32(smem_b + s * PB_BYTES), kb * BK, ti.n0 + 128 * (int)rank);
-                    else tma_load_2d_pair(&tmB, fb, smem_u32(smem_b + s * PB_BYTES), ti.n0 + 128 * (int)rank, kb * BK);
+                    tma_load_2d_pair(&tmA, fb, smem_u32(smem_a + s * PA_BYTES), (kb0 + kb) * BK, ti.m0 + 128 * (int)rank);
+                    if constexpr (!B_MN) tma_load_2d_pair(&tmB, fb, smem_u32(smem_b + s * PB_BYTES), (kb0 + kb) * BK, ti.n0 + 128 * (int)rank);
+                    else tma_load_2d_pair(&tmB, fb, smem_u32(smem_b + s * PB_BYTES), ti.n0 + 128 * (int)rank, (kb0 + kb) * BK);
                 }
             }
             if (!alive) {
@@ -169,6 +189,8 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             uint32_t it = 0, last = 0xffffffffu;
             bool alive = true;
             for (int t = cluster_id; t < n_total && alive; t += n_clusters) {
+                PairTile ti_; int e_, kb0_, KB;
+                locate(t, ti_, e_, kb0_, KB);
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     if ((it & 1u) != mine) continue;
                     last = it;
@@ -202,13 +224,15 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         bool alive = true;
         const bool vec_ok = (OUT == CINN_F32 || OUT == CINN_F32_BF16) ? (p.ldc % 4 == 0) : (p.ldc % 8 == 0);
         for (int t = cluster_id; t < n_total && alive; t += n_clusters) {
-            const PairTile ti = pair_tile(p, t);
+            PairTile ti; int e, kb0, KB;
+            locate(t, ti, e, kb0, KB);
             const int row = ti.m0 + 128 * (int)rank + q * 32 + lane;
             const bool rvalid = row < p.M;
             const int col0 = ti.n0 + h * 128;
             const bool cvalid = col0 < p.N;
-            const float* sa_ptr = p.sA + (int64_t)(rvalid ? row : 0) * p.sa_stride_m;
-            const float* sb_ptr = p.sB + (int64_t)(cvalid ? col0 / 128 : 0) * p.sb_stride_n;
+            const float* sa_ptr = p.sA + (int64_t)(rvalid ? row : 0) * p.sa_stride_m + (int64_t)kb0 * p.sa_stride_k;
+            const float* sb_ptr = p.sB + (int64_t)(cvalid ? col0 / 128 : 0) * p.sb_stride_n + (int64_t)kb0 * p.sb_stride_k;
+            const int out_row0 = e * p.M;                      // GK: the expert's slice of the (E * M, N) output
             float acc[128];
 #pragma unroll
             for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
@@ -265,17 +289,17 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                     if (mbar_wait(gfull0 + 8 * h, par, abort_flag, (3 << 8) | 3)) {
 #pragma unroll
                         for (int r = 0; r < 2; ++r)
-                            if (col0 + r * 64 < p.N) tma_store_2d(&tmC, slot + r * C_SLOT_BYTES, col0 + r * 64, ti.m0 + 128 * (int)rank);
+                            if (col0 + r * 64 < p.N) tma_store_2d(&tmC, slot + r * C_SLOT_BYTES, col0 + r * 64, out_row0 + ti.m0 + 128 * (int)rank);
                         tma_store_commit();
                     }
                 }
                 __syncwarp();       // the elected lane rejoins its warp before the next warp-collective instruction
                 ++n_rounds;
             } else if (alive && vec_ok) {
-                if (cvalid) store_rows_staged<OUT, 128>(acc, store_stage + warp * 2048, p.C, p.ldc, ti.m0 + 128 * (int)rank + q * 32,
-                                                        p.M, col0, p.N, lane);
+                if (cvalid) store_rows_staged<OUT, 128>(acc, store_stage + warp * 2048, p.C, p.ldc,
+                                                        out_row0 + ti.m0 + 128 * (int)rank + q * 32, out_row0 + p.M, col0, p.N, lane);
             } else if (alive && rvalid && cvalid) {
-                const int64_t base = (int64_t)row * p.ldc + col0;
+                const int64_t base = (int64_t)(out_row0 + row) * p.ldc + col0;
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const int ncols = p.N - (col0 + j * 8);

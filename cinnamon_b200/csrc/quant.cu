@@ -205,10 +205,16 @@ quant_row_generic_kernel(const T* __restrict__ x, int64_t ld_m, int64_t ld_n, ui
 // src/kernels.py:781-783) without first materialising the transpose.
 // One CTA: 64 logical rows (contiguous in memory) x one 128-wide tile.
 // ---------------------------------------------------------------------------
-template <typename T, int DIV, bool ROUND>
+// SEG: the tile axis is cut into per-expert segments, each padded to whole tiles: tile cb reads tile_cnt[cb] source
+// positions starting at tile_src[cb] (the rest of the tile counts as zeros) and only the first *n_tiles tiles exist
+// (`nb` is then the capacity of the output along the tile axis, in tiles).  One launch quantises dY^T of every expert
+// for the grouped weight gradient, with tiles that never straddle two experts.
+template <typename T, int DIV, bool ROUND, bool SEG = false>
 __global__ void __launch_bounds__(256)
 quant_row_transposed_kernel(const T* __restrict__ x, int64_t L, uint8_t* __restrict__ q,
-                            float* __restrict__ scales, int M, int N, int nb, int tiles_per_cta, int N_in) {
+                            float* __restrict__ scales, int M, int N, int nb, int tiles_per_cta, int N_in,
+                            const int* __restrict__ tile_src = nullptr, const int* __restrict__ tile_cnt = nullptr,
+                            const int* __restrict__ n_tiles = nullptr) {
     // N_in <= N: only the first N_in positions along the tile axis are read, the rest count as zeros (a ragged
     // expert range padded to a multiple of 16 without a padded copy of the input)
     constexpr int TM = 64;            // logical rows per CTA
@@ -225,15 +231,19 @@ quant_row_transposed_kernel(const T* __restrict__ x, int64_t L, uint8_t* __restr
     const int warp = threadIdx.x >> 5;
     const int m = m0 + g * 8;
     const int cb_first = blockIdx.y * tiles_per_cta;
-    const int cb_last = min(cb_first + tiles_per_cta, nb);
+    const int cb_last = min(cb_first + tiles_per_cta, SEG ? min(nb, *n_tiles) : nb);
 
     // raw vectors of the next tile are fetched before the current one is converted
     Raw8<T> nxt[4];
     auto fetch = [&](int cb) {
+        int src0 = cb * 128, cnt = N_in - cb * 128;
+        if constexpr (SEG) {
+            if (cb < cb_last) { src0 = tile_src[cb]; cnt = tile_cnt[cb]; }
+        }
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
-            const int n = cb * 128 + nr * 4 + p;
-            nxt[p] = (cb < cb_last && n < N_in && m < M) ? load_raw8<T>(x + (int64_t)n * L + m) : zero_raw8<T>();
+            const int j = nr * 4 + p;
+            nxt[p] = (cb < cb_last && j < cnt && m < M) ? load_raw8<T>(x + (int64_t)(src0 + j) * L + m) : zero_raw8<T>();
         }
     };
     fetch(cb_first);
@@ -789,21 +799,32 @@ quant_block_generic_kernel(const T* __restrict__ x, int64_t ld_m, int64_t ld_n, 
 // in registers.  Optionally the block-scaled bytes are written transposed
 // (K x M), so that the token axis is contiguous.
 // ---------------------------------------------------------------------------
-template <int DIV, bool TRANSPOSE_OUT>
+// SEG: row block blockIdx.y reads tile_cnt[y] source rows starting at tile_src[y] (per-expert segments padded to
+// whole blocks, see quant_row_transposed_kernel); blocks at or past *n_tiles do not exist.
+template <int DIV, bool TRANSPOSE_OUT, bool SEG = false>
 __global__ void __launch_bounds__(256)
 requant_row_to_block_kernel(const uint8_t* __restrict__ xq, const float* __restrict__ xs, int nkb_in,
-                            uint8_t* __restrict__ out, float* __restrict__ scales, int M, int K, int nb, int M_in) {
+                            uint8_t* __restrict__ out, float* __restrict__ scales, int M, int K, int nb, int M_in,
+                            const int* __restrict__ tile_src = nullptr, const int* __restrict__ tile_cnt = nullptr,
+                            const int* __restrict__ n_tiles = nullptr) {
     // M_in <= M: rows at or past M_in are not read and count as zeros (and are written as zeros)
     __shared__ float s_red[8];
     __shared__ __align__(16) uint8_t s_t[TRANSPOSE_OUT ? 128 * (128 + 16) : 16];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int sub = lane & 7;                      // 16-byte chunk within the 128-byte row
     const int r0 = blockIdx.y * 128, c = blockIdx.x * 128 + sub * 16;
+    int src0 = r0, cnt = M_in - r0;
+    if constexpr (SEG) {
+        if ((int)blockIdx.y >= *n_tiles) return;
+        src0 = tile_src[blockIdx.y];
+        cnt = tile_cnt[blockIdx.y];
+    }
     float v[4][16];
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
-        const int r = r0 + p * 32 + warp * 4 + (lane >> 3);
-        if (r < M_in && c < K) {
+        const int rl_in = p * 32 + warp * 4 + (lane >> 3);
+        const int r = src0 + rl_in;
+        if (rl_in < cnt && c < K) {
             const uint4 raw = *reinterpret_cast<const uint4*>(xq + (int64_t)r * K + c);
             const float rs = xs[(int64_t)r * nkb_in + blockIdx.x];
             const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -1342,6 +1363,103 @@ int requant_row_to_block_padded(const void* xq, const float* xs, int64_t M_in, i
         requant_row_to_block_kernel<CINN_DIV_FULL, false><<<grid, 256, 0, st>>>((const uint8_t*)xq, xs, nb, (uint8_t*)out, scales, (int)M, (int)K, nb, (int)M_in);
     else
         requant_row_to_block_kernel<CINN_DIV_RN, false><<<grid, 256, 0, st>>>((const uint8_t*)xq, xs, nb, (uint8_t*)out, scales, (int)M, (int)K, nb, (int)M_in);
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Per-expert segments padded to whole 128-row tiles, for the grouped weight gradient: from the experts' device-side
+// row ranges, kb_start[e] = first tile of expert e (kb_start[E] = number of tiles), and per tile its first source row
+// and its number of valid rows.  One CTA.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+segment_tiles_kernel(const int64_t* __restrict__ starts, const int64_t* __restrict__ ends, int E, int64_t T,
+                     int* __restrict__ kb_start, int* __restrict__ tile_src, int* __restrict__ tile_cnt, int max_tiles) {
+    __shared__ int s_first[1025];
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) {
+            long long s = starts[e], t = ends[e];
+            if (s < 0) s = 0;
+            if (t > T) t = T;
+            const int n = t > s ? (int)(t - s) : 0;
+            s_first[e] = run;
+            run += (n + 127) / 128;
+            if (run > max_tiles) run = max_tiles;           // cannot happen for disjoint ranges; keeps every index in range
+        }
+        s_first[E] = run;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= E; e += 256) kb_start[e] = s_first[e];
+    for (int e = 0; e < E; ++e) {
+        long long s = starts[e], t = ends[e];
+        if (s < 0) s = 0;
+        if (t > T) t = T;
+        const int n = t > s ? (int)(t - s) : 0;
+        const int first = s_first[e], cnt = s_first[e + 1] - first;
+        for (int g = threadIdx.x; g < cnt; g += 256) {
+            tile_src[first + g] = (int)s + g * 128;
+            tile_cnt[first + g] = min(128, n - g * 128);
+        }
+    }
+}
+
+int segment_tiles(const int64_t* starts, const int64_t* ends, int E, int64_t T, int* kb_start, int* tile_src, int* tile_cnt,
+                  int max_tiles, cudaStream_t st) {
+    CINN_CHECK_ARG(E >= 1 && E <= 1024 && T >= 0 && T < (1LL << 31) && max_tiles >= 1, "segment_tiles: 1 <= experts <= 1024");
+    segment_tiles_kernel<<<1, 256, 0, st>>>(starts, ends, E, T, kb_start, tile_src, tile_cnt, max_tiles);
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+// dY (T, M = d_out; row pitch L) -> (M, max_tiles * 128) e4m3, tiles along the tokens of each expert's segment
+template <typename T>
+static int transposed_segmented_typed(const T* x, int64_t M, int64_t L, uint8_t* q, float* scales, int max_tiles,
+                                      const int* tile_src, const int* tile_cnt, const int* n_tiles, int div_mode, cudaStream_t st) {
+    const int64_t slabs = (M + 63) / 64;
+    int per = 4;
+    while (per > 1 && slabs * ((max_tiles + per - 1) / per) < (int64_t)sm_count() * 8) per >>= 1;
+    CINN_CHECK_ARG((max_tiles + per - 1) / per <= 65535, "segmented transposed quantiser: too many tiles");
+    dim3 grid((unsigned)slabs, (unsigned)((max_tiles + per - 1) / per));
+    const int N = max_tiles * 128;
+    if (div_mode == CINN_DIV_FULL)
+        quant_row_transposed_kernel<T, CINN_DIV_FULL, false, true><<<grid, 256, 0, st>>>(x, L, q, scales, (int)M, N, max_tiles, per, 0,
+                                                                                          tile_src, tile_cnt, n_tiles);
+    else
+        quant_row_transposed_kernel<T, CINN_DIV_RN, false, true><<<grid, 256, 0, st>>>(x, L, q, scales, (int)M, N, max_tiles, per, 0,
+                                                                                        tile_src, tile_cnt, n_tiles);
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
+int quantize_transposed_segmented(const void* x, int dtype, int64_t M, int64_t L, void* q, float* scales, int max_tiles,
+                                  const int* tile_src, const int* tile_cnt, const int* n_tiles, int div_mode, cudaStream_t st) {
+    CINN_CHECK_ARG(M > 1 && M % 8 == 0 && L % 8 == 0 && L >= M && max_tiles >= 1, "segmented transposed quantiser: bad shape");
+    CINN_CHECK_ARG(x && q && scales && tile_src && tile_cnt && n_tiles && aligned16(x) && aligned16(q),
+                   "segmented transposed quantiser: null or unaligned pointer");
+    switch (dtype) {
+        case CINN_BF16: return transposed_segmented_typed((const __nv_bfloat16*)x, M, L, (uint8_t*)q, scales, max_tiles, tile_src, tile_cnt, n_tiles, div_mode, st);
+        case CINN_F16: return transposed_segmented_typed((const __half*)x, M, L, (uint8_t*)q, scales, max_tiles, tile_src, tile_cnt, n_tiles, div_mode, st);
+        case CINN_F32: return transposed_segmented_typed((const float*)x, M, L, (uint8_t*)q, scales, max_tiles, tile_src, tile_cnt, n_tiles, div_mode, st);
+        default: set_error("segmented transposed quantiser: unknown dtype tag %d", dtype); return CINN_ERR_INVALID;
+    }
+}
+
+// x_q (T, K) e4m3 + row scales -> block-scaled, transposed: (K, max_tiles * 128), scales (max_tiles, ceil(K/128))
+int requant_row_to_block_segmented(const void* xq, const float* xs, int64_t K, void* out, float* scales, int max_tiles,
+                                   const int* tile_src, const int* tile_cnt, const int* n_tiles, int div_mode, cudaStream_t st) {
+    CINN_CHECK_ARG(K > 0 && K % 16 == 0 && max_tiles >= 1 && max_tiles <= 65535, "segmented requant: bad shape");
+    CINN_CHECK_ARG(xq && xs && out && scales && tile_src && tile_cnt && n_tiles && aligned16(xq) && aligned16(out),
+                   "segmented requant: null or unaligned pointer");
+    const int nb = (int)((K + 127) / 128);
+    dim3 grid((unsigned)nb, (unsigned)max_tiles);
+    const int M = max_tiles * 128;
+    if (div_mode == CINN_DIV_FULL)
+        requant_row_to_block_kernel<CINN_DIV_FULL, true, true><<<grid, 256, 0, st>>>((const uint8_t*)xq, xs, nb, (uint8_t*)out, scales, M, (int)K, nb, M,
+                                                                                    tile_src, tile_cnt, n_tiles);
+    else
+        requant_row_to_block_kernel<CINN_DIV_RN, true, true><<<grid, 256, 0, st>>>((const uint8_t*)xq, xs, nb, (uint8_t*)out, scales, M, (int)K, nb, M,
+                                                                                  tile_src, tile_cnt, n_tiles);
     CINN_CHECK_LAUNCH();
     return CINN_OK;
 }

@@ -77,4 +77,56 @@ int fp8_grouped_wgrad(const void* dY, int dy_dtype, const void* x_q, const float
     return CINN_OK;
 }
 
+// ---------------------------------------------------------------------------
+// The same gradients in four launches for all experts and without the host knowing the row ranges: the experts'
+// segments are padded to whole 128-row tiles on the device (segment_tiles), dY^T and x are quantised per segment in
+// one launch each, and one grouped-K GEMM reduces every expert over its own K blocks.  Same tiles, same bytes and
+// the same sums as the per-expert loop above (zero padding changes neither an amax nor a product).
+// Needs d_out and d_in multiples of 256; starts / ends are DEVICE arrays here.
+// ---------------------------------------------------------------------------
+int segment_tiles(const int64_t* starts, const int64_t* ends, int E, int64_t T, int* kb_start, int* tile_src, int* tile_cnt,
+                  int max_tiles, cudaStream_t st);
+int quantize_transposed_segmented(const void* x, int dtype, int64_t M, int64_t L, void* q, float* scales, int max_tiles,
+                                  const int* tile_src, const int* tile_cnt, const int* n_tiles, int div_mode, cudaStream_t st);
+int requant_row_to_block_segmented(const void* xq, const float* xs, int64_t K, void* out, float* scales, int max_tiles,
+                                   const int* tile_src, const int* tile_cnt, const int* n_tiles, int div_mode, cudaStream_t st);
+int fp8_gemm_grouped_k(const void* A, const float* sA, const void* B, const float* sB, const int* kb_start, int64_t E,
+                       int64_t M, int64_t N, int64_t max_tiles, void* C, int out_dtype, cudaStream_t st);
+
+static inline int64_t fused_max_tiles(int64_t T, int64_t E) { return (T + 127) / 128 + E; }
+
+int64_t grouped_wgrad_fused_scratch_bytes(int64_t T, int64_t E, int64_t d_in, int64_t d_out) {
+    const int64_t mt = fused_max_tiles(T < 0 ? 0 : T, E < 0 ? 0 : E), nkb = (d_in + 127) / 128;
+    return up((E + 1 + 2 * mt) * 4, 256) + up(d_out * mt * 128, 256) + up(d_out * mt * 4, 256) + up(d_in * mt * 128, 256) +
+           up(mt * nkb * 4, 256);
+}
+
+int fp8_grouped_wgrad_fused(const void* dY, int dy_dtype, const void* x_q, const float* x_s, const int64_t* starts_dev,
+                            const int64_t* ends_dev, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* scratch,
+                            int64_t scratch_bytes, void* dW, int out_dtype, int div_mode, cudaStream_t st) {
+    CINN_CHECK_ARG(E >= 1 && E <= 1024 && T >= 0 && d_in > 0 && d_out > 0, "grouped_wgrad_fused: bad shape");
+    CINN_CHECK_ARG(d_in % 256 == 0 && d_out % 256 == 0, "grouped_wgrad_fused: d_in (%lld) and d_out (%lld) must be multiples of 256",
+                   (long long)d_in, (long long)d_out);
+    CINN_CHECK_ARG(dY && x_q && x_s && starts_dev && ends_dev && scratch && dW, "grouped_wgrad_fused: null pointer");
+    CINN_CHECK_ARG(scratch_bytes >= grouped_wgrad_fused_scratch_bytes(T, E, d_in, d_out) && (reinterpret_cast<uintptr_t>(scratch) & 255) == 0,
+                   "grouped_wgrad_fused: the scratch buffer must hold %lld bytes and be 256-byte aligned",
+                   (long long)grouped_wgrad_fused_scratch_bytes(T, E, d_in, d_out));
+    const int64_t mt = fused_max_tiles(T, E), nkb = (d_in + 127) / 128;
+    uint8_t* base = static_cast<uint8_t*>(scratch);
+    int* kb_start = reinterpret_cast<int*>(base);
+    int* tile_src = kb_start + (E + 1);
+    int* tile_cnt = tile_src + mt;
+    uint8_t* a_q = base + up((E + 1 + 2 * mt) * 4, 256);
+    float* a_s = reinterpret_cast<float*>(a_q + up(d_out * mt * 128, 256));
+    uint8_t* b_q = reinterpret_cast<uint8_t*>(a_s) + up(d_out * mt * 4, 256);
+    float* b_s = reinterpret_cast<float*>(b_q + up(d_in * mt * 128, 256));
+    int rc = segment_tiles(starts_dev, ends_dev, (int)E, T, kb_start, tile_src, tile_cnt, (int)mt, st);
+    if (rc) return rc;
+    rc = quantize_transposed_segmented(dY, dy_dtype, d_out, d_out, a_q, a_s, (int)mt, tile_src, tile_cnt, kb_start + E, div_mode, st);
+    if (rc) return rc;
+    rc = requant_row_to_block_segmented(x_q, x_s, d_in, b_q, b_s, (int)mt, tile_src, tile_cnt, kb_start + E, div_mode, st);
+    if (rc) return rc;
+    return fp8_gemm_grouped_k(a_q, a_s, b_q, b_s, kb_start, E, d_out, d_in, mt, dW, out_dtype, st);
+}
+
 }  // namespace cinn

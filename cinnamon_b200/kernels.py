@@ -941,22 +941,38 @@ def fp8_grouped_gemm_dgrad(dy_fp8, dy_scale, w_fp8, w_scale, expert_starts, expe
 
 
 def fp8_grouped_wgrad(grad_out: torch.Tensor, x_fp8: torch.Tensor, x_scale: torch.Tensor, expert_starts, expert_ends,
-                      n_experts: int, d_in: int, d_out: int, w_dtype=torch.float32) -> torch.Tensor:
+                      n_experts: int, d_in: int, d_out: int, w_dtype=torch.float32, fused: bool = None) -> torch.Tensor:
     """``dW[e] = rowwise(dY[e rows]^T) @ blockwise(dequant_rowwise(x_q[e rows]))`` for every expert: the weight
-    gradient of ``FP8MatmulFunction.backward`` (reference src/kernels.py:780-788) expert by expert.  The row
-    ranges are read back once; the per-expert launches (transposing quantiser, re-quantiser, GEMM straight into
-    ``dW[e]``) are enqueued by one library call.  Returns (E, d_out, d_in) of ``w_dtype`` (fp32 holds bf16-rounded
-    values, as a bf16 result cast to the master weight's type would)."""
+    gradient of ``FP8MatmulFunction.backward`` (reference src/kernels.py:780-788) expert by expert.  With ``d_in`` and
+    ``d_out`` multiples of 256: four launches for all experts (segments padded to whole tiles on the device, dY^T
+    and x quantised per segment, one grouped-K GEMM), no host read-back.  Otherwise the row ranges are read back
+    once and three launches per non-empty expert are enqueued by one library call.  Returns (E, d_out, d_in) of
+    ``w_dtype`` (fp32 holds bf16-rounded values, as a bf16 result cast to the master weight's type would)."""
     g = grad_out if grad_out.is_contiguous() else grad_out.contiguous()
     if g.dtype not in _DTYPE_TAG:
         g = g.float()
     x_fp8, x_scale = x_fp8.contiguous(), x_scale.float().contiguous()
     T = g.shape[0]
+    out_tag = _lib.F32_BF16 if w_dtype == torch.float32 else _lib.BF16
+    can_fuse = d_in % 256 == 0 and d_out % 256 == 0 and 1 <= n_experts <= 1024 and T > 0
+    assert not fused or can_fuse, "the one-launch weight gradient needs d_in and d_out multiples of 256"
+    if can_fuse and fused is not False:
+        # all experts in four launches, row ranges read on the device: no host read-back
+        starts = expert_starts.to(torch.int64).contiguous()
+        ends = expert_ends.to(torch.int64).contiguous()
+        need = int(_L.cinn_fp8_grouped_wgrad_fused_scratch_bytes(T, n_experts, d_in, d_out))
+        with torch.cuda.device(g.device):
+            scratch = torch.empty(need, dtype=torch.uint8, device=g.device)
+            grad_w = torch.empty((n_experts, d_out, d_in), dtype=w_dtype, device=g.device)
+            _lib.check(_L.cinn_fp8_grouped_wgrad_fused(_ptr(g), _DTYPE_TAG[g.dtype], _ptr(x_fp8), _ptr(x_scale), _ptr(starts),
+                                                       _ptr(ends), n_experts, T, d_in, d_out, _ptr(scratch), need, _ptr(grad_w),
+                                                       out_tag, _DIV_MODE, _stream(g)), "cinn_fp8_grouped_wgrad_fused")
+        _count(4)
+        return grad_w
     bounds = torch.stack([expert_starts.to(torch.int64), expert_ends.to(torch.int64)]).cpu()     # one host read-back
     starts_h, ends_h = bounds[0].contiguous(), bounds[1].contiguous()
     max_rows = int((ends_h.clamp(max=T) - starts_h.clamp(min=0)).clamp(min=0).max()) if n_experts > 0 else 0
     need = int(_L.cinn_fp8_grouped_wgrad_scratch_bytes(max_rows, d_in, d_out))
-    out_tag = _lib.F32_BF16 if w_dtype == torch.float32 else _lib.BF16
     with torch.cuda.device(g.device):
         scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=g.device)
         grad_w = torch.empty((n_experts, d_out, d_in), dtype=w_dtype, device=g.device)

@@ -496,3 +496,35 @@ def test_config4_grouped_gemm_literal_routing_sampled(K):
             worst = max(worst, rel_fro(got[i:i + 1], ref))
         print(f"C4 {name}-projection, {len(active)} active experts, {len(sample)} sampled rows: worst rel-Fro {worst:.3e} (bf16)")
         del wq, wsc, out
+
+
+FUSED_WGRAD = {
+    "ragged": (6, 512, 256, [5, 0, 130, 1, 257, 64]),
+    "one_owns_all": (4, 256, 512, [0, 0, 700, 0]),
+    "empty_first_last": (5, 256, 256, [0, 128, 0, 129, 0]),
+    "many_small": (16, 256, 256, [1, 2, 3, 127, 128, 129, 0, 0, 255, 256, 257, 16, 17, 15, 64, 1]),
+}
+
+
+@pytest.mark.parametrize("name", list(FUSED_WGRAD))
+def test_grouped_weight_gradient_in_one_gemm(K, name):
+    """cinn_fp8_grouped_wgrad_fused (segments padded to tiles on the device, two quantiser launches, one grouped-K
+    GEMM, no host read-back) against the float64 oracle and against the per-expert loop, whose bytes and sums it
+    must reproduce exactly; a gap of rows that belong to no expert and canary values in dW."""
+    E, d_in, d_out, counts = FUSED_WGRAD[name]
+    x, w, starts, ends = _grouped_case(E, d_in, d_out, counts, seed=60 + len(name), gap=7)
+    g = torch.Generator().manual_seed(61)
+    dy = torch.randn(x.shape[0], d_out, generator=g).bfloat16()
+    _, ref_dw = O.grouped_gemm_fp8_backward_f64(x, w, starts, ends, dy)
+    xq, xs = K.quantize_fp8_rowwise(x.cuda())
+    args = (dy.cuda(), xq, xs, starts.cuda(), ends.cuda(), E, d_in, d_out)
+    fused = K.fp8_grouped_wgrad(*args, w_dtype=torch.float32, fused=True)
+    loop = K.fp8_grouped_wgrad(*args, w_dtype=torch.float32, fused=False)
+    torch.cuda.synchronize()
+    assert K.device_status() == 0
+    assert torch.equal(fused, loop), float((fused - loop).abs().max())
+    assert_bf16_close(fused.to(torch.bfloat16), ref_dw, "grouped wgrad, one GEMM")
+    for e, c in enumerate(counts):
+        if c == 0:
+            assert torch.all(fused[e] == 0)
+    assert torch.equal(K.fp8_grouped_wgrad(*args, w_dtype=torch.bfloat16, fused=True), fused.to(torch.bfloat16))
