@@ -613,9 +613,18 @@ static size_t smem_bytes(int E) {
 
 // Output map for the TMA-store epilogue: (rows, N) of a 2-byte type, boxes of 64 columns x 128 rows, 128-byte swizzle.
 // Sets p.tma_out; when the output cannot go through TMA the (unused) operand map is passed in its place.
-static int make_out_map(CUtensorMap* tc, const CUtensorMap& fallback, GemmParams& p, int out_dtype, int64_t rows) {
+static int make_out_map(CUtensorMap* tc, const CUtensorMap& fallback, GemmParams& p, int out_dtype, int64_t rows,
+                        bool fp32_boxes = false) {
     p.tma_out = 0;
     *tc = fallback;
+    if (((uintptr_t)p.C & 15) != 0) return CINN_OK;               // TMA wants a 16-byte aligned base; plain stores otherwise
+    if (fp32_boxes && (out_dtype == CINN_F32 || out_dtype == CINN_F32_BF16) && p.N % 4 == 0) {
+        // the two-SM kernel also sends 4-byte outputs through TMA: boxes of 32 columns x 128 rows
+        int rc = make_map(tc, p.C, (uint64_t)p.N, (uint64_t)rows, (uint64_t)p.ldc * 4, 32, BM, CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
+        if (rc) return rc;
+        p.tma_out = 1;
+        return CINN_OK;
+    }
     if ((out_dtype == CINN_BF16 || out_dtype == CINN_F16) && p.N % 8 == 0) {
         int rc = make_map(tc, p.C, (uint64_t)p.N, (uint64_t)rows, (uint64_t)p.ldc * 2, 64, BM,
                           out_dtype == CINN_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
@@ -689,7 +698,7 @@ template <bool B_MN>
 static int launch_pair_out(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, int out_dtype, int clusters,
                            cudaStream_t st) {
     CUtensorMap tc;
-    int rc = make_out_map(&tc, ta, p, out_dtype, p.M);
+    int rc = make_out_map(&tc, ta, p, out_dtype, p.M, true);
     if (rc) return rc;
     switch (out_dtype) {
         case CINN_BF16: return launch_pair<B_MN, CINN_BF16>(ta, tb, tc, p, clusters, st);
@@ -875,7 +884,7 @@ int fp8_gemm_grouped_k(const void* A, const float* sA, const void* B, const floa
     p.C = C; p.ldc = N; p.M = (int)M; p.N = (int)N; p.K = 0;
     p.starts = reinterpret_cast<const int64_t*>(kb_start); p.ends = nullptr; p.E = (int)E; p.b_rows_per_expert = 0;
     CUtensorMap tc;
-    rc = make_out_map(&tc, ta, p, out_dtype, E * M);
+    rc = make_out_map(&tc, ta, p, out_dtype, E * M, true);
     if (rc) return rc;
     const int64_t tiles = E * (M / pair::PM) * (N / pair::PN);
     const int clusters = (int)(tiles < gemm_sms() / 2 ? tiles : gemm_sms() / 2);

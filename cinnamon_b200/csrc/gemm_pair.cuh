@@ -262,39 +262,50 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                 __syncwarp();
                 if (lane == 0) mbar_arrive_remote(tempty_leader + 8 * b);
             }
-            constexpr bool TMA_OUT = (OUT == CINN_BF16 || OUT == CINN_F16);
-            if (TMA_OUT && alive && p.tma_out) {
-                // The whole tile has room in shared memory here: each column group of four promotion warps drops its
-                // 128 columns into its two 16 KiB slots (16-byte chunks, 128-byte swizzle) and one thread hands both
-                // boxes to the TMA unit; nobody waits for the unit until the next tile is ready to be staged.
+            if (alive && p.tma_out) {
+                // The tile leaves through TMA stores.  Each column group of four promotion warps owns two 16 KiB slots
+                // (boxes of 128 rows x 128 bytes, 128-byte swizzle): its threads drop their rows into them in 16-byte
+                // chunks and one thread hands the boxes to the TMA unit.  A 2-byte output fits the group's 128 columns
+                // in one round; a 4-byte output takes two rounds of 64 columns.  Nobody waits for the unit until the
+                // slots are needed again.
+                using T = typename OutT<OUT>::type;
+                constexpr int EPR = 128 / (int)sizeof(T);          // elements per 128-byte box row
+                constexpr int PER16 = 16 / (int)sizeof(T);
+                constexpr int ROUNDS = 128 / (2 * EPR);
                 const bool elected = (warp == h * 4) && lane == 0;
                 const uint32_t slot = smem_u32(c_stage) + h * 2 * C_SLOT_BYTES;
                 const int rl = q * 32 + lane;
-                const uint32_t par = n_rounds & 1u;
-                if (elected) tma_store_wait_read();                   // the previous tile has left the slots
-                __syncwarp();
-                if (lane == 0) mbar_arrive(gfree0 + 8 * h);
-                if (!mbar_wait_warp(gfree0 + 8 * h, par, abort_flag, (3 << 8) | 2)) { alive = false; break; }
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const uint4 v = pack16<OUT>(&acc[j * 8]);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                                 ::"r"(slot + (j >> 3) * C_SLOT_BYTES + rl * 128 + (((j & 7) ^ (rl & 7)) << 4)),
-                                   "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-                }
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(gfull0 + 8 * h);
-                if (elected) {
-                    if (mbar_wait(gfull0 + 8 * h, par, abort_flag, (3 << 8) | 3)) {
+                for (int r = 0; r < ROUNDS; ++r) {
+                    const uint32_t par = n_rounds & 1u;
+                    if (elected) tma_store_wait_read();               // the previous boxes have left the slots
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(gfree0 + 8 * h);
+                    if (!mbar_wait_warp(gfree0 + 8 * h, par, abort_flag, (3 << 8) | 2)) { alive = false; break; }
 #pragma unroll
-                        for (int r = 0; r < 2; ++r)
-                            if (col0 + r * 64 < p.N) tma_store_2d(&tmC, slot + r * C_SLOT_BYTES, col0 + r * 64, out_row0 + ti.m0 + 128 * (int)rank);
-                        tma_store_commit();
+                    for (int j = 0; j < 16; ++j) {
+                        const uint4 v = pack16<OUT>(&acc[r * 2 * EPR + (j >> 3) * EPR + (j & 7) * PER16]);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                     ::"r"(slot + (j >> 3) * C_SLOT_BYTES + rl * 128 + (((j & 7) ^ (rl & 7)) << 4)),
+                                       "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
                     }
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(gfull0 + 8 * h);
+                    if (elected) {
+                        if (mbar_wait(gfull0 + 8 * h, par, abort_flag, (3 << 8) | 3)) {
+#pragma unroll
+                            for (int sl = 0; sl < 2; ++sl) {
+                                const int col = col0 + r * 2 * EPR + sl * EPR;
+                                if (col < p.N) tma_store_2d(&tmC, slot + sl * C_SLOT_BYTES, col, out_row0 + ti.m0 + 128 * (int)rank);
+                            }
+                            tma_store_commit();
+                        }
+                    }
+                    __syncwarp();       // the elected lane rejoins its warp before the next warp-collective instruction
+                    ++n_rounds;
                 }
-                __syncwarp();       // the elected lane rejoins its warp before the next warp-collective instruction
-                ++n_rounds;
+                if (!alive) break;
             } else if (alive && vec_ok) {
                 if (cvalid) store_rows_staged<OUT, 128>(acc, store_stage + warp * 2048, p.C, p.ldc,
                                                         out_row0 + ti.m0 + 128 * (int)rank + q * 32, out_row0 + p.M, col0, p.N, lane);
