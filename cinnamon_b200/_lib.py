@@ -38,6 +38,7 @@ SIGNATURES = {
     "cinn_grouped_gemm_16bit": [_vp, _vp, _i32, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32, _vp],
     "cinn_fp8_grouped_gemm_dgrad": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32, _vp],
     "cinn_moe_combine": [_vp, _i32, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _vp],
+    "cinn_zero_rows_outside": [_vp, _i64, _i64, _vp, _vp, _i64, _vp],
     "cinn_moe_combine_backward": [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _vp],
     "cinn_moe_route_workspace_ints": [_i64, _i32],
     "cinn_moe_route": [_vp, _vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],

@@ -80,6 +80,8 @@ int fp8_grouped_wgrad_fused(const void* dY, int dy_dtype, const void* x_q, const
                             int64_t scratch_bytes, void* dW, int out_dtype, int div_mode, cudaStream_t st);
 int grouped_gemm_16bit(const void* A, const void* W, int in_dtype, const int64_t* starts, const int64_t* ends, int64_t E,
                        int64_t T, int64_t d_in, int64_t d_out, void* C, int out_dtype, cudaStream_t st);
+int zero_rows_outside(void* buf, int64_t T, int64_t row_bytes, const int64_t* starts, const int64_t* ends, int64_t E,
+                      cudaStream_t st);
 int moe_combine_backward(const void* rows, int dtype, const int64_t* pos, const float* gates, const float* dy, void* d_rows,
                          float* d_gates, int64_t n_tokens, int64_t n_rows, int top_k, int64_t d, cudaStream_t st);
 int p2p_plan(const int64_t* my_counts, const int64_t* peer_counts, const int64_t* peer_flags, int me, int G, int E,
@@ -312,6 +314,11 @@ int cinn_grouped_gemm_16bit(const void* A, const void* W, int in_dtype, const in
                             void* stream) {
     return cinn::grouped_gemm_16bit(A, W, in_dtype, expert_starts, expert_ends, n_experts, total_rows, d_in, d_out, C, out_dtype,
                                     (cudaStream_t)stream);
+}
+
+int cinn_zero_rows_outside(void* buf, int64_t n_rows, int64_t row_bytes, const int64_t* starts, const int64_t* ends,
+                           int64_t n_ranges, void* stream) {
+    return cinn::zero_rows_outside(buf, n_rows, row_bytes, starts, ends, n_ranges, (cudaStream_t)stream);
 }
 
 int cinn_moe_combine_backward(const void* rows, int rows_dtype, const int64_t* pos, const float* gates, const float* dy,

@@ -240,8 +240,10 @@ __device__ __forceinline__ uint4 pack16(const float* a) {
     if constexpr (OUT == CINN_F32) {
         v = make_uint4(__float_as_uint(a[0]), __float_as_uint(a[1]), __float_as_uint(a[2]), __float_as_uint(a[3]));
     } else if constexpr (OUT == CINN_F32_BF16) {
-        v = make_uint4(__float_as_uint(__bfloat162float(__float2bfloat16_rn(a[0]))), __float_as_uint(__bfloat162float(__float2bfloat16_rn(a[1]))),
-                       __float_as_uint(__bfloat162float(__float2bfloat16_rn(a[2]))), __float_as_uint(__bfloat162float(__float2bfloat16_rn(a[3]))));
+        // two packed conversions, then each half widened again by a shift / a mask
+        __nv_bfloat162 t0 = __floats2bfloat162_rn(a[0], a[1]), t1 = __floats2bfloat162_rn(a[2], a[3]);
+        const uint32_t p0 = *reinterpret_cast<uint32_t*>(&t0), p1 = *reinterpret_cast<uint32_t*>(&t1);
+        v = make_uint4(p0 << 16, p0 & 0xffff0000u, p1 << 16, p1 & 0xffff0000u);
     } else if constexpr (OUT == CINN_BF16) {
         __nv_bfloat162 t0 = __floats2bfloat162_rn(a[0], a[1]), t1 = __floats2bfloat162_rn(a[2], a[3]);
         __nv_bfloat162 t2 = __floats2bfloat162_rn(a[4], a[5]), t3 = __floats2bfloat162_rn(a[6], a[7]);

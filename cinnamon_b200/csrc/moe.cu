@@ -685,6 +685,48 @@ int p2p_return(const void* rows, const int64_t* seg_start, const int64_t* home_b
     return CINN_OK;
 }
 
+// Zero the rows of a (T, row_bytes) buffer that no expert's range [starts[e], ends[e]) covers: the input gradient of
+// the grouped GEMM writes every covered row, so only the others need clearing (instead of a fill of the whole
+// buffer before the GEMM).  One CTA per 128 rows marks the covered ones in shared memory, then clears the rest.
+__global__ void __launch_bounds__(256)
+zero_rows_outside_kernel(uint8_t* __restrict__ buf, int64_t T, int64_t row_bytes, const int64_t* __restrict__ starts,
+                         const int64_t* __restrict__ ends, int E) {
+    __shared__ int covered[128];
+    const int64_t r0 = (int64_t)blockIdx.x * 128;
+    if (threadIdx.x < 128) covered[threadIdx.x] = 0;
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += 256) {
+        int64_t s = starts[e], t = ends[e];
+        if (s < r0) s = r0;
+        if (t > r0 + 128) t = r0 + 128;
+        for (int64_t r = s; r < t; ++r) covered[r - r0] = 1;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int rl = warp; rl < 128; rl += 8) {
+        const int64_t r = r0 + rl;
+        if (r >= T || covered[rl]) continue;
+        uint8_t* row = buf + r * row_bytes;
+        if ((row_bytes & 15) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+            for (int64_t v = lane; v < (row_bytes >> 4); v += 32) reinterpret_cast<uint4*>(row)[v] = make_uint4(0, 0, 0, 0);
+        } else {
+            for (int64_t b = lane; b < row_bytes; b += 32) row[b] = 0;
+        }
+    }
+}
+
+int zero_rows_outside(void* buf, int64_t T, int64_t row_bytes, const int64_t* starts, const int64_t* ends, int64_t E,
+                      cudaStream_t st) {
+    CINN_CHECK_ARG(T >= 0 && row_bytes >= 0 && E >= 0 && E < (1LL << 31), "zero_rows_outside: negative shape");
+    if (T == 0 || row_bytes == 0) return CINN_OK;
+    CINN_CHECK_ARG(buf && (E == 0 || (starts && ends)), "zero_rows_outside: null pointer");
+    const int64_t blocks = (T + 127) / 128;
+    CINN_CHECK_ARG(blocks < (1LL << 31), "zero_rows_outside: too many rows");
+    zero_rows_outside_kernel<<<(unsigned)blocks, 256, 0, st>>>((uint8_t*)buf, T, row_bytes, starts, ends, (int)E);
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
+}
+
 int moe_combine_backward(const void* rows, int dtype, const int64_t* pos, const float* gates, const float* dy, void* d_rows,
                          float* d_gates, int64_t n_tokens, int64_t n_rows, int top_k, int64_t d, cudaStream_t st) {
     CINN_CHECK_ARG(n_tokens >= 0 && n_rows >= 0 && d >= 0, "moe_combine_backward: negative shape");

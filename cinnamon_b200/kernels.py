@@ -932,11 +932,14 @@ def fp8_grouped_gemm_dgrad(dy_fp8, dy_scale, w_fp8, w_scale, expert_starts, expe
     starts = expert_starts.to(torch.int64).contiguous()
     ends = expert_ends.to(torch.int64).contiguous()
     with torch.cuda.device(dy_fp8.device):
-        dx = torch.zeros((T, d_in), dtype=out_dtype, device=dy_fp8.device)     # rows of no expert get no gradient
+        dx = torch.empty((T, d_in), dtype=out_dtype, device=dy_fp8.device)
+        # rows of no expert get no gradient: cleared by a pass that touches only those rows
+        _lib.check(_L.cinn_zero_rows_outside(_ptr(dx), T, d_in * dx.element_size(), _ptr(starts), _ptr(ends), E,
+                                             _stream(dy_fp8)), "cinn_zero_rows_outside")
         _lib.check(_L.cinn_fp8_grouped_gemm_dgrad(_ptr(dy_fp8), _ptr(dy_scale), _ptr(w_fp8), _ptr(w_scale), _ptr(starts),
                                                   _ptr(ends), E, T, d_in, d_out, _ptr(dx), _DTYPE_TAG[out_dtype],
                                                   _stream(dy_fp8)), "cinn_fp8_grouped_gemm_dgrad")
-    _count()
+    _count(2)
     return dx
 
 

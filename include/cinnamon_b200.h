@@ -210,6 +210,13 @@ int cinn_moe_combine(const void* rows, int dtype, const int64_t* pos, const floa
 int cinn_moe_combine_add(const void* rows, int dtype, const int64_t* pos, const float* gates, const void* addend,
                          int addend_dtype, void* y, int64_t n_tokens, int64_t n_rows, int top_k, int64_t d, void* stream);
 
+/* Zero the rows of buf (n_rows x row_bytes) that no range [starts[r], ends[r]) covers (device-side int64 ranges,
+ * clamped to the buffer).  The backward of the grouped GEMM uses it so that rows of no expert get a zero input
+ * gradient without a fill of the whole buffer.  No reference counterpart (the reference's grouped GEMM,
+ * src/kernels.py:526-581, has no backward). */
+int cinn_zero_rows_outside(void* buf, int64_t n_rows, int64_t row_bytes, const int64_t* starts, const int64_t* ends,
+                           int64_t n_ranges, void* stream);
+
 /* Backward of cinn_moe_combine (the reference's gate multiply + scatter_add_, src/layers.py:157-160, is
  * differentiated by autograd there): d_rows[pos[t, j]] = gates[t, j] * dy[t] (type of rows; rows that no pair names
  * are left untouched) and d_gates[t, j] = < rows[pos[t, j]], dy[t] > (fp32; 0 for a skipped pair).  dy (T, d) fp32. */

@@ -528,3 +528,34 @@ def test_grouped_weight_gradient_in_one_gemm(K, name):
         if c == 0:
             assert torch.all(fused[e] == 0)
     assert torch.equal(K.fp8_grouped_wgrad(*args, w_dtype=torch.bfloat16, fused=True), fused.to(torch.bfloat16))
+
+
+def test_zero_rows_outside_ranges(K):
+    """cinn_zero_rows_outside clears exactly the rows that no range covers (gaps, empty / reversed / overlapping /
+    out-of-bounds ranges, a row size that is not a multiple of 16), and the grouped input gradient built on it
+    gives zero rows where no expert has rows."""
+    import ctypes
+    from cinnamon_b200 import _lib
+    dev = torch.device("cuda")
+    for T, row_bytes in ((1000, 256), (517, 36), (128, 16)):
+        buf = torch.full((T, row_bytes), 7, dtype=torch.uint8, device=dev)
+        starts = torch.tensor([-5, 40, 300, 290, 700, 650, 990], dtype=torch.int64, device=dev)
+        ends = torch.tensor([10, 40, 420, 310, 650, 660, 5000], dtype=torch.int64, device=dev)
+        _lib.check(_lib.lib.cinn_zero_rows_outside(ctypes.c_void_p(buf.data_ptr()), T, row_bytes, ctypes.c_void_p(starts.data_ptr()),
+                                                   ctypes.c_void_p(ends.data_ptr()), starts.numel(), None), "zero")
+        covered = torch.zeros(T, dtype=torch.bool)
+        for s, e in zip(starts.tolist(), ends.tolist()):
+            covered[max(s, 0):max(min(e, T), 0)] = True
+        want = torch.where(covered[:, None], torch.tensor(7, dtype=torch.uint8), torch.tensor(0, dtype=torch.uint8)).expand(T, row_bytes)
+        assert torch.equal(buf.cpu(), want)
+    g = torch.Generator(device=dev).manual_seed(5)
+    E, d_in, d_out, T = 3, 256, 384, 700
+    dy = torch.randn(T, d_out, generator=g, device=dev).to(torch.bfloat16)
+    w = (torch.randn(E, d_out, d_in, generator=g, device=dev) * 0.05).to(torch.bfloat16)
+    dq, dsc = K.quantize_fp8_rowwise(dy)
+    wq, wsc = K.quantize_expert_weights(w)
+    starts = torch.tensor([10, 300, 300], dtype=torch.int64, device=dev)
+    ends = torch.tensor([200, 300, 650], dtype=torch.int64, device=dev)
+    dx = K.fp8_grouped_gemm_dgrad(dq, dsc, wq, wsc, starts, ends)
+    assert torch.count_nonzero(dx[:10]) == 0 and torch.count_nonzero(dx[200:300]) == 0 and torch.count_nonzero(dx[650:]) == 0
+    assert torch.count_nonzero(dx[10:200]) > 0 and torch.isfinite(dx.float()).all()
