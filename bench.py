@@ -470,8 +470,9 @@ def bench_kernels(Kmod, dev, x, w, dy, peaks, fp8_peak_burst=None):
 
 
 def extras_small(Kmod, dev):
-    """The MoE plumbing passes and sparse attention on a reduced case (8192 tokens, top-8, d = 7168; attention
-    B 8 x H 8 x L 1024 x K 128): inputs larger than L2 but well under a GB each, for profiler captures.
+    """The MoE plumbing passes, the grouped weight gradient and sparse attention on a reduced case (8192 tokens,
+    top-8, d = 7168; 8 experts x 1024 rows; attention B 8 x H 8 x L 1024 x K 128): inputs larger than L2 but at
+    most about a GB each, for profiler captures.
     Runs every kernel three times and prints one line of CUDA-event timings; not a headline number."""
     g = torch.Generator(device=dev).manual_seed(77)
     T, E, k8, d, I = 8192, 256, 8, 7168, 2048
@@ -496,7 +497,15 @@ def extras_small(Kmod, dev):
         o.backward(go)
         qa.grad = ka.grad = va.grad = None
 
-    passes = {"moe_route": lambda: Kmod.moe_route(logits, bias, k8),
+    # backward of a grouped expert GEMM: 8 experts x 1024 rows, 7168 -> 4096 (a quarter of one 8-way rank's share)
+    Eg, rows_e, d_out = 8, 1024, 4096
+    xg = torch.randn(Eg * rows_e, d, generator=g, device=dev).to(torch.bfloat16)
+    xgq, xgs = Kmod.quantize_fp8_rowwise(xg)
+    gst = torch.arange(Eg, device=dev, dtype=torch.int64) * rows_e
+    ggo = torch.randn(Eg * rows_e, d_out, generator=g, device=dev).to(torch.bfloat16)
+
+    passes = {"grouped_wgrad": lambda: Kmod.fp8_grouped_wgrad(ggo, xgq, xgs, gst, gst + rows_e, Eg, d, d_out, torch.float32),
+              "moe_route": lambda: Kmod.moe_route(logits, bias, k8),
               "gather_rows": lambda: Kmod.gather_quantized_rows(tq, ts, r["token_indices"]),
               "swiglu_quant": lambda: Kmod.swiglu_quantize_rowwise(h12),
               "moe_combine_add": lambda: Kmod.moe_combine(rows, r["pair_pos"], r["pair_gate"], shared),
@@ -513,7 +522,7 @@ def extras_small(Kmod, dev):
 MOE = dict(E=256, d=7168, I=2048, tokens=32768, top_k=8, shared_hidden=2048)
 
 
-def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label, chunks=1, exchange="nccl"):
+def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label, chunks=1, exchange="nccl", splits=1):
     """256 routed experts (SwiGLU 7168 -> 2x2048 -> 7168) + 1 shared expert, 32768 tokens, top-8 with
     sigmoid scores + per-expert bias.  Strong scaling: tokens and experts are both split over the ranks.
     Returns a dict (rank 0) with whole-layer tokens/s, the per-phase times of the most loaded rank, the grouped-GEMM
@@ -540,7 +549,7 @@ def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label, chunks=1
     # the layer as a user builds it: router + this rank's routed experts + the shared expert (round_scale on the
     # shared expert's input, as the reference's converted model has it)
     module = moe.ExpertParallelMoE(router, bias, w12, w3, c["top_k"], shared=moe.FP8SwiGLU(*sw, round_scale=True),
-                                   n_chunks=chunks, exchange=exchange, max_tokens_per_rank=T_local)
+                                   n_chunks=chunks, exchange=exchange, max_tokens_per_rank=T_local, up_splits=splits)
     t1.record()
     torch.cuda.synchronize()
     wq_ms = t0.elapsed_time(t1)
@@ -672,7 +681,8 @@ def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label, chunks=1
                        "bit_equal_to_one_gpu_path": all(i["parity"]["bit_equal_to_one_gpu_path"] for i in infos),
                        "ranks_checked": len(infos)},
             "active_experts_rank0_view": active, "scaling": "strong", "n_gpus": world,
-            "token_chunks": chunks if world > 1 else 1, "exchange": module_exchange if world > 1 else "none"}
+            "token_chunks": chunks if world > 1 else 1, "exchange": module_exchange if world > 1 else "none",
+            "expert_ranges": splits if (world > 1 and module_exchange == "p2p-fused") else 1}
 
 
 # ---------------------------------------------------------------------------------------
@@ -853,6 +863,8 @@ def main():
                     help="expert-parallel exchange (N > 1): all-to-all collectives, or peer stores into symmetric memory")
     ap.add_argument("--moe-chunks", type=int, default=1,
                     help="token chunks of the expert-parallel layer (N > 1): exchanges of one chunk run under the experts of another")
+    ap.add_argument("--moe-splits", type=int, default=2, choices=[1, 2, 4],
+                    help="peer-store exchange (N > 1): ranges of local experts dispatched and up-projected one after the other")
     ap.add_argument("--shape", default=None, help="M,K,N of a smaller case (profiling captures); default is the FFN workload")
     ap.add_argument("--extras-small", action="store_true",
                     help="run only the MoE plumbing passes and sparse attention on a reduced case (profiling captures) and exit")
@@ -955,7 +967,7 @@ def main():
         torch.cuda.empty_cache()
         for scale, label in ((1.0, "bias~N(0,1) as specified"), (0.1, "mild skew: bias~N(0,0.1)")):
             moe_lines.append(bench_moe(Kmod, dev, rank, world, steps=5, warmup=3, bias_scale=scale, label=label,
-                                       chunks=args.moe_chunks, exchange=args.moe_exchange))
+                                       chunks=args.moe_chunks, exchange=args.moe_exchange, splits=args.moe_splits))
         assert Kmod.device_status() == 0, "a kernel reported a device-side failure in the MoE layer"
 
     c5_line = None

@@ -313,12 +313,41 @@ p2p_dispatch_kernel(const uint8_t* __restrict__ q, const float* __restrict__ s, 
                     const int64_t* __restrict__ my_start, const int64_t* __restrict__ peer_q,
                     const int64_t* __restrict__ peer_s, int64_t n_pairs, int64_t n_tokens, int d, int ns, int e_local,
                     int n_ranks, int64_t capacity, const int64_t* __restrict__ peer_flags = nullptr, int me = 0,
-                    int flag_slot = 0, unsigned epoch = 0, unsigned* __restrict__ done = nullptr) {
+                    int flag_slot = 0, unsigned epoch = 0, unsigned* __restrict__ done = nullptr, int e_lo = 0, int e_hi = 0) {
     const int lane = threadIdx.x & 31;
     const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     const int64_t n_warps = (int64_t)gridDim.x * 8;
     const int vecs = d >> 4;
-    for (int64_t r = warp; r < n_pairs; r += n_warps) {
+    // The signalling variant sends the pairs of the local experts [e_lo, e_hi) of every rank: one run of the sorted
+    // pairs per destination rank, taken in the order me + 1, me + 2, ..., me, so that at any moment the ranks write
+    // to different destinations instead of all to rank 0 first.  seg_begin: running length of the runs, seg_src:
+    // where each run starts among the sorted pairs.
+    __shared__ long long seg_begin[65], seg_src[64];
+    int64_t total = n_pairs;
+    if constexpr (SIGNAL) {
+        if (threadIdx.x == 0) {
+            long long run = 0;
+            const int E = e_local * n_ranks;
+            for (int k = 0; k < n_ranks; ++k) {
+                const int r = (me + 1 + k) % n_ranks;
+                const int ea = r * e_local + e_lo, eb = r * e_local + e_hi;
+                const long long a = my_start[ea], b = eb < E ? my_start[eb] : (long long)n_pairs;
+                seg_begin[k] = run;
+                seg_src[k] = a;
+                run += b > a ? b - a : 0;
+            }
+            seg_begin[n_ranks] = run;
+        }
+        __syncthreads();
+        total = seg_begin[n_ranks];
+    }
+    for (int64_t v = warp; v < total; v += n_warps) {
+        int64_t r = v;
+        if constexpr (SIGNAL) {
+            int k = 0;
+            while (k + 1 < n_ranks && seg_begin[k + 1] <= v) ++k;
+            r = seg_src[k] + (v - seg_begin[k]);
+        }
         const int64_t e = sorted_experts[r];
         const int64_t tok = token_indices[r];
         bool ok = e >= 0 && e < (int64_t)e_local * n_ranks && tok >= 0 && tok < n_tokens;
@@ -335,7 +364,7 @@ p2p_dispatch_kernel(const uint8_t* __restrict__ q, const float* __restrict__ s, 
         }
         const uint4* in = reinterpret_cast<const uint4*>(q + tok * d);
         uint4* out = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(peer_q[rank]) + dst * d);
-        for (int v = lane; v < vecs; v += 32) out[v] = __ldg(in + v);
+        for (int v4 = lane; v4 < vecs; v4 += 32) out[v4] = __ldg(in + v4);
         float* so = reinterpret_cast<float*>(peer_s[rank]) + dst * ns;
         for (int c = lane; c < ns; c += 32) so[c] = s[tok * ns + c];
     }
@@ -649,9 +678,12 @@ int p2p_dispatch(const void* q, const float* s, const int64_t* token_indices, co
 int p2p_dispatch_signal(const void* q, const float* s, const int64_t* token_indices, const int64_t* sorted_experts,
                         const int64_t* base_send, const int64_t* my_start, const int64_t* peer_q, const int64_t* peer_s,
                         int64_t n_pairs, int64_t n_tokens, int64_t d, int64_t ns, int e_local, int n_ranks, int64_t capacity,
-                        const int64_t* peer_flags, int me, int flag_slot, unsigned epoch, unsigned* done, cudaStream_t st) {
+                        const int64_t* peer_flags, int me, int flag_slot, unsigned epoch, unsigned* done, int e_lo, int e_hi,
+                        cudaStream_t st) {
     CINN_CHECK_ARG(n_pairs >= 0 && n_tokens >= 0 && d > 0 && ns >= 0 && e_local >= 1 && n_ranks >= 1 && n_ranks <= 64 &&
                    capacity >= 0 && me >= 0 && me < n_ranks && flag_slot >= 0, "p2p_dispatch_signal: bad shape");
+    CINN_CHECK_ARG(0 <= e_lo && e_lo < e_hi && e_hi <= e_local,
+                   "p2p_dispatch_signal: the local expert range [%d, %d) must lie inside [0, %d)", e_lo, e_hi, e_local);
     CINN_CHECK_ARG(q && s && token_indices && sorted_experts && base_send && my_start && peer_q && peer_s && peer_flags && done,
                    "p2p_dispatch_signal: null pointer");
     CINN_CHECK_ARG(d % 16 == 0 && d < (1LL << 31) && ns < (1LL << 31),
@@ -663,7 +695,8 @@ int p2p_dispatch_signal(const void* q, const float* s, const int64_t* token_indi
     if (blocks < 1) blocks = 1;
     p2p_dispatch_kernel<true><<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)q, s, token_indices, sorted_experts, base_send,
                                                                my_start, peer_q, peer_s, n_pairs, n_tokens, (int)d, (int)ns,
-                                                               e_local, n_ranks, capacity, peer_flags, me, flag_slot, epoch, done);
+                                                               e_local, n_ranks, capacity, peer_flags, me, flag_slot, epoch, done,
+                                                               e_lo, e_hi);
     CINN_CHECK_LAUNCH();
     return CINN_OK;
 }

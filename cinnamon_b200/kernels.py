@@ -850,31 +850,38 @@ def p2p_dispatch(x_fp8, x_scale, token_indices, sorted_experts, base_send, my_st
     _count()
 
 
-def p2p_dispatch_signal(x_fp8, x_scale, token_indices, sorted_experts, tables, buffers) -> None:
-    """``p2p_dispatch`` whose last CTA flags "all my rows have landed" to every rank (``cinn_p2p_dispatch_signal``);
+def p2p_dispatch_signal(x_fp8, x_scale, token_indices, sorted_experts, tables, buffers, e_lo: int = 0, e_hi: int = None,
+                        flag_slot: int = None) -> None:
+    """``p2p_dispatch`` for the pairs of the local experts ``[e_lo, e_hi)`` of every rank (default: all), whose last
+    CTA flags "these rows have landed" to every rank under ``flag_slot`` (``cinn_p2p_dispatch_signal``);
     ``tables``: what ``buffers.plan`` returned for this layer call, ``buffers``: a ``p2p.PeerBuffers``."""
     assert x_fp8.is_cuda, "Inputs must be on CUDA"
     n_tokens, d = x_fp8.shape
     x_fp8, x_scale = x_fp8.contiguous(), x_scale.float().contiguous()
     b = buffers
+    e_local = b.n_experts // b.world
     with torch.cuda.device(x_fp8.device):
         _lib.check(_L.cinn_p2p_dispatch_signal(_ptr(x_fp8), _ptr(x_scale), _ptr(token_indices), _ptr(sorted_experts),
                                                _ptr(tables.base_send), _ptr(tables.my_start), _ptr(b.peer_q), _ptr(b.peer_s),
-                                               token_indices.numel(), n_tokens, d, x_scale.shape[1], b.n_experts // b.world,
-                                               b.world, b.capacity_rows, _ptr(b.peer_flags), b.rank, b.LANDED_SLOT,
-                                               b._call & 0x7FFFFFFF, _ptr(b.done), _stream(x_fp8)), "cinn_p2p_dispatch_signal")
+                                               token_indices.numel(), n_tokens, d, x_scale.shape[1], e_local,
+                                               b.world, b.capacity_rows, _ptr(b.peer_flags), b.rank,
+                                               b.LANDED_SLOT if flag_slot is None else flag_slot,
+                                               b._call & 0x7FFFFFFF, _ptr(b.done), e_lo, e_local if e_hi is None else e_hi,
+                                               _stream(x_fp8)), "cinn_p2p_dispatch_signal")
     _count()
 
 
-def p2p_row_table_wait(tables, buffers, n_rows: int, row_bytes: int) -> torch.Tensor:
-    """``p2p_row_table`` that first waits for the "landed" flags of all ranks (``cinn_p2p_row_table_wait``)."""
+def p2p_row_table_wait(tables, buffers, n_rows: int, row_bytes: int, flag_slot: int = None) -> torch.Tensor:
+    """``p2p_row_table`` that first waits for the "landed" flags of all ranks under ``flag_slot``
+    (``cinn_p2p_row_table_wait``); with ``n_rows = 0`` it only waits."""
     b = buffers
     dev = b.flags.device
     with torch.cuda.device(dev):
         table = torch.empty(max(n_rows, 1), dtype=torch.int64, device=dev)[:n_rows]
         _lib.check(_L.cinn_p2p_row_table_wait(_ptr(tables.seg_start), _ptr(tables.home_base), _ptr(b.peer_home), n_rows,
                                               row_bytes, tables.home_base.numel(), b.world, b.home_rows, _ptr(table),
-                                              _ptr(b.peer_flags), b.rank, b.LANDED_SLOT, b._call & 0x7FFFFFFF,
+                                              _ptr(b.peer_flags), b.rank, b.LANDED_SLOT if flag_slot is None else flag_slot,
+                                              b._call & 0x7FFFFFFF,
                                               ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)),
                    "cinn_p2p_row_table_wait")
     _count()

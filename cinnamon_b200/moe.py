@@ -107,15 +107,26 @@ class FP8Experts:
 
     def __call__(self, x_q: torch.Tensor, x_s: torch.Tensor, starts: torch.Tensor, ends: torch.Tensor,
                  out_dtype=torch.bfloat16, row_dst: torch.Tensor = None, n_rows_dev: torch.Tensor = None,
-                 trace: Optional[list] = None) -> torch.Tensor:
+                 trace: Optional[list] = None, up_parts: Optional[list] = None) -> torch.Tensor:
         """x_q (R, d) e4m3 rows grouped by expert, x_s (R, d/128) -> (R, d) ``out_dtype``.
         Rows outside [starts[0], ends[-1]) are not written.  With ``row_dst`` (one byte address per row) the
         down-projection stores every output row there instead (possibly on a peer GPU) and nothing is returned.
         ``n_rows_dev``: device-side count of the leading rows of ``x_q`` that hold data (the rest of the buffer is
-        capacity that no expert range covers)."""
+        capacity that no expert range covers).  ``up_parts``: ``[(e_lo, e_hi, before), ...]`` - the up-projection as
+        one launch per range of experts, ``before()`` (a wait for that range's rows, say) enqueued ahead of each."""
         K = self.K
-        h12 = K.fp8_grouped_gemm(x_q, x_s, self.w12_q, self.w12_s, starts, ends, out_dtype=torch.bfloat16)
-        _mark(trace, "grouped GEMM up-projection")
+        if up_parts is None:
+            h12 = K.fp8_grouped_gemm(x_q, x_s, self.w12_q, self.w12_s, starts, ends, out_dtype=torch.bfloat16)
+            _mark(trace, "grouped GEMM up-projection")
+        else:
+            with torch.cuda.device(x_q.device):
+                h12 = torch.empty((x_q.shape[0], 2 * self.hidden), dtype=torch.bfloat16, device=x_q.device)
+            for lo, hi, before in up_parts:
+                if before is not None:
+                    before()
+                    _mark(trace, f"wait for the rows of experts [{lo}, {hi})")
+                K.fp8_grouped_gemm(x_q, x_s, self.w12_q[lo:hi], self.w12_s[lo:hi], starts[lo:hi], ends[lo:hi], out=h12)
+                _mark(trace, f"grouped GEMM up-projection, experts [{lo}, {hi})")
         h_q, h_s = K.swiglu_quantize_rowwise(h12, n_rows_dev)
         _mark(trace, "SwiGLU + quantise")
         if row_dst is not None:
@@ -377,7 +388,7 @@ def _mark(trace: Optional[list], name: str) -> None:
 
 def moe_forward_p2p(x: torch.Tensor, routing: Routing, experts: Callable, quantize: Callable, buffers, group=None,
                     addend: Optional[torch.Tensor] = None, before_combine: Optional[Callable] = None,
-                    fused_return: bool = False, trace: Optional[list] = None) -> torch.Tensor:
+                    fused_return: bool = False, trace: Optional[list] = None, up_splits: int = 1) -> torch.Tensor:
     """``moe_forward`` with the exchange done by peer stores over NVLink (``cinnamon_b200/p2p.py``) instead of
     all-to-all collectives: the routing counts of all ranks are exchanged (by the plan kernel itself with
     ``fused_return``, else by one small all-gather), then every quantised row is written
@@ -387,7 +398,9 @@ def moe_forward_p2p(x: torch.Tensor, routing: Routing, experts: Callable, quanti
     number of rows this rank received), none at all with ``fused_return``.  ``buffers``: a ``p2p.PeerBuffers``.  ``fused_return``: the expert
     down-projection stores its output rows straight to their home ranks from its epilogue (``experts`` must accept
     ``row_dst``), instead of a separate pass after the GEMM.  Same arithmetic per row as ``moe_forward``; returns
-    fp32 (T, d)."""
+    fp32 (T, d).  ``up_splits`` (with ``fused_return``; 1, 2 or 4): the local experts are cut into that many ranges,
+    each dispatched by a launch of its own with its own "landed" flags, and the up-projection runs range by range, so
+    the experts of the first range are at work while the rows of the later ones still cross NVLink."""
     from . import kernels as K
     from . import p2p
     world, me = dist.get_world_size(group), dist.get_rank(group)
@@ -406,16 +419,26 @@ def moe_forward_p2p(x: torch.Tensor, routing: Routing, experts: Callable, quanti
         _mark(trace, "plan (counts to all ranks + tables)")
         x_q, x_s = quantize(x)
         _mark(trace, "quantise tokens")
-        K.p2p_dispatch_signal(x_q, x_s, routing.token_indices, routing.sorted_experts, t, buffers)
+        n_parts = max(1, min(int(up_splits), 4, e_local))
+        cuts = [e_local * i // n_parts for i in range(n_parts + 1)]
+        slot = lambda i: buffers.LANDED_SLOT + 16 * i                                      # noqa: E731
+        for i in range(n_parts):
+            K.p2p_dispatch_signal(x_q, x_s, routing.token_indices, routing.sorted_experts, t, buffers, cuts[i], cuts[i + 1],
+                                  slot(i))
         _mark(trace, "dispatch (peer stores)")
         if callable(addend):
             addend = addend()                           # the shared expert, on its own stream, from here on
         cap = buffers.capacity_rows
         recv_q = buffers.q.view(cap, buffers.d).view(x_q.dtype)
         recv_s = buffers.s.view(cap, buffers.n_scales)
-        table = K.p2p_row_table_wait(t, buffers, cap, buffers.d * 2)
-        _mark(trace, "wait for all rows + address table")
-        experts(recv_q, recv_s, t.starts, t.ends, row_dst=table, n_rows_dev=t.total_rows, trace=trace)
+        table = K.p2p_row_table_wait(t, buffers, cap, buffers.d * 2, slot(0))
+        _mark(trace, "wait for the first rows + address table" if n_parts > 1 else "wait for all rows + address table")
+        if n_parts == 1:
+            experts(recv_q, recv_s, t.starts, t.ends, row_dst=table, n_rows_dev=t.total_rows, trace=trace)
+        else:
+            wait = lambda i: (lambda: K.p2p_row_table_wait(t, buffers, 0, buffers.d * 2, slot(i)))    # noqa: E731
+            parts = [(cuts[i], cuts[i + 1], wait(i) if i else None) for i in range(n_parts)]
+            experts(recv_q, recv_s, t.starts, t.ends, row_dst=table, n_rows_dev=t.total_rows, trace=trace, up_parts=parts)
         buffers.barrier()                               # every expert output is home
         _mark(trace, "barrier (outputs home)")
         home = buffers.home.view(buffers.home_rows, buffers.d)[:n_pairs]
@@ -584,15 +607,19 @@ class ExpertParallelMoE(torch.nn.Module):
 
     def __init__(self, router_weight: torch.Tensor, expert_bias: torch.Tensor, w12_local: torch.Tensor,
                  w3_local: torch.Tensor, top_k: int, group=None, shared: Optional[FP8SwiGLU] = None, n_chunks: int = 1,
-                 exchange: str = "nccl", max_tokens_per_rank: Optional[int] = None, check_status_every: int = 0):
+                 exchange: str = "nccl", max_tokens_per_rank: Optional[int] = None, check_status_every: int = 0,
+                 up_splits: int = 1):
         """``max_tokens_per_rank`` (peer-store exchanges): the largest number of tokens any rank will ever bring to a
         call; it sizes the receive buffers, whose allocation is a collective, so it must be the same on every rank.
         When omitted the first call agrees on it (one all-reduce of the ranks' token counts, on the first call
         only); a later call with more tokens raises instead of re-allocating (a rank re-allocating on its own would
         leave the others waiting).  ``check_status_every``: read the device status word every so many calls (a host
         synchronisation) and raise when a bounded wait ran out or a row was dropped; 0 = never, the caller polls
-        ``kernels.device_status()`` itself.  The output of a call that left a non-zero status is invalid."""
+        ``kernels.device_status()`` itself.  The output of a call that left a non-zero status is invalid.
+        ``up_splits`` ("p2p-fused"; 1, 2 or 4): ranges of local experts that are dispatched and up-projected one
+        after the other, the experts of one range at work while the rows of the next arrive."""
         super().__init__()
+        self.up_splits = int(up_splits)
         self.max_tokens_per_rank = max_tokens_per_rank
         self.check_status_every = int(check_status_every)
         self._calls = 0
@@ -679,7 +706,8 @@ class ExpertParallelMoE(torch.nn.Module):
                                  "layer with max_tokens_per_rank set to the largest batch (the same value on every rank)")
             y = moe_forward_p2p(flat, r, self.experts, self.K.quantize_fp8_rowwise, self._peer_buffers, self.group,
                                 addend=launch_shared if launch_shared is not None else sh,
-                                before_combine=join, fused_return=self.exchange == "p2p-fused", trace=self.trace)
+                                before_combine=join, fused_return=self.exchange == "p2p-fused", trace=self.trace,
+                                up_splits=self.up_splits)
             self._calls += 1
             if self.check_status_every and self._calls % self.check_status_every == 0:
                 status = self.K.device_status()

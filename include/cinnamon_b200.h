@@ -341,16 +341,21 @@ int cinn_p2p_plan(const int64_t* my_counts, const int64_t* peer_counts, const in
                   int n_experts, int flag_slot, unsigned epoch, int64_t* base_send, int64_t* my_start, int64_t* starts,
                   int64_t* ends, int64_t* seg_start, int64_t* home_base, int64_t* total_rows, void* stream);
 
-/* cinn_p2p_dispatch whose last CTA flags "all my rows have landed" to every rank (slot flag_slot + rank, value
- * epoch); done_counter: one zeroed uint32 in device memory, left zero.  Pairs with cinn_p2p_row_table_wait. */
+/* cinn_p2p_dispatch for the pairs of the local experts [expert_lo, expert_hi) of every rank (0 and experts_per_rank:
+ * all pairs), whose last CTA flags "these rows have landed" to every rank (slot flag_slot + rank, value epoch).
+ * Destinations are served in the order rank + 1, rank + 2, ..., rank, so that the ranks write to different peers at
+ * any moment.  Several calls with disjoint expert ranges and different flag slots let the owner start on the experts
+ * of one range while the rows of the next are still on their way.  done_counter: one zeroed uint32 in device memory,
+ * left zero.  Pairs with cinn_p2p_row_table_wait.  my_start must hold n_experts entries (cinn_p2p_plan's). */
 int cinn_p2p_dispatch_signal(const void* q, const float* s, const int64_t* token_indices, const int64_t* sorted_experts,
                              const int64_t* base_send, const int64_t* my_start, const int64_t* peer_q, const int64_t* peer_s,
                              int64_t n_pairs, int64_t n_tokens, int64_t d, int64_t n_scales, int experts_per_rank, int n_ranks,
                              int64_t capacity_rows, const int64_t* peer_flags, int rank, int flag_slot, unsigned epoch,
-                             unsigned* done_counter, void* stream);
+                             unsigned* done_counter, int expert_lo, int expert_hi, void* stream);
 
 /* cinn_p2p_row_table that first waits (bounded, code (5 << 8) | 6 on expiry) for the flags of cinn_p2p_dispatch_signal
- * from all ranks: work enqueued after it sees every dispatched row. */
+ * from all ranks: work enqueued after it sees every row dispatched under that flag slot.  With n_rows = 0 it only
+ * waits. */
 int cinn_p2p_row_table_wait(const int64_t* seg_start, const int64_t* home_base, const int64_t* peer_home, int64_t n_rows,
                             int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity_rows, int64_t* row_dst,
                             const int64_t* peer_flags, int rank, int flag_slot, unsigned epoch, void* stream);

@@ -278,8 +278,14 @@ y_p2p = [layer3(x) for _ in range(3)][-1]
 # ... and with the way home written by the down-projection's epilogue
 layer4 = moe.ExpertParallelMoE(router, bias, w12[lo:hi], w3[lo:hi], k, shared=moe.FP8SwiGLU(s1, s2, s3), exchange="p2p-fused")
 y_fused = [layer4(x) for _ in range(3)][-1]
+# ... and with the local experts dispatched and up-projected in two and in four ranges
+layer5 = moe.ExpertParallelMoE(router, bias, w12[lo:hi], w3[lo:hi], k, shared=moe.FP8SwiGLU(s1, s2, s3), exchange="p2p-fused", up_splits=2)
+y_split2 = [layer5(x) for _ in range(3)][-1]
+layer6 = moe.ExpertParallelMoE(router, bias, w12[lo:hi], w3[lo:hi], k, shared=moe.FP8SwiGLU(s1, s2, s3), exchange="p2p-fused", up_splits=4)
+y_split4 = [layer6(x) for _ in range(3)][-1]
 torch.cuda.synchronize()
 torch.save({"y_ep": y_ep.cpu(), "y_layer": y_layer.cpu(), "y_chunked": y_chunked.cpu(), "y_p2p": y_p2p.cpu(), "y_fused": y_fused.cpu(), "x": x.cpu(),
+            "y_split2": y_split2.cpu(), "y_split4": y_split4.cpu(),
             "status": K.device_status()},
            os.path.join(sys.argv[2], f"ep_{rank}.pt"))
 dist.barrier(); dist.destroy_process_group()
@@ -321,6 +327,7 @@ def test_expert_parallel_matches_one_gpu(K, tmp_path, world):
         assert rel_fro(got["y_chunked"], (shared(x).float() + y_one).cpu().double()) < 1e-6
         assert torch.equal(got["y_p2p"], got["y_layer"])                  # same rows in the same order: same bits
         assert torch.equal(got["y_fused"], got["y_layer"])
+        assert torch.equal(got["y_split2"], got["y_layer"]) and torch.equal(got["y_split4"], got["y_layer"])
         # same e4m3 payloads and the same per-row arithmetic: only the fp32 summation order of a token's
         # experts could differ, and index_add_ keeps it
         assert rel_fro(got["y_ep"], y_one.cpu().double()) < 1e-6
@@ -394,10 +401,53 @@ def test_dispatch_signal_and_row_table_wait(K):
     K.p2p_dispatch(xq, xs, r["token_indices"], r["sorted_experts"], t.base_send, t.my_start, pq[0], ps[0], E, 1, n)
     K._lib.check(K._lib.lib.cinn_p2p_dispatch_signal(p(xq), p(xs), p(r["token_indices"]), p(r["sorted_experts"]), p(t.base_send),
                                                      p(t.my_start), p(pq[1]), p(ps[1]), n, T, d, d // 128, E, 1, n, p(pf), 0, 128,
-                                                     3, p(done), st), "cinn_p2p_dispatch_signal")
+                                                     3, p(done), 0, E, st), "cinn_p2p_dispatch_signal")
     K._lib.check(K._lib.lib.cinn_p2p_row_table_wait(p(t.seg_start), p(t.home_base), p(ph), n, d * 2, E, 1, n, p(table), p(pf), 0,
                                                     128, 3, st), "cinn_p2p_row_table_wait")
     torch.cuda.synchronize()
     assert K.device_status() == 0 and int(flags[128]) == 3 and int(done) == 0
     assert torch.equal(recv[0], recv[1]) and torch.equal(recs[0], recs[1])
     assert torch.equal(table, K.p2p_row_table(t.seg_start, t.home_base, ph, n, d * 2, 1, n))
+
+
+def test_dispatch_signal_by_expert_ranges(K):
+    """The signalling dispatch called once per range of local experts (two destination ranks, stood in for by two
+    local buffers; this rank is rank 1, so rank 0 is served first): together the calls write exactly the rows the
+    plain dispatch writes, each sets its own flag slot, and a range outside the local experts is refused."""
+    import ctypes
+    from cinnamon_b200 import p2p
+    T, d, E, k, G, me = 160, 256, 8, 2, 2, 1
+    e_local = E // G
+    g = torch.Generator().manual_seed(9)
+    xq, xs = K.quantize_fp8_rowwise(torch.randn(T, d, generator=g).bfloat16().cuda())
+    r = K.moe_route(torch.randn(T, E, generator=g).cuda(), torch.zeros(E).cuda(), k)
+    counts_all = torch.zeros(G, E, dtype=torch.int64)
+    counts_all[me] = r["counts"].cpu()
+    t = p2p.exchange_tables(counts_all, me)
+    t = p2p.ExchangeTables(**{f: getattr(t, f).cuda().reshape(-1) for f in t.__dataclass_fields__})
+    n = T * k
+    bufs = [[torch.zeros(n, d, dtype=torch.uint8, device="cuda") for _ in range(G)] for _ in range(2)]
+    scs = [[torch.zeros(n, d // 128, device="cuda") for _ in range(G)] for _ in range(2)]
+    flags = torch.zeros(256, dtype=torch.int32, device="cuda")
+    done = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ptrs = lambda ts: torch.tensor([x.data_ptr() for x in ts], dtype=torch.int64, device="cuda")   # noqa: E731
+    pq, ps = [ptrs(bufs[i]) for i in range(2)], [ptrs(scs[i]) for i in range(2)]
+    pf = ptrs([flags] * G)
+    p = lambda x: ctypes.c_void_p(x.data_ptr())                                       # noqa: E731
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    K.p2p_dispatch(xq, xs, r["token_indices"], r["sorted_experts"], t.base_send, t.my_start, pq[0], ps[0], e_local, G, n)
+    call = lambda lo, hi, slot: K._lib.lib.cinn_p2p_dispatch_signal(                               # noqa: E731
+        p(xq), p(xs), p(r["token_indices"]), p(r["sorted_experts"]), p(t.base_send), p(t.my_start), p(pq[1]), p(ps[1]), n, T, d,
+        d // 128, e_local, G, n, p(pf), me, slot, 5, p(done), lo, hi, st)
+    K._lib.check(call(0, 1, 128), "range 0")
+    torch.cuda.synchronize()
+    assert int(flags[128 + me]) == 5 and int(flags[144 + me]) == 0
+    covered = sum(int(r["counts"][rk * e_local]) for rk in range(G))
+    written = sum(int((b != 0).any(dim=1).sum()) for b in bufs[1])
+    assert 0 < written <= covered                                    # only the first local expert of every rank so far
+    K._lib.check(call(1, e_local, 144), "range 1")
+    torch.cuda.synchronize()
+    assert K.device_status() == 0 and int(flags[144 + me]) == 5 and int(done) == 0
+    for i in range(G):
+        assert torch.equal(bufs[0][i], bufs[1][i]) and torch.equal(scs[0][i], scs[1][i])
+    assert call(2, 2, 160) != 0 and call(0, e_local + 1, 160) != 0   # empty / out-of-range expert ranges are refused
