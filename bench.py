@@ -522,7 +522,7 @@ def extras_small(Kmod, dev):
 MOE = dict(E=256, d=7168, I=2048, tokens=32768, top_k=8, shared_hidden=2048)
 
 
-def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label, chunks=1, exchange="nccl", splits=1):
+def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label, chunks=1, exchange="nccl", splits=1, dispatch_sms=0):
     """256 routed experts (SwiGLU 7168 -> 2x2048 -> 7168) + 1 shared expert, 32768 tokens, top-8 with
     sigmoid scores + per-expert bias.  Strong scaling: tokens and experts are both split over the ranks.
     Returns a dict (rank 0) with whole-layer tokens/s, the per-phase times of the most loaded rank, the grouped-GEMM
@@ -549,7 +549,7 @@ def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label, chunks=1
     # the layer as a user builds it: router + this rank's routed experts + the shared expert (round_scale on the
     # shared expert's input, as the reference's converted model has it)
     module = moe.ExpertParallelMoE(router, bias, w12, w3, c["top_k"], shared=moe.FP8SwiGLU(*sw, round_scale=True),
-                                   n_chunks=chunks, exchange=exchange, max_tokens_per_rank=T_local, up_splits=splits)
+                                   n_chunks=chunks, exchange=exchange, max_tokens_per_rank=T_local, up_splits=splits, dispatch_sms=dispatch_sms)
     t1.record()
     torch.cuda.synchronize()
     wq_ms = t0.elapsed_time(t1)
@@ -682,7 +682,8 @@ def bench_moe(Kmod, dev, rank, world, steps, warmup, bias_scale, label, chunks=1
                        "ranks_checked": len(infos)},
             "active_experts_rank0_view": active, "scaling": "strong", "n_gpus": world,
             "token_chunks": chunks if world > 1 else 1, "exchange": module_exchange if world > 1 else "none",
-            "expert_ranges": splits if (world > 1 and module_exchange == "p2p-fused") else 1}
+            "expert_ranges": splits if (world > 1 and module_exchange == "p2p-fused") else 1,
+            "dispatch_sms": dispatch_sms if (world > 1 and module_exchange == "p2p-fused") else 0}
 
 
 # ---------------------------------------------------------------------------------------
@@ -863,8 +864,10 @@ def main():
                     help="expert-parallel exchange (N > 1): all-to-all collectives, or peer stores into symmetric memory")
     ap.add_argument("--moe-chunks", type=int, default=1,
                     help="token chunks of the expert-parallel layer (N > 1): exchanges of one chunk run under the experts of another")
-    ap.add_argument("--moe-splits", type=int, default=2, choices=[1, 2, 4],
+    ap.add_argument("--moe-splits", type=int, default=1, choices=[1, 2, 4],
                     help="peer-store exchange (N > 1): ranges of local experts dispatched and up-projected one after the other")
+    ap.add_argument("--moe-dispatch-sms", type=int, default=32,
+                    help="peer-store exchange (N > 1): SMs the dispatch stores come from while the shared expert runs on the rest (0 = dispatch on all SMs, shared expert after it; 32 measured best at 2 and 8 GPUs)")
     ap.add_argument("--shape", default=None, help="M,K,N of a smaller case (profiling captures); default is the FFN workload")
     ap.add_argument("--extras-small", action="store_true",
                     help="run only the MoE plumbing passes and sparse attention on a reduced case (profiling captures) and exit")
@@ -967,7 +970,8 @@ def main():
         torch.cuda.empty_cache()
         for scale, label in ((1.0, "bias~N(0,1) as specified"), (0.1, "mild skew: bias~N(0,0.1)")):
             moe_lines.append(bench_moe(Kmod, dev, rank, world, steps=5, warmup=3, bias_scale=scale, label=label,
-                                       chunks=args.moe_chunks, exchange=args.moe_exchange, splits=args.moe_splits))
+                                       chunks=args.moe_chunks, exchange=args.moe_exchange, splits=args.moe_splits,
+                                       dispatch_sms=args.moe_dispatch_sms))
         assert Kmod.device_status() == 0, "a kernel reported a device-side failure in the MoE layer"
 
     c5_line = None

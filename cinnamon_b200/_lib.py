@@ -55,7 +55,7 @@ SIGNATURES = {
     "cinn_p2p_return": [_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _i64, _vp],
     "cinn_p2p_plan": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_uint, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "cinn_p2p_dispatch_signal": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _i32, _i64, _vp, _i32, _i32,
-                                 ctypes.c_uint, _vp, _i32, _i32, _vp],
+                                 ctypes.c_uint, _vp, _i32, _i32, _i32, _vp],
     "cinn_p2p_row_table_wait": [_vp, _vp, _vp, _i64, _i64, _i32, _i32, _i64, _vp, _vp, _i32, _i32, ctypes.c_uint, _vp],
     "cinn_p2p_barrier": [_vp, _i32, _i32, ctypes.c_uint, _vp],
     "cinn_fp8_grouped_gemm_scatter": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32, _vp],

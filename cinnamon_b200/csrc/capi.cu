@@ -91,7 +91,7 @@ int p2p_dispatch_signal(const void* q, const float* s, const int64_t* token_indi
                         const int64_t* base_send, const int64_t* my_start, const int64_t* peer_q, const int64_t* peer_s,
                         int64_t n_pairs, int64_t n_tokens, int64_t d, int64_t ns, int e_local, int n_ranks, int64_t capacity,
                         const int64_t* peer_flags, int me, int flag_slot, unsigned epoch, unsigned* done, int e_lo, int e_hi,
-                        cudaStream_t st);
+                        int n_sms, cudaStream_t st);
 int p2p_row_table_wait(const int64_t* seg_start, const int64_t* home_base, const int64_t* peer_home, int64_t n_rows,
                        int64_t row_bytes, int n_segments, int n_ranks, int64_t capacity, long long* row_dst,
                        const int64_t* peer_flags, int me, int flag_slot, unsigned epoch, cudaStream_t st);
@@ -339,10 +339,10 @@ int cinn_p2p_dispatch_signal(const void* q, const float* s, const int64_t* token
                              const int64_t* base_send, const int64_t* my_start, const int64_t* peer_q, const int64_t* peer_s,
                              int64_t n_pairs, int64_t n_tokens, int64_t d, int64_t n_scales, int experts_per_rank, int n_ranks,
                              int64_t capacity_rows, const int64_t* peer_flags, int rank, int flag_slot, unsigned epoch,
-                             unsigned* done_counter, int expert_lo, int expert_hi, void* stream) {
+                             unsigned* done_counter, int expert_lo, int expert_hi, int n_sms, void* stream) {
     return cinn::p2p_dispatch_signal(q, s, token_indices, sorted_experts, base_send, my_start, peer_q, peer_s, n_pairs, n_tokens,
                                      d, n_scales, experts_per_rank, n_ranks, capacity_rows, peer_flags, rank, flag_slot, epoch,
-                                     done_counter, expert_lo, expert_hi, (cudaStream_t)stream);
+                                     done_counter, expert_lo, expert_hi, n_sms, (cudaStream_t)stream);
 }
 
 int cinn_p2p_row_table_wait(const int64_t* seg_start, const int64_t* home_base, const int64_t* peer_home, int64_t n_rows,

@@ -306,8 +306,11 @@ __device__ int g_moe_status = 0;      // 0 = fine, otherwise (5 << 8) | reason
 // slot flag_slot + me of each rank's flag array), which replaces a separate barrier launch after the dispatch; the
 // consumer waits for the flags of all ranks (p2p_row_table with wait, or p2p_wait_flags).  `done` is a zeroed
 // device counter that the last CTA resets.
+// Launched with 256 threads per CTA on every SM, or ("narrow") with 1024 threads and so much dynamic shared memory
+// that one CTA fills an SM, one CTA per SM on a chosen number of SMs: the stores are bound by NVLink, not by the SMs,
+// and a persistent GEMM launched beside it then finds the other SMs free.
 template <bool SIGNAL>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 p2p_dispatch_kernel(const uint8_t* __restrict__ q, const float* __restrict__ s, const int64_t* __restrict__ token_indices,
                     const int64_t* __restrict__ sorted_experts, const int64_t* __restrict__ base_send,
                     const int64_t* __restrict__ my_start, const int64_t* __restrict__ peer_q,
@@ -315,8 +318,9 @@ p2p_dispatch_kernel(const uint8_t* __restrict__ q, const float* __restrict__ s, 
                     int n_ranks, int64_t capacity, const int64_t* __restrict__ peer_flags = nullptr, int me = 0,
                     int flag_slot = 0, unsigned epoch = 0, unsigned* __restrict__ done = nullptr, int e_lo = 0, int e_hi = 0) {
     const int lane = threadIdx.x & 31;
-    const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-    const int64_t n_warps = (int64_t)gridDim.x * 8;
+    const int wpc = blockDim.x >> 5;                         // warps per CTA
+    const int64_t warp = (int64_t)blockIdx.x * wpc + (threadIdx.x >> 5);
+    const int64_t n_warps = (int64_t)gridDim.x * wpc;
     const int vecs = d >> 4;
     // The signalling variant sends the pairs of the local experts [e_lo, e_hi) of every rank: one run of the sorted
     // pairs per destination rank, taken in the order me + 1, me + 2, ..., me, so that at any moment the ranks write
@@ -679,7 +683,7 @@ int p2p_dispatch_signal(const void* q, const float* s, const int64_t* token_indi
                         const int64_t* base_send, const int64_t* my_start, const int64_t* peer_q, const int64_t* peer_s,
                         int64_t n_pairs, int64_t n_tokens, int64_t d, int64_t ns, int e_local, int n_ranks, int64_t capacity,
                         const int64_t* peer_flags, int me, int flag_slot, unsigned epoch, unsigned* done, int e_lo, int e_hi,
-                        cudaStream_t st) {
+                        int n_sms, cudaStream_t st) {
     CINN_CHECK_ARG(n_pairs >= 0 && n_tokens >= 0 && d > 0 && ns >= 0 && e_local >= 1 && n_ranks >= 1 && n_ranks <= 64 &&
                    capacity >= 0 && me >= 0 && me < n_ranks && flag_slot >= 0, "p2p_dispatch_signal: bad shape");
     CINN_CHECK_ARG(0 <= e_lo && e_lo < e_hi && e_hi <= e_local,
@@ -689,6 +693,26 @@ int p2p_dispatch_signal(const void* q, const float* s, const int64_t* token_indi
     CINN_CHECK_ARG(d % 16 == 0 && d < (1LL << 31) && ns < (1LL << 31),
                    "p2p_dispatch_signal: the row width (%lld) must be a multiple of 16", (long long)d);
     CINN_CHECK_ARG((reinterpret_cast<uintptr_t>(q) & 15) == 0, "p2p_dispatch_signal: q must be 16-byte aligned");
+    CINN_CHECK_ARG(n_sms >= 0, "p2p_dispatch_signal: negative SM count");
+    if (n_sms > 0) {
+        // narrow: one CTA of 1024 threads per SM on n_sms SMs; 120 KiB of (unused) dynamic shared memory keeps a
+        // second CTA of this kernel off the same SM
+        constexpr int kHold = 120 * 1024;
+        static thread_local bool configured[64] = {};
+        int dev = 0;
+        CINN_CHECK_CUDA(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64 || !configured[dev]) {
+            CINN_CHECK_CUDA(cudaFuncSetAttribute(p2p_dispatch_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kHold));
+            if (dev >= 0 && dev < 64) configured[dev] = true;
+        }
+        const int grid = n_sms < sm_count() ? n_sms : sm_count();
+        p2p_dispatch_kernel<true><<<(unsigned)grid, 1024, kHold, st>>>((const uint8_t*)q, s, token_indices, sorted_experts,
+                                                                      base_send, my_start, peer_q, peer_s, n_pairs, n_tokens,
+                                                                      (int)d, (int)ns, e_local, n_ranks, capacity, peer_flags, me,
+                                                                      flag_slot, epoch, done, e_lo, e_hi);
+        CINN_CHECK_LAUNCH();
+        return CINN_OK;
+    }
     int64_t blocks = (n_pairs + 7) / 8;                     // with no rows one CTA still signals
     const int64_t cap = (int64_t)sm_count() * 16;
     if (blocks > cap) blocks = cap;

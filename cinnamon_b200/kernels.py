@@ -851,10 +851,11 @@ def p2p_dispatch(x_fp8, x_scale, token_indices, sorted_experts, base_send, my_st
 
 
 def p2p_dispatch_signal(x_fp8, x_scale, token_indices, sorted_experts, tables, buffers, e_lo: int = 0, e_hi: int = None,
-                        flag_slot: int = None) -> None:
+                        flag_slot: int = None, n_sms: int = 0) -> None:
     """``p2p_dispatch`` for the pairs of the local experts ``[e_lo, e_hi)`` of every rank (default: all), whose last
     CTA flags "these rows have landed" to every rank under ``flag_slot`` (``cinn_p2p_dispatch_signal``);
-    ``tables``: what ``buffers.plan`` returned for this layer call, ``buffers``: a ``p2p.PeerBuffers``."""
+    ``tables``: what ``buffers.plan`` returned for this layer call, ``buffers``: a ``p2p.PeerBuffers``; ``n_sms`` > 0:
+    the stores come from that many SMs only (the rest stay free for a GEMM on another stream)."""
     assert x_fp8.is_cuda, "Inputs must be on CUDA"
     n_tokens, d = x_fp8.shape
     x_fp8, x_scale = x_fp8.contiguous(), x_scale.float().contiguous()
@@ -867,7 +868,7 @@ def p2p_dispatch_signal(x_fp8, x_scale, token_indices, sorted_experts, tables, b
                                                b.world, b.capacity_rows, _ptr(b.peer_flags), b.rank,
                                                b.LANDED_SLOT if flag_slot is None else flag_slot,
                                                b._call & 0x7FFFFFFF, _ptr(b.done), e_lo, e_local if e_hi is None else e_hi,
-                                               _stream(x_fp8)), "cinn_p2p_dispatch_signal")
+                                               int(n_sms), _stream(x_fp8)), "cinn_p2p_dispatch_signal")
     _count()
 
 

@@ -388,7 +388,8 @@ def _mark(trace: Optional[list], name: str) -> None:
 
 def moe_forward_p2p(x: torch.Tensor, routing: Routing, experts: Callable, quantize: Callable, buffers, group=None,
                     addend: Optional[torch.Tensor] = None, before_combine: Optional[Callable] = None,
-                    fused_return: bool = False, trace: Optional[list] = None, up_splits: int = 1) -> torch.Tensor:
+                    fused_return: bool = False, trace: Optional[list] = None, up_splits: int = 1,
+                    dispatch_sms: int = 0) -> torch.Tensor:
     """``moe_forward`` with the exchange done by peer stores over NVLink (``cinnamon_b200/p2p.py``) instead of
     all-to-all collectives: the routing counts of all ranks are exchanged (by the plan kernel itself with
     ``fused_return``, else by one small all-gather), then every quantised row is written
@@ -400,7 +401,10 @@ def moe_forward_p2p(x: torch.Tensor, routing: Routing, experts: Callable, quanti
     ``row_dst``), instead of a separate pass after the GEMM.  Same arithmetic per row as ``moe_forward``; returns
     fp32 (T, d).  ``up_splits`` (with ``fused_return``; 1, 2 or 4): the local experts are cut into that many ranges,
     each dispatched by a launch of its own with its own "landed" flags, and the up-projection runs range by range, so
-    the experts of the first range are at work while the rows of the later ones still cross NVLink."""
+    the experts of the first range are at work while the rows of the later ones still cross NVLink.
+    ``dispatch_sms`` (with ``fused_return``): the dispatch stores come from that many SMs only and a callable
+    ``addend`` (the shared expert) is enqueued BEFORE the dispatch, so that its GEMMs - which the caller caps to the
+    other SMs - run beside the NVLink-bound stores instead of after them."""
     from . import kernels as K
     from . import p2p
     world, me = dist.get_world_size(group), dist.get_rank(group)
@@ -422,9 +426,11 @@ def moe_forward_p2p(x: torch.Tensor, routing: Routing, experts: Callable, quanti
         n_parts = max(1, min(int(up_splits), 4, e_local))
         cuts = [e_local * i // n_parts for i in range(n_parts + 1)]
         slot = lambda i: buffers.LANDED_SLOT + 16 * i                                      # noqa: E731
+        if callable(addend) and dispatch_sms > 0:
+            addend = addend()                           # the shared expert on its own stream and SMs, beside the dispatch
         for i in range(n_parts):
             K.p2p_dispatch_signal(x_q, x_s, routing.token_indices, routing.sorted_experts, t, buffers, cuts[i], cuts[i + 1],
-                                  slot(i))
+                                  slot(i), n_sms=dispatch_sms)
         _mark(trace, "dispatch (peer stores)")
         if callable(addend):
             addend = addend()                           # the shared expert, on its own stream, from here on
@@ -608,7 +614,7 @@ class ExpertParallelMoE(torch.nn.Module):
     def __init__(self, router_weight: torch.Tensor, expert_bias: torch.Tensor, w12_local: torch.Tensor,
                  w3_local: torch.Tensor, top_k: int, group=None, shared: Optional[FP8SwiGLU] = None, n_chunks: int = 1,
                  exchange: str = "nccl", max_tokens_per_rank: Optional[int] = None, check_status_every: int = 0,
-                 up_splits: int = 1):
+                 up_splits: int = 1, dispatch_sms: int = 0):
         """``max_tokens_per_rank`` (peer-store exchanges): the largest number of tokens any rank will ever bring to a
         call; it sizes the receive buffers, whose allocation is a collective, so it must be the same on every rank.
         When omitted the first call agrees on it (one all-reduce of the ranks' token counts, on the first call
@@ -617,9 +623,12 @@ class ExpertParallelMoE(torch.nn.Module):
         synchronisation) and raise when a bounded wait ran out or a row was dropped; 0 = never, the caller polls
         ``kernels.device_status()`` itself.  The output of a call that left a non-zero status is invalid.
         ``up_splits`` ("p2p-fused"; 1, 2 or 4): ranges of local experts that are dispatched and up-projected one
-        after the other, the experts of one range at work while the rows of the next arrive."""
+        after the other, the experts of one range at work while the rows of the next arrive.
+        ``dispatch_sms`` ("p2p-fused" with a shared expert; 0 = off): the peer stores of the dispatch come from that
+        many SMs and the shared expert's GEMMs run beside them on the other SMs, instead of after the dispatch."""
         super().__init__()
         self.up_splits = int(up_splits)
+        self.dispatch_sms = int(dispatch_sms)
         self.max_tokens_per_rank = max_tokens_per_rank
         self.check_status_every = int(check_status_every)
         self._calls = 0
@@ -668,10 +677,18 @@ class ExpertParallelMoE(torch.nn.Module):
             if self._side is None:
                 self._side = torch.cuda.Stream(flat.device)
 
+            narrow = self.dispatch_sms if self.exchange == "p2p-fused" else 0
+
             def launch_shared():
                 self._side.wait_stream(cur)
+                prev = None
+                if narrow > 0:
+                    n_sm = torch.cuda.get_device_properties(flat.device).multi_processor_count
+                    prev = self.K.set_gemm_sm_limit(max(n_sm - narrow, n_sm // 2))
                 with torch.cuda.stream(self._side):
                     out = self.shared(flat)
+                if prev is not None:
+                    self.K.set_gemm_sm_limit(prev)
                 out.record_stream(cur)
                 return out
             join = lambda: cur.wait_stream(self._side)                    # noqa: E731
@@ -707,7 +724,8 @@ class ExpertParallelMoE(torch.nn.Module):
             y = moe_forward_p2p(flat, r, self.experts, self.K.quantize_fp8_rowwise, self._peer_buffers, self.group,
                                 addend=launch_shared if launch_shared is not None else sh,
                                 before_combine=join, fused_return=self.exchange == "p2p-fused", trace=self.trace,
-                                up_splits=self.up_splits)
+                                up_splits=self.up_splits,
+                                dispatch_sms=self.dispatch_sms if launch_shared is not None else 0)
             self._calls += 1
             if self.check_status_every and self._calls % self.check_status_every == 0:
                 status = self.K.device_status()

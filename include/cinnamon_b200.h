@@ -346,12 +346,14 @@ int cinn_p2p_plan(const int64_t* my_counts, const int64_t* peer_counts, const in
  * Destinations are served in the order rank + 1, rank + 2, ..., rank, so that the ranks write to different peers at
  * any moment.  Several calls with disjoint expert ranges and different flag slots let the owner start on the experts
  * of one range while the rows of the next are still on their way.  done_counter: one zeroed uint32 in device memory,
- * left zero.  Pairs with cinn_p2p_row_table_wait.  my_start must hold n_experts entries (cinn_p2p_plan's). */
+ * left zero.  Pairs with cinn_p2p_row_table_wait.  my_start must hold n_experts entries (cinn_p2p_plan's).
+ * n_sms: 0 = CTAs on every SM; > 0 = one large CTA on each of that many SMs, so that a persistent GEMM enqueued on
+ * another stream (capped with cinn_set_gemm_sm_limit to the remaining SMs) runs beside the stores. */
 int cinn_p2p_dispatch_signal(const void* q, const float* s, const int64_t* token_indices, const int64_t* sorted_experts,
                              const int64_t* base_send, const int64_t* my_start, const int64_t* peer_q, const int64_t* peer_s,
                              int64_t n_pairs, int64_t n_tokens, int64_t d, int64_t n_scales, int experts_per_rank, int n_ranks,
                              int64_t capacity_rows, const int64_t* peer_flags, int rank, int flag_slot, unsigned epoch,
-                             unsigned* done_counter, int expert_lo, int expert_hi, void* stream);
+                             unsigned* done_counter, int expert_lo, int expert_hi, int n_sms, void* stream);
 
 /* cinn_p2p_row_table that first waits (bounded, code (5 << 8) | 6 on expiry) for the flags of cinn_p2p_dispatch_signal
  * from all ranks: work enqueued after it sees every row dispatched under that flag slot.  With n_rows = 0 it only

@@ -283,9 +283,12 @@ layer5 = moe.ExpertParallelMoE(router, bias, w12[lo:hi], w3[lo:hi], k, shared=mo
 y_split2 = [layer5(x) for _ in range(3)][-1]
 layer6 = moe.ExpertParallelMoE(router, bias, w12[lo:hi], w3[lo:hi], k, shared=moe.FP8SwiGLU(s1, s2, s3), exchange="p2p-fused", up_splits=4)
 y_split4 = [layer6(x) for _ in range(3)][-1]
+# ... and with the dispatch stores coming from 24 SMs while the shared expert's GEMMs run on the others
+layer7 = moe.ExpertParallelMoE(router, bias, w12[lo:hi], w3[lo:hi], k, shared=moe.FP8SwiGLU(s1, s2, s3), exchange="p2p-fused", dispatch_sms=24)
+y_narrow = [layer7(x) for _ in range(3)][-1]
 torch.cuda.synchronize()
 torch.save({"y_ep": y_ep.cpu(), "y_layer": y_layer.cpu(), "y_chunked": y_chunked.cpu(), "y_p2p": y_p2p.cpu(), "y_fused": y_fused.cpu(), "x": x.cpu(),
-            "y_split2": y_split2.cpu(), "y_split4": y_split4.cpu(),
+            "y_split2": y_split2.cpu(), "y_split4": y_split4.cpu(), "y_narrow": y_narrow.cpu(),
             "status": K.device_status()},
            os.path.join(sys.argv[2], f"ep_{rank}.pt"))
 dist.barrier(); dist.destroy_process_group()
@@ -328,6 +331,7 @@ def test_expert_parallel_matches_one_gpu(K, tmp_path, world):
         assert torch.equal(got["y_p2p"], got["y_layer"])                  # same rows in the same order: same bits
         assert torch.equal(got["y_fused"], got["y_layer"])
         assert torch.equal(got["y_split2"], got["y_layer"]) and torch.equal(got["y_split4"], got["y_layer"])
+        assert torch.equal(got["y_narrow"], got["y_layer"])
         # same e4m3 payloads and the same per-row arithmetic: only the fp32 summation order of a token's
         # experts could differ, and index_add_ keeps it
         assert rel_fro(got["y_ep"], y_one.cpu().double()) < 1e-6
@@ -401,7 +405,7 @@ def test_dispatch_signal_and_row_table_wait(K):
     K.p2p_dispatch(xq, xs, r["token_indices"], r["sorted_experts"], t.base_send, t.my_start, pq[0], ps[0], E, 1, n)
     K._lib.check(K._lib.lib.cinn_p2p_dispatch_signal(p(xq), p(xs), p(r["token_indices"]), p(r["sorted_experts"]), p(t.base_send),
                                                      p(t.my_start), p(pq[1]), p(ps[1]), n, T, d, d // 128, E, 1, n, p(pf), 0, 128,
-                                                     3, p(done), 0, E, st), "cinn_p2p_dispatch_signal")
+                                                     3, p(done), 0, E, 0, st), "cinn_p2p_dispatch_signal")
     K._lib.check(K._lib.lib.cinn_p2p_row_table_wait(p(t.seg_start), p(t.home_base), p(ph), n, d * 2, E, 1, n, p(table), p(pf), 0,
                                                     128, 3, st), "cinn_p2p_row_table_wait")
     torch.cuda.synchronize()
@@ -438,13 +442,15 @@ def test_dispatch_signal_by_expert_ranges(K):
     K.p2p_dispatch(xq, xs, r["token_indices"], r["sorted_experts"], t.base_send, t.my_start, pq[0], ps[0], e_local, G, n)
     call = lambda lo, hi, slot: K._lib.lib.cinn_p2p_dispatch_signal(                               # noqa: E731
         p(xq), p(xs), p(r["token_indices"]), p(r["sorted_experts"]), p(t.base_send), p(t.my_start), p(pq[1]), p(ps[1]), n, T, d,
-        d // 128, e_local, G, n, p(pf), me, slot, 5, p(done), lo, hi, st)
+        d // 128, e_local, G, n, p(pf), me, slot, 5, p(done), lo, hi, sms, st)
+    sms = 0
     K._lib.check(call(0, 1, 128), "range 0")
     torch.cuda.synchronize()
     assert int(flags[128 + me]) == 5 and int(flags[144 + me]) == 0
     covered = sum(int(r["counts"][rk * e_local]) for rk in range(G))
     written = sum(int((b != 0).any(dim=1).sum()) for b in bufs[1])
     assert 0 < written <= covered                                    # only the first local expert of every rank so far
+    sms = 3                                                          # the second range from three SMs only
     K._lib.check(call(1, e_local, 144), "range 1")
     torch.cuda.synchronize()
     assert K.device_status() == 0 and int(flags[144 + me]) == 5 and int(done) == 0
