@@ -1,7 +1,7 @@
 """Generates tests/golden/reference_vectors.npz from the reference checkout.
 
-Run in a container that has the reference tree (default /root/reference, or
-$CINNAMON_REFERENCE):   python tests/golden/make_golden.py
+Run in a container that has the reference tree ($CINNAMON_REFERENCE, else the
+`reference_path` of BASELINE.json):   python tests/golden/make_golden.py
 
 What the reference can produce without a GPU:
   * scales of its two quantiser kernels (src/kernels.py:19-132) executed by the
@@ -18,7 +18,11 @@ os.environ["TRITON_INTERPRET"] = "1"
 import numpy as np
 import torch
 
-REF = os.environ.get("CINNAMON_REFERENCE", "/root/reference")
+REF = os.environ.get("CINNAMON_REFERENCE")
+if not REF:                          # else the checkout that BASELINE.json names
+    import json
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "BASELINE.json")) as _f:
+        REF = json.load(_f)["reference_path"]
 sys.path.insert(0, os.path.join(REF, "src"))
 import kernels as ref  # noqa: E402  (the reference's src/kernels.py)
 

@@ -1,6 +1,6 @@
 """Generates tests/golden/indexer_vectors.npz from the reference checkout.
 
-Run in a container that has the reference tree (default /root/reference, or $CINNAMON_REFERENCE):
+Run in a container that has the reference tree ($CINNAMON_REFERENCE, else `reference_path` of BASELINE.json):
 
     python tests/golden/make_golden_indexer.py
 
@@ -15,7 +15,11 @@ import numpy as np
 import torch
 import triton
 
-REF = os.environ.get("CINNAMON_REFERENCE", "/root/reference")
+REF = os.environ.get("CINNAMON_REFERENCE")
+if not REF:                          # else the checkout that BASELINE.json names
+    import json
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "BASELINE.json")) as _f:
+        REF = json.load(_f)["reference_path"]
 sys.path.insert(0, os.path.join(REF, "src"))
 import kernels as ref  # noqa: E402  (the reference's src/kernels.py)
 

@@ -1,7 +1,7 @@
 """Generates tests/golden/moe_vectors.npz: the reference's own ``MoE`` block (src/layers.py:89-179) run on the CPU
 (its fallback expert loop, :76-87) in training mode with the balance loss on, for seeded weights and inputs.
 
-Run where the reference tree is present (default $CINNAMON_REFERENCE or /root/reference):
+Run where the reference tree is present ($CINNAMON_REFERENCE, else `reference_path` of BASELINE.json):
     python tests/golden/make_golden_moe.py
 
 Recorded per case: every parameter (so the test loads the very same weights), the input, the output, the balance
@@ -14,7 +14,11 @@ import sys
 import numpy as np
 import torch
 
-REF = os.environ.get("CINNAMON_REFERENCE", "/root/reference")
+REF = os.environ.get("CINNAMON_REFERENCE")
+if not REF:                          # else the checkout that BASELINE.json names
+    import json
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "BASELINE.json")) as _f:
+        REF = json.load(_f)["reference_path"]
 sys.path.insert(0, os.path.join(REF, "src"))
 import layers as ref_layers  # noqa: E402  (the reference's src/layers.py)
 
