@@ -251,12 +251,21 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                 if (!mbar_wait_warp(tfull0 + 8 * b, bph, abort_flag, (3 << 8) | 1)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * PN + h * 128;
+                // packed fp32x2 FMAs: half the issue slots of 128 scalar ones, the same IEEE result in every lane
+                uint64_t s2;
+                asm("mov.b64 %0, {%1, %1};" : "=l"(s2) : "f"(s));
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
                     float v[16];
                     tc_ld16(taddr + c * 16, v);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) acc[c * 16 + j] = fmaf(v[j], s, acc[c * 16 + j]);
+                    for (int j = 0; j < 16; j += 2)
+                        asm("{\n\t.reg .b64 a, x;\n\t"
+                            "mov.b64 a, {%0, %1};\n\t"
+                            "mov.b64 x, {%2, %3};\n\t"
+                            "fma.rn.f32x2 a, x, %4, a;\n\t"
+                            "mov.b64 {%0, %1}, a;\n\t}"
+                            : "+f"(acc[c * 16 + j]), "+f"(acc[c * 16 + j + 1]) : "f"(v[j]), "f"(v[j + 1]), "l"(s2));
                 }
                 tc_fence_before();
                 __syncwarp();
