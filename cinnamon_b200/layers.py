@@ -11,8 +11,9 @@ differs is how the work is done:
   * the routed experts are two differentiable grouped GEMMs on e4m3 operands with a one-kernel SwiGLU between them
     (the reference's grouped GEMM has no backward, so its routed experts receive no gradient on a GPU);
   * gate multiply and scatter-add are one gather pass with the shared experts' output folded in;
-  * with ``group`` the experts are sharded ``n_routed / world`` per rank and tokens travel to their experts and back
-    by all-to-all, forward and backward (``moe.moe_forward_train``).  Expert counts for the bias update are then
+  * with ``group`` the experts are sharded ``n_routed / world`` per rank and tokens travel to their experts and back,
+    forward and backward (``moe.moe_forward_train``): by all-to-all collectives, or with ``exchange="p2p"`` (GPUs of
+    one node) by peer stores over NVLink into symmetric memory.  Expert counts for the bias update are then
     summed over the ranks (the reference, which replicates every expert, keeps them rank-local).
 
 On CPU tensors the block computes the same mathematics with torch (the reference's own fallback loop,
@@ -75,8 +76,13 @@ class MoE(nn.Module):
     """Routed + shared experts (src/layers.py:89-179).  ``group``: process group over which the routed experts are
     sharded (None = all experts on this rank)."""
 
-    def __init__(self, n_routed, n_shared, top_k, d_model, hidden_dim, expert_scale, gamma, balance_alpha=0.0, group=None):
+    def __init__(self, n_routed, n_shared, top_k, d_model, hidden_dim, expert_scale, gamma, balance_alpha=0.0, group=None,
+                 exchange: str = "nccl"):
         super().__init__()
+        assert exchange in ("nccl", "p2p"), "exchange: 'nccl' (all-to-all collectives) or 'p2p' (peer stores over NVLink)"
+        self.exchange = exchange
+        self._peer = None                # p2p.PeerBuffers, allocated (collectively) by the first sharded call on GPUs
+        self._peer_tokens = 0
         world = dist.get_world_size(group) if group is not None else 1
         self.group = group
         self.sharded = world > 1
@@ -108,6 +114,22 @@ class MoE(nn.Module):
         normalised = scores / (scores.sum(dim=-1, keepdim=True) + 1e-9)
         return self.balance_alpha * (share * normalised.view(batch, seq, -1).mean(dim=1)).sum(dim=-1).mean()
 
+    def _peer_buffers(self, n_tokens: int, d: int, device):
+        """Receive buffers of the peer-store exchange, sized on the first call for the largest token count among the
+        ranks (one all-reduce, that call only) and for fp32 rows, the widest that travel."""
+        if self._peer is None:
+            from . import p2p
+            m = torch.tensor([n_tokens], dtype=torch.int64, device=device)
+            dist.all_reduce(m, op=dist.ReduceOp.MAX, group=self.group)
+            self._peer_tokens = int(m.item())
+            home_rows = self._peer_tokens * self.top_k
+            self._peer = p2p.PeerBuffers(self.group, device, home_rows * dist.get_world_size(self.group), home_rows, 4 * d, 1,
+                                         n_experts=self.n_routed)
+        if n_tokens > self._peer_tokens:
+            raise ValueError(f"{n_tokens} tokens in this call, but the peer buffers were sized for {self._peer_tokens} per rank "
+                             "by the first call")
+        return self._peer
+
     def forward(self, x):
         batch, seq, d = x.shape
         shared_out = self.shared_experts[0](x) if len(self.shared_experts) == 1 else sum(e(x) for e in self.shared_experts)
@@ -129,8 +151,11 @@ class MoE(nn.Module):
         picked = scores.gather(-1, chosen)
         gates = picked / (picked.sum(dim=-1, keepdim=True) + 1e-9)
         experts = lambda rows, starts, ends: self.routed_experts(rows, starts, ends)          # noqa: E731
+        peer = None
+        if self.sharded and self.exchange == "p2p" and flat.is_cuda:
+            peer = self._peer_buffers(flat.shape[0], d, flat.device)
         y = _moe.moe_forward_train(flat, routing, gates, experts, self.group if self.sharded else None,
-                                   addend=shared_out.reshape(-1, d))
+                                   addend=shared_out.reshape(-1, d), peer=peer)
         if self.training:
             counts = routing.counts
             if self.sharded:

@@ -339,8 +339,51 @@ class _AllToAllRows(torch.autograd.Function):
         return all_to_all_rows(grad.contiguous(), recv, send, ctx.group), None, None, None, None
 
 
+def _peer_move(rows: torch.Tensor, to_experts: bool, tabs, peer, sorted_experts: torch.Tensor, n_out: int) -> torch.Tensor:
+    """One direction of the peer-store exchange for rows of any element type (``cinnamon_b200/p2p.py``):
+    ``to_experts``: my sorted pairs' rows -> their places in the expert-grouped buffers of the experts' ranks;
+    otherwise: my expert-grouped rows -> their pairs' places on the ranks the tokens live on.  Barriers before (the
+    buffers' previous contents are done with on every rank) and after (every row has landed); the result is copied
+    out of the symmetric buffer, which the next exchange overwrites."""
+    from . import kernels as K
+    n, d = rows.shape
+    row_bytes = d * rows.element_size()
+    assert row_bytes <= peer.d and row_bytes % 16 == 0, "peer buffers were sized for narrower rows"
+    as_bytes = rows.contiguous().view(torch.uint8).view(n, row_bytes)
+    peer.barrier()
+    if to_experts:
+        if n:
+            idx = torch.arange(n, dtype=torch.int64, device=rows.device)
+            no_scale = torch.zeros((n, 1), dtype=torch.float32, device=rows.device)
+            K.p2p_dispatch(as_bytes, no_scale, idx, sorted_experts, tabs.base_send, tabs.my_start, peer.peer_q, peer.peer_s,
+                           peer.n_experts // peer.world, peer.world, peer.capacity_rows)
+        peer.barrier()
+        flat = peer.q
+    else:
+        if n:
+            K.p2p_return(as_bytes, tabs.seg_start, tabs.home_base, peer.peer_home, peer.world, peer.home_rows)
+        peer.barrier()
+        flat = peer.home.view(torch.uint8)
+    return flat[: n_out * row_bytes].clone().view(rows.dtype).view(n_out, d)
+
+
+class _PeerRows(torch.autograd.Function):
+    """``_peer_move`` whose backward is the move the other way with the same address tables: a row's gradient travels
+    back along the row's path.  ``anchor``: see ``_AllToAllRows`` (the barriers involve every rank)."""
+
+    @staticmethod
+    def forward(ctx, rows, to_experts, tabs, peer, sorted_experts, n_out, anchor):
+        ctx.args = (not to_experts, tabs, peer, sorted_experts, rows.shape[0])
+        return _peer_move(rows, to_experts, tabs, peer, sorted_experts, n_out)
+
+    @staticmethod
+    def backward(ctx, grad):
+        to_experts, tabs, peer, sorted_experts, n_out = ctx.args
+        return _peer_move(grad, to_experts, tabs, peer, sorted_experts, n_out), None, None, None, None, None, None
+
+
 def moe_forward_train(x: torch.Tensor, routing: Routing, gates: torch.Tensor, experts: Callable, group=None,
-                      addend: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      addend: Optional[torch.Tensor] = None, peer=None) -> torch.Tensor:
     """The routed part of ``MoE.forward`` (src/layers.py:137-160) built from differentiable pieces, with the experts
     sharded over ``group``: gather -> all-to-all -> regroup by expert -> ``experts(rows, starts, ends)`` -> inverse
     permutation -> all-to-all home -> gate-weighted sum (+ ``addend``).  In the backward the two exchanges run in
@@ -351,8 +394,27 @@ def moe_forward_train(x: torch.Tensor, routing: Routing, gates: torch.Tensor, ex
     ``gates`` (T, k): the normalised gates, differentiable, in the order of ``routing.pair_pos`` (ascending expert
     id per token).  ``experts`` must be differentiable.  ``group=None`` means every expert is on this rank (also
     inside a data-parallel job: nothing is exchanged).  Works on any backend (the CPU ranks of the tests pass a
-    torch expert function).  Returns (T, d) fp32."""
+    torch expert function).  ``peer`` (a ``p2p.PeerBuffers`` sized in bytes for the widest rows, GPUs of one node):
+    both exchanges, forward and backward, are peer stores over NVLink instead of all-to-all collectives - the
+    rows land expert-grouped, so the regrouping permutations go too.  Returns (T, d) fp32."""
     world = dist.get_world_size(group) if group is not None else 1
+    if world > 1 and peer is not None and x.is_cuda:
+        from . import p2p
+        n_pairs = routing.token_indices.numel()
+        assert n_pairs <= peer.home_rows, "peer buffers too small"
+        t = peer.plan(routing.counts.to(torch.int64).contiguous())
+        # the tables belong to `peer` and the next layer call overwrites them: the backward needs its own copy
+        tabs = p2p.ExchangeTables(**{f: getattr(t, f).clone() for f in t.__dataclass_fields__})
+        n_recv = int(tabs.total_rows)                      # host read-back: sizes the experts' input
+        assert n_recv <= peer.capacity_rows, "peer buffers too small"
+        rows = x.index_select(0, routing.token_indices)
+        anchor = torch.zeros((), dtype=rows.dtype, device=rows.device, requires_grad=torch.is_grad_enabled())
+        received = _PeerRows.apply(rows, True, tabs, peer, routing.sorted_experts, n_recv, anchor)
+        out_rows = experts(received, tabs.starts, tabs.ends)
+        out_rows = out_rows + (received.sum() * 0).to(out_rows.dtype)
+        out_rows = _PeerRows.apply(out_rows, False, tabs, peer, routing.sorted_experts, n_pairs, anchor)
+        from . import kernels as K
+        return K.moe_combine_autograd(out_rows, routing.pair_pos, gates, addend)
     if world > 1:
         plan = make_plan(routing.counts, group, n_pairs=routing.token_indices.numel())
     else:

@@ -80,7 +80,7 @@ dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
 E, k, d, h = 8, 2, 256, 512
 torch.manual_seed(3)
 full = layers.MoE(E, 1, k, d, h, 2, 0.01, 0.02).cuda()
-sharded = layers.MoE(E, 1, k, d, h, 2, 0.01, 0.02, group=dist.group.WORLD).cuda()
+sharded = layers.MoE(E, 1, k, d, h, 2, 0.01, 0.02, group=dist.group.WORLD, exchange=sys.argv[3]).cuda()
 el = E // world
 with torch.no_grad():
     sharded.router.weight.copy_(full.router.weight)
@@ -110,6 +110,11 @@ gz = lambda p: p.grad if p.grad is not None else torch.zeros_like(p)
 # rows are the two ranks' tokens in one list, unsharded they arrive in two calls: same mathematics, different e4m3 tiles
 ok.append(close(gz(sharded.routed_experts.w12), full.routed_experts.w12.grad[rank * el:(rank + 1) * el], 0.1))
 ok.append(close(gz(sharded.routed_experts.w3), full.routed_experts.w3.grad[rank * el:(rank + 1) * el], 0.1))
+# a second step through the same block (the exchange buffers and their flags are reused)
+x2 = (xs[rank] * 0.5).clone().requires_grad_(True)
+y2, bl2 = sharded(x2)
+(y2.pow(2).sum() + bl2).backward()
+ok.append(bool(torch.isfinite(y2).all()) and bool(torch.isfinite(x2.grad).all()) and float(x2.grad.abs().sum()) > 0)
 torch.cuda.synchronize()
 with open(os.path.join(sys.argv[2], f"ok_{rank}"), "w") as f:
     f.write(repr([bool(v) for v in ok]) + f" status {K.device_status()}" + (" " + repr(diffs) if not all(ok) else ""))
@@ -117,7 +122,10 @@ dist.barrier(); dist.destroy_process_group()
 '''
 
 
-def test_sharded_moe_block_trains_like_the_unsharded_one_on_gpus(K, tmp_path):
+@pytest.mark.parametrize("exchange", ["nccl", "p2p"])
+def test_sharded_moe_block_trains_like_the_unsharded_one_on_gpus(K, tmp_path, exchange):
+    """Outputs and all gradients of the expert-sharded block on 2 GPUs against the unsharded block, with the rows
+    exchanged by all-to-all collectives and by peer stores over NVLink (forward and backward)."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     script = tmp_path / "ep_train.py"
@@ -126,8 +134,9 @@ def test_sharded_moe_block_trains_like_the_unsharded_one_on_gpus(K, tmp_path):
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     subprocess.check_call([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-                           "--master-addr", "127.0.0.1", "--master-port", str(port), str(script), ROOT, str(tmp_path)],
+                           "--master-addr", "127.0.0.1", "--master-port", str(port), str(script), ROOT, str(tmp_path),
+                           exchange],
                           timeout=600, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
     for rank in range(2):
         text = (tmp_path / f"ok_{rank}").read_text()
-        assert text == "[True, True, True, True, True, True] status 0", f"rank {rank}: {text}"
+        assert text == "[True, True, True, True, True, True, True] status 0", f"rank {rank}: {text}"
