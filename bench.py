@@ -153,8 +153,11 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, smax, reasons = [], None, set()
+        sm, smax, reasons, power, mask = [], None, set(), [], 0
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        # bits of clocks_event_reasons.active (NVML): what the part itself names as the reason for its clock
+        bits = {0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x10: "sync_boost",
+                0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
         for ln in self.lines:
             p = [t.strip() for t in ln.split(",")]
             if len(p) < 9:
@@ -167,12 +170,22 @@ class ClockSampler:
                 smax = float(p[2])
             except ValueError:
                 continue
+            try:
+                power.append(float(p[3]))
+                mask |= int(p[4], 16)
+            except ValueError:
+                pass
             for name, val in zip(names, p[5:9]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
+        for bit, name in bits.items():
+            if mask & bit:
+                reasons.add(name)
         sm.sort()
+        power.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "power_w": power[len(power) // 2] if power else None,
+                "active_mask": hex(mask)}
 
 
 def make_inputs(seed: int, pinned: bool):
