@@ -210,7 +210,7 @@ quant_row_generic_kernel(const T* __restrict__ x, int64_t ld_m, int64_t ld_n, ui
 // (`nb` is then the capacity of the output along the tile axis, in tiles).  One launch quantises dY^T of every expert
 // for the grouped weight gradient, with tiles that never straddle two experts.
 template <typename T, int DIV, bool ROUND, bool SEG = false>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 quant_row_transposed_kernel(const T* __restrict__ x, int64_t L, uint8_t* __restrict__ q,
                             float* __restrict__ scales, int M, int N, int nb, int tiles_per_cta, int N_in,
                             const int* __restrict__ tile_src = nullptr, const int* __restrict__ tile_cnt = nullptr,
