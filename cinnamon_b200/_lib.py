@@ -62,7 +62,7 @@ SIGNATURES = {
     "cinn_p2p_row_table": [_vp, _vp, _vp, _i64, _i64, _i32, _i32, _i64, _vp, _vp],
     "cinn_fp8_grouped_wgrad_scratch_bytes": [_i64, _i64, _i64],
     "cinn_fp8_grouped_wgrad_fused_scratch_bytes": [_i64, _i64, _i64, _i64],
-    "cinn_fp8_grouped_wgrad_fused": [_vp, _i32, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _i32, _i32, _vp],
+    "cinn_fp8_grouped_wgrad_fused": [_vp, _i32, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _i32, _i32, _vp, _vp, _vp],
     "cinn_fp8_grouped_wgrad": [_vp, _i32, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _i32, _i32, _vp],
     "cinn_swiglu": [_vp, _vp, _i32, _i64, _i64, _vp],
     "cinn_swiglu_backward": [_vp, _vp, _vp, _i32, _i64, _i64, _vp],

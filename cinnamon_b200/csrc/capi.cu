@@ -77,7 +77,8 @@ long long set_p2p_wait_limit(long long cycles);
 int64_t grouped_wgrad_fused_scratch_bytes(int64_t T, int64_t E, int64_t d_in, int64_t d_out);
 int fp8_grouped_wgrad_fused(const void* dY, int dy_dtype, const void* x_q, const float* x_s, const int64_t* starts_dev,
                             const int64_t* ends_dev, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* scratch,
-                            int64_t scratch_bytes, void* dW, int out_dtype, int div_mode, cudaStream_t st);
+                            int64_t scratch_bytes, void* dW, int out_dtype, int div_mode, void* dy_q_row, float* dy_s_row,
+                            cudaStream_t st);
 int grouped_gemm_16bit(const void* A, const void* W, int in_dtype, const int64_t* starts, const int64_t* ends, int64_t E,
                        int64_t T, int64_t d_in, int64_t d_out, void* C, int out_dtype, cudaStream_t st);
 int zero_rows_outside(void* buf, int64_t T, int64_t row_bytes, const int64_t* starts, const int64_t* ends, int64_t E,
@@ -305,9 +306,11 @@ int64_t cinn_fp8_grouped_wgrad_fused_scratch_bytes(int64_t total_rows, int64_t n
 
 int cinn_fp8_grouped_wgrad_fused(const void* dY, int dy_dtype, const void* x_q, const float* x_scales, const int64_t* expert_starts,
                                  const int64_t* expert_ends, int64_t n_experts, int64_t total_rows, int64_t d_in, int64_t d_out,
-                                 void* scratch, int64_t scratch_bytes, void* dW, int out_dtype, int div_mode, void* stream) {
+                                 void* scratch, int64_t scratch_bytes, void* dW, int out_dtype, int div_mode, void* dy_q_row,
+                                 float* dy_row_scales, void* stream) {
     return cinn::fp8_grouped_wgrad_fused(dY, dy_dtype, x_q, x_scales, expert_starts, expert_ends, n_experts, total_rows, d_in, d_out,
-                                         scratch, scratch_bytes, dW, out_dtype, div_mode, (cudaStream_t)stream);
+                                         scratch, scratch_bytes, dW, out_dtype, div_mode, dy_q_row, dy_row_scales,
+                                         (cudaStream_t)stream);
 }
 
 int cinn_grouped_gemm_16bit(const void* A, const void* W, int in_dtype, const int64_t* expert_starts, const int64_t* expert_ends,

@@ -325,15 +325,28 @@ quant_row_transposed_kernel(const T* __restrict__ x, int64_t L, uint8_t* __restr
 // One 128 x 128 piece held as v[i][j] = x[mt + i][n + j].  `ok` is this thread's verdict on its input (a
 // bounded wait that ran out makes it false); the CTA leaves together when any thread says so.  `after_sync`
 // runs once every thread has taken its input out of shared memory.
-template <int DIV, bool ROUND, typename AfterSync>
+// SEG: the piece is tile `bm` of a token axis cut into per-expert segments that are padded to whole tiles: its rows
+// are the `cnt` source rows from `src0` on (the row-wise bytes and scales go to those rows; the rest of the piece
+// counts as zeros), while the transposed bytes and their scales go to the padded position `bm` of an output whose
+// token axis is `M` long (`nb_m` tiles).
+template <int DIV, bool ROUND, bool SEG = false, typename AfterSync>
 __device__ __forceinline__ bool dual_tile(float (&v)[8][8], float (*s_amax)[128], uint8_t* s_out, bool ok,
                                           uint8_t* __restrict__ q_row, float* __restrict__ s_row,
                                           uint8_t* __restrict__ q_col, float* __restrict__ s_col, int M, int N, int nb_n,
-                                          int nb_m, int bm, int bn, AfterSync&& after_sync) {
+                                          int nb_m, int bm, int bn, AfterSync&& after_sync, int src0 = 0, int cnt = 128) {
     const int sub = threadIdx.x & 15, hw = threadIdx.x >> 4, warp = threadIdx.x >> 5;
     const int m0 = bm * 128, n0 = bn * 128;
     const int n = n0 + sub * 8;
-    const int mt = m0 + hw * 8;
+    const int mt = SEG ? src0 + hw * 8 : m0 + hw * 8;          // first row of this thread's row-wise outputs
+    const int m_rows = SEG ? src0 + cnt : M;                    // one past the last row that is written row-wise
+    if constexpr (SEG) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (hw * 8 + i >= cnt) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[i][j] = 0.0f;
+            }
+    }
 
     // column tiles first: their reduction needs the barrier, the row tiles fill the wait
     float cam[8];
@@ -361,7 +374,7 @@ __device__ __forceinline__ bool dual_tile(float (&v)[8][8], float (*s_amax)[128]
         for (int o = 8; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
         const float s = scale_from_amax<DIV, ROUND>(a);
         const float d = divisor_of<DIV>(s);
-        if (mt + i < M && n < N) {
+        if (mt + i < m_rows && n < N) {
             uint2 o2;
             o2.x = cvt_e4m3x4(scaled_clamped<DIV>(v[i][0], d), scaled_clamped<DIV>(v[i][1], d),
                               scaled_clamped<DIV>(v[i][2], d), scaled_clamped<DIV>(v[i][3], d));
@@ -637,6 +650,73 @@ quant_row_dual_tma_kernel(const __grid_constant__ CUtensorMap tmX, uint8_t* __re
     if (!alive && threadIdx.x == 0) {
         atomicCAS(&g_quant_status, 0, (4 << 8) | 1);
         // loads still in flight target this CTA's shared memory: give them their (bounded) time before leaving
+        for (int j = 1; j < DUAL_STAGES; ++j)
+            if (t + j * stride < total) mbar_wait_bounded(full0 + 8 * ((k + j) % DUAL_STAGES), ((k + j) / DUAL_STAGES) & 1);
+    }
+}
+
+// The dual quantiser over a token axis cut into per-expert segments (the backward of the grouped expert GEMM): one
+// pass over dY yields its row-wise quantisation (what the grouped input gradient reads, in place of the rows) and the
+// quantisation of dY^T along the tokens of each segment, padded to whole tiles (what the grouped weight gradient
+// reads).  Tile y of the padded axis holds tile_cnt[y] rows from tile_src[y] on; only the first *n_tiles tiles exist.
+// Same TMA ring as the dense kernel; the elected thread leaves each stage's (first row, row count) beside the barriers.
+template <typename T, int DIV>
+__global__ void __launch_bounds__(256, 2)
+quant_row_dual_seg_kernel(const __grid_constant__ CUtensorMap tmX, uint8_t* __restrict__ q_row, float* __restrict__ s_row,
+                          uint8_t* __restrict__ q_col, float* __restrict__ s_col, int M_pad, int N, int nb_n, int nb_m,
+                          const int* __restrict__ tile_src, const int* __restrict__ tile_cnt, const int* __restrict__ n_tiles) {
+    static_assert(sizeof(T) == 2, "the TMA-fed path takes 2-byte inputs");
+    extern __shared__ __align__(128) uint8_t dsm[];
+    uint8_t* stages = dsm;
+    uint8_t* s_out = dsm + DUAL_STAGES * DUAL_STAGE_BYTES;
+    float (*s_amax)[128] = reinterpret_cast<float (*)[128]>(s_out + 128 * 128);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_out + 128 * 128 + 8 * 128 * 4);
+    volatile int* s_meta = reinterpret_cast<volatile int*>(bars + DUAL_STAGES);      // (src0, cnt) per stage
+    const uint32_t full0 = smem_u32(bars);
+    const int sub = threadIdx.x & 15, hw = threadIdx.x >> 4;
+    const int stride = gridDim.x;
+    const int total = *n_tiles * nb_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < DUAL_STAGES; ++s) mbar_init(full0 + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    auto issue = [&](int t, int s) {                     // one elected thread
+        const int bm = t / nb_n, bn = t - bm * nb_n;
+        const int src0 = tile_src[bm];
+        s_meta[2 * s] = src0;
+        s_meta[2 * s + 1] = tile_cnt[bm];
+        mbar_expect_tx(full0 + 8 * s, DUAL_STAGE_BYTES);
+        tma_load_2d(&tmX, full0 + 8 * s, smem_u32(stages + s * DUAL_STAGE_BYTES), bn * 128, src0);
+    };
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < DUAL_STAGES; ++s)
+            if ((int)blockIdx.x + s * stride < total) issue(blockIdx.x + s * stride, s);
+    }
+    int k = 0;
+    int t = blockIdx.x;
+    bool alive = true;
+    for (; t < total; t += stride, ++k) {
+        const int s = k % DUAL_STAGES;
+        const bool ok = mbar_wait_bounded(full0 + 8 * s, (k / DUAL_STAGES) & 1);
+        const int src0 = s_meta[2 * s], cnt = s_meta[2 * s + 1];
+        const uint8_t* src = stages + s * DUAL_STAGE_BYTES + (hw * 8) * 256 + sub * 16;
+        float v[8][8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            Raw8<T> r;
+            r.a = *reinterpret_cast<const uint4*>(src + i * 256);
+            unpack_raw8<T>(r, v[i]);
+        }
+        const int tn = t + DUAL_STAGES * stride;
+        const int bm = t / nb_n, bn = t - bm * nb_n;
+        alive = dual_tile<DIV, false, true>(v, s_amax, s_out, ok, q_row, s_row, q_col, s_col, M_pad, N, nb_n, nb_m, bm, bn,
+                                            [&] { if (threadIdx.x == 0 && tn < total) issue(tn, s); }, src0, cnt);
+        if (!alive) break;
+    }
+    if (!alive && threadIdx.x == 0) {
+        atomicCAS(&g_quant_status, 0, (4 << 8) | 1);
         for (int j = 1; j < DUAL_STAGES; ++j)
             if (t + j * stride < total) mbar_wait_bounded(full0 + 8 * ((k + j) % DUAL_STAGES), ((k + j) / DUAL_STAGES) & 1);
     }
@@ -1554,6 +1634,41 @@ int quantize_transposed_segmented(const void* x, int dtype, int64_t M, int64_t L
         case CINN_F32: return transposed_segmented_typed((const float*)x, M, L, (uint8_t*)q, scales, max_tiles, tile_src, tile_cnt, n_tiles, div_mode, st);
         default: set_error("segmented transposed quantiser: unknown dtype tag %d", dtype); return CINN_ERR_INVALID;
     }
+}
+
+// dY (T, N) of a 2-byte type -> q_row (T, N) + s_row (T, N / 128) for the rows inside segments, and the transposed,
+// segment-padded quantisation q_col (N, max_tiles * 128) + s_col (N, max_tiles); one pass (quant_row_dual_seg_kernel).
+int quantize_dual_segmented(const void* x, int dtype, int64_t T, int64_t N, void* q_row, float* s_row, void* q_col, float* s_col,
+                            int max_tiles, const int* tile_src, const int* tile_cnt, const int* n_tiles, int div_mode,
+                            cudaStream_t st) {
+    CINN_CHECK_ARG((dtype == CINN_BF16 || dtype == CINN_F16) && T >= 1 && T < (1LL << 31) && N >= 128 && N % 128 == 0 &&
+                   max_tiles >= 1 && max_tiles <= 65535, "segmented dual quantiser: 2-byte input, N a multiple of 128");
+    CINN_CHECK_ARG(x && q_row && s_row && q_col && s_col && tile_src && tile_cnt && n_tiles && aligned16(x) && aligned16(q_row) &&
+                   aligned16(q_col), "segmented dual quantiser: null or unaligned pointer");
+    CUtensorMap tm;
+    int rc = encode_map_2d(&tm, x, (uint64_t)N, (uint64_t)T, (uint64_t)N * 2, 128, 128, CU_TENSOR_MAP_DATA_TYPE_UINT16,
+                           CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    const int nb_n = (int)(N / 128);
+    const int64_t total = (int64_t)nb_n * max_tiles;
+    const int grid = (int)(total < 2 * (int64_t)sm_count() ? total : 2 * (int64_t)sm_count());
+#define CINN_DS(TT, DIV)                                                                                              \
+    do {                                                                                                              \
+        auto kern = quant_row_dual_seg_kernel<TT, DIV>;                                                               \
+        static std::once_flag once;                                                                                   \
+        static cudaError_t attr_err = cudaSuccess;                                                                    \
+        std::call_once(once, [&] {                                                                                    \
+            attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DUAL_SMEM_BYTES);      \
+        });                                                                                                           \
+        CINN_CHECK_CUDA(attr_err);                                                                                    \
+        kern<<<grid, 256, DUAL_SMEM_BYTES, st>>>(tm, (uint8_t*)q_row, s_row, (uint8_t*)q_col, s_col, max_tiles * 128, (int)N, \
+                                                 nb_n, max_tiles, tile_src, tile_cnt, n_tiles);                       \
+    } while (0)
+    if (dtype == CINN_BF16) { if (div_mode == CINN_DIV_FULL) CINN_DS(__nv_bfloat16, CINN_DIV_FULL); else CINN_DS(__nv_bfloat16, CINN_DIV_RN); }
+    else                    { if (div_mode == CINN_DIV_FULL) CINN_DS(__half, CINN_DIV_FULL);        else CINN_DS(__half, CINN_DIV_RN); }
+#undef CINN_DS
+    CINN_CHECK_LAUNCH();
+    return CINN_OK;
 }
 
 // x_q (T, K) e4m3 + row scales -> block-scaled, transposed: (K, max_tiles * 128), scales (max_tiles, ceil(K/128))

@@ -88,6 +88,9 @@ int segment_tiles(const int64_t* starts, const int64_t* ends, int E, int64_t T, 
                   int max_tiles, cudaStream_t st);
 int quantize_transposed_segmented(const void* x, int dtype, int64_t M, int64_t L, void* q, float* scales, int max_tiles,
                                   const int* tile_src, const int* tile_cnt, const int* n_tiles, int div_mode, cudaStream_t st);
+int quantize_dual_segmented(const void* x, int dtype, int64_t T, int64_t N, void* q_row, float* s_row, void* q_col, float* s_col,
+                            int max_tiles, const int* tile_src, const int* tile_cnt, const int* n_tiles, int div_mode,
+                            cudaStream_t st);
 int requant_row_to_block_segmented(const void* xq, const float* xs, int64_t K, void* out, float* scales, int max_tiles,
                                    const int* tile_src, const int* tile_cnt, const int* n_tiles, int div_mode, cudaStream_t st);
 int fp8_gemm_grouped_k(const void* A, const float* sA, const void* B, const float* sB, const int* kb_start, int64_t E,
@@ -103,8 +106,12 @@ int64_t grouped_wgrad_fused_scratch_bytes(int64_t T, int64_t E, int64_t d_in, in
 
 int fp8_grouped_wgrad_fused(const void* dY, int dy_dtype, const void* x_q, const float* x_s, const int64_t* starts_dev,
                             const int64_t* ends_dev, int64_t E, int64_t T, int64_t d_in, int64_t d_out, void* scratch,
-                            int64_t scratch_bytes, void* dW, int out_dtype, int div_mode, cudaStream_t st) {
+                            int64_t scratch_bytes, void* dW, int out_dtype, int div_mode, void* dy_q_row, float* dy_s_row,
+                            cudaStream_t st) {
     CINN_CHECK_ARG(E >= 1 && E <= 1024 && T >= 0 && d_in > 0 && d_out > 0, "grouped_wgrad_fused: bad shape");
+    CINN_CHECK_ARG((dy_q_row == nullptr) == (dy_s_row == nullptr), "grouped_wgrad_fused: pass both row-wise outputs or neither");
+    CINN_CHECK_ARG(dy_q_row == nullptr || dy_dtype == CINN_BF16 || dy_dtype == CINN_F16,
+                   "grouped_wgrad_fused: the row-wise quantisation of dY comes with 2-byte gradients only");
     CINN_CHECK_ARG(d_in % 256 == 0 && d_out % 256 == 0, "grouped_wgrad_fused: d_in (%lld) and d_out (%lld) must be multiples of 256",
                    (long long)d_in, (long long)d_out);
     CINN_CHECK_ARG(dY && x_q && x_s && starts_dev && ends_dev && scratch && dW, "grouped_wgrad_fused: null pointer");
@@ -122,7 +129,12 @@ int fp8_grouped_wgrad_fused(const void* dY, int dy_dtype, const void* x_q, const
     float* b_s = reinterpret_cast<float*>(b_q + up(d_in * mt * 128, 256));
     int rc = segment_tiles(starts_dev, ends_dev, (int)E, T, kb_start, tile_src, tile_cnt, (int)mt, st);
     if (rc) return rc;
-    rc = quantize_transposed_segmented(dY, dy_dtype, d_out, d_out, a_q, a_s, (int)mt, tile_src, tile_cnt, kb_start + E, div_mode, st);
+    if (dy_q_row != nullptr)
+        // both quantisations of dY in one pass: the caller's grouped input gradient reads the row-wise one
+        rc = quantize_dual_segmented(dY, dy_dtype, T, d_out, dy_q_row, dy_s_row, a_q, a_s, (int)mt, tile_src, tile_cnt, kb_start + E,
+                                     div_mode, st);
+    else
+        rc = quantize_transposed_segmented(dY, dy_dtype, d_out, d_out, a_q, a_s, (int)mt, tile_src, tile_cnt, kb_start + E, div_mode, st);
     if (rc) return rc;
     rc = requant_row_to_block_segmented(x_q, x_s, d_in, b_q, b_s, (int)mt, tile_src, tile_cnt, kb_start + E, div_mode, st);
     if (rc) return rc;

@@ -952,13 +952,17 @@ def fp8_grouped_gemm_dgrad(dy_fp8, dy_scale, w_fp8, w_scale, expert_starts, expe
 
 
 def fp8_grouped_wgrad(grad_out: torch.Tensor, x_fp8: torch.Tensor, x_scale: torch.Tensor, expert_starts, expert_ends,
-                      n_experts: int, d_in: int, d_out: int, w_dtype=torch.float32, fused: bool = None) -> torch.Tensor:
+                      n_experts: int, d_in: int, d_out: int, w_dtype=torch.float32, fused: bool = None,
+                      with_row_quant: bool = False):
     """``dW[e] = rowwise(dY[e rows]^T) @ blockwise(dequant_rowwise(x_q[e rows]))`` for every expert: the weight
     gradient of ``FP8MatmulFunction.backward`` (reference src/kernels.py:780-788) expert by expert.  With ``d_in`` and
     ``d_out`` multiples of 256: four launches for all experts (segments padded to whole tiles on the device, dY^T
     and x quantised per segment, one grouped-K GEMM), no host read-back.  Otherwise the row ranges are read back
     once and three launches per non-empty expert are enqueued by one library call.  Returns (E, d_out, d_in) of
-    ``w_dtype`` (fp32 holds bf16-rounded values, as a bf16 result cast to the master weight's type would)."""
+    ``w_dtype`` (fp32 holds bf16-rounded values, as a bf16 result cast to the master weight's type would).
+    ``with_row_quant``: also return the row-wise quantisation of ``grad_out`` (e4m3 bytes and scales; defined for the
+    rows inside expert ranges) as ``(grad_w, dy_fp8, dy_scale)`` - on the four-launch path with 2-byte gradients it
+    comes out of the pass that quantises dY^T, so dY is read once for the input and the weight gradient."""
     g = grad_out if grad_out.is_contiguous() else grad_out.contiguous()
     if g.dtype not in _DTYPE_TAG:
         g = g.float()
@@ -972,13 +976,20 @@ def fp8_grouped_wgrad(grad_out: torch.Tensor, x_fp8: torch.Tensor, x_scale: torc
         starts = expert_starts.to(torch.int64).contiguous()
         ends = expert_ends.to(torch.int64).contiguous()
         need = int(_L.cinn_fp8_grouped_wgrad_fused_scratch_bytes(T, n_experts, d_in, d_out))
+        one_pass = with_row_quant and g.dtype in (torch.bfloat16, torch.float16)
         with torch.cuda.device(g.device):
             scratch = torch.empty(need, dtype=torch.uint8, device=g.device)
             grad_w = torch.empty((n_experts, d_out, d_in), dtype=w_dtype, device=g.device)
+            g_q = torch.empty((T, d_out), dtype=torch.float8_e4m3fn, device=g.device) if one_pass else None
+            g_s = torch.empty((T, d_out // 128), dtype=torch.float32, device=g.device) if one_pass else None
             _lib.check(_L.cinn_fp8_grouped_wgrad_fused(_ptr(g), _DTYPE_TAG[g.dtype], _ptr(x_fp8), _ptr(x_scale), _ptr(starts),
                                                        _ptr(ends), n_experts, T, d_in, d_out, _ptr(scratch), need, _ptr(grad_w),
-                                                       out_tag, _DIV_MODE, _stream(g)), "cinn_fp8_grouped_wgrad_fused")
+                                                       out_tag, _DIV_MODE, _ptr(g_q) if one_pass else None,
+                                                       _ptr(g_s) if one_pass else None, _stream(g)),
+                       "cinn_fp8_grouped_wgrad_fused")
         _count(4)
+        if with_row_quant:
+            return (grad_w, g_q, g_s) if one_pass else (grad_w, *quantize_fp8_rowwise(g, block_size=128))
         return grad_w
     bounds = torch.stack([expert_starts.to(torch.int64), expert_ends.to(torch.int64)]).cpu()     # one host read-back
     starts_h, ends_h = bounds[0].contiguous(), bounds[1].contiguous()
@@ -992,6 +1003,8 @@ def fp8_grouped_wgrad(grad_out: torch.Tensor, x_fp8: torch.Tensor, x_scale: torc
                                              T, d_in, d_out, _ptr(scratch), scratch.numel(), _ptr(grad_w), out_tag, _DIV_MODE,
                                              _stream(g)), "cinn_fp8_grouped_wgrad")
     _count(3 * n_experts)
+    if with_row_quant:
+        return (grad_w, *quantize_fp8_rowwise(g, block_size=128))
     return grad_w
 
 
@@ -1090,11 +1103,11 @@ class MoEGroupedGemmFunction(torch.autograd.Function):
         x_fp8, x_scale, w_fp8, w_scale, starts, ends = ctx.saved_tensors
         E, d_out, d_in = w_fp8.shape
         g = grad_out if grad_out.is_contiguous() else grad_out.contiguous()
-        g_fp8, g_scale = quantize_fp8_rowwise(g, block_size=128)
         dx_dtype = ctx.x_dtype if ctx.x_dtype in _DTYPE_TAG else torch.float32
-        grad_x = fp8_grouped_gemm_dgrad(g_fp8, g_scale, w_fp8, w_scale, starts, ends, out_dtype=dx_dtype)
         w_dtype = ctx.w_dtype if ctx.w_dtype in (torch.float32, torch.bfloat16) else torch.float32
-        grad_w = fp8_grouped_wgrad(g, x_fp8, x_scale, starts, ends, E, d_in, d_out, w_dtype)
+        # the weight gradient first: its pass over dY also yields the row-wise quantisation the input gradient reads
+        grad_w, g_fp8, g_scale = fp8_grouped_wgrad(g, x_fp8, x_scale, starts, ends, E, d_in, d_out, w_dtype, with_row_quant=True)
+        grad_x = fp8_grouped_gemm_dgrad(g_fp8, g_scale, w_fp8, w_scale, starts, ends, out_dtype=dx_dtype)
         return grad_x.to(ctx.x_dtype), grad_w.to(ctx.w_dtype), None, None, None
 
 

@@ -190,11 +190,15 @@ int cinn_fp8_grouped_wgrad(const void* dY, int dy_dtype, const void* x_q, const 
  * 128-row tiles on the device, dY^T and x are quantised per segment in one launch each, and one GEMM reduces every
  * expert over its own K blocks (tcgen05, two-SM tiles).  Same arithmetic as cinn_fp8_grouped_wgrad; an expert
  * without rows gets zeros.  d_in and d_out multiples of 256; scratch: cinn_fp8_grouped_wgrad_fused_scratch_bytes
- * bytes, 256-byte aligned. */
+ * bytes, 256-byte aligned.
+ * dy_q_row (total_rows, d_out) e4m3 + dy_row_scales (total_rows, d_out / 128), both or neither (NULL): when given
+ * (bf16 / fp16 dY), the pass that quantises dY^T also leaves the row-wise quantisation of dY there for the rows inside
+ * expert ranges - the operand of cinn_fp8_grouped_gemm_dgrad - so that dY is read once for both gradients. */
 int64_t cinn_fp8_grouped_wgrad_fused_scratch_bytes(int64_t total_rows, int64_t n_experts, int64_t d_in, int64_t d_out);
 int cinn_fp8_grouped_wgrad_fused(const void* dY, int dy_dtype, const void* x_q, const float* x_scales, const int64_t* expert_starts,
                                  const int64_t* expert_ends, int64_t n_experts, int64_t total_rows, int64_t d_in, int64_t d_out,
-                                 void* scratch, int64_t scratch_bytes, void* dW, int out_dtype, int div_mode, void* stream);
+                                 void* scratch, int64_t scratch_bytes, void* dW, int out_dtype, int div_mode, void* dy_q_row,
+                                 float* dy_row_scales, void* stream);
 
 /* y[t, :] = sum_j gates[t, j] * rows[pos[t, j], :]  for t < n_tokens, j < top_k; fp32 result, no atomics.
  * Replaces the gate multiply, torch.zeros and scatter_add_ at the end of MoE.forward (src/layers.py:157-160).

@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 import torch
 
-from _util import assert_bf16_close, rel_fro
+from _util import assert_bf16_close, bits_of, bytes_of, rel_fro
 from oracle import fp8_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -528,6 +528,22 @@ def test_grouped_weight_gradient_in_one_gemm(K, name):
         if c == 0:
             assert torch.all(fused[e] == 0)
     assert torch.equal(K.fp8_grouped_wgrad(*args, w_dtype=torch.bfloat16, fused=True), fused.to(torch.bfloat16))
+    # the same call that also hands back the row-wise quantisation of dY (one pass over dY for both): same dW bits,
+    # and inside the expert ranges the bytes and scales of the row-wise quantiser
+    both, gq, gs = K.fp8_grouped_wgrad(*args, w_dtype=torch.float32, fused=True, with_row_quant=True)
+    wq, ws = K.quantize_fp8_rowwise(dy.cuda())
+    assert torch.equal(both, fused)
+    inside = torch.zeros(x.shape[0], dtype=torch.bool)
+    for a, b in zip(starts.tolist(), ends.tolist()):
+        inside[a:b] = True
+    assert inside.any() and not inside.all()
+    ins = inside.numpy()
+    assert np.array_equal(bytes_of(gq)[ins], bytes_of(wq)[ins]) and np.array_equal(bits_of(gs)[ins], bits_of(ws)[ins])
+    for dt in (torch.float16, torch.float32):                     # fp32 gradients take the two-pass route
+        both, gq, gs = K.fp8_grouped_wgrad(dy.cuda().to(dt), *args[1:], w_dtype=torch.float32, fused=True, with_row_quant=True)
+        wq, ws = K.quantize_fp8_rowwise(dy.cuda().to(dt))
+        assert torch.equal(both, fused)
+        assert np.array_equal(bytes_of(gq)[ins], bytes_of(wq)[ins]) and np.array_equal(bits_of(gs)[ins], bits_of(ws)[ins])
 
 
 def test_zero_rows_outside_ranges(K):
